@@ -1,0 +1,225 @@
+/*
+ * nvfp4r_b200 - C ABI of the B200 (sm_100a) NVFP4 W4A4 decode path.
+ *
+ * Plain pointers and sizes only; every pointer is a DEVICE pointer unless a
+ * comment says otherwise. Nothing here allocates, frees or synchronises: all
+ * buffers are caller-owned for the duration of the (stream-ordered) call and
+ * every entry point is safe to call during CUDA-graph capture unless stated
+ * otherwise. `stream` is a cudaStream_t passed as void* (NULL = legacy default
+ * stream). Every function returns NVFP4R_OK (0) or a negative nvfp4r_status.
+ *
+ * Each declaration names the interface of the reference (aiha-lab/ReSET) that
+ * it stands in for, as <path within the reference>:<lines>.
+ *
+ * Data formats
+ *   codes   : uint8, two e2m1 values per byte, even K element in the low nibble
+ *             (kernels/tests/conftest.py:11-15,35-38)
+ *   scales  : uint8 holding e4m3fn, one per 16 consecutive K elements, either
+ *             "flat" row-major [rows, K/16] or "swizzled" 128x4 tiles
+ *             [ceil(rows/128), ceil(K/64), 32, 4, 4]
+ *             (kernels/python/nvfp4r/vllm_integration.py:25-31,99-117)
+ *   out     : NVFP4R_BF16 / NVFP4R_F16 / NVFP4R_F32, row-major
+ */
+#ifndef NVFP4R_B200_H_
+#define NVFP4R_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#if defined(__GNUC__)
+#define NVFP4R_API __attribute__((visibility("default")))
+#else
+#define NVFP4R_API
+#endif
+
+typedef enum nvfp4r_status {
+    NVFP4R_OK = 0,
+    NVFP4R_ERR_INVALID_ARGUMENT = -1,  /* null pointer, non-positive size, bad enum   */
+    NVFP4R_ERR_UNSUPPORTED_SHAPE = -2, /* divisibility / size limits of this build    */
+    NVFP4R_ERR_ALIGNMENT = -3,         /* pointer or stride not aligned as required   */
+    NVFP4R_ERR_CUDA = -4,              /* a CUDA runtime call failed; see last_error  */
+    NVFP4R_ERR_DEVICE_TIMEOUT = -5     /* a bounded device-side wait gave up          */
+} nvfp4r_status;
+
+/* Output element type. 0/1 follow the reference adapter's `out_dtype_int`
+ * (kernels/python/nvfp4r/vllm_integration.py:203-205): 0 = bf16, 1 = fp16.     */
+typedef enum nvfp4r_dtype { NVFP4R_BF16 = 0, NVFP4R_F16 = 1, NVFP4R_F32 = 2 } nvfp4r_dtype;
+
+typedef enum nvfp4r_sf_layout { NVFP4R_SF_FLAT = 0, NVFP4R_SF_SWIZZLED = 1 } nvfp4r_sf_layout;
+
+/* Reciprocal used by the quantizer for 1/(sf * (1/gs_inv)).
+ *   EXACT  : IEEE division; bit-exact against the CPU oracle.
+ *   APPROX : rcp.approx.ftz, the arithmetic of the CUDA op the reference calls.   */
+typedef enum nvfp4r_rcp_mode { NVFP4R_RCP_EXACT = 0, NVFP4R_RCP_APPROX = 1 } nvfp4r_rcp_mode;
+
+/* Human-readable text for a status code (host pointer, static storage). */
+NVFP4R_API const char* nvfp4r_status_string(int status);
+/* Text of the last CUDA error seen by this thread inside the library. */
+NVFP4R_API const char* nvfp4r_last_error(void);
+/* Library version, 1000*major + minor. */
+NVFP4R_API int nvfp4r_version(void);
+
+/* ------------------------------------------------------------------------- *
+ * Activation quantizer: bf16 [M,K] -> e2m1 codes [M,K/2] + e4m3 scales.
+ * Stands in for `vops.scaled_fp4_quant(x_2d, input_global_scale_inv,
+ * is_sf_swizzled_layout=...)` as called by the reference at
+ * kernels/python/nvfp4r/vllm_integration.py:213 (flat) and :248,278 (swizzled).
+ *   x              bf16, row stride `x_row_stride` elements, rows 16-byte aligned
+ *   global_scale_inv  one float on the device (the layer's input_global_scale_inv)
+ *   codes          [M, K/2] contiguous
+ *   scales         flat: [M, K/16]; swizzled: [ceil(M/128)*128, ceil(K/64)*4],
+ *                  padding written as 0
+ * K % 16 == 0.
+ * ------------------------------------------------------------------------- */
+NVFP4R_API int nvfp4r_quant(const void* x, int64_t x_row_stride, int M, int K,
+                            const float* global_scale_inv, void* codes, void* scales,
+                            int sf_layout, int rcp_mode, void* stream);
+
+/* ------------------------------------------------------------------------- *
+ * Small-M GEMV on pre-quantized operands:
+ *   out[l, n] = alpha * sum_k dq(weight[l, n, k]) * dq(x[l, 0, k])
+ * Stands in for `torch.ops.nvfp4r.gemv(weight, weight_scale, x, x_scale, out,
+ * alpha)` - kernels/csrc/bindings.cpp:27-84 and kernels/cuda/gemv/gemv_nvfp4.cu:
+ * 817-1006 - with the same tensor meaning: weight [L,N,K/2], weight_scale
+ * [L,N,K/16] (flat), x [L,P,K/2] and x_scale [L,P,K/16] of which only row 0 of
+ * the P axis is read, out [L,N] contiguous. Strides are in bytes for the uint8
+ * operands. `w_stride_l == 0` (and `wsf_stride_l == 0`) means one weight
+ * broadcast over the L decode tokens (Tensor.expand), the decode case: the
+ * weight is then streamed from HBM once for all L tokens. K % 32 == 0.
+ * ------------------------------------------------------------------------- */
+NVFP4R_API int nvfp4r_gemv(const void* weight, const void* weight_scale,
+                           const void* x, const void* x_scale, void* out,
+                           int L, int N, int K,
+                           int64_t w_stride_l, int64_t w_stride_n,
+                           int64_t wsf_stride_l, int64_t wsf_stride_n,
+                           int64_t x_stride_l, int64_t xsf_stride_l,
+                           float alpha, int out_dtype, void* stream);
+
+/* ------------------------------------------------------------------------- *
+ * Fused decode linear: quantize M <= NVFP4R_LINEAR_MAX_M bf16 tokens and
+ * multiply by one NVFP4 weight in a single launch:
+ *   out[m, n] = alpha * sum_k dq(W[n, k]) * dq(quant(x[m, :]))[k]
+ * Stands in for the decode branch of `_nvfp4r_linear_impl`
+ * (kernels/python/nvfp4r/vllm_integration.py:211-222: scaled_fp4_quant + expand +
+ * empty + nvfp4r.gemv). The quantized codes/scales equal nvfp4r_quant's with the
+ * same rcp_mode; they stay on chip. weight [N,K/2] and weight_scale [N,K/16]
+ * (flat) contiguous; x bf16 with row stride `x_row_stride` elements; out [M,N]
+ * contiguous.
+ * ------------------------------------------------------------------------- */
+#define NVFP4R_LINEAR_MAX_M 16
+NVFP4R_API int nvfp4r_linear(const void* x, int64_t x_row_stride, int M, int K,
+                             const float* global_scale_inv,
+                             const void* weight, const void* weight_scale, int N,
+                             float alpha, void* out, int out_dtype, int rcp_mode,
+                             void* stream);
+
+/* ------------------------------------------------------------------------- *
+ * Block-scale layout conversion, [rows, K/16] flat <-> 128x4 swizzled tiles.
+ * `nvfp4r_unswizzle_blockscale` stands in for `_unswizzle_blockscale`
+ * (kernels/python/nvfp4r/vllm_integration.py:99-117), used once per layer by
+ * `prime_nvfp4r_caches` (:359-396); `nvfp4r_swizzle_blockscale` is its inverse
+ * (padding written as 0).
+ * ------------------------------------------------------------------------- */
+NVFP4R_API int nvfp4r_unswizzle_blockscale(const void* swizzled, void* flat,
+                                           int rows, int K, void* stream);
+NVFP4R_API int nvfp4r_swizzle_blockscale(const void* flat, void* swizzled,
+                                         int rows, int K, void* stream);
+
+/* ------------------------------------------------------------------------- *
+ * ReSET step-aware temperature, one decode step for a batch of requests.
+ * Stands in for `ReSETRequest.__call__` + `entropy_of` + `scale_by_temperature`
+ * (reset/reset/logits_processor.py:101-134, :32-36, :22-29) applied to every row,
+ * without the per-token host synchronisation of the reference.
+ *
+ * Per row b: boundary test on the last one/two generated ids, token entropy
+ * H = -sum p*log(max(p,1e-10)), step-entropy estimate, running mean, temperature
+ * choice, state update, then logits[b,:] /= temp in place (temp <= 1e-6: 0 at the
+ * argmax, -inf elsewhere). State lives in `nvfp4r_reset_state` records on the
+ * device, one per request slot, zero-initialised by the caller at request start.
+ * ------------------------------------------------------------------------- */
+#define NVFP4R_RESET_MAX_WINDOW 64
+
+typedef struct nvfp4r_reset_state {
+    double window_buf[NVFP4R_RESET_MAX_WINDOW]; /* ring of the last <= window entropies */
+    double step_sum;      /* sum of entropies since the last step boundary          */
+    double total_sum;     /* sum of all entropies of the request                    */
+    int64_t total_count;  /* number of tokens seen                                  */
+    int32_t step_count;   /* entropies since the last boundary                      */
+    int32_t window_count; /* valid entries in window_buf                            */
+    int32_t window_head;  /* index of the oldest entry                              */
+    int32_t reserved;
+} nvfp4r_reset_state;
+
+typedef struct nvfp4r_reset_params {
+    double t_high;   /* temperature for tokens at or above the threshold            */
+    double t_low;    /* temperature for tokens below it                             */
+    double tau0;     /* global threshold used while the step is not "uncertain"     */
+    int32_t window;  /* w, 1..NVFP4R_RESET_MAX_WINDOW                               */
+    int32_t reserved;
+} nvfp4r_reset_params;
+
+/* What a step decided, one record per row (optional output, for logging/tests). */
+typedef struct nvfp4r_reset_decision {
+    double entropy;  /* float32 entropy widened to double, as the reference holds it */
+    double h_step;
+    double h_bar;
+    double temp;
+    int32_t boundary;
+    int32_t high_step;
+} nvfp4r_reset_decision;
+
+/* Bytes of scratch one call needs for B rows (host arithmetic only). */
+NVFP4R_API size_t nvfp4r_reset_workspace_bytes(int B);
+
+/*   logits      fp32 [B,V] in/out, row stride `row_stride` elements
+ *   states      records indexed by request slot
+ *   state_slots [B] int32: index into `states` for each row, or -1 to leave the
+ *               row untouched (request without ReSET); may be NULL (slot = row)
+ *   last_ids    [B,2] int32: the two most recent generated ids of the request
+ *               (oldest first), -1 where there is none yet; NULL = never a boundary
+ *   nl_bitmap / dnl_bitmap  ceil(V/32) uint32 words: bit set = id decodes to a
+ *               single newline / contains a double newline; may be NULL (no ids)
+ *   params      one record on the HOST, copied by value into the launch
+ *   decisions   [B] or NULL
+ *   workspace   >= nvfp4r_reset_workspace_bytes(B) bytes of device scratch, 8-byte
+ *               aligned, contents irrelevant on entry; calls that share a
+ *               workspace must be ordered on the stream
+ */
+NVFP4R_API int nvfp4r_reset_step(float* logits, int64_t row_stride, int B, int V,
+                                 nvfp4r_reset_state* states, const int32_t* state_slots,
+                                 const int32_t* last_ids,
+                                 const uint32_t* nl_bitmap, const uint32_t* dnl_bitmap,
+                                 const nvfp4r_reset_params* params,
+                                 nvfp4r_reset_decision* decisions,
+                                 void* workspace, size_t workspace_bytes, void* stream);
+
+/* Token entropy only: H[b] = -sum p*log(max(p,1e-10)) for each row, as float32.
+ * Stands in for `entropy_of` (reset/reset/logits_processor.py:32-36). Same
+ * workspace rule as nvfp4r_reset_step. */
+NVFP4R_API int nvfp4r_entropy(const float* logits, int64_t row_stride, int B, int V,
+                              float* entropy, void* workspace, size_t workspace_bytes,
+                              void* stream);
+
+/* ------------------------------------------------------------------------- *
+ * Process-wide tuning of the streaming GEMV (not part of the reference's
+ * surface; the reference reads the like from NVFP4R_GEMV_* environment
+ * variables at kernels/cuda/gemv/gemv_nvfp4.cu:870-948). Negative = keep.
+ *   ctas_per_sm   grid size = SM count * ctas_per_sm (default 1)
+ *   use_pdl       1 = launch with programmatic stream serialization (default 1)
+ *   force_generic 1 = always use the plain-load fallback kernel (default 0)
+ * ------------------------------------------------------------------------- */
+NVFP4R_API int nvfp4r_set_gemv_tuning(int ctas_per_sm, int use_pdl, int force_generic);
+
+/* Reads and clears the device-side time-out flag of the current device
+ * (synchronises the device; diagnostics only). Returns 0, or
+ * NVFP4R_ERR_DEVICE_TIMEOUT if a bounded wait inside a kernel gave up. */
+NVFP4R_API int nvfp4r_check_device_status(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* NVFP4R_B200_H_ */

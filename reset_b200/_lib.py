@@ -1,0 +1,87 @@
+"""ctypes binding of ``libnvfp4r_b200.so`` (the C ABI in ``include/nvfp4r_b200.h``).
+
+There is no fallback: if the library is missing or a call fails, an exception is
+raised. Build it with ``python -m reset_b200.build``.
+"""
+
+from __future__ import annotations
+
+import ctypes as C
+from pathlib import Path
+
+PKG = Path(__file__).resolve().parent
+LIB_PATH = PKG / "libnvfp4r_b200.so"
+
+OK = 0
+BF16, F16, F32 = 0, 1, 2
+SF_FLAT, SF_SWIZZLED = 0, 1
+RCP_EXACT, RCP_APPROX = 0, 1
+RESET_MAX_WINDOW = 64
+LINEAR_MAX_M = 16
+
+
+class ResetState(C.Structure):
+    _fields_ = [("window_buf", C.c_double * RESET_MAX_WINDOW), ("step_sum", C.c_double),
+                ("total_sum", C.c_double), ("total_count", C.c_int64),
+                ("step_count", C.c_int32), ("window_count", C.c_int32),
+                ("window_head", C.c_int32), ("reserved", C.c_int32)]
+
+
+class ResetParams(C.Structure):
+    _fields_ = [("t_high", C.c_double), ("t_low", C.c_double), ("tau0", C.c_double),
+                ("window", C.c_int32), ("reserved", C.c_int32)]
+
+
+class ResetDecision(C.Structure):
+    _fields_ = [("entropy", C.c_double), ("h_step", C.c_double), ("h_bar", C.c_double),
+                ("temp", C.c_double), ("boundary", C.c_int32), ("high_step", C.c_int32)]
+
+
+_vp, _i, _i64, _f, _sz = C.c_void_p, C.c_int, C.c_int64, C.c_float, C.c_size_t
+
+# name -> (restype, argtypes); every symbol include/nvfp4r_b200.h declares
+PROTOTYPES = {
+    "nvfp4r_status_string": (C.c_char_p, [_i]),
+    "nvfp4r_last_error": (C.c_char_p, []),
+    "nvfp4r_version": (_i, []),
+    "nvfp4r_quant": (_i, [_vp, _i64, _i, _i, _vp, _vp, _vp, _i, _i, _vp]),
+    "nvfp4r_gemv": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i64, _i64, _i64, _i64, _i64, _i64,
+                         _f, _i, _vp]),
+    "nvfp4r_linear": (_i, [_vp, _i64, _i, _i, _vp, _vp, _vp, _i, _f, _vp, _i, _i, _vp]),
+    "nvfp4r_unswizzle_blockscale": (_i, [_vp, _vp, _i, _i, _vp]),
+    "nvfp4r_swizzle_blockscale": (_i, [_vp, _vp, _i, _i, _vp]),
+    "nvfp4r_reset_workspace_bytes": (_sz, [_i]),
+    "nvfp4r_reset_step": (_i, [_vp, _i64, _i, _i, _vp, _vp, _vp, _vp, _vp,
+                               C.POINTER(ResetParams), _vp, _vp, _sz, _vp]),
+    "nvfp4r_entropy": (_i, [_vp, _i64, _i, _i, _vp, _vp, _sz, _vp]),
+    "nvfp4r_set_gemv_tuning": (_i, [_i, _i, _i]),
+    "nvfp4r_check_device_status": (_i, []),
+}
+
+_lib = None
+
+
+class Nvfp4rError(RuntimeError):
+    """A C-ABI call returned a non-zero status."""
+
+
+def lib() -> C.CDLL:
+    """Load the shared library once and attach the prototypes."""
+    global _lib
+    if _lib is None:
+        if not LIB_PATH.exists():
+            raise ImportError(f"{LIB_PATH} is missing: run `python -m reset_b200.build` "
+                              "(there is no CPU or PyTorch fallback)")
+        handle = C.CDLL(str(LIB_PATH))
+        for name, (res, args) in PROTOTYPES.items():
+            fn = getattr(handle, name)          # AttributeError if a symbol is not exported
+            fn.restype, fn.argtypes = res, args
+        _lib = handle
+    return _lib
+
+
+def check(status: int, what: str) -> None:
+    if status != OK:
+        l = lib()
+        raise Nvfp4rError(f"{what}: {l.nvfp4r_status_string(status).decode()} "
+                          f"({status}): {l.nvfp4r_last_error().decode()}")

@@ -1,0 +1,165 @@
+"""Tensor-level wrappers over the C ABI: they take ``torch`` CUDA tensors, pass raw
+device pointers, sizes and the current CUDA stream to ``libnvfp4r_b200.so`` and
+raise on any non-zero status. PyTorch is used for memory and streams only."""
+
+from __future__ import annotations
+
+import ctypes as C
+
+import torch
+
+from . import _lib as L
+
+_DTYPE_CODE = {torch.bfloat16: L.BF16, torch.float16: L.F16, torch.float32: L.F32}
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _need_cuda(*tensors):
+    for t in tensors:
+        if t is not None and not t.is_cuda:
+            raise ValueError("nvfp4r: all tensors must be CUDA tensors")
+
+
+def _u8(t: torch.Tensor) -> torch.Tensor:
+    return t if t.dtype == torch.uint8 else t.view(torch.uint8)
+
+
+def quant(x: torch.Tensor, global_scale_inv: torch.Tensor, *, swizzled: bool = False,
+          rcp_mode: int = L.RCP_EXACT):
+    """bf16 [M,K] -> (codes uint8 [M,K/2], scales uint8). Flat scales are [M,K/16];
+    swizzled ones [ceil(M/128)*128, ceil(K/64)*4]."""
+    _need_cuda(x, global_scale_inv)
+    if x.dtype != torch.bfloat16 or x.dim() != 2 or x.stride(1) != 1:
+        raise ValueError("quant: x must be bf16 [M,K] with unit inner stride")
+    M, K = x.shape
+    codes = torch.empty((M, K // 2), dtype=torch.uint8, device=x.device)
+    if swizzled:
+        shape = ((M + 127) // 128 * 128, (K // 16 + 3) // 4 * 4)
+    else:
+        shape = (M, K // 16)
+    scales = torch.empty(shape, dtype=torch.uint8, device=x.device)
+    with torch.cuda.device(x.device):
+        st = L.lib().nvfp4r_quant(x.data_ptr(), x.stride(0), M, K, global_scale_inv.data_ptr(),
+                                  codes.data_ptr(), scales.data_ptr(),
+                                  L.SF_SWIZZLED if swizzled else L.SF_FLAT, rcp_mode, _stream())
+    L.check(st, "nvfp4r_quant")
+    return codes, scales
+
+
+def gemv_out(weight, weight_scale, x, x_scale, out, alpha: float = 1.0) -> None:
+    """The reference's out-variant: 3-D operands, ``out`` [L,N] mutated in place."""
+    _need_cuda(weight, weight_scale, x, x_scale, out)
+    w, ws, a, a_s = _u8(weight), _u8(weight_scale), _u8(x), _u8(x_scale)
+    if not (w.dim() == ws.dim() == a.dim() == a_s.dim() == 3):
+        raise ValueError("gemv: inputs must be 3D [L, N_or_P, K/2_or_K/16]")
+    if not (a.is_contiguous() and a_s.is_contiguous()):
+        raise ValueError("gemv: x / x_scale must be contiguous")
+    Lb, N, K2 = w.shape
+    K = K2 * 2
+    if tuple(ws.shape) != (Lb, N, K // 16):
+        raise ValueError("weight_scale shape mismatch with weight")
+    if a.shape[0] != Lb or a.shape[2] != K2:
+        raise ValueError("x.K mismatch with weight.K")
+    if a_s.shape[0] != Lb or a_s.shape[1] != a.shape[1] or a_s.shape[2] * 16 != K:
+        raise ValueError("x_scale shape mismatch with x")
+    if out.dtype not in _DTYPE_CODE or not out.is_contiguous() or tuple(out.shape) != (Lb, N):
+        raise ValueError("out must be a contiguous [L, N] float16/bfloat16/float32 tensor")
+    if w.stride(2) != 1 or ws.stride(2) != 1:
+        raise ValueError("gemv: weight / weight_scale must have unit inner stride")
+    with torch.cuda.device(w.device):
+        st = L.lib().nvfp4r_gemv(w.data_ptr(), ws.data_ptr(), a.data_ptr(), a_s.data_ptr(),
+                                 out.data_ptr(), Lb, N, K, w.stride(0), w.stride(1),
+                                 ws.stride(0), ws.stride(1), a.stride(0), a_s.stride(0),
+                                 float(alpha), _DTYPE_CODE[out.dtype], _stream())
+    L.check(st, "nvfp4r_gemv")
+
+
+def linear(x: torch.Tensor, global_scale_inv: torch.Tensor, weight: torch.Tensor,
+           weight_scale_flat: torch.Tensor, alpha: float, out: torch.Tensor | None = None,
+           out_dtype: torch.dtype | None = None, rcp_mode: int = L.RCP_EXACT) -> torch.Tensor:
+    """Fused quantize + GEMV for M <= 16 bf16 tokens. weight [N,K/2], scales [N,K/16]."""
+    _need_cuda(x, global_scale_inv, weight, weight_scale_flat, out)
+    if x.dtype != torch.bfloat16 or x.dim() != 2 or x.stride(1) != 1:
+        raise ValueError("linear: x must be bf16 [M,K] with unit inner stride")
+    M, K = x.shape
+    w, ws = _u8(weight), _u8(weight_scale_flat)
+    N = w.shape[0]
+    if not (w.is_contiguous() and ws.is_contiguous()) or w.shape[1] * 2 != K \
+            or ws.numel() != N * (K // 16):
+        raise ValueError("linear: weight [N,K/2] and weight_scale [N,K/16] must be contiguous")
+    if out is None:
+        out = torch.empty((M, N), dtype=out_dtype or x.dtype, device=x.device)
+    elif tuple(out.shape) != (M, N) or not out.is_contiguous():
+        raise ValueError("linear: out must be contiguous [M,N]")
+    with torch.cuda.device(x.device):
+        st = L.lib().nvfp4r_linear(x.data_ptr(), x.stride(0), M, K, global_scale_inv.data_ptr(),
+                                   w.data_ptr(), ws.data_ptr(), N, float(alpha), out.data_ptr(),
+                                   _DTYPE_CODE[out.dtype], rcp_mode, _stream())
+    L.check(st, "nvfp4r_linear")
+    return out
+
+
+def unswizzle_blockscale(swizzled: torch.Tensor, rows: int, K: int) -> torch.Tensor:
+    _need_cuda(swizzled)
+    sw = _u8(swizzled).contiguous()
+    flat = torch.empty((rows, K // 16), dtype=torch.uint8, device=sw.device)
+    with torch.cuda.device(sw.device):
+        st = L.lib().nvfp4r_unswizzle_blockscale(sw.data_ptr(), flat.data_ptr(), rows, K, _stream())
+    L.check(st, "nvfp4r_unswizzle_blockscale")
+    return flat
+
+
+def swizzle_blockscale(flat: torch.Tensor) -> torch.Tensor:
+    _need_cuda(flat)
+    f = _u8(flat).contiguous()
+    rows, cols = f.shape
+    out = torch.empty(((rows + 127) // 128 * 128, (cols + 3) // 4 * 4), dtype=torch.uint8,
+                      device=f.device)
+    with torch.cuda.device(f.device):
+        st = L.lib().nvfp4r_swizzle_blockscale(f.data_ptr(), out.data_ptr(), rows, cols * 16, _stream())
+    L.check(st, "nvfp4r_swizzle_blockscale")
+    return out
+
+
+def reset_workspace(B: int, device) -> torch.Tensor:
+    n = L.lib().nvfp4r_reset_workspace_bytes(B)
+    return torch.empty((n + 7) // 8, dtype=torch.int64, device=device)
+
+
+def entropy(logits: torch.Tensor, workspace: torch.Tensor | None = None) -> torch.Tensor:
+    """fp32 [B,V] -> fp32 [B] token entropies."""
+    _need_cuda(logits)
+    if logits.dtype != torch.float32 or logits.dim() != 2 or logits.stride(1) != 1:
+        raise ValueError("entropy: logits must be fp32 [B,V] with unit inner stride")
+    B, V = logits.shape
+    ws = workspace if workspace is not None else reset_workspace(B, logits.device)
+    out = torch.empty(B, dtype=torch.float32, device=logits.device)
+    with torch.cuda.device(logits.device):
+        st = L.lib().nvfp4r_entropy(logits.data_ptr(), logits.stride(0), B, V, out.data_ptr(),
+                                    ws.data_ptr(), ws.numel() * 8, _stream())
+    L.check(st, "nvfp4r_entropy")
+    return out
+
+
+def reset_step(logits: torch.Tensor, states: torch.Tensor, params: L.ResetParams, *,
+               state_slots: torch.Tensor | None = None, last_ids: torch.Tensor | None = None,
+               nl_bitmap: torch.Tensor | None = None, dnl_bitmap: torch.Tensor | None = None,
+               decisions: torch.Tensor | None = None, workspace: torch.Tensor) -> None:
+    """One ReSET step in place on fp32 logits [B,V]. ``states`` is a uint8 tensor of
+    ``sizeof(nvfp4r_reset_state)`` bytes per slot; ``decisions`` (optional) a uint8
+    tensor of ``sizeof(nvfp4r_reset_decision)`` bytes per row."""
+    _need_cuda(logits, states, state_slots, last_ids, nl_bitmap, dnl_bitmap, decisions, workspace)
+    if logits.dtype != torch.float32 or logits.dim() != 2 or logits.stride(1) != 1:
+        raise ValueError("reset_step: logits must be fp32 [B,V] with unit inner stride")
+    B, V = logits.shape
+    ptr = lambda t: t.data_ptr() if t is not None else None
+    with torch.cuda.device(logits.device):
+        st = L.lib().nvfp4r_reset_step(logits.data_ptr(), logits.stride(0), B, V, states.data_ptr(),
+                                       ptr(state_slots), ptr(last_ids), ptr(nl_bitmap),
+                                       ptr(dnl_bitmap), C.byref(params), ptr(decisions),
+                                       workspace.data_ptr(), workspace.numel() * workspace.element_size(),
+                                       _stream())
+    L.check(st, "nvfp4r_reset_step")

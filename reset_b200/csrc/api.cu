@@ -1,0 +1,243 @@
+// extern "C" entry points: argument checks, then the kernel launchers.
+#include <cstdio>
+#include <cstring>
+
+#include "../../include/nvfp4r_b200.h"
+#include "kernels.h"
+#include "reset_kernels.h"
+
+namespace {
+
+thread_local char g_last_error[256] = "";
+
+int cuda_fail(cudaError_t e, const char* where) {
+    std::snprintf(g_last_error, sizeof(g_last_error), "%s: %s", where, cudaGetErrorString(e));
+    return NVFP4R_ERR_CUDA;
+}
+int fail(int code, const char* why) {
+    std::snprintf(g_last_error, sizeof(g_last_error), "%s", why);
+    return code;
+}
+inline bool aligned(const void* p, uintptr_t a) { return (reinterpret_cast<uintptr_t>(p) % a) == 0; }
+inline cudaStream_t as_stream(void* s) { return static_cast<cudaStream_t>(s); }
+
+}  // namespace
+
+extern "C" {
+
+const char* nvfp4r_status_string(int status) {
+    switch (status) {
+        case NVFP4R_OK: return "ok";
+        case NVFP4R_ERR_INVALID_ARGUMENT: return "invalid argument";
+        case NVFP4R_ERR_UNSUPPORTED_SHAPE: return "unsupported shape";
+        case NVFP4R_ERR_ALIGNMENT: return "pointer or stride alignment";
+        case NVFP4R_ERR_CUDA: return "CUDA runtime error";
+        case NVFP4R_ERR_DEVICE_TIMEOUT: return "device-side wait timed out";
+        default: return "unknown status";
+    }
+}
+
+const char* nvfp4r_last_error(void) { return g_last_error; }
+
+int nvfp4r_version(void) { return 1000 * 0 + 1; }
+
+int nvfp4r_quant(const void* x, int64_t x_row_stride, int M, int K, const float* gs,
+                 void* codes, void* scales, int sf_layout, int rcp_mode, void* stream) {
+    if (!x || !gs || !codes || !scales) return fail(NVFP4R_ERR_INVALID_ARGUMENT, "quant: null pointer");
+    if (M < 0 || K <= 0) return fail(NVFP4R_ERR_INVALID_ARGUMENT, "quant: M/K must be positive");
+    if (sf_layout != NVFP4R_SF_FLAT && sf_layout != NVFP4R_SF_SWIZZLED)
+        return fail(NVFP4R_ERR_INVALID_ARGUMENT, "quant: bad sf_layout");
+    if (rcp_mode != NVFP4R_RCP_EXACT && rcp_mode != NVFP4R_RCP_APPROX)
+        return fail(NVFP4R_ERR_INVALID_ARGUMENT, "quant: bad rcp_mode");
+    if (K % 16 != 0) return fail(NVFP4R_ERR_UNSUPPORTED_SHAPE, "quant: K must be a multiple of 16");
+    if (!aligned(x, 16) || (x_row_stride % 8) != 0 || !aligned(codes, 8))
+        return fail(NVFP4R_ERR_ALIGNMENT, "quant: x rows must be 16-byte aligned, codes 8-byte");
+    if (x_row_stride < K) return fail(NVFP4R_ERR_INVALID_ARGUMENT, "quant: row stride < K");
+    if (M == 0) return NVFP4R_OK;
+    cudaError_t e = nvfp4r::launch_quant(x, x_row_stride, M, K, gs, codes, scales,
+                                         sf_layout == NVFP4R_SF_SWIZZLED, rcp_mode, as_stream(stream));
+    return e == cudaSuccess ? NVFP4R_OK : cuda_fail(e, "quant launch");
+}
+
+int nvfp4r_gemv(const void* weight, const void* weight_scale, const void* x, const void* x_scale,
+                void* out, int L, int N, int K, int64_t w_stride_l, int64_t w_stride_n,
+                int64_t wsf_stride_l, int64_t wsf_stride_n, int64_t x_stride_l,
+                int64_t xsf_stride_l, float alpha, int out_dtype, void* stream) {
+    if (!weight || !weight_scale || !x || !x_scale || !out)
+        return fail(NVFP4R_ERR_INVALID_ARGUMENT, "gemv: null pointer");
+    if (L < 0 || N < 0 || K <= 0) return fail(NVFP4R_ERR_INVALID_ARGUMENT, "gemv: bad sizes");
+    if (out_dtype < NVFP4R_BF16 || out_dtype > NVFP4R_F32)
+        return fail(NVFP4R_ERR_INVALID_ARGUMENT, "gemv: bad out_dtype");
+    if (K % 32 != 0) return fail(NVFP4R_ERR_UNSUPPORTED_SHAPE, "gemv: K must be a multiple of 32");
+    if (w_stride_n < K / 2 || wsf_stride_n < K / 16)
+        return fail(NVFP4R_ERR_INVALID_ARGUMENT, "gemv: weight row stride smaller than a row");
+    if (!aligned(weight, 16) || !aligned(x, 16) || (w_stride_n % 16) || (x_stride_l % 16) ||
+        (w_stride_l % 16) || !aligned(weight_scale, 2) || !aligned(x_scale, 2) ||
+        (wsf_stride_n % 2) || (xsf_stride_l % 2) || (wsf_stride_l % 2))
+        return fail(NVFP4R_ERR_ALIGNMENT, "gemv: codes need 16-byte, scales 2-byte alignment");
+    if (L == 0 || N == 0) return NVFP4R_OK;
+
+    const size_t out_elt = out_dtype == NVFP4R_F32 ? 4 : 2;
+    nvfp4r::GemvArgs a = {};
+    a.w_stride_n = w_stride_n;
+    a.wsf_stride_n = wsf_stride_n;
+    a.x_stride = x_stride_l;
+    a.xsf_stride = xsf_stride_l;
+    a.out_stride = N;
+    a.out_dtype = out_dtype;
+    a.N = N;
+    a.K = K;
+    a.alpha = alpha;
+    const bool broadcast = (w_stride_l == 0 && wsf_stride_l == 0);
+    const int group = broadcast ? 8 : 1;
+    for (int l0 = 0; l0 < L; l0 += group) {
+        const int m = broadcast ? (L - l0 < group ? L - l0 : group) : 1;
+        a.w = static_cast<const uint8_t*>(weight) + (broadcast ? 0 : l0 * w_stride_l);
+        a.wsf = static_cast<const uint8_t*>(weight_scale) + (broadcast ? 0 : l0 * wsf_stride_l);
+        a.x = static_cast<const uint8_t*>(x) + l0 * x_stride_l;
+        a.xsf = static_cast<const uint8_t*>(x_scale) + l0 * xsf_stride_l;
+        a.out = static_cast<uint8_t*>(out) + static_cast<size_t>(l0) * N * out_elt;
+        a.M = m;
+        cudaError_t e = nvfp4r::gemv_stream_supported(a)
+                            ? nvfp4r::launch_gemv_stream(a, as_stream(stream))
+                            : nvfp4r::launch_gemv_generic(a, as_stream(stream));
+        if (e != cudaSuccess) return cuda_fail(e, "gemv launch");
+    }
+    return NVFP4R_OK;
+}
+
+int nvfp4r_linear(const void* x, int64_t x_row_stride, int M, int K, const float* gs,
+                  const void* weight, const void* weight_scale, int N, float alpha, void* out,
+                  int out_dtype, int rcp_mode, void* stream) {
+    if (!x || !gs || !weight || !weight_scale || !out)
+        return fail(NVFP4R_ERR_INVALID_ARGUMENT, "linear: null pointer");
+    if (M < 0 || N < 0 || K <= 0) return fail(NVFP4R_ERR_INVALID_ARGUMENT, "linear: bad sizes");
+    if (M > NVFP4R_LINEAR_MAX_M) return fail(NVFP4R_ERR_UNSUPPORTED_SHAPE, "linear: M above NVFP4R_LINEAR_MAX_M");
+    if (out_dtype < NVFP4R_BF16 || out_dtype > NVFP4R_F32)
+        return fail(NVFP4R_ERR_INVALID_ARGUMENT, "linear: bad out_dtype");
+    if (rcp_mode != NVFP4R_RCP_EXACT && rcp_mode != NVFP4R_RCP_APPROX)
+        return fail(NVFP4R_ERR_INVALID_ARGUMENT, "linear: bad rcp_mode");
+    if (K % 32 != 0) return fail(NVFP4R_ERR_UNSUPPORTED_SHAPE, "linear: K must be a multiple of 32");
+    if (!aligned(x, 16) || (x_row_stride % 8) || !aligned(weight, 16) || !aligned(weight_scale, 2))
+        return fail(NVFP4R_ERR_ALIGNMENT, "linear: x/weight need 16-byte alignment");
+    if (x_row_stride < K) return fail(NVFP4R_ERR_INVALID_ARGUMENT, "linear: row stride < K");
+    if (M == 0 || N == 0) return NVFP4R_OK;
+
+    const size_t out_elt = out_dtype == NVFP4R_F32 ? 4 : 2;
+    nvfp4r::GemvArgs a = {};
+    a.w = static_cast<const uint8_t*>(weight);
+    a.wsf = static_cast<const uint8_t*>(weight_scale);
+    a.w_stride_n = K / 2;
+    a.wsf_stride_n = K / 16;
+    a.xb_stride = x_row_stride;
+    a.gs = gs;
+    a.rcp_mode = rcp_mode;
+    a.out_stride = N;
+    a.out_dtype = out_dtype;
+    a.N = N;
+    a.K = K;
+    a.alpha = alpha;
+    for (int m0 = 0; m0 < M; m0 += 8) {
+        a.M = M - m0 < 8 ? M - m0 : 8;
+        a.xb = static_cast<const uint8_t*>(x) + static_cast<size_t>(m0) * x_row_stride * 2;
+        a.out = static_cast<uint8_t*>(out) + static_cast<size_t>(m0) * N * out_elt;
+        cudaError_t e = nvfp4r::gemv_stream_supported(a)
+                            ? nvfp4r::launch_gemv_stream(a, as_stream(stream))
+                            : nvfp4r::launch_gemv_generic(a, as_stream(stream));
+        if (e != cudaSuccess) return cuda_fail(e, "linear launch");
+    }
+    return NVFP4R_OK;
+}
+
+int nvfp4r_unswizzle_blockscale(const void* swizzled, void* flat, int rows, int K, void* stream) {
+    if (!swizzled || !flat) return fail(NVFP4R_ERR_INVALID_ARGUMENT, "unswizzle: null pointer");
+    if (rows < 0 || K <= 0 || K % 16) return fail(NVFP4R_ERR_UNSUPPORTED_SHAPE, "unswizzle: K % 16");
+    if (rows == 0) return NVFP4R_OK;
+    cudaError_t e = nvfp4r::launch_sf_layout(swizzled, flat, rows, K, true, as_stream(stream));
+    return e == cudaSuccess ? NVFP4R_OK : cuda_fail(e, "unswizzle launch");
+}
+
+int nvfp4r_swizzle_blockscale(const void* flat, void* swizzled, int rows, int K, void* stream) {
+    if (!swizzled || !flat) return fail(NVFP4R_ERR_INVALID_ARGUMENT, "swizzle: null pointer");
+    if (rows < 0 || K <= 0 || K % 16) return fail(NVFP4R_ERR_UNSUPPORTED_SHAPE, "swizzle: K % 16");
+    if (rows == 0) return NVFP4R_OK;
+    cudaError_t e = nvfp4r::launch_sf_layout(flat, swizzled, rows, K, false, as_stream(stream));
+    return e == cudaSuccess ? NVFP4R_OK : cuda_fail(e, "swizzle launch");
+}
+
+size_t nvfp4r_reset_workspace_bytes(int B) {
+    return B > 0 ? static_cast<size_t>(B) * sizeof(nvfp4r::RowScratch) : 0;
+}
+
+int nvfp4r_reset_step(float* logits, int64_t row_stride, int B, int V, nvfp4r_reset_state* states,
+                      const int32_t* state_slots, const int32_t* last_ids,
+                      const uint32_t* nl_bitmap, const uint32_t* dnl_bitmap,
+                      const nvfp4r_reset_params* params, nvfp4r_reset_decision* decisions,
+                      void* workspace, size_t workspace_bytes, void* stream) {
+    if (!logits || !states || !params || !workspace)
+        return fail(NVFP4R_ERR_INVALID_ARGUMENT, "reset_step: null pointer");
+    if (B < 0 || V <= 0 || row_stride < V) return fail(NVFP4R_ERR_INVALID_ARGUMENT, "reset_step: bad sizes");
+    if (params->window < 1 || params->window > NVFP4R_RESET_MAX_WINDOW)
+        return fail(NVFP4R_ERR_UNSUPPORTED_SHAPE, "reset_step: window outside 1..NVFP4R_RESET_MAX_WINDOW");
+    if (workspace_bytes < nvfp4r_reset_workspace_bytes(B))
+        return fail(NVFP4R_ERR_INVALID_ARGUMENT, "reset_step: workspace too small");
+    if (!aligned(workspace, 8) || !aligned(logits, 4) || !aligned(states, 8))
+        return fail(NVFP4R_ERR_ALIGNMENT, "reset_step: workspace/states need 8-byte alignment");
+    if (B == 0) return NVFP4R_OK;
+    nvfp4r::ResetLaunch p = {};
+    p.logits = logits;
+    p.row_stride = row_stride;
+    p.B = B;
+    p.V = V;
+    p.scratch = static_cast<nvfp4r::RowScratch*>(workspace);
+    p.states = states;
+    p.state_slots = state_slots;
+    p.last_ids = last_ids;
+    p.nl_bitmap = nl_bitmap;
+    p.dnl_bitmap = dnl_bitmap;
+    p.params = *params;
+    p.decisions = decisions;
+    p.entropy_out = nullptr;
+    p.needs_state = 1;
+    cudaError_t e = nvfp4r::launch_reset(p, true, as_stream(stream));
+    return e == cudaSuccess ? NVFP4R_OK : cuda_fail(e, "reset_step launch");
+}
+
+int nvfp4r_entropy(const float* logits, int64_t row_stride, int B, int V, float* entropy,
+                   void* workspace, size_t workspace_bytes, void* stream) {
+    if (!logits || !entropy || !workspace) return fail(NVFP4R_ERR_INVALID_ARGUMENT, "entropy: null pointer");
+    if (B < 0 || V <= 0 || row_stride < V) return fail(NVFP4R_ERR_INVALID_ARGUMENT, "entropy: bad sizes");
+    if (workspace_bytes < nvfp4r_reset_workspace_bytes(B))
+        return fail(NVFP4R_ERR_INVALID_ARGUMENT, "entropy: workspace too small");
+    if (!aligned(workspace, 8) || !aligned(logits, 4))
+        return fail(NVFP4R_ERR_ALIGNMENT, "entropy: workspace needs 8-byte alignment");
+    if (B == 0) return NVFP4R_OK;
+    nvfp4r::ResetLaunch p = {};
+    p.logits = logits;
+    p.row_stride = row_stride;
+    p.B = B;
+    p.V = V;
+    p.scratch = static_cast<nvfp4r::RowScratch*>(workspace);
+    p.entropy_out = entropy;
+    p.needs_state = 0;
+    cudaError_t e = nvfp4r::launch_reset(p, false, as_stream(stream));
+    return e == cudaSuccess ? NVFP4R_OK : cuda_fail(e, "entropy launch");
+}
+
+int nvfp4r_set_gemv_tuning(int ctas_per_sm, int use_pdl, int force_generic) {
+    nvfp4r::GemvTuning& t = nvfp4r::gemv_tuning();
+    if (ctas_per_sm > 8) return fail(NVFP4R_ERR_INVALID_ARGUMENT, "tuning: ctas_per_sm > 8");
+    if (ctas_per_sm > 0) t.ctas_per_sm = ctas_per_sm;
+    if (use_pdl >= 0) t.use_pdl = use_pdl ? 1 : 0;
+    if (force_generic >= 0) t.force_generic = force_generic ? 1 : 0;
+    return NVFP4R_OK;
+}
+
+int nvfp4r_check_device_status(void) {
+    int flag = 0;
+    cudaError_t e = nvfp4r::read_and_clear_device_status(&flag);
+    if (e != cudaSuccess) return cuda_fail(e, "device status");
+    return flag ? fail(NVFP4R_ERR_DEVICE_TIMEOUT, "a bounded device-side wait gave up") : NVFP4R_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,44 @@
+// Launch record and scratch layout of the ReSET step kernels.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/nvfp4r_b200.h"
+
+namespace nvfp4r {
+
+constexpr int kResetMaxSlices = 32;
+
+// One record per logits row, in caller-provided (or static) scratch memory.
+struct RowScratch {
+    float pmax[kResetMaxSlices];    // slice max
+    float psum[kResetMaxSlices];    // slice sum of exp(x - slice max)
+    int parg[kResetMaxSlices];      // slice argmax (index within the row)
+    double pent[kResetMaxSlices];   // slice sum of p*log(max(p,1e-10))
+    double temp;                    // temperature chosen for the row
+    unsigned ticket;                // arrival counter of the entropy kernel
+    int argmax;                     // row argmax
+};
+
+struct ResetLaunch {
+    const float* logits;
+    int64_t row_stride;
+    int B, V;
+    int n_slices, slice_len;
+    RowScratch* scratch;
+    nvfp4r_reset_state* states;
+    const int32_t* state_slots;
+    const int32_t* last_ids;
+    const uint32_t* nl_bitmap;
+    const uint32_t* dnl_bitmap;
+    nvfp4r_reset_params params;
+    nvfp4r_reset_decision* decisions;
+    float* entropy_out;
+    int needs_state;     // 0: entropy only
+};
+
+int reset_pick_slices(int B, int V);
+cudaError_t launch_reset(ResetLaunch p, bool scale, cudaStream_t stream);
+
+}  // namespace nvfp4r

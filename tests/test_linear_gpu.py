@@ -1,0 +1,89 @@
+"""GPU parity of the fused quantize+GEMV (``nvfp4r_linear``)."""
+
+from __future__ import annotations
+
+import zlib
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import nvfp4 as onv
+from helpers import cuda, make_activation, make_weight, rel_l2
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def capi():
+    from reset_b200 import capi as c
+    return c
+
+
+QWEN3_8B = {"qkv_proj": (6144, 4096), "o_proj": (4096, 4096),
+            "gate_up_proj": (24576, 4096), "down_proj": (4096, 12288)}
+
+
+@pytest.mark.parametrize("name", list(QWEN3_8B))
+@pytest.mark.parametrize("M", [1, 2, 4, 8])
+def test_linear_qwen3_8b_shapes(capi, name, M):
+    """BASELINE config 1: the Qwen3-8B decode linears incl. activation quantization.
+    Row count is cut to 512 rows of the full N for the oracle's sake; the full-N
+    case is covered by the property test below."""
+    N, K = QWEN3_8B[name]
+    Nt = 512
+    wc, wsf, gs_w = make_weight(Nt, K, seed=zlib.crc32(f"{name}{M}w".encode()) % 1000)
+    xb = make_activation(M, K, seed=zlib.crc32(f"{name}{M}x".encode()) % 1000)
+    gs_x = onv.global_scale_for(xb.float().numpy())
+    gs_inv = float(np.float32(1.0) / np.float32(gs_x))
+    alpha = gs_w * gs_x
+    gs = torch.tensor([gs_inv], dtype=torch.float32, device="cuda")
+    out = capi.linear(xb.cuda(), gs, cuda(wc), cuda(wsf), alpha, out_dtype=torch.float32)
+    torch.cuda.synchronize()
+    xc, xsf = onv.quantize_nvfp4(xb.float().numpy(), gs_inv)
+    exact = onv.linear_f64(wc, wsf, xc, xsf, alpha=alpha)
+    assert rel_l2(out.cpu().numpy(), exact) <= 1e-3
+    assert rel_l2(out.cpu().numpy(), exact) <= 1e-5
+    out_bf = capi.linear(xb.cuda(), gs, cuda(wc), cuda(wsf), alpha)
+    assert out_bf.dtype == torch.bfloat16
+    ref_bf = torch.from_numpy(exact.astype(np.float32)).to(torch.bfloat16)
+    ulp = (out_bf.cpu().view(torch.int16).int() - ref_bf.view(torch.int16).int()).abs().max().item()
+    assert ulp <= 1
+
+
+@pytest.mark.parametrize("N,K,M", [(24576, 4096, 1), (4096, 12288, 8), (6144, 4096, 3), (5120, 3200, 2)])
+def test_linear_equals_quant_then_gemv_full_size(capi, N, K, M):
+    """Size-independent property at full size: the fused launch gives bit-identical
+    output to nvfp4r_quant followed by nvfp4r_gemv on the same inputs."""
+    w, ws = onv.random_nvfp4((N,), K, seed=3)
+    xb = make_activation(M, K, seed=4).cuda()
+    gs = torch.tensor([123.0], dtype=torch.float32, device="cuda")
+    wd, wsd = cuda(w), cuda(ws)
+    fused = capi.linear(xb, gs, wd, wsd, 0.5, out_dtype=torch.float32)
+    xc, xsf = capi.quant(xb, gs)
+    out = torch.empty((M, N), dtype=torch.float32, device="cuda")
+    capi.gemv_out(wd.unsqueeze(0).expand(M, -1, -1), wsd.unsqueeze(0).expand(M, -1, -1),
+                  xc.view(M, 1, -1), xsf.view(M, 1, -1), out, 0.5)
+    torch.cuda.synchronize()
+    assert torch.equal(fused, out)
+
+
+def test_linear_m_above_eight_and_strided_x(capi):
+    N, K, M = 256, 2048, 13
+    w, ws = onv.random_nvfp4((N,), K, seed=5)
+    big = make_activation(M, 2 * K, seed=6).cuda()
+    xb = big[:, K:]
+    gs = torch.tensor([77.0], dtype=torch.float32, device="cuda")
+    out = capi.linear(xb, gs, cuda(w), cuda(ws), 1.0, out_dtype=torch.float32)
+    torch.cuda.synchronize()
+    xc, xsf = onv.quantize_nvfp4(xb.cpu().float().numpy(), 77.0)
+    assert rel_l2(out.cpu().numpy(), onv.linear_f64(w, ws, xc, xsf)) <= 1e-5
+
+
+def test_linear_rejects_m_above_limit(capi):
+    from reset_b200 import _lib
+    w, ws = onv.random_nvfp4((8,), 64, seed=1)
+    xb = make_activation(17, 64, seed=2).cuda()
+    gs = torch.tensor([1.0], dtype=torch.float32, device="cuda")
+    with pytest.raises(_lib.Nvfp4rError):
+        capi.linear(xb, gs, cuda(w), cuda(ws), 1.0)
