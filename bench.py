@@ -1,0 +1,356 @@
+"""Benchmark of the NVFP4 W4A4 decode linear path on B200.
+
+Workload (``config.workload``): the Qwen3-8B decode linear set - qkv_proj 4096->6144,
+o_proj 4096->4096, gate_up_proj 4096->24576, down_proj 12288->4096 - in NVFP4 W4A4 at
+M in {1,2,4,8}, each call including the activation quantization (one fused launch per
+linear). One *step* is one pass over the 4 x 4 = 16 (linear, M) pairs. Every launch
+reads a different copy of its weight (``weight_copies`` copies per linear, > 1 GB in
+total, cycled), so no launch finds its weight in L2.
+
+Metric: HBM GB/s = algorithmic bytes of the step / step time, where the algorithmic
+bytes of one linear are N*K/2 + N*K/16 (weight codes + scales, counted once whatever
+M is) + M*K*2 (bf16 activations in) + M*N*2 (bf16 out).
+
+``python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]``; under
+torchrun (N > 1) the linears are tensor-parallel: qkv/gate_up column-sharded, o/down
+row-sharded with an NCCL all-reduce of the [M, hidden] partial sums after each.
+Rank 0 prints one JSON line.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import tempfile
+import time
+from pathlib import Path
+
+import torch
+
+REPO = Path(__file__).resolve().parent
+sys.path.insert(0, str(REPO))
+
+LINEARS = [  # name, N, K, tensor-parallel style
+    ("qkv_proj", 6144, 4096, "column"),
+    ("o_proj", 4096, 4096, "row"),
+    ("gate_up_proj", 24576, 4096, "column"),
+    ("down_proj", 4096, 12288, "row"),
+]
+M_VALUES = (1, 2, 4, 8)
+HIDDEN = 4096
+WEIGHT_COPIES = 12
+FALLBACK_HBM_GBS = 6650.0
+# dram__bytes_read.sum + dram__bytes_write.sum per launch, averaged over the 16
+# launches of one step, from profiles/gemv_stream_qwen3_8b_step.txt
+NCU_TRAFFIC_BYTES_PER_LAUNCH = None
+
+
+def linear_bytes(N: int, K: int, M: int) -> int:
+    return N * K // 2 + N * K // 16 + M * K * 2 + M * N * 2
+
+
+def step_bytes(tp: int = 1) -> int:
+    return sum(linear_bytes(N, K, M) for _, N, K, _ in LINEARS for M in M_VALUES)
+
+
+def measured_peak():
+    p = REPO / "MEASURED_PEAKS.json"
+    if p.exists():
+        try:
+            return float(json.loads(p.read_text())["hbm_gbs"]), "measured"
+        except Exception:
+            pass
+    return FALLBACK_HBM_GBS, "fallback"
+
+
+class ClockSampler:
+    """nvidia-smi samples of SM clock and throttle reasons during the timed region."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.tmp = tempfile.NamedTemporaryFile("w+", suffix=".csv", delete=False)
+        self.proc = None
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                 "-i", str(index), "-lms", "100"], stdout=self.tmp, stderr=subprocess.DEVNULL)
+        except OSError:
+            self.proc = None
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        self.tmp.flush()
+        rows = [r.strip().split(", ") for r in Path(self.tmp.name).read_text().splitlines() if r.strip()]
+        os.unlink(self.tmp.name)
+        sm = sorted(int(r[0]) for r in rows if r[0].isdigit())
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = sorted({n for r in rows if len(r) >= 6 for n, v in zip(names, r[2:6]) if v == "Active"})
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None,
+                "sm_max_mhz": int(rows[0][1]) if rows and rows[0][1].isdigit() else None,
+                "samples": len(sm), "reasons": reasons}
+
+
+# --------------------------------------------------------------------------- ours
+
+def build_weights(rank: int, tp: int, device):
+    """Random NVFP4 codes + scale bytes (scales below 1.0, as the reference's own test
+    generator bounds them) for this rank's shard of every linear, WEIGHT_COPIES copies."""
+    g = torch.Generator(device=device).manual_seed(1234 + rank)
+    shards = []
+    for name, N, K, style in LINEARS:
+        n = N // tp if style == "column" else N
+        k = K // tp if style == "row" else K
+        copies = []
+        for _ in range(WEIGHT_COPIES):
+            w = torch.randint(0, 256, (n, k // 2), dtype=torch.uint8, device=device, generator=g)
+            s = torch.randint(1, 0x38, (n, k // 16), dtype=torch.uint8, device=device, generator=g)
+            copies.append((w, s))
+        shards.append((name, n, k, style, copies))
+    return shards
+
+
+def make_inputs(shards, device, seed):
+    g = torch.Generator(device="cpu").manual_seed(seed)
+    xs = {}
+    for name, n, k, style, _ in shards:
+        for M in M_VALUES:
+            x = torch.randn(M, k, generator=g, dtype=torch.float32)
+            cols = torch.randperm(k, generator=g)[: max(1, k // 1000)]
+            x[:, cols] *= 20.0
+            xs[(name, M)] = x.to(torch.bfloat16)
+    return xs
+
+
+def run_ours(args, rank, world, local_rank):
+    import torch.distributed as dist
+
+    from reset_b200 import nvfp4r  # registers torch.ops.nvfp4r.* (raises if not built)
+
+    device = torch.device("cuda", local_rank)
+    torch.cuda.set_device(device)
+    tp = world
+    if world > 1:
+        dist.init_process_group("nccl", device_id=device)
+    shards = build_weights(rank, tp, device)
+    host_x = make_inputs(shards, device, seed=7)
+    pinned_x = {k: v.pin_memory() for k, v in host_x.items()}
+    dev_x = {k: v.to(device) for k, v in host_x.items()}
+    gs = torch.tensor([100.0], dtype=torch.float32, device=device)
+    pinned_out = {(name, M): torch.empty((M, n), dtype=torch.bfloat16).pin_memory()
+                  for name, n, k, style, _ in shards for M in M_VALUES}
+    counters = {name: 0 for name, *_ in shards}
+    launches = 0
+
+    def one_linear(name, n, k, style, copies, M, x):
+        nonlocal launches
+        w, s = copies[counters[name] % WEIGHT_COPIES]
+        counters[name] += 1
+        out = nvfp4r.linear(x, gs, w, s, 1.0, torch.bfloat16)
+        launches += 1
+        if world > 1 and style == "row":
+            dist.all_reduce(out)
+        return out
+
+    def step_resident():
+        for M in M_VALUES:
+            for name, n, k, style, copies in shards:
+                one_linear(name, n, k, style, copies, M, dev_x[(name, M)])
+
+    def step_e2e():
+        for M in M_VALUES:
+            for name, n, k, style, copies in shards:
+                x = pinned_x[(name, M)].to(device, non_blocking=True)
+                out = one_linear(name, n, k, style, copies, M, x)
+                pinned_out[(name, M)].copy_(out, non_blocking=True)
+
+    def timed(fn, steps, warmup):
+        for _ in range(warmup):
+            fn()
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        ms = torch.tensor([e0.elapsed_time(e1)], dtype=torch.float64, device=device)
+        if world > 1:
+            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        return float(ms.item())
+
+    sampler = ClockSampler(local_rank) if rank == 0 else None
+    launches = 0
+    ms_total = timed(step_resident, args.steps, args.warmup)
+    timed_launches = launches - args.warmup * 16
+    clocks = sampler.stop() if sampler else None
+    ms_e2e = timed(step_e2e, args.steps, max(3, args.warmup))
+
+    # per-(linear, M) latency table, each pair timed alone over rotating copies
+    detail = {}
+    if world == 1:
+        for name, n, k, style, copies in shards:
+            for M in M_VALUES:
+                reps = 60
+                for _ in range(WEIGHT_COPIES):
+                    one_linear(name, n, k, style, copies, M, dev_x[(name, M)])
+                torch.cuda.synchronize()
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+                for _ in range(reps):
+                    one_linear(name, n, k, style, copies, M, dev_x[(name, M)])
+                e1.record()
+                torch.cuda.synchronize()
+                us = e0.elapsed_time(e1) / reps * 1e3
+                detail[f"{name}_M{M}"] = {"us": round(us, 2),
+                                          "gbs": round(linear_bytes(n, k, M) / us / 1e3, 1)}
+
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return None
+    peak, peak_kind = measured_peak()
+    bytes_step = step_bytes()
+    ms_step = ms_total / args.steps
+    gbs = bytes_step / (ms_step * 1e-3) / 1e9
+    gbs_e2e = bytes_step / (ms_e2e / args.steps * 1e-3) / 1e9
+    for v in detail.values():
+        v["pct_of_peak"] = round(100.0 * v["gbs"] / peak, 1)
+    line = {
+        "metric": "HBM GB/s over the Qwen3-8B NVFP4 W4A4 decode linear set, M=1..8, incl. activation quantization",
+        "value": round(gbs, 1), "unit": "GB/s", "n_gpus": world, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": round(ms_step, 5), "higher_is_better": True,
+        "scaling": "strong", "vs_baseline": None, "dtype": "e2m1 x e2m1 (f16 block sums, f32 accumulate)",
+        "data": "synthetic",
+        "config": {"workload": "Qwen3-8B decode linears qkv/o/gate_up/down x M{1,2,4,8}, fused quant+GEMV",
+                   "launches_per_step": 16, "weight_copies": WEIGHT_COPIES,
+                   "l2": "every launch reads a weight copy not touched for >1 GB of traffic (inputs larger than L2)",
+                   "parallelism": f"tp{world}"},
+        "e2e": {"value": round(gbs_e2e, 1), "unit": "GB/s",
+                "h2d_bytes_per_step": sum(M * k * 2 for _, n, k, _, _ in shards for M in M_VALUES),
+                "d2h_bytes_per_step": sum(M * n * 2 for _, n, k, _, _ in shards for M in M_VALUES)},
+        "gpu_launches": timed_launches,
+        "clocks": clocks,
+        "roofline": {"bound": "hbm", "achieved": round(gbs / world, 1), "peak": peak, "unit": "GB/s",
+                     "frac": round(gbs / world / peak, 4), "peak_kind": f"of {peak_kind}",
+                     "kernel": "gemv_stream_kernel (16 launches per step)",
+                     "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH},
+        "detail_us_gbs": detail,
+    }
+    if world == 1:
+        line["cpu_baseline"] = cpu_baseline(sample_repeats=2)
+    if world > 1:
+        dist.destroy_process_group()
+    return line
+
+
+# ---------------------------------------------------------------------- reference / CPU
+
+def _cpu_pass(weights, xs, gs_inv):
+    """One M=1 pass over the four linears with the torch-CPU port of the reference's
+    dequantise-then-matmul (incl. the activation quantizer)."""
+    from oracle import torch_port as otp
+    for (w, s), x in zip(weights, xs):
+        xc, xsf = otp.quantize_torch(x, gs_inv)
+        otp.linear_torch(w, s, xc, xsf, 1.0)
+
+
+def _cpu_setup():
+    g = torch.Generator().manual_seed(99)
+    weights, xs = [], []
+    for name, N, K, _ in LINEARS:
+        weights.append((torch.randint(0, 256, (N, K // 2), dtype=torch.uint8, generator=g),
+                        torch.randint(1, 0x38, (N, K // 16), dtype=torch.uint8, generator=g)))
+        xs.append(torch.randn(1, K, generator=g).to(torch.bfloat16))
+    nbytes = sum(linear_bytes(N, K, 1) for _, N, K, _ in LINEARS)
+    return weights, xs, nbytes
+
+
+def cpu_baseline(sample_repeats: int) -> dict:
+    torch.set_num_threads(os.cpu_count() or 1)
+    weights, xs, nbytes = _cpu_setup()
+    _cpu_pass(weights, xs, 100.0)
+    ts = []
+    for _ in range(sample_repeats):
+        t0 = time.perf_counter()
+        _cpu_pass(weights, xs, 100.0)
+        ts.append(time.perf_counter() - t0)
+    t = sorted(ts)[len(ts) // 2]
+    return {"value": round(nbytes / t / 1e9, 3), "unit": "GB/s", "cores": torch.get_num_threads(),
+            "kind": "port",
+            "sample": f"M=1 pass over the four Qwen3-8B linears (1 of the 4 M values), "
+                      f"median of {sample_repeats}, {t * 1e3:.0f} ms per pass"}
+
+
+def run_reference(args, rank, world):
+    """The reference's CPU implementation of the path (PyTorch gather-dequantise +
+    fp32 matmul, kernels/tests/conftest.py:23-55) timed on the host cores through its
+    port in oracle/torch_port.py; the Python reference itself is not present on the
+    GPU box."""
+    if rank != 0:
+        return None
+    torch.set_num_threads(os.cpu_count() or 1)
+    weights, xs, nbytes = _cpu_setup()
+    for _ in range(args.warmup):
+        _cpu_pass(weights, xs, 100.0)
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        _cpu_pass(weights, xs, 100.0)
+    t = (time.perf_counter() - t0) / args.steps
+    gbs = nbytes / t / 1e9
+    sample = "each step = the M=1 pass over the four Qwen3-8B linears incl. activation quantization"
+    return {
+        "impl": "reference",
+        "metric": "HBM GB/s over the Qwen3-8B NVFP4 W4A4 decode linear set, M=1..8, incl. activation quantization",
+        "value": round(gbs, 3), "unit": "GB/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": round(t * 1e3, 3), "higher_is_better": True, "scaling": "strong",
+        "vs_baseline": None, "dtype": "f32 dequantise + f32 matmul on CPU", "data": "synthetic",
+        "config": {"workload": "Qwen3-8B decode linears qkv/o/gate_up/down x M{1,2,4,8}, fused quant+GEMV",
+                   "sample": sample, "parallelism": "host cores"},
+        "cpu_baseline": {"value": round(gbs, 3), "unit": "GB/s", "cores": torch.get_num_threads(),
+                         "kind": "port", "sample": sample},
+        "e2e": {"value": round(gbs, 3), "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=30)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.impl == "reference":
+        line = run_reference(args, rank, world)
+    else:
+        if not torch.cuda.is_available():
+            raise SystemExit("bench.py: no CUDA device (there is no CPU fallback for the product path)")
+        line = run_ours(args, rank, world, local_rank)
+    if line is not None:
+        print(json.dumps(line), flush=True)
+
+
+if __name__ == "__main__":
+    main()

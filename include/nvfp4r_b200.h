@@ -118,6 +118,32 @@ NVFP4R_API int nvfp4r_linear(const void* x, int64_t x_row_stride, int M, int K,
                              void* stream);
 
 /* ------------------------------------------------------------------------- *
+ * Tensor-core GEMM (tcgen05 block-scaled MMA, kind mxf4nvf4, one e4m3 scale per
+ * 16 elements) for M above the GEMV crossover:
+ *   C[m, n] = alpha * sum_k dq(A[m, k]) * dq(B[n, k])
+ * Stands in for `torch.ops.nvfp4r.gemm(A, B, SFA, SFB, C, alpha)` -
+ * kernels/csrc/bindings.cpp:86-103 and kernels/cuda/gemm/gemm_nvfp4.cu:517-659.
+ *   A   [M, K/2] activation codes, contiguous     SFA swizzled, >= ceil(M/128)*128 rows
+ *   B   [N, K/2] weight codes, contiguous         SFB swizzled, >= ceil(N/128)*128 rows
+ *   C   M*N elements of out_dtype (bf16 / fp16 / fp32)
+ *   c_layout  NVFP4R_C_N_MAJOR: element (m,n) at C[n*M + m], the layout the
+ *             reference kernel writes (gemm_nvfp4.cu:581, ops.py:86-88);
+ *             NVFP4R_C_M_MAJOR: element (m,n) at C[m*N + n].
+ * Any M >= 1 (the reference needs M % 64 == 0), N % 128 == 0, K % 256 == 0, any
+ * such K (the reference has a fixed table, gemm_nvfp4.cu:633-650).
+ * `workspace` (>= nvfp4r_gemm_workspace_bytes(M, N) bytes, 16-byte aligned) holds
+ * split-K partial sums and tile tickets; its first use must find it zeroed, and
+ * every call leaves it zeroed again. Calls sharing a workspace must be ordered
+ * on the stream. The first call on a device builds TMA descriptors on the host
+ * (cuTensorMapEncodeTiled) and caches them per (pointer, shape).
+ * ------------------------------------------------------------------------- */
+typedef enum nvfp4r_c_layout { NVFP4R_C_M_MAJOR = 0, NVFP4R_C_N_MAJOR = 1 } nvfp4r_c_layout;
+NVFP4R_API size_t nvfp4r_gemm_workspace_bytes(int M, int N);
+NVFP4R_API int nvfp4r_gemm(const void* A, const void* B, const void* SFA, const void* SFB,
+                           void* C, int M, int N, int K, float alpha, int out_dtype,
+                           int c_layout, void* workspace, size_t workspace_bytes, void* stream);
+
+/* ------------------------------------------------------------------------- *
  * Block-scale layout conversion, [rows, K/16] flat <-> 128x4 swizzled tiles.
  * `nvfp4r_unswizzle_blockscale` stands in for `_unswizzle_blockscale`
  * (kernels/python/nvfp4r/vllm_integration.py:99-117), used once per layer by

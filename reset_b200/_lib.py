@@ -16,6 +16,7 @@ OK = 0
 BF16, F16, F32 = 0, 1, 2
 SF_FLAT, SF_SWIZZLED = 0, 1
 RCP_EXACT, RCP_APPROX = 0, 1
+C_M_MAJOR, C_N_MAJOR = 0, 1
 RESET_MAX_WINDOW = 64
 LINEAR_MAX_M = 16
 
@@ -48,6 +49,8 @@ PROTOTYPES = {
     "nvfp4r_gemv": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i64, _i64, _i64, _i64, _i64, _i64,
                          _f, _i, _vp]),
     "nvfp4r_linear": (_i, [_vp, _i64, _i, _i, _vp, _vp, _vp, _i, _f, _vp, _i, _i, _vp]),
+    "nvfp4r_gemm_workspace_bytes": (_sz, [_i, _i]),
+    "nvfp4r_gemm": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _f, _i, _i, _vp, _sz, _vp]),
     "nvfp4r_unswizzle_blockscale": (_i, [_vp, _vp, _i, _i, _vp]),
     "nvfp4r_swizzle_blockscale": (_i, [_vp, _vp, _i, _i, _vp]),
     "nvfp4r_reset_workspace_bytes": (_sz, [_i]),

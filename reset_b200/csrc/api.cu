@@ -149,6 +149,37 @@ int nvfp4r_linear(const void* x, int64_t x_row_stride, int M, int K, const float
     return NVFP4R_OK;
 }
 
+size_t nvfp4r_gemm_workspace_bytes(int M, int N) {
+    return nvfp4r::gemm_workspace_bytes(M, N);
+}
+
+int nvfp4r_gemm(const void* A, const void* B, const void* SFA, const void* SFB, void* C, int M, int N,
+                int K, float alpha, int out_dtype, int c_layout, void* workspace,
+                size_t workspace_bytes, void* stream) {
+    if (!A || !B || !SFA || !SFB || !C) return fail(NVFP4R_ERR_INVALID_ARGUMENT, "gemm: null pointer");
+    if (M < 0 || N < 0 || K <= 0) return fail(NVFP4R_ERR_INVALID_ARGUMENT, "gemm: bad sizes");
+    if (out_dtype < NVFP4R_BF16 || out_dtype > NVFP4R_F32)
+        return fail(NVFP4R_ERR_INVALID_ARGUMENT, "gemm: bad out_dtype");
+    if (c_layout != NVFP4R_C_M_MAJOR && c_layout != NVFP4R_C_N_MAJOR)
+        return fail(NVFP4R_ERR_INVALID_ARGUMENT, "gemm: bad c_layout");
+    if (N % 128 != 0) return fail(NVFP4R_ERR_UNSUPPORTED_SHAPE, "gemm: N must be a multiple of 128");
+    if (K % 256 != 0) return fail(NVFP4R_ERR_UNSUPPORTED_SHAPE, "gemm: K must be a multiple of 256");
+    if (!aligned(A, 16) || !aligned(B, 16) || !aligned(SFA, 16) || !aligned(SFB, 16) || !aligned(C, 16))
+        return fail(NVFP4R_ERR_ALIGNMENT, "gemm: operands need 16-byte alignment");
+    if (M == 0 || N == 0) return NVFP4R_OK;
+    if (!workspace || workspace_bytes < nvfp4r_gemm_workspace_bytes(M, N) || !aligned(workspace, 16))
+        return fail(NVFP4R_ERR_INVALID_ARGUMENT, "gemm: workspace missing, too small or misaligned");
+    nvfp4r::GemmArgs g = {};
+    g.A = A; g.B = B; g.SFA = SFA; g.SFB = SFB; g.C = C;
+    g.M = M; g.N = N; g.K = K;
+    g.alpha = alpha; g.out_dtype = out_dtype; g.c_n_major = (c_layout == NVFP4R_C_N_MAJOR);
+    g.workspace = workspace;
+    const char* why = nullptr;
+    cudaError_t e = nvfp4r::launch_gemm(g, as_stream(stream), &why);
+    if (why != nullptr) return fail(NVFP4R_ERR_UNSUPPORTED_SHAPE, why);
+    return e == cudaSuccess ? NVFP4R_OK : cuda_fail(e, "gemm launch");
+}
+
 int nvfp4r_unswizzle_blockscale(const void* swizzled, void* flat, int rows, int K, void* stream) {
     if (!swizzled || !flat) return fail(NVFP4R_ERR_INVALID_ARGUMENT, "unswizzle: null pointer");
     if (rows < 0 || K <= 0 || K % 16) return fail(NVFP4R_ERR_UNSUPPORTED_SHAPE, "unswizzle: K % 16");

@@ -28,9 +28,10 @@ constexpr int kChunkBytes = 1024;                    // code bytes per row per t
 constexpr int kUnitsPerLane = kChunkBytes / kUnitBytes / kWarp;   // 2
 constexpr int kSlotRowBytes = kChunkBytes + kChunkBytes / 8;      // codes + scales
 constexpr int kSlotBytes = kRowsPerGroup * kSlotRowBytes;         // 4608
-constexpr int kSlots = 3;                            // per warp
-constexpr int kRingBytes = kWarps * kSlots * kSlotBytes;          // 110592
 constexpr int kMaxTokens = 8;
+// Ring depth per warp: 3 slots (110592 B per CTA) or 2 slots (73728 B, three
+// CTAs per SM).
+__host__ __device__ constexpr int ring_bytes(int slots) { return kWarps * slots * kSlotBytes; }
 
 struct StreamParams {
     GemvArgs a;
@@ -112,9 +113,10 @@ __device__ __forceinline__ void issue_tile(const StreamParams& p, int lane, int 
     }
 }
 
-template <int MT>
-__global__ void __launch_bounds__(kThreads, 1)
+template <int MT, int kSlots>
+__global__ void __launch_bounds__(kThreads, kSlots == 2 ? 3 : 1)
 gemv_stream_kernel(const __grid_constant__ StreamParams p) {
+    constexpr int kRingBytes = ring_bytes(kSlots);
     extern __shared__ __align__(128) uint8_t smem[];
     __shared__ __align__(8) uint64_t bars[kWarps * kSlots];
 
@@ -225,10 +227,24 @@ gemv_stream_kernel(const __grid_constant__ StreamParams p) {
                         Unit16 xu;
                         decode_codes(lds128(tok + chunk_off + u * kUnitBytes), xu);
                         const float2 sx = decode_scale_pair(lds16(tok + K2 + chunk_off / 8 + u * 2));
+                        // eight independent f16 chains (4 rows x 2 blocks), interleaved
+                        __half2 d[kRowsPerGroup][2];
 #pragma unroll
                         for (int r = 0; r < kRowsPerGroup; ++r) {
-                            const float d0 = block_dot(&wu[r].h[0], &xu.h[0]) * sx.x;
-                            const float d1 = block_dot(&wu[r].h[8], &xu.h[8]) * sx.y;
+                            d[r][0] = __hmul2(as_half2(wu[r].h[0]), as_half2(xu.h[0]));
+                            d[r][1] = __hmul2(as_half2(wu[r].h[8]), as_half2(xu.h[8]));
+                        }
+#pragma unroll
+                        for (int i = 1; i < 8; ++i)
+#pragma unroll
+                            for (int r = 0; r < kRowsPerGroup; ++r) {
+                                d[r][0] = __hfma2(as_half2(wu[r].h[i]), as_half2(xu.h[i]), d[r][0]);
+                                d[r][1] = __hfma2(as_half2(wu[r].h[8 + i]), as_half2(xu.h[8 + i]), d[r][1]);
+                            }
+#pragma unroll
+                        for (int r = 0; r < kRowsPerGroup; ++r) {
+                            const float d0 = __half2float(__hadd(__low2half(d[r][0]), __high2half(d[r][0]))) * sx.x;
+                            const float d1 = __half2float(__hadd(__low2half(d[r][1]), __high2half(d[r][1]))) * sx.y;
                             acc[r][m] = fmaf(d0, ws[r].x, acc[r][m]);
                             acc[r][m] = fmaf(d1, ws[r].y, acc[r][m]);
                         }
@@ -390,7 +406,7 @@ bool gemv_stream_supported(const GemvArgs& a) {
         if (a.x_stride % 16 != 0 || a.xsf_stride % 16 != 0) return false;
     }
     const int64_t xbytes = static_cast<int64_t>(a.M) * (a.K / 2 + a.K / 16);
-    return kRingBytes + xbytes <= 227 * 1024 - 1024;
+    return ring_bytes(3) + xbytes <= 227 * 1024 - 1024;
 }
 
 cudaError_t launch_gemv_stream(const GemvArgs& a, cudaStream_t stream) {
@@ -399,27 +415,32 @@ cudaError_t launch_gemv_stream(const GemvArgs& a, cudaStream_t stream) {
     p.n_groups = (a.N + kRowsPerGroup - 1) / kRowsPerGroup;
     p.n_chunks = (a.K / 2 + kChunkBytes - 1) / kChunkBytes;
     p.x_token_bytes = a.K / 2 + a.K / 16;
-    const size_t smem = kRingBytes + static_cast<size_t>(a.M) * p.x_token_bytes;
+    const GemvTuning& tune = gemv_tuning();
+    int ctas_per_sm = tune.ctas_per_sm > 0 ? tune.ctas_per_sm : 1;
+    if (a.M > 1 && ctas_per_sm > 2) ctas_per_sm = 2;     // register budget of the M > 1 variants
+    const bool two_slots = ctas_per_sm >= 3;
+    const size_t smem = ring_bytes(two_slots ? 2 : 3) + static_cast<size_t>(a.M) * p.x_token_bytes;
 
-    void (*kern)(StreamParams) = nullptr;
-    if (a.M == 1) kern = gemv_stream_kernel<1>;
-    else if (a.M == 2) kern = gemv_stream_kernel<2>;
-    else if (a.M <= 4) kern = gemv_stream_kernel<4>;
-    else kern = gemv_stream_kernel<8>;
+    using Kern = void (*)(StreamParams);
+    static const Kern table[4][2] = {
+        {gemv_stream_kernel<1, 3>, gemv_stream_kernel<1, 2>},
+        {gemv_stream_kernel<2, 3>, gemv_stream_kernel<2, 3>},
+        {gemv_stream_kernel<4, 3>, gemv_stream_kernel<4, 3>},
+        {gemv_stream_kernel<8, 3>, gemv_stream_kernel<8, 3>}};
+    const int ki = a.M == 1 ? 0 : a.M == 2 ? 1 : a.M <= 4 ? 2 : 3;
+    const Kern kern = table[ki][two_slots ? 1 : 0];
 
-    static bool attr_done[4][64] = {};
+    static bool attr_done[4][2][64] = {};
     int dev = 0;
     cudaError_t e = cudaGetDevice(&dev);
     if (e != cudaSuccess) return e;
-    const int ki = a.M == 1 ? 0 : a.M == 2 ? 1 : a.M <= 4 ? 2 : 3;
-    if (dev >= 0 && dev < 64 && !attr_done[ki][dev]) {
+    if (dev >= 0 && dev < 64 && !attr_done[ki][two_slots][dev]) {
         e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024 - 1024);
         if (e != cudaSuccess) return e;
-        attr_done[ki][dev] = true;
+        attr_done[ki][two_slots][dev] = true;
     }
 
-    const GemvTuning& tune = gemv_tuning();
-    int grid = device_sm_count() * (tune.ctas_per_sm > 0 ? tune.ctas_per_sm : 1);
+    int grid = device_sm_count() * ctas_per_sm;
     if (grid > p.n_groups) grid = p.n_groups;
 
     cudaLaunchConfig_t cfg = {};

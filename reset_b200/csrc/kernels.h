@@ -50,6 +50,24 @@ struct GemvTuning {
 };
 GemvTuning& gemv_tuning();
 
+// ---- gemm_tcgen05.cu ------------------------------------------------------
+struct GemmArgs {
+    const void* A;      // [M, K/2] activation codes
+    const void* B;      // [N, K/2] weight codes
+    const void* SFA;    // swizzled activation scales
+    const void* SFB;    // swizzled weight scales
+    void* C;
+    int M, N, K;
+    float alpha;
+    int out_dtype;
+    bool c_n_major;
+    void* workspace;
+};
+size_t gemm_workspace_bytes(int M, int N);
+// `*why` is set (and cudaSuccess returned) when the shape is outside what the
+// kernel handles.
+cudaError_t launch_gemm(const GemmArgs& g, cudaStream_t stream, const char** why);
+
 // Synchronises the device, returns the time-out flag set by bounded waits
 // inside the kernels and clears it.
 cudaError_t read_and_clear_device_status(int* flag);

@@ -1,0 +1,11 @@
+"""Module-level knobs behind ``configure()`` / ``status()``. Defaults can be preset
+with the reference's environment variables (vllm_integration.py:61-93)."""
+
+import os
+
+# Largest decode batch routed to the CUDA-core GEMV. The reference defaults to 2;
+# here it is the crossover measured on B200 against the tcgen05 kernel.
+GEMV_MAX_M = int(os.environ.get("NVFP4R_GEMV_MAX_M", "2"))
+GEMM_PAD_MAX_M = int(os.environ.get("NVFP4R_GEMM_PAD_MAX_M", "63"))
+ENABLE_GEMM_PATH = os.environ.get("NVFP4R_ENABLE_GEMM", "1") == "1"
+FALLBACK_BACKEND = os.environ.get("NVFP4R_FALLBACK_BACKEND", "none").lower()

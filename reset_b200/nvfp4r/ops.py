@@ -1,0 +1,56 @@
+"""Convenience wrappers around ``torch.ops.nvfp4r.*`` (reference:
+kernels/python/nvfp4r/ops.py:23-88). Integrations should call the ops directly so
+the calls stay traceable."""
+
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+
+def _ensure_3d(t: torch.Tensor, name: str) -> torch.Tensor:
+    if t.dim() == 3:
+        return t
+    if t.dim() == 2:
+        return t.unsqueeze(0)
+    raise ValueError(f"{name}: expected 2D or 3D tensor, got {t.dim()}D")
+
+
+def gemv(weight, weight_scale, x, x_scale, out: Optional[torch.Tensor] = None,
+         alpha: float = 1.0) -> torch.Tensor:
+    """``y = alpha * W @ x`` on pre-quantized NVFP4 operands (ops.py:23-58).
+
+    weight [L,N,K/2] u8, weight_scale [L,N,K/16] u8 (e4m3), x [L,P,K/2] (row 0 of P
+    is read), x_scale [L,P,K/16], out optional [L,N] fp16/bf16. 2-D inputs gain a
+    leading L=1. A weight expanded over L (stride 0) is streamed once for all L."""
+    w, ws = _ensure_3d(weight, "weight"), _ensure_3d(weight_scale, "weight_scale")
+    a, a_s = _ensure_3d(x, "x"), _ensure_3d(x_scale, "x_scale")
+    if out is None:
+        out = torch.empty((w.shape[0], w.shape[1]), dtype=torch.float16, device=w.device)
+    torch.ops.nvfp4r.gemv(w, ws, a, a_s, out, alpha)
+    return out
+
+
+def gemm(A, B, SFA, SFB, C, alpha: float = 1.0) -> torch.Tensor:
+    """``C = alpha * A @ B^T`` on the tensor cores (ops.py:62-88). The kernel writes
+    ``C``'s buffer N-major; the returned view is the [M,N] result."""
+    M, N = C.shape
+    torch.ops.nvfp4r.gemm(A, B, SFA, SFB, C, alpha)
+    return C.view(N, M).transpose(0, 1)
+
+
+def quant(x: torch.Tensor, global_scale_inv: torch.Tensor, swizzled: bool = False,
+          rcp_mode: int = 1):
+    """bf16 [M,K] -> (codes [M,K/2] u8, e4m3 scales u8), the op the reference borrows
+    from vLLM (vllm_integration.py:213). ``rcp_mode`` 1 matches that op bit for bit,
+    0 uses IEEE division."""
+    return torch.ops.nvfp4r.quant(x, global_scale_inv, swizzled, rcp_mode)
+
+
+def linear(x: torch.Tensor, global_scale_inv: torch.Tensor, weight: torch.Tensor,
+           weight_scale_flat: torch.Tensor, alpha: float, out_dtype: torch.dtype = torch.bfloat16,
+           rcp_mode: int = 1) -> torch.Tensor:
+    """Quantize up to 16 bf16 tokens and multiply by one NVFP4 weight in one launch."""
+    code = {torch.bfloat16: 0, torch.float16: 1, torch.float32: 2}[out_dtype]
+    return torch.ops.nvfp4r.linear(x, global_scale_inv, weight, weight_scale_flat, alpha, code, rcp_mode)

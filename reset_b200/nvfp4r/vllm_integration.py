@@ -1,0 +1,162 @@
+"""vLLM adapter for the nvfp4r kernels: same entry points as the reference's
+``nvfp4r.vllm_integration`` (kernels/python/nvfp4r/vllm_integration.py):
+
+* :func:`apply_nvfp4r_linear` (reference :448-496) - the hot path, one custom-op
+  dispatch per linear;
+* :func:`prime_nvfp4r_caches` (reference :359-396) - one-shot per-layer preparation;
+* :func:`_unswizzle_blockscale` (reference :99-117).
+
+Differences from the reference, all inside the dispatch:
+
+* M <= ``gemv_max_m``: ONE launch (``torch.ops.nvfp4r.linear``: quantize + GEMV fused)
+  instead of ``scaled_fp4_quant`` + ``expand`` + ``empty`` + ``nvfp4r.gemv``.
+* M  > ``gemv_max_m``: own quantizer (swizzled scales) + own tcgen05 GEMM for any M,
+  written M-major; no padding to 64 rows, no transpose/contiguous copy.
+* There is no CUTLASS/FlashInfer fallback branch (reference :299-318): a shape the
+  kernels cannot take raises.
+
+For a vLLM with the NVFP4 kernel registry (``model_executor/kernels/linear/nvfp4``),
+:class:`Nvfp4rLinearKernel` plugs in under ``VLLM_NVFP4_GEMM_BACKEND=nvfp4r`` through
+:func:`register_with_vllm`; no vLLM file is patched.
+"""
+
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+from .. import capi
+from . import _config
+
+_OUT_DTYPE_INT = {torch.bfloat16: 0, torch.float16: 1, torch.float32: 2}
+
+
+def _unswizzle_blockscale(sw_u8: torch.Tensor, M: int, K: int) -> torch.Tensor:
+    """128x4-tiled block scales -> flat ``[M, K/16]`` uint8 (reference :99-117)."""
+    return capi.unswizzle_blockscale(sw_u8.view(torch.uint8), M, K)
+
+
+def prime_nvfp4r_caches(layer: torch.nn.Module) -> None:
+    """Fill the per-layer derived state the hot path reads (reference :359-396):
+
+    ``_nvfp4r_alpha_host``            Python float of ``layer.alpha``
+    ``_nvfp4r_weight_scale_flat_3d``  ``[1, N, K/16]`` uint8 flat block scales
+
+    ``layer.weight_scale`` may be swizzled (the reference's case, vLLM's CUTLASS
+    format) or still flat ``[N, K/16]``; ``layer._nvfp4r_weight_scale_is_flat`` says
+    which when it is set, otherwise the shape decides. Idempotent.
+    """
+    if getattr(layer, "_nvfp4r_caches_primed", False):
+        return
+    alpha_t = getattr(layer, "alpha", None)
+    if alpha_t is None or not torch.is_tensor(alpha_t):
+        return
+    layer._nvfp4r_alpha_host = float(alpha_t.item())
+    K = getattr(layer, "input_size_per_partition", None)
+    N = getattr(layer, "output_size_per_partition", None)
+    ws = getattr(layer, "weight_scale", None)
+    if K is not None and N is not None and ws is not None and K // 16 > 0:
+        ws_u8 = ws.data.view(torch.uint8)
+        flat_hint = getattr(layer, "_nvfp4r_weight_scale_is_flat", None)
+        is_flat = flat_hint if flat_hint is not None else (
+            tuple(ws_u8.shape) == (N, K // 16) and (N % 128 != 0 or (K // 16) % 4 != 0))
+        flat = ws_u8.contiguous() if is_flat else _unswizzle_blockscale(ws_u8, N, K)
+        layer._nvfp4r_weight_scale_flat_3d = flat.reshape(1, N, K // 16).contiguous()
+    layer._nvfp4r_caches_primed = True
+
+
+def nvfp4r_linear(x_2d: torch.Tensor, weight: torch.Tensor, weight_scale_swizzled: torch.Tensor,
+                  weight_scale_flat_3d: torch.Tensor, input_global_scale_inv: torch.Tensor,
+                  alpha_host: float, output_size: int, gemv_max_m: int, out_dtype_int: int,
+                  enable_gemm: bool) -> torch.Tensor:
+    """All M-dependent branching of one linear (reference ``_nvfp4r_linear_impl``,
+    :165-318). Returns ``[M, output_size]`` in the requested dtype."""
+    M = x_2d.shape[0]
+    if M <= gemv_max_m or not enable_gemm:
+        if M <= 16:
+            return torch.ops.nvfp4r.linear(x_2d, input_global_scale_inv, weight,
+                                           weight_scale_flat_3d, alpha_host, out_dtype_int, 1)
+        parts = [torch.ops.nvfp4r.linear(x_2d[i:i + 16], input_global_scale_inv, weight,
+                                         weight_scale_flat_3d, alpha_host, out_dtype_int, 1)
+                 for i in range(0, M, 16)]
+        return torch.cat(parts, dim=0)
+    return torch.ops.nvfp4r.linear_tc(x_2d, input_global_scale_inv, weight, weight_scale_swizzled,
+                                      alpha_host, out_dtype_int, 1)
+
+
+def apply_nvfp4r_linear(layer: torch.nn.Module, x: torch.Tensor,
+                        bias: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Hot path (reference :448-496). Reads only tensors and constant Python
+    attributes of ``layer``: no ``.item()``, no ``setattr``, no environment reads."""
+    output_size = layer.output_size_per_partition
+    if getattr(layer, "weights_padding_cols", 0) != 0:
+        raise RuntimeError("nvfp4r: K-padded weights are not supported (no fallback backend)")
+    output_shape = (*x.shape[:-1], output_size)
+    x_2d = x.reshape(-1, x.shape[-1])
+    out = nvfp4r_linear(x_2d, layer.weight, layer.weight_scale, layer._nvfp4r_weight_scale_flat_3d,
+                        layer.input_global_scale_inv, layer._nvfp4r_alpha_host, output_size,
+                        _config.GEMV_MAX_M, _OUT_DTYPE_INT[x.dtype], _config.ENABLE_GEMM_PATH)
+    if bias is not None:
+        out = out + bias
+    return out.view(*output_shape)
+
+
+def register_with_vllm() -> bool:
+    """Make ``VLLM_NVFP4_GEMM_BACKEND=nvfp4r`` resolve to :class:`Nvfp4rLinearKernel` in a
+    vLLM that has the NVFP4 linear-kernel registry. Returns False when this vLLM has no
+    such registry (the reference's patched-vLLM route then applies: the patched
+    ``apply_nvfp4_linear`` calls :func:`apply_nvfp4r_linear`)."""
+    try:
+        import vllm.model_executor.kernels.linear as vk
+        from vllm.model_executor.kernels.linear.nvfp4.base import NvFp4LinearKernel
+    except ImportError:
+        return False
+    table = getattr(vk, "_NVFP4_BACKEND_TO_KERNEL", None)
+    if table is None:
+        return False
+    if "nvfp4r" not in table:
+        table["nvfp4r"] = _make_kernel_class(NvFp4LinearKernel)
+    return True
+
+
+def _make_kernel_class(base):
+    class Nvfp4rLinearKernel(base):
+        """NVFP4 linear through the nvfp4r B200 kernels."""
+
+        @classmethod
+        def is_supported(cls, compute_capability=None):
+            if not torch.cuda.is_available():
+                return False, "CUDA device required"
+            major, minor = torch.cuda.get_device_capability()
+            if (major, minor) != (10, 0):
+                return False, "nvfp4r kernels are built for sm_100a only"
+            return True, None
+
+        @classmethod
+        def can_implement(cls, config):
+            return True, None
+
+        def process_weights_after_loading(self, layer: torch.nn.Module) -> None:
+            # the checkpoint's flat [N, K/16] scales are kept for the GEMV and a
+            # swizzled copy is made for the tensor-core GEMM
+            flat = layer.weight_scale.data.view(torch.uint8).contiguous()
+            layer._nvfp4r_weight_scale_is_flat = True
+            prime_nvfp4r_caches(layer)
+            layer.weight_scale = torch.nn.Parameter(
+                capi.swizzle_blockscale(flat).view(torch.float8_e4m3fn), requires_grad=False)
+            layer.weights_padding_cols = 0
+
+        def apply_weights(self, layer, x, bias=None):
+            return apply_nvfp4r_linear(layer, x, bias)
+
+    return Nvfp4rLinearKernel
+
+
+def enable() -> None:  # pragma: no cover
+    """No-op kept for callers of the reference's legacy shim (reference :502-508)."""
+    return
+
+
+def disable() -> None:  # pragma: no cover
+    return
