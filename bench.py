@@ -152,14 +152,11 @@ def run_ours(args, rank, world, local_rank):
     pinned_out = {(name, M): torch.empty((M, n), dtype=torch.bfloat16).pin_memory()
                   for name, n, k, style, _ in shards for M in M_VALUES}
     counters = {name: 0 for name, *_ in shards}
-    launches = 0
 
     def one_linear(name, n, k, style, copies, M, x):
-        nonlocal launches
         w, s = copies[counters[name] % WEIGHT_COPIES]
         counters[name] += 1
         out = nvfp4r.linear(x, gs, w, s, 1.0, torch.bfloat16)
-        launches += 1
         if world > 1 and style == "row":
             dist.all_reduce(out)
         return out
@@ -176,17 +173,40 @@ def run_ours(args, rank, world, local_rank):
                 out = one_linear(name, n, k, style, copies, M, x)
                 pinned_out[(name, M)].copy_(out, non_blocking=True)
 
-    def timed(fn, steps, warmup):
-        for _ in range(warmup):
-            fn()
+    def capture_phases(fn):
+        """One CUDA graph per phase of the weight-copy cycle: a step launches each
+        linear 4 times, so WEIGHT_COPIES / 4 consecutive steps walk through all
+        copies; replaying the phases in order repeats exactly the eager sequence."""
+        phases = WEIGHT_COPIES // len(M_VALUES)
+        graphs = []
+        side = torch.cuda.Stream(device=device)
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            for name in counters:
+                counters[name] = 0
+            for _ in range(phases):
+                fn()                                   # eager warm-up of every copy
+            for name in counters:
+                counters[name] = 0
+            for _ in range(phases):
+                g = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g, stream=side):
+                    fn()
+                graphs.append(g)
+        torch.cuda.current_stream().wait_stream(side)
+        return graphs
+
+    def timed(graphs, steps, warmup):
+        for i in range(warmup):
+            graphs[i % len(graphs)].replay()
         torch.cuda.synchronize()
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
-        for _ in range(steps):
-            fn()
+        for i in range(steps):
+            graphs[i % len(graphs)].replay()
         e1.record()
         torch.cuda.synchronize()
         if world > 1:
@@ -196,12 +216,37 @@ def run_ours(args, rank, world, local_rank):
             dist.all_reduce(ms, op=dist.ReduceOp.MAX)
         return float(ms.item())
 
+    if args.case:
+        # one (linear, M) pair launched eagerly, for profiler captures on a small case
+        cname, cm = args.case.split(":")
+        cm = int(cm)
+        name, n, k, style, copies = next(sh for sh in shards if sh[0] == cname)
+        for _ in range(args.warmup):
+            one_linear(name, n, k, style, copies, cm, dev_x[(name, cm)])
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(args.steps):
+            one_linear(name, n, k, style, copies, cm, dev_x[(name, cm)])
+        e1.record()
+        torch.cuda.synchronize()
+        us = e0.elapsed_time(e1) / args.steps * 1e3
+        return {"case": args.case, "us_eager": round(us, 2), "launches": args.steps,
+                "algorithmic_bytes": linear_bytes(n, k, cm)}
+
     sampler = ClockSampler(local_rank) if rank == 0 else None
-    launches = 0
-    ms_total = timed(step_resident, args.steps, args.warmup)
-    timed_launches = launches - args.warmup * 16
+    g_res = capture_phases(step_resident)
+    # keep the GPU busy long enough before the timed region for clock samples to exist
+    t_end = time.perf_counter() + 0.4
+    while time.perf_counter() < t_end:
+        for g in g_res:
+            g.replay()
+        torch.cuda.synchronize()
+    ms_total = timed(g_res, args.steps, args.warmup)
+    timed_launches = args.steps * 16
+    g_e2e = capture_phases(step_e2e)
+    ms_e2e = timed(g_e2e, args.steps, max(3, args.warmup))
     clocks = sampler.stop() if sampler else None
-    ms_e2e = timed(step_e2e, args.steps, max(3, args.warmup))
 
     # per-(linear, M) latency table, each pair timed alone over rotating copies
     detail = {}
@@ -242,6 +287,7 @@ def run_ours(args, rank, world, local_rank):
         "config": {"workload": "Qwen3-8B decode linears qkv/o/gate_up/down x M{1,2,4,8}, fused quant+GEMV",
                    "launches_per_step": 16, "weight_copies": WEIGHT_COPIES,
                    "l2": "every launch reads a weight copy not touched for >1 GB of traffic (inputs larger than L2)",
+                   "launch": "CUDA-graph replay, one graph per step",
                    "parallelism": f"tp{world}"},
         "e2e": {"value": round(gbs_e2e, 1), "unit": "GB/s",
                 "h2d_bytes_per_step": sum(M * k * 2 for _, n, k, _, _ in shards for M in M_VALUES),
@@ -334,9 +380,10 @@ def run_reference(args, rank, world):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=30)
+    ap.add_argument("--steps", type=int, default=600)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--case", default="", help="profile one pair, e.g. gate_up_proj:1 (eager launches)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     rank = int(os.environ.get("RANK", "0"))
