@@ -130,18 +130,34 @@ NVFP4R_API int nvfp4r_linear(const void* x, int64_t x_row_stride, int M, int K,
  *             reference kernel writes (gemm_nvfp4.cu:581, ops.py:86-88);
  *             NVFP4R_C_M_MAJOR: element (m,n) at C[m*N + n].
  * Any M >= 1 (the reference needs M % 64 == 0), N % 128 == 0, K % 256 == 0, any
- * such K (the reference has a fixed table, gemm_nvfp4.cu:633-650).
- * `workspace` (>= nvfp4r_gemm_workspace_bytes(M, N) bytes, 16-byte aligned) holds
+ * such K (the reference has a fixed table, gemm_nvfp4.cu:633-650). Rows are taken 32
+ * at a time, each pass streaming the weight once: built for decode-sized M.
+ * `workspace` (>= nvfp4r_gemm_workspace_bytes(M, N, K) bytes, 16-byte aligned) holds
  * split-K partial sums and tile tickets; its first use must find it zeroed, and
  * every call leaves it zeroed again. Calls sharing a workspace must be ordered
  * on the stream. The first call on a device builds TMA descriptors on the host
  * (cuTensorMapEncodeTiled) and caches them per (pointer, shape).
  * ------------------------------------------------------------------------- */
 typedef enum nvfp4r_c_layout { NVFP4R_C_M_MAJOR = 0, NVFP4R_C_N_MAJOR = 1 } nvfp4r_c_layout;
-NVFP4R_API size_t nvfp4r_gemm_workspace_bytes(int M, int N);
+NVFP4R_API size_t nvfp4r_gemm_workspace_bytes(int M, int N, int K);
 NVFP4R_API int nvfp4r_gemm(const void* A, const void* B, const void* SFA, const void* SFB,
                            void* C, int M, int N, int K, float alpha, int out_dtype,
                            int c_layout, void* workspace, size_t workspace_bytes, void* stream);
+
+/* Fused decode linear on the tensor cores: quantize M bf16 tokens on chip and
+ * multiply by one NVFP4 weight, result M-major [M, N]. Stands in for the padded-GEMM
+ * branch of `_nvfp4r_linear_impl` (kernels/python/nvfp4r/vllm_integration.py:224-274:
+ * scaled_fp4_quant + pad to 64 rows + nvfp4r.gemm + transpose + contiguous) in one
+ * launch per 32 rows. weight [N,K/2]; weight_scale_swizzled in 128x4 tiles (the layout
+ * vLLM keeps in layer.weight_scale); workspace as for nvfp4r_gemm. */
+NVFP4R_API int nvfp4r_linear_tc(const void* x, int64_t x_row_stride, int M, int K,
+                                const float* global_scale_inv, const void* weight,
+                                const void* weight_scale_swizzled, int N, float alpha,
+                                void* out, int out_dtype, int rcp_mode,
+                                void* workspace, size_t workspace_bytes, void* stream);
+
+/* Debug/tuning: force the K split and ring depth of the tensor-core kernel (0 = automatic). */
+NVFP4R_API int nvfp4r_set_gemm_tuning(int splits, int stages);
 
 /* ------------------------------------------------------------------------- *
  * Block-scale layout conversion, [rows, K/16] flat <-> 128x4 swizzled tiles.

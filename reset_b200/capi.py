@@ -102,6 +102,48 @@ def linear(x: torch.Tensor, global_scale_inv: torch.Tensor, weight: torch.Tensor
     return out
 
 
+def gemm_workspace(M: int, N: int, K: int, device) -> torch.Tensor:
+    """Zero-initialised scratch for the tensor-core kernel (it leaves it zeroed)."""
+    n = L.lib().nvfp4r_gemm_workspace_bytes(M, N, K)
+    return torch.zeros((n + 15) // 16 * 2, dtype=torch.int64, device=device)
+
+
+def linear_tc(x: torch.Tensor, global_scale_inv: torch.Tensor, weight: torch.Tensor,
+              weight_scale_swizzled: torch.Tensor, alpha: float, workspace: torch.Tensor,
+              out_dtype: torch.dtype = torch.bfloat16, rcp_mode: int = L.RCP_EXACT) -> torch.Tensor:
+    """Fused quantize + tcgen05 GEMM: bf16 [M,K] x NVFP4 weight [N,K/2] -> [M,N]."""
+    _need_cuda(x, global_scale_inv, weight, weight_scale_swizzled, workspace)
+    if x.dtype != torch.bfloat16 or x.dim() != 2 or x.stride(1) != 1:
+        raise ValueError("linear_tc: x must be bf16 [M,K] with unit inner stride")
+    M, K = x.shape
+    w, ws = _u8(weight), _u8(weight_scale_swizzled)
+    N = w.shape[0]
+    out = torch.empty((M, N), dtype=out_dtype, device=x.device)
+    with torch.cuda.device(x.device):
+        st = L.lib().nvfp4r_linear_tc(x.data_ptr(), x.stride(0), M, K, global_scale_inv.data_ptr(),
+                                      w.data_ptr(), ws.data_ptr(), N, float(alpha), out.data_ptr(),
+                                      _DTYPE_CODE[out_dtype], rcp_mode, workspace.data_ptr(),
+                                      workspace.numel() * workspace.element_size(), _stream())
+    L.check(st, "nvfp4r_linear_tc")
+    return out
+
+
+def gemm(A, B, SFA, SFB, C: torch.Tensor, alpha: float, workspace: torch.Tensor,
+         n_major: bool = True) -> None:
+    """Pre-quantized tensor-core GEMM; C's buffer is written N-major (the reference's
+    layout) or M-major."""
+    _need_cuda(A, B, SFA, SFB, C, workspace)
+    a, b, sa, sb = _u8(A), _u8(B), _u8(SFA), _u8(SFB)
+    M, K2 = a.shape
+    N = b.shape[0]
+    with torch.cuda.device(a.device):
+        st = L.lib().nvfp4r_gemm(a.data_ptr(), b.data_ptr(), sa.data_ptr(), sb.data_ptr(), C.data_ptr(),
+                                 M, N, 2 * K2, float(alpha), _DTYPE_CODE[C.dtype],
+                                 L.C_N_MAJOR if n_major else L.C_M_MAJOR, workspace.data_ptr(),
+                                 workspace.numel() * workspace.element_size(), _stream())
+    L.check(st, "nvfp4r_gemm")
+
+
 def unswizzle_blockscale(swizzled: torch.Tensor, rows: int, K: int) -> torch.Tensor:
     _need_cuda(swizzled)
     sw = _u8(swizzled).contiguous()

@@ -149,35 +149,74 @@ int nvfp4r_linear(const void* x, int64_t x_row_stride, int M, int K, const float
     return NVFP4R_OK;
 }
 
-size_t nvfp4r_gemm_workspace_bytes(int M, int N) {
-    return nvfp4r::gemm_workspace_bytes(M, N);
+size_t nvfp4r_gemm_workspace_bytes(int M, int N, int K) {
+    return nvfp4r::gemm_workspace_bytes(M, N, K);
+}
+
+static int tc_common_checks(const char* who, int M, int N, int K, int out_dtype, const void* workspace,
+                            size_t workspace_bytes) {
+    if (M < 0 || N < 0 || K <= 0) return fail(NVFP4R_ERR_INVALID_ARGUMENT, "tensor-core path: bad sizes");
+    if (out_dtype < NVFP4R_BF16 || out_dtype > NVFP4R_F32)
+        return fail(NVFP4R_ERR_INVALID_ARGUMENT, "tensor-core path: bad out_dtype");
+    if (N % 128 != 0) return fail(NVFP4R_ERR_UNSUPPORTED_SHAPE, "tensor-core path: N must be a multiple of 128");
+    if (K % 256 != 0) return fail(NVFP4R_ERR_UNSUPPORTED_SHAPE, "tensor-core path: K must be a multiple of 256");
+    if (M == 0 || N == 0) return NVFP4R_OK;
+    if (!workspace || workspace_bytes < nvfp4r_gemm_workspace_bytes(M, N, K) || !aligned(workspace, 16))
+        return fail(NVFP4R_ERR_INVALID_ARGUMENT, "tensor-core path: workspace missing, too small or misaligned");
+    (void)who;
+    return NVFP4R_OK;
 }
 
 int nvfp4r_gemm(const void* A, const void* B, const void* SFA, const void* SFB, void* C, int M, int N,
                 int K, float alpha, int out_dtype, int c_layout, void* workspace,
                 size_t workspace_bytes, void* stream) {
     if (!A || !B || !SFA || !SFB || !C) return fail(NVFP4R_ERR_INVALID_ARGUMENT, "gemm: null pointer");
-    if (M < 0 || N < 0 || K <= 0) return fail(NVFP4R_ERR_INVALID_ARGUMENT, "gemm: bad sizes");
-    if (out_dtype < NVFP4R_BF16 || out_dtype > NVFP4R_F32)
-        return fail(NVFP4R_ERR_INVALID_ARGUMENT, "gemm: bad out_dtype");
     if (c_layout != NVFP4R_C_M_MAJOR && c_layout != NVFP4R_C_N_MAJOR)
         return fail(NVFP4R_ERR_INVALID_ARGUMENT, "gemm: bad c_layout");
-    if (N % 128 != 0) return fail(NVFP4R_ERR_UNSUPPORTED_SHAPE, "gemm: N must be a multiple of 128");
-    if (K % 256 != 0) return fail(NVFP4R_ERR_UNSUPPORTED_SHAPE, "gemm: K must be a multiple of 256");
-    if (!aligned(A, 16) || !aligned(B, 16) || !aligned(SFA, 16) || !aligned(SFB, 16) || !aligned(C, 16))
+    int st = tc_common_checks("gemm", M, N, K, out_dtype, workspace, workspace_bytes);
+    if (st != NVFP4R_OK || M == 0 || N == 0) return st;
+    if (!aligned(A, 16) || !aligned(B, 16) || !aligned(SFA, 16) || !aligned(SFB, 16))
         return fail(NVFP4R_ERR_ALIGNMENT, "gemm: operands need 16-byte alignment");
-    if (M == 0 || N == 0) return NVFP4R_OK;
-    if (!workspace || workspace_bytes < nvfp4r_gemm_workspace_bytes(M, N) || !aligned(workspace, 16))
-        return fail(NVFP4R_ERR_INVALID_ARGUMENT, "gemm: workspace missing, too small or misaligned");
-    nvfp4r::GemmArgs g = {};
-    g.A = A; g.B = B; g.SFA = SFA; g.SFB = SFB; g.C = C;
-    g.M = M; g.N = N; g.K = K;
-    g.alpha = alpha; g.out_dtype = out_dtype; g.c_n_major = (c_layout == NVFP4R_C_N_MAJOR);
-    g.workspace = workspace;
+    nvfp4r::TcLinearArgs g = {};
+    g.w = B; g.wsf_swizzled = SFB;
+    g.a_codes = A; g.a_sf_swizzled = SFA;
+    g.out = C; g.out_dtype = out_dtype; g.c_n_major = (c_layout == NVFP4R_C_N_MAJOR);
+    g.M = M; g.N = N; g.K = K; g.alpha = alpha; g.workspace = workspace;
     const char* why = nullptr;
-    cudaError_t e = nvfp4r::launch_gemm(g, as_stream(stream), &why);
+    cudaError_t e = nvfp4r::launch_linear_tc(g, as_stream(stream), &why);
     if (why != nullptr) return fail(NVFP4R_ERR_UNSUPPORTED_SHAPE, why);
     return e == cudaSuccess ? NVFP4R_OK : cuda_fail(e, "gemm launch");
+}
+
+int nvfp4r_linear_tc(const void* x, int64_t x_row_stride, int M, int K, const float* gs,
+                     const void* weight, const void* weight_scale_swizzled, int N, float alpha,
+                     void* out, int out_dtype, int rcp_mode, void* workspace, size_t workspace_bytes,
+                     void* stream) {
+    if (!x || !gs || !weight || !weight_scale_swizzled || !out)
+        return fail(NVFP4R_ERR_INVALID_ARGUMENT, "linear_tc: null pointer");
+    if (rcp_mode != NVFP4R_RCP_EXACT && rcp_mode != NVFP4R_RCP_APPROX)
+        return fail(NVFP4R_ERR_INVALID_ARGUMENT, "linear_tc: bad rcp_mode");
+    int st = tc_common_checks("linear_tc", M, N, K, out_dtype, workspace, workspace_bytes);
+    if (st != NVFP4R_OK || M == 0 || N == 0) return st;
+    if (!aligned(x, 16) || (x_row_stride % 8) || !aligned(weight, 16) || !aligned(weight_scale_swizzled, 16))
+        return fail(NVFP4R_ERR_ALIGNMENT, "linear_tc: x/weight need 16-byte alignment");
+    if (x_row_stride < K) return fail(NVFP4R_ERR_INVALID_ARGUMENT, "linear_tc: row stride < K");
+    nvfp4r::TcLinearArgs g = {};
+    g.w = weight; g.wsf_swizzled = weight_scale_swizzled;
+    g.xb = x; g.xb_stride = x_row_stride; g.gs = gs; g.rcp_mode = rcp_mode;
+    g.out = out; g.out_dtype = out_dtype; g.c_n_major = false;
+    g.M = M; g.N = N; g.K = K; g.alpha = alpha; g.workspace = workspace;
+    const char* why = nullptr;
+    cudaError_t e = nvfp4r::launch_linear_tc(g, as_stream(stream), &why);
+    if (why != nullptr) return fail(NVFP4R_ERR_UNSUPPORTED_SHAPE, why);
+    return e == cudaSuccess ? NVFP4R_OK : cuda_fail(e, "linear_tc launch");
+}
+
+int nvfp4r_set_gemm_tuning(int splits, int stages) {
+    if (splits < 0 || splits > 16 || stages < 0 || stages > 10)
+        return fail(NVFP4R_ERR_INVALID_ARGUMENT, "gemm tuning: splits 0..16, stages 0..10");
+    nvfp4r::set_tc_tuning(splits, stages);
+    return NVFP4R_OK;
 }
 
 int nvfp4r_unswizzle_blockscale(const void* swizzled, void* flat, int rows, int K, void* stream) {
@@ -265,9 +304,11 @@ int nvfp4r_set_gemv_tuning(int ctas_per_sm, int use_pdl, int force_generic) {
 }
 
 int nvfp4r_check_device_status(void) {
-    int flag = 0;
+    int flag = 0, flag2 = 0;
     cudaError_t e = nvfp4r::read_and_clear_device_status(&flag);
+    if (e == cudaSuccess) e = nvfp4r::read_and_clear_tc_status(&flag2);
     if (e != cudaSuccess) return cuda_fail(e, "device status");
+    flag |= flag2;
     return flag ? fail(NVFP4R_ERR_DEVICE_TIMEOUT, "a bounded device-side wait gave up") : NVFP4R_OK;
 }
 

@@ -51,22 +51,31 @@ struct GemvTuning {
 GemvTuning& gemv_tuning();
 
 // ---- gemm_tcgen05.cu ------------------------------------------------------
-struct GemmArgs {
-    const void* A;      // [M, K/2] activation codes
-    const void* B;      // [N, K/2] weight codes
-    const void* SFA;    // swizzled activation scales
-    const void* SFB;    // swizzled weight scales
-    void* C;
+// One NVFP4 weight [N,K/2] (+ swizzled scales) against M activation rows, either
+// bf16 rows quantized on the fly (xb) or pre-quantized codes + swizzled scales.
+struct TcLinearArgs {
+    const void* w;               // [N, K/2] weight codes
+    const void* wsf_swizzled;    // 128x4-tiled weight scales
+    const void* xb;              // bf16 [M, K] (fused quantizer) or nullptr
+    int64_t xb_stride;           // elements
+    const float* gs;
+    int rcp_mode;
+    const void* a_codes;         // [M, K/2] when xb == nullptr
+    const void* a_sf_swizzled;
+    void* out;
+    int out_dtype;
+    bool c_n_major;              // element (m,n) at out[n*M + m] instead of out[m*N + n]
     int M, N, K;
     float alpha;
-    int out_dtype;
-    bool c_n_major;
     void* workspace;
 };
-size_t gemm_workspace_bytes(int M, int N);
+size_t gemm_workspace_bytes(int M, int N, int K);
 // `*why` is set (and cudaSuccess returned) when the shape is outside what the
 // kernel handles.
-cudaError_t launch_gemm(const GemmArgs& g, cudaStream_t stream, const char** why);
+cudaError_t launch_linear_tc(const TcLinearArgs& g, cudaStream_t stream, const char** why);
+cudaError_t read_and_clear_tc_status(int* flag);
+// 0 = automatic
+void set_tc_tuning(int splits, int stages);
 
 // Synchronises the device, returns the time-out flag set by bounded waits
 // inside the kernels and clears it.

@@ -106,8 +106,9 @@ void gemm_op(const at::Tensor& A, const at::Tensor& B, const at::Tensor& SFA, co
     const int64_t M = A.size(0), K2 = A.size(1), N = B.size(0);
     TORCH_CHECK(B.size(1) == K2 && C.size(0) == M && C.size(1) == N, "gemm: shape mismatch");
     const c10::cuda::OptionalCUDAGuard guard(A.device());
-    at::Tensor& ws = gemm_workspace(A.device(), nvfp4r_gemm_workspace_bytes(static_cast<int>(M),
-                                                                           static_cast<int>(N)));
+    at::Tensor& ws = gemm_workspace(A.device(), nvfp4r_gemm_workspace_bytes(
+                                                    static_cast<int>(M), static_cast<int>(N),
+                                                    static_cast<int>(2 * K2)));
     const int st = nvfp4r_gemm(A.data_ptr(), B.data_ptr(), SFA.data_ptr(), SFB.data_ptr(), C.data_ptr(),
                                static_cast<int>(M), static_cast<int>(N), static_cast<int>(2 * K2),
                                static_cast<float>(alpha), dtype_code(C.scalar_type(), "gemm"),
@@ -164,6 +165,37 @@ at::Tensor linear_op(const at::Tensor& x, const at::Tensor& global_scale_inv, co
     return out;
 }
 
+// Padded-GEMM branch of the reference's `_nvfp4r_linear_impl`
+// (vllm_integration.py:224-274) as one op: on-chip quantizer + tcgen05 GEMM, [M,N] out.
+at::Tensor linear_tc_op(const at::Tensor& x, const at::Tensor& global_scale_inv, const at::Tensor& weight,
+                        const at::Tensor& weight_scale_swizzled, double alpha, int64_t out_dtype_int,
+                        int64_t rcp_mode) {
+    TORCH_CHECK(x.is_cuda() && weight.is_cuda() && weight_scale_swizzled.is_cuda() &&
+                    global_scale_inv.is_cuda(), "linear_tc: tensors must be CUDA");
+    TORCH_CHECK(x.scalar_type() == at::kBFloat16 && x.dim() == 2 && x.stride(1) == 1,
+                "linear_tc: x must be bfloat16 [M,K] with unit inner stride");
+    TORCH_CHECK(weight.dim() == 2 && weight.is_contiguous() && weight_scale_swizzled.is_contiguous(),
+                "linear_tc: weight [N,K/2] and its swizzled scales must be contiguous");
+    const int64_t M = x.size(0), K = x.size(1), N = weight.size(0);
+    TORCH_CHECK(weight.size(1) * 2 == K, "linear_tc: weight shape mismatch with x");
+    TORCH_CHECK(weight_scale_swizzled.numel() >= ((N + 127) / 128 * 128) * ((K / 16 + 3) / 4 * 4),
+                "linear_tc: swizzled weight_scale too small");
+    const c10::cuda::OptionalCUDAGuard guard(x.device());
+    const auto dt = out_dtype_int == 0 ? at::kBFloat16 : out_dtype_int == 1 ? at::kHalf : at::kFloat;
+    auto out = at::empty({M, N}, x.options().dtype(dt));
+    at::Tensor& ws = gemm_workspace(x.device(), nvfp4r_gemm_workspace_bytes(
+                                                    static_cast<int>(M), static_cast<int>(N),
+                                                    static_cast<int>(K)));
+    const int st = nvfp4r_linear_tc(x.data_ptr(), x.stride(0), static_cast<int>(M), static_cast<int>(K),
+                                    global_scale_inv.data_ptr<float>(), weight.data_ptr(),
+                                    weight_scale_swizzled.data_ptr(), static_cast<int>(N),
+                                    static_cast<float>(alpha), out.data_ptr(),
+                                    static_cast<int>(out_dtype_int), static_cast<int>(rcp_mode),
+                                    ws.data_ptr(), static_cast<size_t>(ws.nbytes()), current_stream());
+    check_status(st, "linear_tc");
+    return out;
+}
+
 at::Tensor entropy_op(const at::Tensor& logits, at::Tensor workspace) {
     TORCH_CHECK(logits.is_cuda() && logits.scalar_type() == at::kFloat && logits.dim() == 2 &&
                     logits.stride(1) == 1, "entropy: logits must be CUDA float32 [B,V]");
@@ -209,6 +241,8 @@ TORCH_LIBRARY(nvfp4r, m) {
     m.def("quant(Tensor x, Tensor global_scale_inv, bool swizzled=False, int rcp_mode=1) -> (Tensor, Tensor)");
     m.def("linear(Tensor x, Tensor global_scale_inv, Tensor weight, Tensor weight_scale_flat, "
           "float alpha, int out_dtype_int=0, int rcp_mode=1) -> Tensor");
+    m.def("linear_tc(Tensor x, Tensor global_scale_inv, Tensor weight, Tensor weight_scale_swizzled, "
+          "float alpha, int out_dtype_int=0, int rcp_mode=1) -> Tensor");
     m.def("entropy(Tensor logits, Tensor workspace) -> Tensor");
     m.def("reset_step(Tensor(a!) logits, Tensor(b!) states, Tensor? state_slots, Tensor? last_ids, "
           "Tensor? nl_bitmap, Tensor? dnl_bitmap, float t_high, float t_low, float tau0, int window, "
@@ -220,6 +254,7 @@ TORCH_LIBRARY_IMPL(nvfp4r, CUDA, m) {
     m.impl("gemm", &gemm_op);
     m.impl("quant", &quant_op);
     m.impl("linear", &linear_op);
+    m.impl("linear_tc", &linear_tc_op);
     m.impl("entropy", &entropy_op);
     m.impl("reset_step", &reset_step_op);
 }

@@ -32,6 +32,12 @@ def _linear_fake(x, global_scale_inv, weight, weight_scale_flat, alpha, out_dtyp
     return x.new_empty((x.shape[0], weight.shape[0]), dtype=_OUT_DTYPES[out_dtype_int])
 
 
+@torch.library.register_fake("nvfp4r::linear_tc")
+def _linear_tc_fake(x, global_scale_inv, weight, weight_scale_swizzled, alpha, out_dtype_int=0,
+                    rcp_mode=1):
+    return x.new_empty((x.shape[0], weight.shape[0]), dtype=_OUT_DTYPES[out_dtype_int])
+
+
 @torch.library.register_fake("nvfp4r::entropy")
 def _entropy_fake(logits, workspace):
     return logits.new_empty((logits.shape[0],))
