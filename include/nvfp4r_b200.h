@@ -156,6 +156,35 @@ NVFP4R_API int nvfp4r_linear_tc(const void* x, int64_t x_row_stride, int M, int 
                                 void* out, int out_dtype, int rcp_mode,
                                 void* workspace, size_t workspace_bytes, void* stream);
 
+/* ------------------------------------------------------------------------- *
+ * Packed-weight decode linear: the fast path for every M <= 32 per launch.
+ * The weight is re-laid out ONCE per layer (the work the reference does in
+ * `prime_nvfp4r_caches`, kernels/python/nvfp4r/vllm_integration.py:359-396, where it
+ * un-swizzles the scales) into blocks of 128 rows x 256 K-elements, each block 18 432
+ * contiguous bytes: 16 KB of codes in the tensor core's shared-memory image (K-major,
+ * 128-byte swizzle) followed by 2 KB of block scales in tcgen05.cp order. The linear then
+ * streams the weight with one 36 KB bulk copy per pipeline stage.
+ *   nvfp4r_packed_weight_bytes(N, K)   = N*K/2 + N*K/16 (0 if the shape is unsupported)
+ *   nvfp4r_pack_weight                 weight [N,K/2] + flat scales [N,K/16] -> packed
+ *                                      (packed 1024-byte aligned; N % 128 == 0, K % 256 == 0)
+ *   nvfp4r_linear_packed               out[M,N] = alpha * quant(x)[M,K] . W^T, same
+ *                                      arithmetic and rcp_mode meaning as nvfp4r_linear;
+ *                                      workspace >= nvfp4r_linear_packed_workspace_bytes,
+ *                                      zeroed before first use, left ready for the next call
+ * Stands in for the whole of `_nvfp4r_linear_impl` for decode-sized M
+ * (vllm_integration.py:165-274) in one launch per 32 rows.
+ * ------------------------------------------------------------------------- */
+NVFP4R_API size_t nvfp4r_packed_weight_bytes(int N, int K);
+NVFP4R_API size_t nvfp4r_linear_packed_workspace_bytes(int M, int N, int K);
+NVFP4R_API int nvfp4r_pack_weight(const void* weight, const void* weight_scale_flat, void* packed,
+                                  int N, int K, void* stream);
+NVFP4R_API int nvfp4r_linear_packed(const void* x, int64_t x_row_stride, int M, int K,
+                                    const float* global_scale_inv, const void* packed, int N,
+                                    float alpha, void* out, int out_dtype, int rcp_mode,
+                                    void* workspace, size_t workspace_bytes, void* stream);
+/* Debug/tuning: force the K split of the packed linear (0 = automatic). */
+NVFP4R_API int nvfp4r_set_packed_tuning(int splits);
+
 /* Debug/tuning: force the K split and ring depth of the tensor-core kernel (0 = automatic). */
 NVFP4R_API int nvfp4r_set_gemm_tuning(int splits, int stages);
 

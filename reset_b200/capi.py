@@ -144,6 +144,45 @@ def gemm(A, B, SFA, SFB, C: torch.Tensor, alpha: float, workspace: torch.Tensor,
     L.check(st, "nvfp4r_gemm")
 
 
+def pack_weight(weight: torch.Tensor, weight_scale_flat: torch.Tensor) -> torch.Tensor:
+    """[N,K/2] codes + flat [N,K/16] scales -> packed block format (uint8, N*K*9/16 bytes)."""
+    _need_cuda(weight, weight_scale_flat)
+    w, ws = _u8(weight).contiguous(), _u8(weight_scale_flat).contiguous()
+    N, K = w.shape[0], w.shape[1] * 2
+    n = L.lib().nvfp4r_packed_weight_bytes(N, K)
+    if n == 0:
+        raise ValueError("pack_weight: needs N % 128 == 0 and K % 256 == 0")
+    packed = torch.empty(n, dtype=torch.uint8, device=w.device)
+    with torch.cuda.device(w.device):
+        st = L.lib().nvfp4r_pack_weight(w.data_ptr(), ws.data_ptr(), packed.data_ptr(), N, K, _stream())
+    L.check(st, "nvfp4r_pack_weight")
+    return packed
+
+
+def packed_workspace(M: int, N: int, K: int, device) -> torch.Tensor:
+    n = L.lib().nvfp4r_linear_packed_workspace_bytes(M, N, K)
+    return torch.zeros((n + 15) // 16 * 2, dtype=torch.int64, device=device)
+
+
+def linear_packed(x: torch.Tensor, global_scale_inv: torch.Tensor, packed: torch.Tensor, N: int,
+                  alpha: float, workspace: torch.Tensor, out_dtype: torch.dtype = torch.bfloat16,
+                  rcp_mode: int = L.RCP_EXACT, out: torch.Tensor | None = None) -> torch.Tensor:
+    """Fused quantize + tensor-core linear over a packed weight: bf16 [M,K] -> [M,N]."""
+    _need_cuda(x, global_scale_inv, packed, workspace)
+    if x.dtype != torch.bfloat16 or x.dim() != 2 or x.stride(1) != 1:
+        raise ValueError("linear_packed: x must be bf16 [M,K] with unit inner stride")
+    M, K = x.shape
+    if out is None:
+        out = torch.empty((M, N), dtype=out_dtype, device=x.device)
+    with torch.cuda.device(x.device):
+        st = L.lib().nvfp4r_linear_packed(x.data_ptr(), x.stride(0), M, K, global_scale_inv.data_ptr(),
+                                          packed.data_ptr(), N, float(alpha), out.data_ptr(),
+                                          _DTYPE_CODE[out.dtype], rcp_mode, workspace.data_ptr(),
+                                          workspace.numel() * workspace.element_size(), _stream())
+    L.check(st, "nvfp4r_linear_packed")
+    return out
+
+
 def unswizzle_blockscale(swizzled: torch.Tensor, rows: int, K: int) -> torch.Tensor:
     _need_cuda(swizzled)
     sw = _u8(swizzled).contiguous()

@@ -212,8 +212,66 @@ int nvfp4r_linear_tc(const void* x, int64_t x_row_stride, int M, int K, const fl
     return e == cudaSuccess ? NVFP4R_OK : cuda_fail(e, "linear_tc launch");
 }
 
+NVFP4R_API int nvfp4r_debug_read_prof(long long* out8) {
+    cudaDeviceSynchronize();
+    return nvfp4r::read_tc_prof(out8) == cudaSuccess ? 0 : -4;
+}
+
+size_t nvfp4r_packed_weight_bytes(int N, int K) {
+    if (N <= 0 || K <= 0 || N % 128 || K % 256) return 0;
+    return nvfp4r::packed_weight_bytes(N, K);
+}
+
+size_t nvfp4r_linear_packed_workspace_bytes(int M, int N, int K) {
+    return nvfp4r::packed_workspace_bytes(M, N, K);
+}
+
+int nvfp4r_pack_weight(const void* weight, const void* weight_scale_flat, void* packed, int N, int K,
+                       void* stream) {
+    if (!weight || !weight_scale_flat || !packed) return fail(NVFP4R_ERR_INVALID_ARGUMENT, "pack_weight: null pointer");
+    if (N <= 0 || K <= 0) return fail(NVFP4R_ERR_INVALID_ARGUMENT, "pack_weight: bad sizes");
+    if (N % 128 != 0 || K % 256 != 0)
+        return fail(NVFP4R_ERR_UNSUPPORTED_SHAPE, "pack_weight: N % 128 == 0 and K % 256 == 0 required");
+    if (!aligned(weight, 16) || !aligned(weight_scale_flat, 4) || !aligned(packed, 1024))
+        return fail(NVFP4R_ERR_ALIGNMENT, "pack_weight: weight 16-byte, scales 4-byte, packed 1024-byte aligned");
+    cudaError_t e = nvfp4r::launch_pack_weight(weight, weight_scale_flat, packed, N, K, as_stream(stream));
+    return e == cudaSuccess ? NVFP4R_OK : cuda_fail(e, "pack_weight launch");
+}
+
+int nvfp4r_linear_packed(const void* x, int64_t x_row_stride, int M, int K, const float* gs,
+                         const void* packed, int N, float alpha, void* out, int out_dtype, int rcp_mode,
+                         void* workspace, size_t workspace_bytes, void* stream) {
+    if (!x || !gs || !packed || !out) return fail(NVFP4R_ERR_INVALID_ARGUMENT, "linear_packed: null pointer");
+    if (rcp_mode != NVFP4R_RCP_EXACT && rcp_mode != NVFP4R_RCP_APPROX)
+        return fail(NVFP4R_ERR_INVALID_ARGUMENT, "linear_packed: bad rcp_mode");
+    if (M < 0 || N < 0 || K <= 0) return fail(NVFP4R_ERR_INVALID_ARGUMENT, "linear_packed: bad sizes");
+    if (out_dtype < NVFP4R_BF16 || out_dtype > NVFP4R_F32)
+        return fail(NVFP4R_ERR_INVALID_ARGUMENT, "linear_packed: bad out_dtype");
+    if (N % 128 != 0 || K % 256 != 0)
+        return fail(NVFP4R_ERR_UNSUPPORTED_SHAPE, "linear_packed: N % 128 == 0 and K % 256 == 0 required");
+    if (M == 0 || N == 0) return NVFP4R_OK;
+    if (!workspace || workspace_bytes < nvfp4r_linear_packed_workspace_bytes(M, N, K) || !aligned(workspace, 16))
+        return fail(NVFP4R_ERR_INVALID_ARGUMENT, "linear_packed: workspace missing, too small or misaligned");
+    if (!aligned(x, 16) || (x_row_stride % 8) || !aligned(packed, 1024))
+        return fail(NVFP4R_ERR_ALIGNMENT, "linear_packed: x 16-byte, packed weight 1024-byte aligned");
+    if (x_row_stride < K) return fail(NVFP4R_ERR_INVALID_ARGUMENT, "linear_packed: row stride < K");
+    nvfp4r::PackedLinearArgs g = {};
+    g.packed = packed; g.xb = x; g.xb_stride = x_row_stride; g.gs = gs; g.rcp_mode = rcp_mode;
+    g.out = out; g.out_dtype = out_dtype; g.M = M; g.N = N; g.K = K; g.alpha = alpha; g.workspace = workspace;
+    const char* why = nullptr;
+    cudaError_t e = nvfp4r::launch_linear_packed(g, as_stream(stream), &why);
+    if (why != nullptr) return fail(NVFP4R_ERR_UNSUPPORTED_SHAPE, why);
+    return e == cudaSuccess ? NVFP4R_OK : cuda_fail(e, "linear_packed launch");
+}
+
+int nvfp4r_set_packed_tuning(int splits) {
+    if (splits < 0 || splits > 64) return fail(NVFP4R_ERR_INVALID_ARGUMENT, "packed tuning: splits 0..64");
+    nvfp4r::set_packed_tuning(splits);
+    return NVFP4R_OK;
+}
+
 int nvfp4r_set_gemm_tuning(int splits, int stages) {
-    if (splits < 0 || splits > 16 || stages < 0 || stages > 10)
+    if (splits < 0 || splits > 16 || stages < 0 || (stages & 0xff) > 10)
         return fail(NVFP4R_ERR_INVALID_ARGUMENT, "gemm tuning: splits 0..16, stages 0..10");
     nvfp4r::set_tc_tuning(splits, stages);
     return NVFP4R_OK;
@@ -306,9 +364,11 @@ int nvfp4r_set_gemv_tuning(int ctas_per_sm, int use_pdl, int force_generic) {
 int nvfp4r_check_device_status(void) {
     int flag = 0, flag2 = 0;
     cudaError_t e = nvfp4r::read_and_clear_device_status(&flag);
+    int flag3 = 0;
     if (e == cudaSuccess) e = nvfp4r::read_and_clear_tc_status(&flag2);
+    if (e == cudaSuccess) e = nvfp4r::read_and_clear_packed_status(&flag3);
     if (e != cudaSuccess) return cuda_fail(e, "device status");
-    flag |= flag2;
+    flag |= flag2 | flag3;
     return flag ? fail(NVFP4R_ERR_DEVICE_TIMEOUT, "a bounded device-side wait gave up") : NVFP4R_OK;
 }
 

@@ -31,6 +31,7 @@
 
 #include "kernels.h"
 #include "quant_core.cuh"
+#include "tcgen05_ptx.cuh"
 
 namespace nvfp4r {
 namespace {
@@ -65,103 +66,15 @@ struct alignas(64) TcParams {
     float alpha;
     int tiles, splits, iters;  // N/128, K-parts per tile, K/256
     int stages;
+    int debug;                 // timing experiments only: bit0 no SFB cp, bit1 no SFA cp, bit2 no MMA
     float* partials;           // [tiles][splits][BN][128] fp32
     unsigned* tickets;         // [tiles]
 };
 
 __device__ int g_tc_status = 0;
+__device__ long long g_tc_prof[8];   // timing experiments (debug bit 3), CTA 0 only
 
-// ---- PTX wrappers ------------------------------------------------------------
-
-__device__ __forceinline__ bool elect_one() {
-    uint32_t pred;
-    asm volatile("{\n\t.reg .pred p;\n\telect.sync _|p, 0xffffffff;\n\tselp.u32 %0, 1, 0, p;\n\t}"
-                 : "=r"(pred));
-    return pred != 0;
-}
-__device__ __forceinline__ void fence_proxy_async_smem() {
-    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-}
-__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, int x, int y, int z,
-                                            uint32_t bar, uint64_t policy) {
-    asm volatile(
-        "cp.async.bulk.tensor.3d.shared::cta.global.mbarrier::complete_tx::bytes.L2::cache_hint "
-        "[%0], [%1, {%2, %3, %4}], [%5], %6;"
-        :: "r"(dst), "l"(map), "r"(x), "r"(y), "r"(z), "r"(bar), "l"(policy) : "memory");
-}
-__device__ __forceinline__ void tmem_alloc(uint32_t smem_dst, uint32_t cols) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
-                 :: "r"(smem_dst), "r"(cols) : "memory");
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
-}
-__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t cols) {
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" :: "r"(taddr), "r"(cols) : "memory");
-}
-__device__ __forceinline__ void tc_fence_before() {
-    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-}
-__device__ __forceinline__ void tc_fence_after() {
-    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-}
-__device__ __forceinline__ void tc_commit(uint32_t bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];"
-                 :: "r"(bar) : "memory");
-}
-__device__ __forceinline__ void tc_cp_scales(uint32_t taddr, uint64_t desc) {
-    asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" :: "r"(taddr), "l"(desc) : "memory");
-}
-__device__ __forceinline__ void tc_mma_nvf4(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,
-                                            uint32_t idesc, uint32_t sfa_tmem, uint32_t sfb_tmem,
-                                            uint32_t accumulate) {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %6, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::mxf4nvf4.block_scale.scale_vec::4X "
-        "[%0], %1, %2, %3, [%4], [%5], p;\n\t}"
-        :: "r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(sfa_tmem), "r"(sfb_tmem),
-           "r"(accumulate) : "memory");
-}
-__device__ __forceinline__ void tmem_ld16(uint32_t taddr, float v[16]) {
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
-        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
-        : "=f"(v[0]), "=f"(v[1]), "=f"(v[2]), "=f"(v[3]), "=f"(v[4]), "=f"(v[5]), "=f"(v[6]),
-          "=f"(v[7]), "=f"(v[8]), "=f"(v[9]), "=f"(v[10]), "=f"(v[11]), "=f"(v[12]), "=f"(v[13]),
-          "=f"(v[14]), "=f"(v[15])
-        : "r"(taddr) : "memory");
-}
-__device__ __forceinline__ void tmem_ld_wait() {
-    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-}
-__device__ __forceinline__ void named_barrier(int id, int threads) {
-    asm volatile("bar.sync %0, %1;" :: "r"(id), "r"(threads) : "memory");
-}
-
-// Shared-memory matrix descriptor: K-major operand, 128-byte swizzle, 8-row groups
-// 1024 B apart. Fields: start >> 4 in bits 0-13, stride-byte-offset >> 4 in bits 32-45,
-// fixed 1 in bit 46, swizzle mode 2 (128 B) in bits 61-63.
-__device__ __forceinline__ uint64_t desc_operand(uint32_t smem_addr) {
-    return (static_cast<uint64_t>(smem_addr & 0x3FFFFu) >> 4) |
-           (static_cast<uint64_t>(1024 >> 4) << 32) | (1ull << 46) | (2ull << 61);
-}
-// Scale chunk (512 B = 32 rows x 16 B), no swizzle, 8-row groups 128 B apart.
-__device__ __forceinline__ uint64_t desc_scales(uint32_t smem_addr) {
-    return (static_cast<uint64_t>(smem_addr & 0x3FFFFu) >> 4) |
-           (static_cast<uint64_t>(128 >> 4) << 32) | (1ull << 46);
-}
-
-// Byte offset of (row, byte b of the 128-byte chunk row) in a 128B-swizzled K-major tile.
-__device__ __forceinline__ uint32_t swz128(int row, int b) {
-    return static_cast<uint32_t>((row >> 3) * 1024 + (row & 7) * 128 +
-                                 ((((b >> 4) ^ (row & 7)) << 4) | (b & 15)));
-}
-
-struct WaitFail {
-    bool failed = false;
-    __device__ __forceinline__ bool wait(uint32_t bar, uint32_t parity) {
-        if (!failed && !mbar_wait_bounded(bar, parity, 20000000u)) failed = true;
-        return !failed;
-    }
-};
+using namespace tc;
 
 // -------------------------------------------------------------------------------
 
@@ -302,11 +215,17 @@ linear_tc_kernel(const __grid_constant__ TcParams p) {
     if (warp == 0) {
         // ---------------- producer -------------------------------------------------------
         if (lane == 0) {
+            long long t_wait = 0, t_issue = 0;
             for (int i = issued; i < total; ++i) {
                 const int s = i % p.stages;
+                const long long c0 = clock64();
                 if (!wf.wait(bar_empty + 8 * s, ((i / p.stages) - 1) & 1)) break;
+                const long long c1 = clock64();
                 issue(i);
+                const long long c2 = clock64();
+                t_wait += c1 - c0; t_issue += c2 - c1;
             }
+            if ((p.debug & 8) && c == 0) { g_tc_prof[0] = t_wait; g_tc_prof[1] = t_issue; g_tc_prof[6] = total - issued; }
         }
     } else if (warp == 1) {
         // ---------------- MMA issuer -----------------------------------------------------
@@ -314,6 +233,8 @@ linear_tc_kernel(const __grid_constant__ TcParams p) {
             constexpr uint32_t idesc = (1u << 7) | (1u << 10) | (static_cast<uint32_t>(BN >> 3) << 17) |
                                        (static_cast<uint32_t>(kTileRows >> 7) << 27);
             int i = 0;
+            long long t_wait = 0, t_issue = 0;
+            const long long t_begin = clock64();
             for (int ti = 0; ti < my_tiles && !wf.failed; ++ti) {
                 const int buf = ti & 1;
                 if (ti >= 2 && !wf.wait(bar_accempty + 8 * buf, ((ti >> 1) - 1) & 1)) break;
@@ -321,7 +242,10 @@ linear_tc_kernel(const __grid_constant__ TcParams p) {
                 const uint32_t d_tmem = tmem + buf * BN;
                 for (int j = 0; j < n_it; ++j, ++i) {
                     const int s = i % p.stages;
+                    const long long c0 = clock64();
                     if (!wf.wait(bar_full + 8 * s, (i / p.stages) & 1)) break;
+                    const long long c1 = clock64();
+                    t_wait += c1 - c0;
                     tc_fence_after();
                     const uint32_t a_smem = ring + s * kStageBytes;
                     const uint32_t sfa_smem = a_smem + kStageA;
@@ -329,19 +253,21 @@ linear_tc_kernel(const __grid_constant__ TcParams p) {
                     const uint32_t sfb_smem = b_sf + j * 4 * 512;
 #pragma unroll
                     for (int k = 0; k < 4; ++k) {
-                        tc_cp_scales(tmem + kColSFA + 4 * k, desc_scales(sfa_smem + k * 512));
-                        tc_cp_scales(tmem + kColSFB + 4 * k, desc_scales(sfb_smem + k * 512));
+                        if (!(p.debug & 2)) tc_cp_scales(tmem + kColSFA + 4 * k, desc_scales(sfa_smem + k * 512));
+                        if (!(p.debug & 1)) tc_cp_scales(tmem + kColSFB + 4 * k, desc_scales(sfb_smem + k * 512));
                     }
 #pragma unroll
                     for (int k = 0; k < 4; ++k) {
-                        tc_mma_nvf4(d_tmem, desc_operand(a_smem + k * 32), desc_operand(b_smem + k * 32),
+                        if (!(p.debug & 4)) tc_mma_nvf4(d_tmem, desc_operand(a_smem + k * 32), desc_operand(b_smem + k * 32),
                                     idesc, tmem + kColSFA + 4 * k, tmem + kColSFB + 4 * k,
                                     (j > 0 || k > 0) ? 1u : 0u);
                     }
                     tc_commit(bar_empty + 8 * s);
+                    t_issue += clock64() - c1;
                 }
                 tc_commit(bar_accfull + 8 * buf);
             }
+            if ((p.debug & 8) && c == 0) { g_tc_prof[2] = t_wait; g_tc_prof[3] = t_issue; g_tc_prof[4] = clock64() - t_begin; g_tc_prof[5] = total; }
         }
     } else {
         // ---------------- epilogue (warps 2..5) ------------------------------------------
@@ -474,7 +400,7 @@ bool weight_map(const void* w, int N, int K, CUtensorMap* out) {
 }
 
 struct Plan { int splits, stages, grid, bn; size_t smem; };
-int g_force_splits = 0, g_force_stages = 0;
+int g_force_splits = 0, g_force_stages = 0, g_debug = 0;
 
 // Choose the K split: smallest number of parts whose unit count fills the SMs well and
 // whose per-CTA activation footprint leaves room for a deep ring.
@@ -556,6 +482,7 @@ cudaError_t launch_linear_tc(const TcLinearArgs& g, cudaStream_t stream, const c
         p.splits = plan.splits;
         p.iters = g.K / kBK;
         p.stages = plan.stages;
+        p.debug = g_debug;
         const size_t tickets = (static_cast<size_t>(p.tiles) * sizeof(unsigned) + 255) / 256 * 256;
         p.tickets = static_cast<unsigned*>(g.workspace);
         p.partials = reinterpret_cast<float*>(static_cast<uint8_t*>(g.workspace) + tickets);
@@ -588,8 +515,14 @@ cudaError_t launch_linear_tc(const TcLinearArgs& g, cudaStream_t stream, const c
 }
 
 void set_tc_tuning(int splits, int stages) {
+    g_debug = stages >> 8;
+    stages &= 0xff;
     g_force_splits = splits;
     g_force_stages = stages;
+}
+
+cudaError_t read_tc_prof(long long* out8) {
+    return cudaMemcpyFromSymbol(out8, g_tc_prof, 8 * sizeof(long long));
 }
 
 cudaError_t read_and_clear_tc_status(int* flag) {

@@ -74,8 +74,30 @@ size_t gemm_workspace_bytes(int M, int N, int K);
 // kernel handles.
 cudaError_t launch_linear_tc(const TcLinearArgs& g, cudaStream_t stream, const char** why);
 cudaError_t read_and_clear_tc_status(int* flag);
+cudaError_t read_tc_prof(long long* out8);
 // 0 = automatic
 void set_tc_tuning(int splits, int stages);
+
+// ---- linear_packed.cu -----------------------------------------------------
+struct PackedLinearArgs {
+    const void* packed;          // weight in the packed block format
+    const void* xb;              // bf16 [M, K]
+    int64_t xb_stride;
+    const float* gs;
+    int rcp_mode;
+    void* out;                   // [M, N]
+    int out_dtype;
+    int M, N, K;
+    float alpha;
+    void* workspace;
+};
+size_t packed_weight_bytes(int N, int K);
+size_t packed_workspace_bytes(int M, int N, int K);
+cudaError_t launch_pack_weight(const void* w, const void* sf_flat, void* packed, int N, int K,
+                               cudaStream_t stream);
+cudaError_t launch_linear_packed(const PackedLinearArgs& g, cudaStream_t stream, const char** why);
+cudaError_t read_and_clear_packed_status(int* flag);
+void set_packed_tuning(int splits);
 
 // Synchronises the device, returns the time-out flag set by bounded waits
 // inside the kernels and clears it.

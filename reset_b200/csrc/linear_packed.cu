@@ -1,0 +1,432 @@
+// Decode linear on the tensor cores over a PRE-PACKED weight: the product path of the
+// vLLM adapter for every M <= 32.
+//
+// Packed weight format (built once per layer by pack_weight_kernel): the weight is cut
+// into blocks of 128 rows x 256 K-elements; block (tile, kb) occupies 18 432 contiguous
+// bytes at ((tile * K/256) + kb) * 18432:
+//   [0, 16384)      the block's codes exactly as the tensor core wants them in shared
+//                   memory: K-major rows of 128 B, 128-byte swizzle (16-byte unit index
+//                   XOR row%8), 8-row groups 1024 B apart
+//   [16384, 18432)  the block's 128 x 16 scales as four 512-byte chunks (one per 64
+//                   K-elements) in the 32x4x4 order that tcgen05.cp 32x128b.warpx4 copies
+// Consecutive K blocks of a tile are contiguous, so a pipeline stage of 1 or 2 blocks is
+// ONE 1-D bulk copy of 18 or 36 KB: perfectly sequential DRAM reads, one TMA instruction
+// and one mbarrier transaction per 36 KB, no tensor map.
+//
+// Why this shape (measured on B200, see the profile notes of this kernel):
+//   * a thread that issues bulk copies is held ~190 cycles per copy and the MMA thread
+//     spends ~550 cycles per stage on barrier wait + commit regardless of the work in it,
+//     so stages must be few and large;
+//   * shared memory per CTA stays under half an SM (two 36 KB stages + the activations of
+//     a K part of at most 2048 elements) so that the CTA of the NEXT linear, launched with
+//     programmatic stream serialization, becomes resident while this one still runs and
+//     starts pulling its own weights at once;
+//   * the activation block scales are copied into tensor memory once per kernel and stay
+//     there (128 columns), the weight scales ride with each stage.
+//
+// Persistent CTAs (one per SM), roles and split-K protocol as in gemm_tcgen05.cu.
+#include "kernels.h"
+#include "quant_core.cuh"
+#include "tcgen05_ptx.cuh"
+
+namespace nvfp4r {
+namespace {
+
+using namespace tc;
+
+constexpr int kTileRows = 128;
+constexpr int kBlockK = 256;
+constexpr int kCodesBytes = kTileRows * (kBlockK / 2);      // 16384
+constexpr int kSfBytes = kTileRows * (kBlockK / 16);        // 2048
+constexpr int kBlockBytes = kCodesBytes + kSfBytes;         // 18432
+constexpr int kBlocksPerStage = 2;
+constexpr int kStageBytes = kBlocksPerStage * kBlockBytes;  // 36864
+constexpr int kStages = 2;
+constexpr int kMaxPartBlocks = 8;                           // K part <= 2048 elements
+constexpr int kThreadsP = 192;
+constexpr int kEpilogueThreads = 128;
+
+struct PackedParams {
+    const uint8_t* packed;
+    const void* xb;            // bf16 [M, K]
+    int64_t xb_stride;
+    const float* gs;
+    int rcp_mode;
+    void* out;
+    int out_dtype;
+    int64_t ldc;               // elements between tokens in out
+    int M, m0, N, K;
+    float alpha;
+    int tiles, splits, kblocks;
+    float* partials;
+    unsigned* tickets;
+};
+
+__device__ int g_packed_status = 0;
+
+// ---- one-time re-layout ----------------------------------------------------------
+
+// One thread moves one 16-byte unit of codes; the first K/256*... threads of each block
+// also move the scales. grid = (K/256, N/128), block = 1024 threads (128 rows x 8 units).
+__global__ void __launch_bounds__(1024)
+pack_weight_kernel(const uint8_t* __restrict__ w, const uint8_t* __restrict__ sf_flat,
+                   uint8_t* __restrict__ packed, int N, int K) {
+    const int kb = blockIdx.x, tile = blockIdx.y;
+    const int row = threadIdx.x >> 3, unit = threadIdx.x & 7;
+    uint8_t* dst = packed + (static_cast<int64_t>(tile) * (K / kBlockK) + kb) * kBlockBytes;
+    const int64_t n = static_cast<int64_t>(tile) * kTileRows + row;
+    const uint4 v = *reinterpret_cast<const uint4*>(w + n * (K / 2) + kb * 128 + unit * 16);
+    *reinterpret_cast<uint4*>(dst + swz128(row, unit * 16)) = v;
+    // scales: 16 per row in this block = 4 chunks x 4; threads with unit < 4 move 4 bytes
+    if (unit < 4) {
+        const uint32_t s4 = *reinterpret_cast<const uint32_t*>(sf_flat + n * (K / 16) + kb * 16 + unit * 4);
+        *reinterpret_cast<uint32_t*>(dst + kCodesBytes + unit * 512 + (row % 32) * 16 + (row / 32) * 4) = s4;
+    }
+}
+
+// ---- the linear ---------------------------------------------------------------------
+
+template <int BN>
+__global__ void __launch_bounds__(kThreadsP, 1)
+linear_packed_kernel(const __grid_constant__ PackedParams p) {
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
+    const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    uint8_t* smem = smem_raw + (smem_base - smem_u32(smem_raw));
+
+    __shared__ __align__(8) uint64_t bars[2 * kStages + 4];
+    __shared__ uint32_t s_tmem;
+    __shared__ int s_last;
+
+    const int tid = threadIdx.x, warp = tid / kWarp, lane = tid % kWarp;
+    const int S = p.splits;
+    const int ctas_per_part = gridDim.x / S;           // CTAs beyond S * ctas_per_part idle
+    const int c = blockIdx.x;
+    const bool active = c < S * ctas_per_part;
+    const int part = c % S, rank_in_part = c / S;
+    const int kb0 = static_cast<int>((static_cast<int64_t>(p.kblocks) * part) / S);
+    const int kb1 = static_cast<int>((static_cast<int64_t>(p.kblocks) * (part + 1)) / S);
+    const int nkb = kb1 - kb0;                                        // <= kMaxPartBlocks
+    const int stages_per_tile = (nkb + kBlocksPerStage - 1) / kBlocksPerStage;
+    const int my_tiles = (active && rank_in_part < p.tiles)
+                             ? (p.tiles - rank_in_part + ctas_per_part - 1) / ctas_per_part : 0;
+    const int total = my_tiles * stages_per_tile;
+
+    const uint32_t ring = smem_base;
+    const uint32_t b_tile = ring + kStages * kStageBytes;            // nkb blocks of BN x 128 B
+    const uint32_t b_sf = b_tile + kMaxPartBlocks * (BN * 128);       // nkb * 4 chunks of 512 B
+    uint8_t* b_tile_g = smem + kStages * kStageBytes;
+    uint8_t* b_sf_g = b_tile_g + kMaxPartBlocks * (BN * 128);
+
+    const uint32_t bar_full = smem_u32(&bars[0]);
+    const uint32_t bar_empty = smem_u32(&bars[kStages]);
+    const uint32_t bar_accfull = smem_u32(&bars[2 * kStages]);
+    const uint32_t bar_accempty = smem_u32(&bars[2 * kStages + 2]);
+
+    constexpr uint32_t kTmemCols = 256;
+    constexpr uint32_t kColSFA = 2 * BN;                              // 16 columns per block in a stage
+    constexpr uint32_t kColSFB = kColSFA + 16 * kBlocksPerStage;      // 16 columns per block of the part
+
+    if (warp == 0 && lane == 0) {
+        for (int s = 0; s < kStages; ++s) {
+            mbar_init(bar_full + 8 * s, 1);
+            mbar_init(bar_empty + 8 * s, 1);
+        }
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(bar_accfull + 8 * b, 1);
+            mbar_init(bar_accempty + 8 * b, kEpilogueThreads / kWarp);
+        }
+        mbar_fence_init();
+    }
+    if (warp == 1) tmem_alloc(smem_u32(&s_tmem), kTmemCols);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = s_tmem;
+
+    const uint64_t policy = l2_policy_evict_first();
+    auto stage_blocks = [&](int j) { return min(kBlocksPerStage, nkb - j * kBlocksPerStage); };
+    auto issue = [&](int i) {                          // stage i of this CTA's sequence
+        const int ti = i / stages_per_tile, j = i - ti * stages_per_tile;
+        const int tile = rank_in_part + ti * ctas_per_part;
+        const int s = i % kStages;
+        const uint32_t bytes = static_cast<uint32_t>(stage_blocks(j)) * kBlockBytes;
+        mbar_expect_tx(bar_full + 8 * s, bytes);
+        bulk_g2s(ring + s * kStageBytes,
+                 p.packed + (static_cast<int64_t>(tile) * p.kblocks + kb0 + j * kBlocksPerStage) * kBlockBytes,
+                 bytes, bar_full + 8 * s, policy);
+    };
+
+    int issued = 0;
+    if (warp == 0 && lane == 0) {
+        const int first = min(kStages, total);
+        for (; issued < first; ++issued) issue(issued);
+    }
+    pdl_launch_dependents();
+    pdl_wait_prior();
+
+    // ---- prologue: quantize this part's activations into operand layout --------------
+    if (active) {
+        const int blk0 = kb0 * (kBlockK / 16);
+        const int blocks = nkb * (kBlockK / 16);
+        const float gs = __ldg(p.gs);
+        const QuantScales qe = make_quant_scales<kRcpExact>(gs);
+        const QuantScales qa = make_quant_scales<kRcpApprox>(gs);
+        const __nv_bfloat16* xb = static_cast<const __nv_bfloat16*>(p.xb);
+        for (int i = tid; i < p.M * blocks; i += kThreadsP) {
+            const int m = i / blocks, blk = i - m * blocks;
+            const uint4* src = reinterpret_cast<const uint4*>(
+                xb + (p.m0 + m) * p.xb_stride + static_cast<int64_t>(blk0 + blk) * 16);
+            const uint4 lo = __ldg(src), hi = __ldg(src + 1);
+            uint32_t cw[2];
+            const uint32_t sf = (p.rcp_mode == kRcpExact) ? quantize_block16<kRcpExact>(lo, hi, qe, cw)
+                                                          : quantize_block16<kRcpApprox>(lo, hi, qa, cw);
+            *reinterpret_cast<uint2*>(b_tile_g + (blk >> 4) * (BN * 128) + swz128(m, (blk & 15) * 8)) =
+                make_uint2(cw[0], cw[1]);
+            b_sf_g[(blk >> 2) * 512 + m * 16 + (blk & 3)] = static_cast<uint8_t>(sf);
+        }
+        // Rows M..BN-1 of the operand are never written: whatever they hold only reaches
+        // accumulator columns that are not stored.
+        fence_proxy_async_smem();
+    }
+    __syncthreads();
+
+    WaitFail wf;
+    if (warp == 0) {
+        // ---------------- producer -------------------------------------------------------
+        if (lane == 0) {
+            for (int i = issued; i < total; ++i) {
+                const int s = i % kStages;
+                if (!wf.wait(bar_empty + 8 * s, ((i / kStages) - 1) & 1)) break;
+                issue(i);
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------- MMA issuer -----------------------------------------------------
+        if (lane == 0 && my_tiles > 0) {
+            constexpr uint32_t idesc = (1u << 7) | (1u << 10) | (static_cast<uint32_t>(BN >> 3) << 17) |
+                                       (static_cast<uint32_t>(kTileRows >> 7) << 27);
+            // activation scales: once, resident in tensor memory for the whole kernel
+            for (int ch = 0; ch < nkb * 4; ++ch)
+                tc_cp_scales(tmem + kColSFB + 4 * ch, desc_scales(b_sf + ch * 512));
+            int i = 0;
+            for (int ti = 0; ti < my_tiles && !wf.failed; ++ti) {
+                const int buf = ti & 1;
+                if (ti >= 2 && !wf.wait(bar_accempty + 8 * buf, ((ti >> 1) - 1) & 1)) break;
+                tc_fence_after();
+                const uint32_t d_tmem = tmem + buf * BN;
+                for (int j = 0; j < stages_per_tile; ++j, ++i) {
+                    const int s = i % kStages;
+                    if (!wf.wait(bar_full + 8 * s, (i / kStages) & 1)) break;
+                    tc_fence_after();
+                    const int nb = stage_blocks(j);
+                    for (int b = 0; b < nb; ++b) {
+                        const uint32_t a_smem = ring + s * kStageBytes + b * kBlockBytes;
+                        const int blk = j * kBlocksPerStage + b;              // block within the part
+                        const uint32_t b_smem = b_tile + blk * (BN * 128);
+#pragma unroll
+                        for (int k = 0; k < 4; ++k)
+                            tc_cp_scales(tmem + kColSFA + 16 * b + 4 * k,
+                                         desc_scales(a_smem + kCodesBytes + k * 512));
+#pragma unroll
+                        for (int k = 0; k < 4; ++k)
+                            tc_mma_nvf4(d_tmem, desc_operand(a_smem + k * 32), desc_operand(b_smem + k * 32),
+                                        idesc, tmem + kColSFA + 16 * b + 4 * k,
+                                        tmem + kColSFB + 16 * blk + 4 * k, (blk > 0 || k > 0) ? 1u : 0u);
+                    }
+                    tc_commit(bar_empty + 8 * s);
+                }
+                tc_commit(bar_accfull + 8 * buf);
+            }
+        }
+    } else {
+        // ---------------- epilogue (warps 2..5) ------------------------------------------
+        const int q = warp & 3;
+        const int row_in_tile = q * 32 + lane;
+        const int et = tid - 2 * kWarp;
+        for (int ti = 0; ti < my_tiles; ++ti) {
+            const int buf = ti & 1;
+            const int tile = rank_in_part + ti * ctas_per_part;
+            if (!wf.wait(bar_accfull + 8 * buf, (ti >> 1) & 1)) break;
+            tc_fence_after();
+            float acc[BN];
+#pragma unroll
+            for (int h = 0; h < BN / 16; ++h)
+                tmem_ld16(tmem + (static_cast<uint32_t>(q * 32) << 16) + buf * BN + h * 16, &acc[h * 16]);
+            tmem_ld_wait();
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar_accempty + 8 * buf);
+
+            const int64_t n = static_cast<int64_t>(tile) * kTileRows + row_in_tile;
+            auto store = [&](int m, float v) {
+                const int64_t idx = (p.m0 + m) * p.ldc + n;
+                v *= p.alpha;
+                if (p.out_dtype == 0) static_cast<__nv_bfloat16*>(p.out)[idx] = __float2bfloat16_rn(v);
+                else if (p.out_dtype == 1) static_cast<__half*>(p.out)[idx] = __float2half_rn(v);
+                else static_cast<float*>(p.out)[idx] = v;
+            };
+            if (S == 1) {
+#pragma unroll
+                for (int m = 0; m < BN; ++m)
+                    if (m < p.M) store(m, acc[m]);
+            } else {
+                float* slot = p.partials + (static_cast<int64_t>(tile) * S + part) * (BN * kTileRows);
+#pragma unroll
+                for (int m = 0; m < BN; ++m)
+                    if (m < p.M) __stcg(slot + m * kTileRows + row_in_tile, acc[m]);
+                __threadfence();
+                named_barrier(1, kEpilogueThreads);
+                if (et == 0) {
+                    const unsigned t = atomicAdd(p.tickets + tile, 1u);
+                    s_last = (t == static_cast<unsigned>(S) - 1u) ? 1 : 0;
+                    if (s_last) p.tickets[tile] = 0u;
+                    __threadfence();
+                }
+                named_barrier(1, kEpilogueThreads);
+                if (s_last) {
+                    const float* base = p.partials + static_cast<int64_t>(tile) * S * (BN * kTileRows);
+#pragma unroll
+                    for (int m = 0; m < BN; ++m) {
+                        if (m < p.M) {
+                            float v = 0.0f;
+                            for (int s = 0; s < S; ++s)
+                                v += __ldcg(base + s * (BN * kTileRows) + m * kTileRows + row_in_tile);
+                            store(m, v);
+                        }
+                    }
+                }
+                named_barrier(1, kEpilogueThreads);
+            }
+        }
+    }
+
+    if (wf.failed && lane == 0) atomicExch(&g_packed_status, 1);
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem, kTmemCols);
+    }
+}
+
+struct PackedPlan { int splits, grid, bn; size_t smem; };
+int g_force_packed_splits = 0;
+
+// Parts of at most kMaxPartBlocks K blocks; among the admissible split counts take the
+// one that keeps the most SMs busy (fewer parts on a tie).
+bool plan_packed(int M, int N, int K, PackedPlan* plan) {
+    const int G = device_sm_count();
+    const int tiles = N / kTileRows, kblocks = K / kBlockK;
+    const int min_s = (kblocks + kMaxPartBlocks - 1) / kMaxPartBlocks;
+    if (min_s > G) return false;
+    int best = -1;
+    double best_score = -1.0;
+    for (int s = min_s; s <= kblocks && s <= G && s <= 64; ++s) {
+        const int per_part = G / s;
+        if (per_part < 1) break;
+        const int rounds = (tiles + per_part - 1) / per_part;
+        const double fill = static_cast<double>(tiles) * s / (static_cast<double>(rounds) * G);
+        const double score = fill - 0.004 * (s - min_s);
+        if (score > best_score) { best_score = score; best = s; }
+    }
+    if (g_force_packed_splits >= min_s && g_force_packed_splits <= kblocks && g_force_packed_splits <= G)
+        best = g_force_packed_splits;
+    if (best < 0) return false;
+    plan->splits = best;
+    plan->bn = M <= 16 ? 16 : 32;
+    plan->grid = G;
+    plan->smem = static_cast<size_t>(kStages) * kStageBytes + kMaxPartBlocks * (plan->bn * 128 + 4 * 512) + 1024;
+    return true;
+}
+
+}  // namespace
+
+size_t packed_weight_bytes(int N, int K) {
+    return static_cast<size_t>(N / kTileRows) * (K / kBlockK) * kBlockBytes;
+}
+
+size_t packed_workspace_bytes(int M, int N, int K) {
+    if (M <= 0 || N <= 0 || K <= 0 || N % kTileRows || K % kBlockK) return 16;
+    PackedPlan plan;
+    if (!plan_packed(M < 32 ? M : 32, N, K, &plan)) return 16;
+    const size_t tiles = N / kTileRows;
+    const size_t tickets = (tiles * sizeof(unsigned) + 255) / 256 * 256;
+    const size_t partials = plan.splits > 1 ? tiles * plan.splits * plan.bn * kTileRows * sizeof(float) : 0;
+    return tickets + partials + 256;
+}
+
+cudaError_t launch_pack_weight(const void* w, const void* sf_flat, void* packed, int N, int K,
+                               cudaStream_t stream) {
+    const dim3 grid(static_cast<unsigned>(K / kBlockK), static_cast<unsigned>(N / kTileRows));
+    pack_weight_kernel<<<grid, 1024, 0, stream>>>(static_cast<const uint8_t*>(w),
+                                                  static_cast<const uint8_t*>(sf_flat),
+                                                  static_cast<uint8_t*>(packed), N, K);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_linear_packed(const PackedLinearArgs& g, cudaStream_t stream, const char** why) {
+    *why = nullptr;
+    if (g.N % kTileRows != 0) { *why = "packed linear: N must be a multiple of 128"; return cudaSuccess; }
+    if (g.K % kBlockK != 0) { *why = "packed linear: K must be a multiple of 256"; return cudaSuccess; }
+    for (int m0 = 0; m0 < g.M; m0 += 32) {
+        const int m = g.M - m0 < 32 ? g.M - m0 : 32;
+        PackedPlan plan;
+        if (!plan_packed(m, g.N, g.K, &plan)) { *why = "packed linear: K too large for this device"; return cudaSuccess; }
+        PackedParams p = {};
+        p.packed = static_cast<const uint8_t*>(g.packed);
+        p.xb = g.xb;
+        p.xb_stride = g.xb_stride;
+        p.gs = g.gs;
+        p.rcp_mode = g.rcp_mode;
+        p.out = g.out;
+        p.out_dtype = g.out_dtype;
+        p.ldc = g.N;
+        p.M = m;
+        p.m0 = m0;
+        p.N = g.N;
+        p.K = g.K;
+        p.alpha = g.alpha;
+        p.tiles = g.N / kTileRows;
+        p.splits = plan.splits;
+        p.kblocks = g.K / kBlockK;
+        const size_t tickets = (static_cast<size_t>(p.tiles) * sizeof(unsigned) + 255) / 256 * 256;
+        p.tickets = static_cast<unsigned*>(g.workspace);
+        p.partials = reinterpret_cast<float*>(static_cast<uint8_t*>(g.workspace) + tickets);
+
+        void (*kern)(PackedParams) = plan.bn == 16 ? linear_packed_kernel<16> : linear_packed_kernel<32>;
+        static bool attr_done[2][64] = {};
+        int dev = 0;
+        cudaError_t e = cudaGetDevice(&dev);
+        if (e != cudaSuccess) return e;
+        const int ki = plan.bn == 16 ? 0 : 1;
+        if (dev >= 0 && dev < 64 && !attr_done[ki][dev]) {
+            e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
+            if (e != cudaSuccess) return e;
+            attr_done[ki][dev] = true;
+        }
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(static_cast<unsigned>(plan.grid));
+        cfg.blockDim = dim3(kThreadsP);
+        cfg.dynamicSmemBytes = plan.smem;
+        cfg.stream = stream;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = gemv_tuning().use_pdl ? 1 : 0;
+        e = cudaLaunchKernelEx(&cfg, kern, p);
+        if (e != cudaSuccess) return e;
+    }
+    return cudaSuccess;
+}
+
+void set_packed_tuning(int splits) { g_force_packed_splits = splits; }
+
+cudaError_t read_and_clear_packed_status(int* flag) {
+    cudaError_t e = cudaMemcpyFromSymbol(flag, g_packed_status, sizeof(int));
+    if (e != cudaSuccess) return e;
+    const int zero = 0;
+    return cudaMemcpyToSymbol(g_packed_status, &zero, sizeof(int));
+}
+
+}  // namespace nvfp4r
