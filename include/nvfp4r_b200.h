@@ -166,7 +166,7 @@ NVFP4R_API int nvfp4r_linear_tc(const void* x, int64_t x_row_stride, int M, int 
  * streams the weight with one 36 KB bulk copy per pipeline stage.
  *   nvfp4r_packed_weight_bytes(N, K)   = N*K/2 + N*K/16 (0 if the shape is unsupported)
  *   nvfp4r_pack_weight                 weight [N,K/2] + flat scales [N,K/16] -> packed
- *                                      (packed 1024-byte aligned; N % 128 == 0, K % 256 == 0)
+ *                                      (packed 16-byte aligned; N % 128 == 0, K % 256 == 0)
  *   nvfp4r_linear_packed               out[M,N] = alpha * quant(x)[M,K] . W^T, same
  *                                      arithmetic and rcp_mode meaning as nvfp4r_linear;
  *                                      workspace >= nvfp4r_linear_packed_workspace_bytes,

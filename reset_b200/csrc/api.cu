@@ -212,6 +212,10 @@ int nvfp4r_linear_tc(const void* x, int64_t x_row_stride, int M, int K, const fl
     return e == cudaSuccess ? NVFP4R_OK : cuda_fail(e, "linear_tc launch");
 }
 
+NVFP4R_API int nvfp4r_debug_read_trace(unsigned long long* out16) {
+    cudaDeviceSynchronize();
+    return nvfp4r::read_packed_trace(out16) == cudaSuccess ? 0 : -4;
+}
 NVFP4R_API int nvfp4r_debug_read_prof(long long* out8) {
     cudaDeviceSynchronize();
     return nvfp4r::read_tc_prof(out8) == cudaSuccess ? 0 : -4;
@@ -232,8 +236,8 @@ int nvfp4r_pack_weight(const void* weight, const void* weight_scale_flat, void* 
     if (N <= 0 || K <= 0) return fail(NVFP4R_ERR_INVALID_ARGUMENT, "pack_weight: bad sizes");
     if (N % 128 != 0 || K % 256 != 0)
         return fail(NVFP4R_ERR_UNSUPPORTED_SHAPE, "pack_weight: N % 128 == 0 and K % 256 == 0 required");
-    if (!aligned(weight, 16) || !aligned(weight_scale_flat, 4) || !aligned(packed, 1024))
-        return fail(NVFP4R_ERR_ALIGNMENT, "pack_weight: weight 16-byte, scales 4-byte, packed 1024-byte aligned");
+    if (!aligned(weight, 16) || !aligned(weight_scale_flat, 4) || !aligned(packed, 16))
+        return fail(NVFP4R_ERR_ALIGNMENT, "pack_weight: weight 16-byte, scales 4-byte, packed 16-byte aligned");
     cudaError_t e = nvfp4r::launch_pack_weight(weight, weight_scale_flat, packed, N, K, as_stream(stream));
     return e == cudaSuccess ? NVFP4R_OK : cuda_fail(e, "pack_weight launch");
 }
@@ -252,8 +256,8 @@ int nvfp4r_linear_packed(const void* x, int64_t x_row_stride, int M, int K, cons
     if (M == 0 || N == 0) return NVFP4R_OK;
     if (!workspace || workspace_bytes < nvfp4r_linear_packed_workspace_bytes(M, N, K) || !aligned(workspace, 16))
         return fail(NVFP4R_ERR_INVALID_ARGUMENT, "linear_packed: workspace missing, too small or misaligned");
-    if (!aligned(x, 16) || (x_row_stride % 8) || !aligned(packed, 1024))
-        return fail(NVFP4R_ERR_ALIGNMENT, "linear_packed: x 16-byte, packed weight 1024-byte aligned");
+    if (!aligned(x, 16) || (x_row_stride % 8) || !aligned(packed, 16))
+        return fail(NVFP4R_ERR_ALIGNMENT, "linear_packed: x and packed weight need 16-byte alignment");
     if (x_row_stride < K) return fail(NVFP4R_ERR_INVALID_ARGUMENT, "linear_packed: row stride < K");
     nvfp4r::PackedLinearArgs g = {};
     g.packed = packed; g.xb = x; g.xb_stride = x_row_stride; g.gs = gs; g.rcp_mode = rcp_mode;
@@ -265,7 +269,7 @@ int nvfp4r_linear_packed(const void* x, int64_t x_row_stride, int M, int K, cons
 }
 
 int nvfp4r_set_packed_tuning(int splits) {
-    if (splits < 0 || splits > 64) return fail(NVFP4R_ERR_INVALID_ARGUMENT, "packed tuning: splits 0..64");
+    if (splits < 0 || (splits & 0xff) > 64) return fail(NVFP4R_ERR_INVALID_ARGUMENT, "packed tuning: splits 0..64");
     nvfp4r::set_packed_tuning(splits);
     return NVFP4R_OK;
 }

@@ -315,16 +315,19 @@ linear_tc_kernel(const __grid_constant__ TcParams p) {
                 }
                 named_barrier(1, kEpilogueThreads);
                 if (s_last) {
+                    // all loads first (independent, many in flight), parts added in part order
                     const float* base = p.partials + static_cast<int64_t>(tile) * S * (BN * kTileRows);
 #pragma unroll
-                    for (int m = 0; m < BN; ++m) {
-                        if (m < p.M) {
-                            float v = 0.0f;
-                            for (int s = 0; s < S; ++s)
-                                v += __ldcg(base + s * (BN * kTileRows) + m * kTileRows + row_in_tile);
-                            store(m, v);
-                        }
+                    for (int m = 0; m < BN; ++m) acc[m] = 0.0f;
+                    for (int s = 0; s < S; ++s) {
+#pragma unroll
+                        for (int m = 0; m < BN; ++m)
+                            if (m < p.M)
+                                acc[m] += __ldcg(base + s * (BN * kTileRows) + m * kTileRows + row_in_tile);
                     }
+#pragma unroll
+                    for (int m = 0; m < BN; ++m)
+                        if (m < p.M) store(m, acc[m]);
                 }
                 named_barrier(1, kEpilogueThreads);    // s_last is reused by the next tile
             }

@@ -98,6 +98,7 @@ cudaError_t launch_pack_weight(const void* w, const void* sf_flat, void* packed,
 cudaError_t launch_linear_packed(const PackedLinearArgs& g, cudaStream_t stream, const char** why);
 cudaError_t read_and_clear_packed_status(int* flag);
 void set_packed_tuning(int splits);
+cudaError_t read_packed_trace(unsigned long long* out16);
 
 // Synchronises the device, returns the time-out flag set by bounded waits
 // inside the kernels and clears it.

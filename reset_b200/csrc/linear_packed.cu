@@ -63,6 +63,16 @@ struct PackedParams {
 };
 
 __device__ int g_packed_status = 0;
+// Optional time line of CTA 0 (nanoseconds of %globaltimer), filled when g_packed_trace != 0.
+__device__ int g_packed_trace = 0;
+__device__ unsigned long long g_packed_times[4 * 16];
+__device__ unsigned g_packed_launch = 0;
+__device__ __forceinline__ unsigned long long gtime() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+    return t;
+}
+#define TRACE(slot) do { if (trace) g_packed_times[(launch_id & 3) * 16 + (slot)] = gtime(); } while (0)
 
 // ---- one-time re-layout ----------------------------------------------------------
 
@@ -84,10 +94,16 @@ pack_weight_kernel(const uint8_t* __restrict__ w, const uint8_t* __restrict__ sf
     }
 }
 
+__device__ __forceinline__ unsigned ticket_acq_rel(unsigned* addr) {
+    unsigned old;
+    asm volatile("atom.add.acq_rel.gpu.global.u32 %0, [%1], 1;" : "=r"(old) : "l"(addr) : "memory");
+    return old;
+}
+
 // ---- the linear ---------------------------------------------------------------------
 
 template <int BN>
-__global__ void __launch_bounds__(kThreadsP, 1)
+__global__ void __launch_bounds__(kThreadsP, 2)
 linear_packed_kernel(const __grid_constant__ PackedParams p) {
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -98,6 +114,14 @@ linear_packed_kernel(const __grid_constant__ PackedParams p) {
     __shared__ int s_last;
 
     const int tid = threadIdx.x, warp = tid / kWarp, lane = tid % kWarp;
+    const bool trace = (g_packed_trace != 0) && blockIdx.x == 0 && lane == 0;
+    __shared__ unsigned s_launch_id;
+    if (g_packed_trace != 0 && blockIdx.x == 0) {
+        if (tid == 0) s_launch_id = atomicAdd(&g_packed_launch, 1u);
+        __syncthreads();
+    }
+    const unsigned launch_id = (g_packed_trace != 0 && blockIdx.x == 0) ? s_launch_id : 0u;
+    if (warp == 0) TRACE(0);
     const int S = p.splits;
     const int ctas_per_part = gridDim.x / S;           // CTAs beyond S * ctas_per_part idle
     const int c = blockIdx.x;
@@ -124,7 +148,8 @@ linear_packed_kernel(const __grid_constant__ PackedParams p) {
 
     constexpr uint32_t kTmemCols = 256;
     constexpr uint32_t kColSFA = 2 * BN;                              // 16 columns per block in a stage
-    constexpr uint32_t kColSFB = kColSFA + 16 * kBlocksPerStage;      // 16 columns per block of the part
+    constexpr uint32_t kColSFB = kColSFA + 16 * kBlocksPerStage;      // likewise for the activations
+    constexpr uint32_t kColSFBres = kColSFB + 16 * kBlocksPerStage;   // 16 per block of the K part
 
     if (warp == 0 && lane == 0) {
         for (int s = 0; s < kStages; ++s) {
@@ -161,8 +186,10 @@ linear_packed_kernel(const __grid_constant__ PackedParams p) {
         const int first = min(kStages, total);
         for (; issued < first; ++issued) issue(issued);
     }
+    if (warp == 0) TRACE(1);
     pdl_launch_dependents();
     pdl_wait_prior();
+    if (warp == 0) TRACE(2);
 
     // ---- prologue: quantize this part's activations into operand layout --------------
     if (active) {
@@ -172,23 +199,43 @@ linear_packed_kernel(const __grid_constant__ PackedParams p) {
         const QuantScales qe = make_quant_scales<kRcpExact>(gs);
         const QuantScales qa = make_quant_scales<kRcpApprox>(gs);
         const __nv_bfloat16* xb = static_cast<const __nv_bfloat16*>(p.xb);
-        for (int i = tid; i < p.M * blocks; i += kThreadsP) {
-            const int m = i / blocks, blk = i - m * blocks;
-            const uint4* src = reinterpret_cast<const uint4*>(
-                xb + (p.m0 + m) * p.xb_stride + static_cast<int64_t>(blk0 + blk) * 16);
-            const uint4 lo = __ldg(src), hi = __ldg(src + 1);
-            uint32_t cw[2];
-            const uint32_t sf = (p.rcp_mode == kRcpExact) ? quantize_block16<kRcpExact>(lo, hi, qe, cw)
-                                                          : quantize_block16<kRcpApprox>(lo, hi, qa, cw);
-            *reinterpret_cast<uint2*>(b_tile_g + (blk >> 4) * (BN * 128) + swz128(m, (blk & 15) * 8)) =
-                make_uint2(cw[0], cw[1]);
-            b_sf_g[(blk >> 2) * 512 + m * 16 + (blk & 3)] = static_cast<uint8_t>(sf);
+        // four blocks per thread per round: all eight 16-byte loads are issued before any
+        // of the arithmetic, so a round costs one memory round trip
+        const int n_items = p.M * blocks;
+        for (int i0 = tid; i0 < n_items; i0 += 4 * kThreadsP) {
+            uint4 lo[4], hi[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const int i = i0 + u * kThreadsP;
+                if (i < n_items) {
+                    const int m = i / blocks, blk = i - m * blocks;
+                    const uint4* src = reinterpret_cast<const uint4*>(
+                        xb + (p.m0 + m) * p.xb_stride + static_cast<int64_t>(blk0 + blk) * 16);
+                    lo[u] = __ldg(src);
+                    hi[u] = __ldg(src + 1);
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const int i = i0 + u * kThreadsP;
+                if (i < n_items) {
+                    const int m = i / blocks, blk = i - m * blocks;
+                    uint32_t cw[2];
+                    const uint32_t sf = (p.rcp_mode == kRcpExact)
+                                            ? quantize_block16<kRcpExact>(lo[u], hi[u], qe, cw)
+                                            : quantize_block16<kRcpApprox>(lo[u], hi[u], qa, cw);
+                    *reinterpret_cast<uint2*>(b_tile_g + (blk >> 4) * (BN * 128) + swz128(m, (blk & 15) * 8)) =
+                        make_uint2(cw[0], cw[1]);
+                    b_sf_g[(blk >> 2) * 512 + m * 16 + (blk & 3)] = static_cast<uint8_t>(sf);
+                }
+            }
         }
         // Rows M..BN-1 of the operand are never written: whatever they hold only reaches
         // accumulator columns that are not stored.
         fence_proxy_async_smem();
     }
     __syncthreads();
+    if (warp == 0) TRACE(3);
 
     WaitFail wf;
     if (warp == 0) {
@@ -205,9 +252,12 @@ linear_packed_kernel(const __grid_constant__ PackedParams p) {
         if (lane == 0 && my_tiles > 0) {
             constexpr uint32_t idesc = (1u << 7) | (1u << 10) | (static_cast<uint32_t>(BN >> 3) << 17) |
                                        (static_cast<uint32_t>(kTileRows >> 7) << 27);
-            // activation scales: once, resident in tensor memory for the whole kernel
-            for (int ch = 0; ch < nkb * 4; ++ch)
-                tc_cp_scales(tmem + kColSFB + 4 * ch, desc_scales(b_sf + ch * 512));
+            // A CTA that walks several tiles copies the activation scales into tensor
+            // memory once; a single-tile CTA copies them with the stage that uses them.
+            const bool sfb_resident = my_tiles >= 2;
+            if (sfb_resident)
+                for (int ch = 0; ch < nkb * 4; ++ch)
+                    tc_cp_scales(tmem + kColSFBres + 4 * ch, desc_scales(b_sf + ch * 512));
             int i = 0;
             for (int ti = 0; ti < my_tiles && !wf.failed; ++ti) {
                 const int buf = ti & 1;
@@ -217,6 +267,7 @@ linear_packed_kernel(const __grid_constant__ PackedParams p) {
                 for (int j = 0; j < stages_per_tile; ++j, ++i) {
                     const int s = i % kStages;
                     if (!wf.wait(bar_full + 8 * s, (i / kStages) & 1)) break;
+                    if (i == 0) TRACE(4);
                     tc_fence_after();
                     const int nb = stage_blocks(j);
                     for (int b = 0; b < nb; ++b) {
@@ -224,19 +275,26 @@ linear_packed_kernel(const __grid_constant__ PackedParams p) {
                         const int blk = j * kBlocksPerStage + b;              // block within the part
                         const uint32_t b_smem = b_tile + blk * (BN * 128);
 #pragma unroll
-                        for (int k = 0; k < 4; ++k)
+                        for (int k = 0; k < 4; ++k) {
                             tc_cp_scales(tmem + kColSFA + 16 * b + 4 * k,
                                          desc_scales(a_smem + kCodesBytes + k * 512));
+                            if (!sfb_resident)
+                                tc_cp_scales(tmem + kColSFB + 16 * b + 4 * k,
+                                             desc_scales(b_sf + (blk * 4 + k) * 512));
+                        }
+                        const uint32_t sfb_col = sfb_resident ? kColSFBres + 16 * blk : kColSFB + 16 * b;
 #pragma unroll
                         for (int k = 0; k < 4; ++k)
                             tc_mma_nvf4(d_tmem, desc_operand(a_smem + k * 32), desc_operand(b_smem + k * 32),
                                         idesc, tmem + kColSFA + 16 * b + 4 * k,
-                                        tmem + kColSFB + 16 * blk + 4 * k, (blk > 0 || k > 0) ? 1u : 0u);
+                                        tmem + sfb_col + 4 * k, (blk > 0 || k > 0) ? 1u : 0u);
                     }
                     tc_commit(bar_empty + 8 * s);
                 }
                 tc_commit(bar_accfull + 8 * buf);
+                if (ti == 0) TRACE(5);
             }
+            TRACE(6);
         }
     } else {
         // ---------------- epilogue (warps 2..5) ------------------------------------------
@@ -247,6 +305,8 @@ linear_packed_kernel(const __grid_constant__ PackedParams p) {
             const int buf = ti & 1;
             const int tile = rank_in_part + ti * ctas_per_part;
             if (!wf.wait(bar_accfull + 8 * buf, (ti >> 1) & 1)) break;
+            if (warp == 2 && ti == 0) TRACE(7);
+            if (warp == 2 && ti == my_tiles - 1) TRACE(8);
             tc_fence_after();
             float acc[BN];
 #pragma unroll
@@ -274,32 +334,36 @@ linear_packed_kernel(const __grid_constant__ PackedParams p) {
 #pragma unroll
                 for (int m = 0; m < BN; ++m)
                     if (m < p.M) __stcg(slot + m * kTileRows + row_in_tile, acc[m]);
-                __threadfence();
+                // The CTA barrier orders every thread's partial stores before thread 0's
+                // release; the acquire side is the same atomic followed by the second barrier.
                 named_barrier(1, kEpilogueThreads);
                 if (et == 0) {
-                    const unsigned t = atomicAdd(p.tickets + tile, 1u);
+                    const unsigned t = ticket_acq_rel(p.tickets + tile);
                     s_last = (t == static_cast<unsigned>(S) - 1u) ? 1 : 0;
                     if (s_last) p.tickets[tile] = 0u;
-                    __threadfence();
                 }
                 named_barrier(1, kEpilogueThreads);
                 if (s_last) {
+                    // all loads first (independent, many in flight), parts added in part order
                     const float* base = p.partials + static_cast<int64_t>(tile) * S * (BN * kTileRows);
 #pragma unroll
-                    for (int m = 0; m < BN; ++m) {
-                        if (m < p.M) {
-                            float v = 0.0f;
-                            for (int s = 0; s < S; ++s)
-                                v += __ldcg(base + s * (BN * kTileRows) + m * kTileRows + row_in_tile);
-                            store(m, v);
-                        }
+                    for (int m = 0; m < BN; ++m) acc[m] = 0.0f;
+                    for (int s = 0; s < S; ++s) {
+#pragma unroll
+                        for (int m = 0; m < BN; ++m)
+                            if (m < p.M)
+                                acc[m] += __ldcg(base + s * (BN * kTileRows) + m * kTileRows + row_in_tile);
                     }
+#pragma unroll
+                    for (int m = 0; m < BN; ++m)
+                        if (m < p.M) store(m, acc[m]);
                 }
                 named_barrier(1, kEpilogueThreads);
             }
         }
     }
 
+    if (warp == 2) TRACE(9);
     if (wf.failed && lane == 0) atomicExch(&g_packed_status, 1);
     tc_fence_before();
     __syncthreads();
@@ -311,11 +375,13 @@ linear_packed_kernel(const __grid_constant__ PackedParams p) {
 
 struct PackedPlan { int splits, grid, bn; size_t smem; };
 int g_force_packed_splits = 0;
+int g_packed_ctas_per_sm = 2;
 
 // Parts of at most kMaxPartBlocks K blocks; among the admissible split counts take the
 // one that keeps the most SMs busy (fewer parts on a tie).
 bool plan_packed(int M, int N, int K, PackedPlan* plan) {
-    const int G = device_sm_count();
+    const int bn_ = M <= 16 ? 16 : 32;
+    const int G = device_sm_count() * ((bn_ == 16 && g_packed_ctas_per_sm == 2) ? 2 : 1);
     const int tiles = N / kTileRows, kblocks = K / kBlockK;
     const int min_s = (kblocks + kMaxPartBlocks - 1) / kMaxPartBlocks;
     if (min_s > G) return false;
@@ -420,7 +486,16 @@ cudaError_t launch_linear_packed(const PackedLinearArgs& g, cudaStream_t stream,
     return cudaSuccess;
 }
 
-void set_packed_tuning(int splits) { g_force_packed_splits = splits; }
+void set_packed_tuning(int splits) {
+    g_force_packed_splits = splits & 0xff;
+    g_packed_ctas_per_sm = ((splits >> 9) & 1) ? 1 : 2;
+    const int trace = (splits >> 8) & 1;
+    cudaMemcpyToSymbol(g_packed_trace, &trace, sizeof(int));
+}
+
+cudaError_t read_packed_trace(unsigned long long* out16) {
+    return cudaMemcpyFromSymbol(out16, g_packed_times, 64 * sizeof(unsigned long long));
+}
 
 cudaError_t read_and_clear_packed_status(int* flag) {
     cudaError_t e = cudaMemcpyFromSymbol(flag, g_packed_status, sizeof(int));

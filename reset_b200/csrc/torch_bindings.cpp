@@ -196,6 +196,51 @@ at::Tensor linear_tc_op(const at::Tensor& x, const at::Tensor& global_scale_inv,
     return out;
 }
 
+// One-time re-layout of a weight into the packed block format (18 KB per 128 x 256 block).
+at::Tensor pack_weight_op(const at::Tensor& weight, const at::Tensor& weight_scale_flat) {
+    TORCH_CHECK(weight.is_cuda() && weight_scale_flat.is_cuda(), "pack_weight: tensors must be CUDA");
+    TORCH_CHECK(weight.dim() == 2 && weight.is_contiguous() && weight_scale_flat.is_contiguous(),
+                "pack_weight: weight [N,K/2] and flat weight_scale [N,K/16] must be contiguous");
+    const int64_t N = weight.size(0), K = weight.size(1) * 2;
+    TORCH_CHECK(weight_scale_flat.numel() == N * (K / 16), "pack_weight: weight_scale shape mismatch");
+    const size_t bytes = nvfp4r_packed_weight_bytes(static_cast<int>(N), static_cast<int>(K));
+    TORCH_CHECK(bytes > 0, "pack_weight: needs N % 128 == 0 and K % 256 == 0");
+    const c10::cuda::OptionalCUDAGuard guard(weight.device());
+    auto packed = at::empty({static_cast<int64_t>(bytes)}, weight.options().dtype(at::kByte));
+    check_status(nvfp4r_pack_weight(weight.data_ptr(), weight_scale_flat.data_ptr(), packed.data_ptr(),
+                                    static_cast<int>(N), static_cast<int>(K), current_stream()),
+                 "pack_weight");
+    return packed;
+}
+
+// The adapter's product path: on-chip quantizer + tensor-core linear over a packed weight.
+at::Tensor linear_packed_op(const at::Tensor& x, const at::Tensor& global_scale_inv,
+                            const at::Tensor& packed, int64_t N, double alpha, int64_t out_dtype_int,
+                            int64_t rcp_mode) {
+    TORCH_CHECK(x.is_cuda() && packed.is_cuda() && global_scale_inv.is_cuda(),
+                "linear_packed: tensors must be CUDA");
+    TORCH_CHECK(x.scalar_type() == at::kBFloat16 && x.dim() == 2 && x.stride(1) == 1,
+                "linear_packed: x must be bfloat16 [M,K] with unit inner stride");
+    const int64_t M = x.size(0), K = x.size(1);
+    TORCH_CHECK(packed.is_contiguous() &&
+                    static_cast<size_t>(packed.nbytes()) ==
+                        nvfp4r_packed_weight_bytes(static_cast<int>(N), static_cast<int>(K)),
+                "linear_packed: packed weight does not match N and K");
+    const c10::cuda::OptionalCUDAGuard guard(x.device());
+    const auto dt = out_dtype_int == 0 ? at::kBFloat16 : out_dtype_int == 1 ? at::kHalf : at::kFloat;
+    auto out = at::empty({M, N}, x.options().dtype(dt));
+    at::Tensor& ws = gemm_workspace(x.device(), nvfp4r_linear_packed_workspace_bytes(
+                                                    static_cast<int>(M), static_cast<int>(N),
+                                                    static_cast<int>(K)));
+    const int st = nvfp4r_linear_packed(x.data_ptr(), x.stride(0), static_cast<int>(M), static_cast<int>(K),
+                                        global_scale_inv.data_ptr<float>(), packed.data_ptr(),
+                                        static_cast<int>(N), static_cast<float>(alpha), out.data_ptr(),
+                                        static_cast<int>(out_dtype_int), static_cast<int>(rcp_mode),
+                                        ws.data_ptr(), static_cast<size_t>(ws.nbytes()), current_stream());
+    check_status(st, "linear_packed");
+    return out;
+}
+
 at::Tensor entropy_op(const at::Tensor& logits, at::Tensor workspace) {
     TORCH_CHECK(logits.is_cuda() && logits.scalar_type() == at::kFloat && logits.dim() == 2 &&
                     logits.stride(1) == 1, "entropy: logits must be CUDA float32 [B,V]");
@@ -243,6 +288,9 @@ TORCH_LIBRARY(nvfp4r, m) {
           "float alpha, int out_dtype_int=0, int rcp_mode=1) -> Tensor");
     m.def("linear_tc(Tensor x, Tensor global_scale_inv, Tensor weight, Tensor weight_scale_swizzled, "
           "float alpha, int out_dtype_int=0, int rcp_mode=1) -> Tensor");
+    m.def("pack_weight(Tensor weight, Tensor weight_scale_flat) -> Tensor");
+    m.def("linear_packed(Tensor x, Tensor global_scale_inv, Tensor packed, int N, float alpha, "
+          "int out_dtype_int=0, int rcp_mode=1) -> Tensor");
     m.def("entropy(Tensor logits, Tensor workspace) -> Tensor");
     m.def("reset_step(Tensor(a!) logits, Tensor(b!) states, Tensor? state_slots, Tensor? last_ids, "
           "Tensor? nl_bitmap, Tensor? dnl_bitmap, float t_high, float t_low, float tau0, int window, "
@@ -255,6 +303,8 @@ TORCH_LIBRARY_IMPL(nvfp4r, CUDA, m) {
     m.impl("quant", &quant_op);
     m.impl("linear", &linear_op);
     m.impl("linear_tc", &linear_tc_op);
+    m.impl("pack_weight", &pack_weight_op);
+    m.impl("linear_packed", &linear_packed_op);
     m.impl("entropy", &entropy_op);
     m.impl("reset_step", &reset_step_op);
 }

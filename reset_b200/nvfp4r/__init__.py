@@ -15,9 +15,9 @@ import torch  # noqa: F401  (libtorch must be loaded before the extension)
 from .. import _C  # noqa: F401  (registers torch.ops.nvfp4r.*; raises if not built)
 from . import _fake  # noqa: F401  (FakeTensor impls for torch.compile)
 from . import _config
-from .ops import gemm, gemv, linear, quant
+from .ops import gemm, gemv, linear, linear_auto, linear_packed, pack_weight, quant
 
-__all__ = ["gemv", "gemm", "quant", "linear", "enable", "disable", "configure", "status"]
+__all__ = ["gemv", "gemm", "quant", "linear", "linear_packed", "linear_auto", "pack_weight", "enable", "disable", "configure", "status"]
 __version__ = "0.1.0"
 
 

@@ -9,3 +9,9 @@ GEMV_MAX_M = int(os.environ.get("NVFP4R_GEMV_MAX_M", "2"))
 GEMM_PAD_MAX_M = int(os.environ.get("NVFP4R_GEMM_PAD_MAX_M", "63"))
 ENABLE_GEMM_PATH = os.environ.get("NVFP4R_ENABLE_GEMM", "1") == "1"
 FALLBACK_BACKEND = os.environ.get("NVFP4R_FALLBACK_BACKEND", "none").lower()
+
+# Measured crossover between the CUDA-core GEMV and the packed tensor-core linear on
+# B200 (L2-cold weights, CUDA-graph replay): the GEMV's shorter fixed latency wins only
+# for the smallest batches on weights of at most this many bytes; everything else goes
+# to the tensor cores. Index = M.
+GEMV_MAX_WEIGHT_BYTES = {1: 30_000_000, 2: 10_000_000}

@@ -38,6 +38,16 @@ def _linear_tc_fake(x, global_scale_inv, weight, weight_scale_swizzled, alpha, o
     return x.new_empty((x.shape[0], weight.shape[0]), dtype=_OUT_DTYPES[out_dtype_int])
 
 
+@torch.library.register_fake("nvfp4r::pack_weight")
+def _pack_weight_fake(weight, weight_scale_flat):
+    return weight.new_empty((weight.numel() * 9 // 8,), dtype=torch.uint8)
+
+
+@torch.library.register_fake("nvfp4r::linear_packed")
+def _linear_packed_fake(x, global_scale_inv, packed, N, alpha, out_dtype_int=0, rcp_mode=1):
+    return x.new_empty((x.shape[0], N), dtype=_OUT_DTYPES[out_dtype_int])
+
+
 @torch.library.register_fake("nvfp4r::entropy")
 def _entropy_fake(logits, workspace):
     return logits.new_empty((logits.shape[0],))

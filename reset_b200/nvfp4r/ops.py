@@ -54,3 +54,35 @@ def linear(x: torch.Tensor, global_scale_inv: torch.Tensor, weight: torch.Tensor
     """Quantize up to 16 bf16 tokens and multiply by one NVFP4 weight in one launch."""
     code = {torch.bfloat16: 0, torch.float16: 1, torch.float32: 2}[out_dtype]
     return torch.ops.nvfp4r.linear(x, global_scale_inv, weight, weight_scale_flat, alpha, code, rcp_mode)
+
+
+def pack_weight(weight: torch.Tensor, weight_scale_flat: torch.Tensor) -> torch.Tensor:
+    """Re-lay a weight [N,K/2] + flat scales [N,K/16] out once for the tensor-core path."""
+    return torch.ops.nvfp4r.pack_weight(weight, weight_scale_flat)
+
+
+def linear_packed(x: torch.Tensor, global_scale_inv: torch.Tensor, packed: torch.Tensor, N: int,
+                  alpha: float, out_dtype: torch.dtype = torch.bfloat16, rcp_mode: int = 1) -> torch.Tensor:
+    """Quantize M bf16 tokens and multiply by a packed NVFP4 weight on the tensor cores."""
+    code = {torch.bfloat16: 0, torch.float16: 1, torch.float32: 2}[out_dtype]
+    return torch.ops.nvfp4r.linear_packed(x, global_scale_inv, packed, N, alpha, code, rcp_mode)
+
+
+def use_gemv(M: int, N: int, K: int, gemv_max_m: int) -> bool:
+    """The measured crossover: True when the CUDA-core GEMV is the faster path."""
+    from . import _config
+    if M > gemv_max_m:
+        return False
+    limit = _config.GEMV_MAX_WEIGHT_BYTES.get(M)
+    return limit is not None and N * K * 9 // 16 <= limit
+
+
+def linear_auto(x, global_scale_inv, weight, weight_scale_flat, packed, N: int, alpha: float,
+                out_dtype: torch.dtype = torch.bfloat16, rcp_mode: int = 1) -> torch.Tensor:
+    """One decode linear through whichever kernel the measured crossover picks. ``packed``
+    may be None (shape outside the tensor-core kernel's N % 128 / K % 256)."""
+    from . import _config
+    M, K = x.shape
+    if packed is None or (weight is not None and use_gemv(M, N, K, _config.GEMV_MAX_M)):
+        return linear(x, global_scale_inv, weight, weight_scale_flat, alpha, out_dtype, rcp_mode)
+    return linear_packed(x, global_scale_inv, packed, N, alpha, out_dtype, rcp_mode)

@@ -8,10 +8,13 @@
 
 Differences from the reference, all inside the dispatch:
 
-* M <= ``gemv_max_m``: ONE launch (``torch.ops.nvfp4r.linear``: quantize + GEMV fused)
-  instead of ``scaled_fp4_quant`` + ``expand`` + ``empty`` + ``nvfp4r.gemv``.
-* M  > ``gemv_max_m``: own quantizer (swizzled scales) + own tcgen05 GEMM for any M,
-  written M-major; no padding to 64 rows, no transpose/contiguous copy.
+* every decode batch is ONE launch per 32 rows. Below the measured crossover
+  (``gemv_max_m`` and a weight-size bound, ``_config.GEMV_MAX_WEIGHT_BYTES``) that launch
+  is ``torch.ops.nvfp4r.linear`` (quantize + CUDA-core GEMV fused, instead of
+  ``scaled_fp4_quant`` + ``expand`` + ``empty`` + ``nvfp4r.gemv``); above it it is
+  ``torch.ops.nvfp4r.linear_packed`` (quantize + tcgen05 block-scaled MMA over a weight
+  re-laid out once per layer), for any M, written M-major: no padding to 64 rows, no
+  transpose/contiguous copy.
 * There is no CUTLASS/FlashInfer fallback branch (reference :299-318): a shape the
   kernels cannot take raises.
 
@@ -42,6 +45,8 @@ def prime_nvfp4r_caches(layer: torch.nn.Module) -> None:
 
     ``_nvfp4r_alpha_host``            Python float of ``layer.alpha``
     ``_nvfp4r_weight_scale_flat_3d``  ``[1, N, K/16]`` uint8 flat block scales
+    ``_nvfp4r_weight_packed``         the weight in the packed block format of the
+                                      tensor-core path (None when N % 128 or K % 256)
 
     ``layer.weight_scale`` may be swizzled (the reference's case, vLLM's CUTLASS
     format) or still flat ``[N, K/16]``; ``layer._nvfp4r_weight_scale_is_flat`` says
@@ -63,26 +68,32 @@ def prime_nvfp4r_caches(layer: torch.nn.Module) -> None:
             tuple(ws_u8.shape) == (N, K // 16) and (N % 128 != 0 or (K // 16) % 4 != 0))
         flat = ws_u8.contiguous() if is_flat else _unswizzle_blockscale(ws_u8, N, K)
         layer._nvfp4r_weight_scale_flat_3d = flat.reshape(1, N, K // 16).contiguous()
+        layer._nvfp4r_weight_packed = None
+        if N % 128 == 0 and K % 256 == 0 and getattr(layer, "weights_padding_cols", 0) == 0:
+            layer._nvfp4r_weight_packed = capi.pack_weight(
+                layer.weight.data.view(torch.uint8), layer._nvfp4r_weight_scale_flat_3d[0])
     layer._nvfp4r_caches_primed = True
 
 
-def nvfp4r_linear(x_2d: torch.Tensor, weight: torch.Tensor, weight_scale_swizzled: torch.Tensor,
-                  weight_scale_flat_3d: torch.Tensor, input_global_scale_inv: torch.Tensor,
+def nvfp4r_linear(x_2d: torch.Tensor, weight: torch.Tensor, weight_scale_flat_3d: torch.Tensor,
+                  weight_packed: Optional[torch.Tensor], input_global_scale_inv: torch.Tensor,
                   alpha_host: float, output_size: int, gemv_max_m: int, out_dtype_int: int,
                   enable_gemm: bool) -> torch.Tensor:
     """All M-dependent branching of one linear (reference ``_nvfp4r_linear_impl``,
     :165-318). Returns ``[M, output_size]`` in the requested dtype."""
-    M = x_2d.shape[0]
-    if M <= gemv_max_m or not enable_gemm:
-        if M <= 16:
-            return torch.ops.nvfp4r.linear(x_2d, input_global_scale_inv, weight,
-                                           weight_scale_flat_3d, alpha_host, out_dtype_int, 1)
-        parts = [torch.ops.nvfp4r.linear(x_2d[i:i + 16], input_global_scale_inv, weight,
-                                         weight_scale_flat_3d, alpha_host, out_dtype_int, 1)
-                 for i in range(0, M, 16)]
-        return torch.cat(parts, dim=0)
-    return torch.ops.nvfp4r.linear_tc(x_2d, input_global_scale_inv, weight, weight_scale_swizzled,
-                                      alpha_host, out_dtype_int, 1)
+    from .ops import use_gemv
+    M, K = x_2d.shape
+    tc_ok = enable_gemm and weight_packed is not None
+    if tc_ok and not use_gemv(M, output_size, K, gemv_max_m):
+        return torch.ops.nvfp4r.linear_packed(x_2d, input_global_scale_inv, weight_packed,
+                                              output_size, alpha_host, out_dtype_int, 1)
+    if M <= 16:
+        return torch.ops.nvfp4r.linear(x_2d, input_global_scale_inv, weight, weight_scale_flat_3d,
+                                       alpha_host, out_dtype_int, 1)
+    parts = [torch.ops.nvfp4r.linear(x_2d[i:i + 16], input_global_scale_inv, weight,
+                                     weight_scale_flat_3d, alpha_host, out_dtype_int, 1)
+             for i in range(0, M, 16)]
+    return torch.cat(parts, dim=0)
 
 
 def apply_nvfp4r_linear(layer: torch.nn.Module, x: torch.Tensor,
@@ -94,9 +105,10 @@ def apply_nvfp4r_linear(layer: torch.nn.Module, x: torch.Tensor,
         raise RuntimeError("nvfp4r: K-padded weights are not supported (no fallback backend)")
     output_shape = (*x.shape[:-1], output_size)
     x_2d = x.reshape(-1, x.shape[-1])
-    out = nvfp4r_linear(x_2d, layer.weight, layer.weight_scale, layer._nvfp4r_weight_scale_flat_3d,
-                        layer.input_global_scale_inv, layer._nvfp4r_alpha_host, output_size,
-                        _config.GEMV_MAX_M, _OUT_DTYPE_INT[x.dtype], _config.ENABLE_GEMM_PATH)
+    out = nvfp4r_linear(x_2d, layer.weight, layer._nvfp4r_weight_scale_flat_3d,
+                        layer._nvfp4r_weight_packed, layer.input_global_scale_inv,
+                        layer._nvfp4r_alpha_host, output_size, _config.GEMV_MAX_M,
+                        _OUT_DTYPE_INT[x.dtype], _config.ENABLE_GEMM_PATH)
     if bias is not None:
         out = out + bias
     return out.view(*output_shape)
