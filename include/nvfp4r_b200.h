@@ -268,6 +268,28 @@ NVFP4R_API int nvfp4r_reset_step(float* logits, int64_t row_stride, int B, int V
                                  nvfp4r_reset_decision* decisions,
                                  void* workspace, size_t workspace_bytes, void* stream);
 
+/* ReSET step without any caller-provided scratch. No counterpart in the reference (its
+ * processor is PyTorch code and allocates freely); it exists for hosts that cannot
+ * allocate device memory when they need the processor: a sampler plug-in inside an engine
+ * whose memory pool already owns the whole GPU, or a C host that only holds fixed input
+ * and output buffers. Same arguments, arithmetic and results as nvfp4r_reset_step, minus
+ * the workspace: the scratch is a static array inside the library (41 984 B of device
+ * memory on every GPU that loads it, held until the process exits).
+ *   - B <= NVFP4R_RESET_STATIC_MAX_ROWS, otherwise NVFP4R_ERR_UNSUPPORTED_SHAPE.
+ *   - Calls no cudaMalloc/cudaFree and no allocating library routine.
+ *   - The first call on each device looks the array's address up
+ *     (cudaGetSymbolAddress, with that device current); make that first call outside any
+ *     stream capture.
+ *   - All calls on a device share the one array: two calls that overlap on the GPU
+ *     (different streams without ordering) race on it. Order them. */
+#define NVFP4R_RESET_STATIC_MAX_ROWS 64
+NVFP4R_API int nvfp4r_reset_step_static(float* logits, int64_t row_stride, int B, int V,
+                                        nvfp4r_reset_state* states, const int32_t* state_slots,
+                                        const int32_t* last_ids,
+                                        const uint32_t* nl_bitmap, const uint32_t* dnl_bitmap,
+                                        const nvfp4r_reset_params* params,
+                                        nvfp4r_reset_decision* decisions, void* stream);
+
 /* Token entropy only: H[b] = -sum p*log(max(p,1e-10)) for each row, as float32.
  * Stands in for `entropy_of` (reset/reset/logits_processor.py:32-36). Same
  * workspace rule as nvfp4r_reset_step. */

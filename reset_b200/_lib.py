@@ -18,6 +18,7 @@ SF_FLAT, SF_SWIZZLED = 0, 1
 RCP_EXACT, RCP_APPROX = 0, 1
 C_M_MAJOR, C_N_MAJOR = 0, 1
 RESET_MAX_WINDOW = 64
+RESET_STATIC_MAX_ROWS = 64
 LINEAR_MAX_M = 16
 
 
@@ -63,6 +64,8 @@ PROTOTYPES = {
     "nvfp4r_reset_workspace_bytes": (_sz, [_i]),
     "nvfp4r_reset_step": (_i, [_vp, _i64, _i, _i, _vp, _vp, _vp, _vp, _vp,
                                C.POINTER(ResetParams), _vp, _vp, _sz, _vp]),
+    "nvfp4r_reset_step_static": (_i, [_vp, _i64, _i, _i, _vp, _vp, _vp, _vp, _vp,
+                                      C.POINTER(ResetParams), _vp, _vp]),
     "nvfp4r_entropy": (_i, [_vp, _i64, _i, _i, _vp, _vp, _sz, _vp]),
     "nvfp4r_set_gemv_tuning": (_i, [_i, _i, _i]),
     "nvfp4r_check_device_status": (_i, []),

@@ -335,6 +335,42 @@ int nvfp4r_reset_step(float* logits, int64_t row_stride, int B, int V, nvfp4r_re
     return e == cudaSuccess ? NVFP4R_OK : cuda_fail(e, "reset_step launch");
 }
 
+int nvfp4r_reset_step_static(float* logits, int64_t row_stride, int B, int V,
+                             nvfp4r_reset_state* states, const int32_t* state_slots,
+                             const int32_t* last_ids, const uint32_t* nl_bitmap,
+                             const uint32_t* dnl_bitmap, const nvfp4r_reset_params* params,
+                             nvfp4r_reset_decision* decisions, void* stream) {
+    if (!logits || !states || !params)
+        return fail(NVFP4R_ERR_INVALID_ARGUMENT, "reset_step_static: null pointer");
+    if (B < 0 || V <= 0 || row_stride < V)
+        return fail(NVFP4R_ERR_INVALID_ARGUMENT, "reset_step_static: bad sizes");
+    if (B > NVFP4R_RESET_STATIC_MAX_ROWS)
+        return fail(NVFP4R_ERR_UNSUPPORTED_SHAPE,
+                    "reset_step_static: more rows than NVFP4R_RESET_STATIC_MAX_ROWS; use "
+                    "nvfp4r_reset_step with a workspace");
+    if (params->window < 1 || params->window > NVFP4R_RESET_MAX_WINDOW)
+        return fail(NVFP4R_ERR_UNSUPPORTED_SHAPE, "reset_step_static: window outside 1..NVFP4R_RESET_MAX_WINDOW");
+    if (!aligned(logits, 4) || !aligned(states, 8))
+        return fail(NVFP4R_ERR_ALIGNMENT, "reset_step_static: states need 8-byte alignment");
+    if (B == 0) return NVFP4R_OK;
+    nvfp4r::ResetLaunch p = {};
+    p.logits = logits;
+    p.row_stride = row_stride;
+    p.B = B;
+    p.V = V;
+    p.states = states;
+    p.state_slots = state_slots;
+    p.last_ids = last_ids;
+    p.nl_bitmap = nl_bitmap;
+    p.dnl_bitmap = dnl_bitmap;
+    p.params = *params;
+    p.decisions = decisions;
+    p.entropy_out = nullptr;
+    p.needs_state = 1;
+    cudaError_t e = nvfp4r::launch_reset_static(p, as_stream(stream));
+    return e == cudaSuccess ? NVFP4R_OK : cuda_fail(e, "reset_step_static launch");
+}
+
 int nvfp4r_entropy(const float* logits, int64_t row_stride, int B, int V, float* entropy,
                    void* workspace, size_t workspace_bytes, void* stream) {
     if (!logits || !entropy || !workspace) return fail(NVFP4R_ERR_INVALID_ARGUMENT, "entropy: null pointer");

@@ -40,5 +40,7 @@ struct ResetLaunch {
 
 int reset_pick_slices(int B, int V);
 cudaError_t launch_reset(ResetLaunch p, bool scale, cudaStream_t stream);
+// Same step with the scratch taken from a static device array (no_alloc.cu).
+cudaError_t launch_reset_static(ResetLaunch p, cudaStream_t stream);
 
 }  // namespace nvfp4r
