@@ -94,6 +94,40 @@ pack_weight_kernel(const uint8_t* __restrict__ w, const uint8_t* __restrict__ sf
     }
 }
 
+// ---- thread-block cluster helpers (split-K reduction through distributed shared memory)
+__device__ __forceinline__ uint32_t cluster_rank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ uint32_t map_to_rank(uint32_t smem_addr, uint32_t rank) {
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_addr), "r"(rank));
+    return r;
+}
+__device__ __forceinline__ void st_cluster_f32(uint32_t addr, float v) {
+    asm volatile("st.shared::cluster.f32 [%0], %1;" :: "r"(addr), "f"(v) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_remote(uint32_t cluster_addr) {
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" :: "r"(cluster_addr) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait_cluster(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile("{\n\t.reg .pred p;\n\t"
+                 "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
+                 "selp.u32 %0, 1, 0, p;\n\t}"
+                 : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ bool mbar_wait_cluster_bounded(uint32_t bar, uint32_t parity) {
+    for (uint32_t i = 0; i < 20000000u; ++i)
+        if (mbar_try_wait_cluster(bar, parity)) return true;
+    return false;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+
 __device__ __forceinline__ unsigned ticket_acq_rel(unsigned* addr) {
     unsigned old;
     asm volatile("atom.add.acq_rel.gpu.global.u32 %0, [%1], 1;" : "=r"(old) : "l"(addr) : "memory");
@@ -102,14 +136,20 @@ __device__ __forceinline__ unsigned ticket_acq_rel(unsigned* addr) {
 
 // ---- the linear ---------------------------------------------------------------------
 
-template <int BN>
+// kCluster: the S CTAs that share a tile form a thread-block cluster (cluster rank = K
+// part) and reduce their partial tiles through distributed shared memory: every CTA owns
+// 128/S rows of the tile, receives the other parts' values for those rows with
+// st.shared::cluster + a remote mbarrier arrive, adds them in part order and stores.
+// Without it (S == 1, or S not a cluster size) partials go through global scratch and a
+// ticket.
+template <int BN, bool kCluster>
 __global__ void __launch_bounds__(kThreadsP, 2)
 linear_packed_kernel(const __grid_constant__ PackedParams p) {
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t* smem = smem_raw + (smem_base - smem_u32(smem_raw));
 
-    __shared__ __align__(8) uint64_t bars[2 * kStages + 4];
+    __shared__ __align__(8) uint64_t bars[2 * kStages + 6];
     __shared__ uint32_t s_tmem;
     __shared__ int s_last;
 
@@ -137,14 +177,23 @@ linear_packed_kernel(const __grid_constant__ PackedParams p) {
 
     const uint32_t ring = smem_base;
     const uint32_t b_tile = ring + kStages * kStageBytes;            // nkb blocks of BN x 128 B
-    const uint32_t b_sf = b_tile + kMaxPartBlocks * (BN * 128);       // nkb * 4 chunks of 512 B
+    // activation scale chunks: tcgen05.cp reads 32 rows x 16 B per chunk, but only rows
+    // < BN matter, so with BN == 16 consecutive chunks overlap by half (stride 256 B)
+    constexpr int kSfbStride = (BN == 16) ? 256 : 512;
+    constexpr int kSfbBytes = kMaxPartBlocks * 4 * kSfbStride + 256;
+    const uint32_t b_sf = b_tile + kMaxPartBlocks * (BN * 128);
     uint8_t* b_tile_g = smem + kStages * kStageBytes;
     uint8_t* b_sf_g = b_tile_g + kMaxPartBlocks * (BN * 128);
+    // cluster reduction: values received for the rows this CTA owns, [part][token][row]
+    const uint32_t recv = b_sf + kSfbBytes;
+    float* recv_g = reinterpret_cast<float*>(b_sf_g + kSfbBytes);
 
     const uint32_t bar_full = smem_u32(&bars[0]);
     const uint32_t bar_empty = smem_u32(&bars[kStages]);
     const uint32_t bar_accfull = smem_u32(&bars[2 * kStages]);
     const uint32_t bar_accempty = smem_u32(&bars[2 * kStages + 2]);
+    const uint32_t bar_redfull = smem_u32(&bars[2 * kStages + 4]);
+    const uint32_t bar_redfree = smem_u32(&bars[2 * kStages + 5]);
 
     constexpr uint32_t kTmemCols = 256;
     constexpr uint32_t kColSFA = 2 * BN;                              // 16 columns per block in a stage
@@ -159,6 +208,10 @@ linear_packed_kernel(const __grid_constant__ PackedParams p) {
         for (int b = 0; b < 2; ++b) {
             mbar_init(bar_accfull + 8 * b, 1);
             mbar_init(bar_accempty + 8 * b, kEpilogueThreads / kWarp);
+        }
+        if (kCluster) {
+            mbar_init(bar_redfull, (S - 1) * (kTileRows / S));   // one arrival per sending thread
+            mbar_init(bar_redfree, S - 1);                       // one arrival per peer CTA
         }
         mbar_fence_init();
     }
@@ -188,6 +241,7 @@ linear_packed_kernel(const __grid_constant__ PackedParams p) {
     }
     if (warp == 0) TRACE(1);
     pdl_launch_dependents();
+    if (kCluster) cluster_sync_all();      // every CTA's reduction barriers are initialised
     pdl_wait_prior();
     if (warp == 0) TRACE(2);
 
@@ -226,7 +280,7 @@ linear_packed_kernel(const __grid_constant__ PackedParams p) {
                                             : quantize_block16<kRcpApprox>(lo[u], hi[u], qa, cw);
                     *reinterpret_cast<uint2*>(b_tile_g + (blk >> 4) * (BN * 128) + swz128(m, (blk & 15) * 8)) =
                         make_uint2(cw[0], cw[1]);
-                    b_sf_g[(blk >> 2) * 512 + m * 16 + (blk & 3)] = static_cast<uint8_t>(sf);
+                    b_sf_g[(blk >> 2) * kSfbStride + m * 16 + (blk & 3)] = static_cast<uint8_t>(sf);
                 }
             }
         }
@@ -257,7 +311,7 @@ linear_packed_kernel(const __grid_constant__ PackedParams p) {
             const bool sfb_resident = my_tiles >= 2;
             if (sfb_resident)
                 for (int ch = 0; ch < nkb * 4; ++ch)
-                    tc_cp_scales(tmem + kColSFBres + 4 * ch, desc_scales(b_sf + ch * 512));
+                    tc_cp_scales(tmem + kColSFBres + 4 * ch, desc_scales(b_sf + ch * kSfbStride));
             int i = 0;
             for (int ti = 0; ti < my_tiles && !wf.failed; ++ti) {
                 const int buf = ti & 1;
@@ -280,7 +334,7 @@ linear_packed_kernel(const __grid_constant__ PackedParams p) {
                                          desc_scales(a_smem + kCodesBytes + k * 512));
                             if (!sfb_resident)
                                 tc_cp_scales(tmem + kColSFB + 16 * b + 4 * k,
-                                             desc_scales(b_sf + (blk * 4 + k) * 512));
+                                             desc_scales(b_sf + (blk * 4 + k) * kSfbStride));
                         }
                         const uint32_t sfb_col = sfb_resident ? kColSFBres + 16 * blk : kColSFB + 16 * b;
 #pragma unroll
@@ -329,6 +383,37 @@ linear_packed_kernel(const __grid_constant__ PackedParams p) {
 #pragma unroll
                 for (int m = 0; m < BN; ++m)
                     if (m < p.M) store(m, acc[m]);
+            } else if (kCluster) {
+                // reduce-scatter over the cluster: rows [o*R, (o+1)*R) of the tile belong to
+                // the CTA of rank o; recv[part][token][row - o*R] in the owner's shared memory
+                const int R = kTileRows / S;
+                const int owner = row_in_tile / R, r_local = row_in_tile - owner * R;
+                if (ti >= 1) {                              // peers have read tile ti-1's values
+                    if (!mbar_wait_cluster_bounded(bar_redfree, (ti - 1) & 1)) wf.failed = true;
+                }
+                if (owner != part) {
+                    const uint32_t dst = map_to_rank(recv, owner) +
+                                         static_cast<uint32_t>((part * BN * R + r_local) * 4);
+#pragma unroll
+                    for (int m = 0; m < BN; ++m)
+                        if (m < p.M) st_cluster_f32(dst + m * R * 4, acc[m]);
+                    mbar_arrive_remote(map_to_rank(bar_redfull, owner));
+                } else {
+                    if (!mbar_wait_cluster_bounded(bar_redfull, ti & 1)) wf.failed = true;
+#pragma unroll
+                    for (int m = 0; m < BN; ++m) {
+                        if (m < p.M) {
+                            float v = 0.0f;
+                            for (int s = 0; s < S; ++s)     // part order: deterministic
+                                v += (s == part) ? acc[m] : recv_g[(s * BN + m) * R + r_local];
+                            store(m, v);
+                        }
+                    }
+                }
+                named_barrier(1, kEpilogueThreads);         // this CTA's owners are done reading
+                if (et == 0)
+                    for (int r = 0; r < S; ++r)
+                        if (r != part) mbar_arrive_remote(map_to_rank(bar_redfree, r));
             } else {
                 float* slot = p.partials + (static_cast<int64_t>(tile) * S + part) * (BN * kTileRows);
 #pragma unroll
@@ -367,41 +452,57 @@ linear_packed_kernel(const __grid_constant__ PackedParams p) {
     if (wf.failed && lane == 0) atomicExch(&g_packed_status, 1);
     tc_fence_before();
     __syncthreads();
+    // no CTA leaves while a peer may still write to its shared memory or its barriers
+    if (kCluster) cluster_sync_all();
     if (warp == 1) {
         tc_fence_after();
         tmem_dealloc(tmem, kTmemCols);
     }
 }
 
-struct PackedPlan { int splits, grid, bn; size_t smem; };
+struct PackedPlan { int splits, grid, bn; size_t smem; bool cluster; };
+// Off by default: measured slower than the ticket path on B200 (cluster scheduling
+// granularity and lock-step between the CTAs of a cluster); kept selectable for study.
+int g_packed_use_cluster = 0;
 int g_force_packed_splits = 0;
 int g_packed_ctas_per_sm = 2;
 
 // Parts of at most kMaxPartBlocks K blocks; among the admissible split counts take the
 // one that keeps the most SMs busy (fewer parts on a tie).
 bool plan_packed(int M, int N, int K, PackedPlan* plan) {
-    const int bn_ = M <= 16 ? 16 : 32;
-    const int G = device_sm_count() * ((bn_ == 16 && g_packed_ctas_per_sm == 2) ? 2 : 1);
+    const int bn = M <= 16 ? 16 : 32;
+    const int per_sm = (bn == 16 && g_packed_ctas_per_sm == 2) ? 2 : 1;
+    const int G = device_sm_count() * per_sm;
     const int tiles = N / kTileRows, kblocks = K / kBlockK;
     const int min_s = (kblocks + kMaxPartBlocks - 1) / kMaxPartBlocks;
     if (min_s > G) return false;
+    // Estimated time of a split count, fitted to sweeps on B200: the CTAs make
+    // ceil(units / G) rounds; a round streams one unit (largest K part) at the per-CTA share
+    // of HBM bandwidth and pays about a microsecond for the partial-sum hand-over.
     int best = -1;
-    double best_score = -1.0;
+    double best_score = 1e30;
+    const double kb_per_us = 6400.0 * 1000.0 / 1024.0 / G;      // KB per microsecond per CTA
     for (int s = min_s; s <= kblocks && s <= G && s <= 64; ++s) {
-        const int per_part = G / s;
-        if (per_part < 1) break;
-        const int rounds = (tiles + per_part - 1) / per_part;
-        const double fill = static_cast<double>(tiles) * s / (static_cast<double>(rounds) * G);
-        const double score = fill - 0.004 * (s - min_s);
-        if (score > best_score) { best_score = score; best = s; }
+        const bool clusterable = (s == 2 || s == 4 || s == 8);
+        if (g_packed_use_cluster && min_s <= 8 && s > 1 && !clusterable) continue;
+        const int rounds = (tiles * s + G - 1) / G;
+        const int unit_blocks = (kblocks + s - 1) / s;
+        const double score = rounds * (unit_blocks * 18.0 / kb_per_us + (s > 1 ? 1.0 : 0.3)) + 0.01 * s;
+        if (score < best_score) { best_score = score; best = s; }
     }
     if (g_force_packed_splits >= min_s && g_force_packed_splits <= kblocks && g_force_packed_splits <= G)
         best = g_force_packed_splits;
     if (best < 0) return false;
     plan->splits = best;
-    plan->bn = M <= 16 ? 16 : 32;
-    plan->grid = G;
-    plan->smem = static_cast<size_t>(kStages) * kStageBytes + kMaxPartBlocks * (plan->bn * 128 + 4 * 512) + 1024;
+    plan->bn = bn;
+    plan->cluster = g_packed_use_cluster && (best == 2 || best == 4 || best == 8);
+    // whole clusters only; never more CTAs than there is work
+    int clusters = G / best;
+    if (clusters > tiles) clusters = tiles;
+    plan->grid = plan->cluster ? clusters * best : G;
+    const int sfb_stride = bn == 16 ? 256 : 512;
+    plan->smem = static_cast<size_t>(kStages) * kStageBytes + kMaxPartBlocks * (bn * 128) +
+                 (kMaxPartBlocks * 4 * sfb_stride + 256) + static_cast<size_t>(bn) * kTileRows * 4 + 1024;
     return true;
 }
 
@@ -459,12 +560,14 @@ cudaError_t launch_linear_packed(const PackedLinearArgs& g, cudaStream_t stream,
         p.tickets = static_cast<unsigned*>(g.workspace);
         p.partials = reinterpret_cast<float*>(static_cast<uint8_t*>(g.workspace) + tickets);
 
-        void (*kern)(PackedParams) = plan.bn == 16 ? linear_packed_kernel<16> : linear_packed_kernel<32>;
-        static bool attr_done[2][64] = {};
+        void (*kern)(PackedParams) =
+            plan.bn == 16 ? (plan.cluster ? linear_packed_kernel<16, true> : linear_packed_kernel<16, false>)
+                          : (plan.cluster ? linear_packed_kernel<32, true> : linear_packed_kernel<32, false>);
+        static bool attr_done[4][64] = {};
         int dev = 0;
         cudaError_t e = cudaGetDevice(&dev);
         if (e != cudaSuccess) return e;
-        const int ki = plan.bn == 16 ? 0 : 1;
+        const int ki = (plan.bn == 16 ? 0 : 1) + (plan.cluster ? 2 : 0);
         if (dev >= 0 && dev < 64 && !attr_done[ki][dev]) {
             e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
             if (e != cudaSuccess) return e;
@@ -475,11 +578,22 @@ cudaError_t launch_linear_packed(const PackedLinearArgs& g, cudaStream_t stream,
         cfg.blockDim = dim3(kThreadsP);
         cfg.dynamicSmemBytes = plan.smem;
         cfg.stream = stream;
-        cudaLaunchAttribute attr[1];
-        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-        attr[0].val.programmaticStreamSerializationAllowed = 1;
+        cudaLaunchAttribute attr[2];
+        int na = 0;
+        if (gemv_tuning().use_pdl) {
+            attr[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+            attr[na].val.programmaticStreamSerializationAllowed = 1;
+            ++na;
+        }
+        if (plan.cluster) {
+            attr[na].id = cudaLaunchAttributeClusterDimension;
+            attr[na].val.clusterDim.x = static_cast<unsigned>(plan.splits);
+            attr[na].val.clusterDim.y = 1;
+            attr[na].val.clusterDim.z = 1;
+            ++na;
+        }
         cfg.attrs = attr;
-        cfg.numAttrs = gemv_tuning().use_pdl ? 1 : 0;
+        cfg.numAttrs = na;
         e = cudaLaunchKernelEx(&cfg, kern, p);
         if (e != cudaSuccess) return e;
     }
@@ -489,6 +603,7 @@ cudaError_t launch_linear_packed(const PackedLinearArgs& g, cudaStream_t stream,
 void set_packed_tuning(int splits) {
     g_force_packed_splits = splits & 0xff;
     g_packed_ctas_per_sm = ((splits >> 9) & 1) ? 1 : 2;
+    g_packed_use_cluster = ((splits >> 10) & 1) ? 1 : 0;
     const int trace = (splits >> 8) & 1;
     cudaMemcpyToSymbol(g_packed_trace, &trace, sizeof(int));
 }

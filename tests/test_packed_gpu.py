@@ -141,3 +141,24 @@ def test_packed_rejects_bad_shapes(capi):
     w, ws = onv.random_nvfp4((100,), 256, seed=1)
     with pytest.raises(ValueError):
         capi.pack_weight(cuda(w), cuda(ws))
+
+
+@pytest.mark.parametrize("splits", [2, 4, 8])
+def test_linear_packed_cluster_reduction_variant(capi, splits):
+    """Optional split-K through a thread-block cluster and distributed shared memory
+    (tuning bit 10) gives the same result as the default global-scratch ticket path."""
+    from reset_b200 import _lib
+    N, K, M = 1024, 4096, 5
+    w, ws = onv.random_nvfp4((N,), K, seed=15)
+    xb = make_activation(M, K, seed=16).cuda()
+    gs = torch.tensor([80.0], dtype=torch.float32, device="cuda")
+    packed = capi.pack_weight(cuda(w), cuda(ws))
+    big = torch.zeros(8 << 20, dtype=torch.int64, device="cuda")
+    _lib.check(_lib.lib().nvfp4r_set_packed_tuning(splits), "tuning")
+    ref = capi.linear_packed(xb, gs, packed, N, 1.0, big, out_dtype=torch.float32)
+    _lib.check(_lib.lib().nvfp4r_set_packed_tuning(splits | 1024), "tuning")
+    a = capi.linear_packed(xb, gs, packed, N, 1.0, big, out_dtype=torch.float32)
+    b = capi.linear_packed(xb, gs, packed, N, 1.0, big, out_dtype=torch.float32)
+    torch.cuda.synchronize()
+    assert torch.equal(a, b)
+    assert torch.equal(a, ref)          # same parts added in the same order
