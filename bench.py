@@ -285,6 +285,11 @@ def run_ours(args, rank, world, local_rank):
                 detail[f"{name}_M{M}"] = {"us": round(us, 2), "kernel": path_used[(name, M)],
                                           "gbs": round(linear_bytes(n, k, M) / us / 1e3, 1)}
 
+    # free the linear-set weights before the model benchmark
+    del g_res, g_e2e, shards
+    torch.cuda.empty_cache()
+    decode = None if args.no_decode else run_decode(args, rank, world, device)
+
     if rank != 0:
         if world > 1:
             dist.destroy_process_group()
@@ -318,12 +323,52 @@ def run_ours(args, rank, world, local_rank):
                      "kernel": "linear_packed_kernel / gemv_stream_kernel by measured crossover (16 launches per step)",
                      "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH},
         "detail_us_gbs": detail,
+        "decode": decode,
     }
     if world == 1:
         line["cpu_baseline"] = cpu_baseline(sample_repeats=2)
     if world > 1:
         dist.destroy_process_group()
     return line
+
+
+def run_decode(args, rank, world, device):
+    """Qwen3-32B batch-1 decode step (BASELINE config 3): random-init NVFP4 weights, bf16 KV
+    cache at context 2048, one CUDA graph per token, tensor-parallel over `world` ranks with
+    an NCCL all-reduce after o_proj and down_proj."""
+    import torch.distributed as dist
+
+    from reset_b200.decode import QWEN3_32B, DecodeStep
+
+    model = DecodeStep(QWEN3_32B, device, rank=rank, world=world, seed=11)
+    model.capture()
+    for _ in range(3):
+        model.replay()
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    steps = args.decode_steps
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        model.replay()
+    e1.record()
+    torch.cuda.synchronize()
+    ms = torch.tensor([e0.elapsed_time(e1)], dtype=torch.float64, device=device)
+    if world > 1:
+        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+    ms_tok = float(ms.item()) / steps
+    peak, kind = measured_peak()
+    bytes_rank = model.bytes_per_step()
+    out = {"model": QWEN3_32B.name, "batch": 1, "context": QWEN3_32B.context, "tp": world,
+           "tok_s": round(1e3 / ms_tok, 1), "ms_per_token": round(ms_tok, 4), "steps": steps,
+           "hbm_bytes_per_token_per_gpu": bytes_rank,
+           "roofline_tok_s": round(peak * 1e9 / bytes_rank, 1),
+           "frac_of_hbm_roofline": round((bytes_rank / (ms_tok * 1e-3) / 1e9) / peak, 4),
+           "launch": "one CUDA graph per token", "kernels_per_token": model.kernels_per_step()}
+    del model
+    torch.cuda.empty_cache()
+    return out
 
 
 # ---------------------------------------------------------------------- reference / CPU
@@ -402,6 +447,8 @@ def main():
     ap.add_argument("--steps", type=int, default=600)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-decode", action="store_true", help="skip the Qwen3-32B decode-step measurement")
+    ap.add_argument("--decode-steps", type=int, default=30)
     ap.add_argument("--case", default="", help="profile one pair, e.g. gate_up_proj:1 (eager launches)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup

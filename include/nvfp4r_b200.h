@@ -312,6 +312,35 @@ NVFP4R_API int nvfp4r_set_gemv_tuning(int ctas_per_sm, int use_pdl, int force_ge
  * NVFP4R_ERR_DEVICE_TIMEOUT if a bounded wait inside a kernel gave up. */
 NVFP4R_API int nvfp4r_check_device_status(void);
 
+/* ------------------------------------------------------------------------- *
+ * Batch-1 decode-step operators around the linears (bf16 activations). None of these
+ * has a counterpart in the reference: in its deployment vLLM provides them. They let the
+ * full Qwen3 decode step of the benchmark run from one CUDA graph on this library alone.
+ *   nvfp4r_add_rmsnorm      residual += x (x may be NULL); out = RMSNorm(residual) * weight
+ *   nvfp4r_qk_norm_rope_kv  per-head RMSNorm on q and k, rotary embedding (rotate-half) at
+ *                           *position, k/v written to caches [Hkv, Tmax, D], q to q_out
+ *   nvfp4r_attn_decode      GQA attention of one token over the first *seq_len cache rows
+ *   nvfp4r_silu_mul         out[m,i] = silu(gate_up[m,i]) * gate_up[m,I+i]
+ *   nvfp4r_lm_head          logits[v] = W[v,:] . x, bf16 weight, fp32 logits
+ *   nvfp4r_argmax           first index of the row maximum
+ * D == 128, Hq / Hkv <= 8, H % 256 == 0.
+ * ------------------------------------------------------------------------- */
+NVFP4R_API int nvfp4r_add_rmsnorm(const void* x, void* residual, const void* weight, void* out,
+                                  int M, int H, float eps, void* stream);
+NVFP4R_API int nvfp4r_qk_norm_rope_kv(const void* qkv, const void* q_weight, const void* k_weight,
+                                      const int32_t* position, void* kcache, void* vcache,
+                                      void* q_out, int Hq, int Hkv, int D, int Tmax, float theta,
+                                      float eps, void* stream);
+NVFP4R_API size_t nvfp4r_attn_decode_workspace_bytes(int Hq, int Tmax);
+NVFP4R_API int nvfp4r_attn_decode(const void* q, const void* kcache, const void* vcache,
+                                  const int32_t* seq_len, void* out, int Hq, int Hkv, int D,
+                                  int Tmax, void* workspace, size_t workspace_bytes, void* stream);
+NVFP4R_API int nvfp4r_silu_mul(const void* gate_up, void* out, int M, int I, void* stream);
+NVFP4R_API int nvfp4r_lm_head(const void* x, const void* weight, float* logits, int V, int H,
+                              void* stream);
+NVFP4R_API int nvfp4r_argmax(const float* logits, int64_t row_stride, int B, int V, int32_t* out,
+                             void* stream);
+
 #ifdef __cplusplus
 }
 #endif

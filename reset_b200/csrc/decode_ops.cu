@@ -1,0 +1,400 @@
+// Batch-1 decode-step scaffolding around the NVFP4 linears: the operators a Qwen3 decoder
+// layer needs between two linears (residual add + RMSNorm, per-head q/k RMSNorm + rotary
+// embedding + KV-cache write, GQA decode attention, SiLU*up, bf16 lm_head, arg-max).
+// vLLM supplies these in the reference's deployment; they exist here so that the full
+// decode step of the benchmark runs from one CUDA graph with nothing but this library's
+// kernels and NCCL. bf16 activations, fp32 arithmetic.
+#include <cuda_bf16.h>
+
+#include "../../include/nvfp4r_b200.h"
+#include "kernels.h"
+#include "nvfp4_ptx.cuh"
+
+namespace nvfp4r {
+namespace {
+
+__device__ __forceinline__ float warp_sum_f(float v) {
+#pragma unroll
+    for (int s = 16; s > 0; s >>= 1) v += __shfl_xor_sync(0xffffffffu, v, s);
+    return v;
+}
+__device__ __forceinline__ float warp_max_f(float v) {
+#pragma unroll
+    for (int s = 16; s > 0; s >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, s));
+    return v;
+}
+__device__ __forceinline__ float block_sum_f(float v, float* red) {      // blockDim multiple of 32
+    v = warp_sum_f(v);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+    __syncthreads();
+    if (lane == 0) red[warp] = v;
+    __syncthreads();
+    float t = 0.0f;
+    for (int w = 0; w < nw; ++w) t += red[w];
+    return t;
+}
+
+// residual (+= x) ; out = residual * rsqrt(mean(residual^2) + eps) * weight. One CTA per row.
+__global__ void __launch_bounds__(512)
+add_rmsnorm_kernel(const __nv_bfloat16* __restrict__ x, __nv_bfloat16* __restrict__ residual,
+                   const __nv_bfloat16* __restrict__ weight, __nv_bfloat16* __restrict__ out,
+                   int H, float eps) {
+    __shared__ float red[16];
+    pdl_wait_prior();
+    const int64_t row = blockIdx.x;
+    float ss = 0.0f;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) {
+        float v = __bfloat162float(residual[row * H + i]);
+        if (x != nullptr) {
+            v += __bfloat162float(x[row * H + i]);
+            v = __bfloat162float(__float2bfloat16_rn(v));      // the residual stream is bf16
+            residual[row * H + i] = __float2bfloat16_rn(v);
+        }
+        ss += v * v;
+    }
+    const float inv = rsqrtf(block_sum_f(ss, red) / static_cast<float>(H) + eps);
+    for (int i = threadIdx.x; i < H; i += blockDim.x) {
+        const float v = __bfloat162float(residual[row * H + i]);
+        out[row * H + i] = __float2bfloat16_rn(v * inv * __bfloat162float(weight[i]));
+    }
+    pdl_launch_dependents();
+}
+
+// One warp per head of the fused qkv row: q and k heads get RMSNorm(head) * w and the
+// rotary embedding (rotate-half pairs d, d + D/2); k and v are written to the cache at
+// `*position`; q goes to q_out. D == 128.
+__global__ void __launch_bounds__(128)
+qk_norm_rope_kv_kernel(const __nv_bfloat16* __restrict__ qkv, const __nv_bfloat16* __restrict__ q_w,
+                       const __nv_bfloat16* __restrict__ k_w, const int* __restrict__ position,
+                       __nv_bfloat16* __restrict__ kcache, __nv_bfloat16* __restrict__ vcache,
+                       __nv_bfloat16* __restrict__ q_out, int Hq, int Hkv, int Tmax, float theta,
+                       float eps) {
+    constexpr int D = 128;
+    pdl_wait_prior();
+    const int head = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    const int lane = threadIdx.x & 31;
+    if (head >= Hq + 2 * Hkv) return;
+    const int pos = *position;
+    const __nv_bfloat16* src = qkv + static_cast<int64_t>(head) * D;
+    // lane holds dims lane, lane+32 (first half) and lane+64, lane+96 (second half)
+    float v[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) v[j] = __bfloat162float(src[lane + 32 * j]);
+    if (head >= Hq + Hkv) {                                    // value head: plain copy
+        __nv_bfloat16* dst = vcache + (static_cast<int64_t>(head - Hq - Hkv) * Tmax + pos) * D;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) dst[lane + 32 * j] = __float2bfloat16_rn(v[j]);
+        return;
+    }
+    const bool is_q = head < Hq;
+    const __nv_bfloat16* w = is_q ? q_w : k_w;
+    float ss = v[0] * v[0] + v[1] * v[1] + v[2] * v[2] + v[3] * v[3];
+    const float inv = rsqrtf(warp_sum_f(ss) / static_cast<float>(D) + eps);
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+        v[j] = __bfloat162float(__float2bfloat16_rn(v[j] * inv * __bfloat162float(w[lane + 32 * j])));
+    float o[4];
+#pragma unroll
+    for (int j = 0; j < 2; ++j) {
+        const int d = lane + 32 * j;                           // 0..63
+        const float freq = powf(theta, -static_cast<float>(2 * d) / static_cast<float>(D));
+        float s, c;
+        sincosf(static_cast<float>(pos) * freq, &s, &c);
+        o[j] = v[j] * c - v[j + 2] * s;
+        o[j + 2] = v[j + 2] * c + v[j] * s;
+    }
+    __nv_bfloat16* dst = is_q ? q_out + static_cast<int64_t>(head) * D
+                              : kcache + (static_cast<int64_t>(head - Hq) * Tmax + pos) * D;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) dst[lane + 32 * j] = __float2bfloat16_rn(o[j]);
+    pdl_launch_dependents();
+}
+
+// GQA decode attention, split over the context. CTA (kv head, split): the chunk of K and V
+// is staged in shared memory once and shared by the `group` query heads of that kv head
+// (one warp each). Partial (max, sum, acc[128]) per (q head, split) goes to scratch.
+constexpr int kAttnChunk = 128;                                // positions per CTA
+constexpr int kAttnD = 128;
+constexpr int kAttnPitch = kAttnD * 2 + 16;                    // bytes per staged row (bank skew)
+
+__global__ void __launch_bounds__(256)
+attn_decode_partial_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ kcache,
+                           const __nv_bfloat16* __restrict__ vcache, const int* __restrict__ seq_len,
+                           float* __restrict__ scratch, int Hq, int Hkv, int Tmax, float scale) {
+    extern __shared__ __align__(16) uint8_t sm[];
+    uint8_t* ks = sm;
+    uint8_t* vs = sm + kAttnChunk * kAttnPitch;
+    float* qs = reinterpret_cast<float*>(vs + kAttnChunk * kAttnPitch);       // [group][128]
+    float* ps = qs + 8 * kAttnD;                                               // [group][chunk]
+    pdl_wait_prior();
+    const int kvh = blockIdx.x, split = blockIdx.y, n_splits = gridDim.y;
+    const int group = Hq / Hkv;
+    const int len = *seq_len;
+    const int p0 = split * kAttnChunk;
+    const int np = min(kAttnChunk, len - p0);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int qh = kvh * group + warp;
+    float* my = scratch + (static_cast<int64_t>(qh) * n_splits + split) * (kAttnD + 4);
+    if (np <= 0) {
+        if (warp < group && lane == 0) { my[0] = -INFINITY; my[1] = 0.0f; }
+        return;
+    }
+    for (int i = threadIdx.x; i < np * (kAttnD / 8); i += blockDim.x) {
+        const int r = i / (kAttnD / 8), u = i % (kAttnD / 8);
+        const int64_t g = (static_cast<int64_t>(kvh) * Tmax + p0 + r) * kAttnD + u * 8;
+        *reinterpret_cast<uint4*>(ks + r * kAttnPitch + u * 16) = *reinterpret_cast<const uint4*>(kcache + g);
+        *reinterpret_cast<uint4*>(vs + r * kAttnPitch + u * 16) = *reinterpret_cast<const uint4*>(vcache + g);
+    }
+    if (warp < group)
+        for (int d = lane; d < kAttnD; d += 32)
+            qs[warp * kAttnD + d] = __bfloat162float(q[static_cast<int64_t>(qh) * kAttnD + d]) * scale;
+    __syncthreads();
+    if (warp >= group) return;
+    // scores: lane handles positions lane, lane+32, ...
+    float sc[kAttnChunk / 32];
+    float mx = -INFINITY;
+#pragma unroll
+    for (int j = 0; j < kAttnChunk / 32; ++j) {
+        const int r = lane + 32 * j;
+        float acc = 0.0f;
+        if (r < np) {
+            const uint8_t* row = ks + r * kAttnPitch;
+#pragma unroll 4
+            for (int u = 0; u < kAttnD / 8; ++u) {
+                const uint4 kv = *reinterpret_cast<const uint4*>(row + u * 16);
+                const float4 qa = *reinterpret_cast<const float4*>(qs + warp * kAttnD + u * 8);
+                const float4 qb = *reinterpret_cast<const float4*>(qs + warp * kAttnD + u * 8 + 4);
+                const uint32_t w[4] = {kv.x, kv.y, kv.z, kv.w};
+                acc += __uint_as_float(w[0] << 16) * qa.x + __uint_as_float(w[0] & 0xFFFF0000u) * qa.y;
+                acc += __uint_as_float(w[1] << 16) * qa.z + __uint_as_float(w[1] & 0xFFFF0000u) * qa.w;
+                acc += __uint_as_float(w[2] << 16) * qb.x + __uint_as_float(w[2] & 0xFFFF0000u) * qb.y;
+                acc += __uint_as_float(w[3] << 16) * qb.z + __uint_as_float(w[3] & 0xFFFF0000u) * qb.w;
+            }
+            mx = fmaxf(mx, acc);
+        } else {
+            acc = -INFINITY;
+        }
+        sc[j] = acc;
+    }
+    mx = warp_max_f(mx);
+    float sum = 0.0f;
+#pragma unroll
+    for (int j = 0; j < kAttnChunk / 32; ++j) {
+        const float e = (lane + 32 * j < np) ? __expf(sc[j] - mx) : 0.0f;
+        ps[warp * kAttnChunk + lane + 32 * j] = e;
+        sum += e;
+    }
+    sum = warp_sum_f(sum);
+    __syncwarp();
+    // weighted values: lane handles dims 4*lane .. 4*lane+3
+    float o[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+    for (int r = 0; r < np; ++r) {
+        const float pr = ps[warp * kAttnChunk + r];
+        const uint2 vv = *reinterpret_cast<const uint2*>(vs + r * kAttnPitch + lane * 8);
+        o[0] += pr * __uint_as_float(vv.x << 16);
+        o[1] += pr * __uint_as_float(vv.x & 0xFFFF0000u);
+        o[2] += pr * __uint_as_float(vv.y << 16);
+        o[3] += pr * __uint_as_float(vv.y & 0xFFFF0000u);
+    }
+    if (lane == 0) { my[0] = mx; my[1] = sum; }
+    *reinterpret_cast<float4*>(my + 4 + lane * 4) = make_float4(o[0], o[1], o[2], o[3]);
+    pdl_launch_dependents();
+}
+
+// Merge the per-split partials of one q head (one warp per head).
+__global__ void __launch_bounds__(128)
+attn_decode_combine_kernel(const float* __restrict__ scratch, __nv_bfloat16* __restrict__ out, int Hq,
+                           int n_splits) {
+    pdl_wait_prior();
+    const int qh = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    const int lane = threadIdx.x & 31;
+    if (qh >= Hq) return;
+    const float* base = scratch + static_cast<int64_t>(qh) * n_splits * (kAttnD + 4);
+    float mx = -INFINITY;
+    for (int s = 0; s < n_splits; ++s) mx = fmaxf(mx, base[s * (kAttnD + 4)]);
+    float denom = 0.0f, o[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+    for (int s = 0; s < n_splits; ++s) {
+        const float* p = base + s * (kAttnD + 4);
+        const float w = (p[1] > 0.0f) ? __expf(p[0] - mx) : 0.0f;
+        denom += w * p[1];
+        const float4 a = *reinterpret_cast<const float4*>(p + 4 + lane * 4);
+        o[0] += w * a.x; o[1] += w * a.y; o[2] += w * a.z; o[3] += w * a.w;
+    }
+    const float inv = 1.0f / denom;
+    __nv_bfloat16* dst = out + static_cast<int64_t>(qh) * kAttnD + lane * 4;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) dst[j] = __float2bfloat16_rn(o[j] * inv);
+    pdl_launch_dependents();
+}
+
+// out[m, i] = silu(gate_up[m, i]) * gate_up[m, I + i]
+__global__ void __launch_bounds__(256)
+silu_mul_kernel(const __nv_bfloat16* __restrict__ gate_up, __nv_bfloat16* __restrict__ out, int M, int I) {
+    pdl_wait_prior();
+    const int64_t idx = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (idx >= static_cast<int64_t>(M) * I) return;
+    const int64_t m = idx / I, i = idx % I;
+    const float g = __bfloat162float(gate_up[m * 2 * I + i]);
+    const float u = __bfloat162float(gate_up[m * 2 * I + I + i]);
+    out[idx] = __float2bfloat16_rn(g / (1.0f + __expf(-g)) * u);
+    pdl_launch_dependents();
+}
+
+// logits[v] = sum_h W[v, h] * x[h]; bf16 weight streamed once, one warp per row, x in
+// shared memory as fp32. H % 256 == 0.
+__global__ void __launch_bounds__(256)
+lm_head_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ W,
+               float* __restrict__ logits, int V, int H) {
+    extern __shared__ __align__(16) float xs[];
+    pdl_wait_prior();
+    for (int i = threadIdx.x; i < H; i += blockDim.x) xs[i] = __bfloat162float(x[i]);
+    __syncthreads();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int warps = gridDim.x * (blockDim.x >> 5);
+    for (int v = blockIdx.x * (blockDim.x >> 5) + warp; v < V; v += warps) {
+        const uint4* row = reinterpret_cast<const uint4*>(W + static_cast<int64_t>(v) * H);
+        float acc = 0.0f;
+#pragma unroll 4
+        for (int u = lane; u < H / 8; u += 32) {
+            const uint4 w = ldg_stream_16(row + u);
+            const float4 a = *reinterpret_cast<const float4*>(xs + u * 8);
+            const float4 b = *reinterpret_cast<const float4*>(xs + u * 8 + 4);
+            acc += __uint_as_float(w.x << 16) * a.x + __uint_as_float(w.x & 0xFFFF0000u) * a.y;
+            acc += __uint_as_float(w.y << 16) * a.z + __uint_as_float(w.y & 0xFFFF0000u) * a.w;
+            acc += __uint_as_float(w.z << 16) * b.x + __uint_as_float(w.z & 0xFFFF0000u) * b.y;
+            acc += __uint_as_float(w.w << 16) * b.z + __uint_as_float(w.w & 0xFFFF0000u) * b.w;
+        }
+        acc = warp_sum_f(acc);
+        if (lane == 0) logits[v] = acc;
+    }
+    pdl_launch_dependents();
+}
+
+// Row arg-max (lowest index among equal values), one CTA per row.
+__global__ void __launch_bounds__(1024)
+argmax_kernel(const float* __restrict__ logits, int64_t row_stride, int V, int* __restrict__ out) {
+    __shared__ float smax[32];
+    __shared__ int sarg[32];
+    pdl_wait_prior();
+    const float* row = logits + blockIdx.x * row_stride;
+    float best = -INFINITY;
+    int arg = 0x7fffffff;
+    for (int i = threadIdx.x; i < V; i += blockDim.x) {
+        const float v = row[i];
+        if (v > best) { best = v; arg = i; }
+    }
+#pragma unroll
+    for (int s = 16; s > 0; s >>= 1) {
+        const float ob = __shfl_xor_sync(0xffffffffu, best, s);
+        const int oa = __shfl_xor_sync(0xffffffffu, arg, s);
+        if (ob > best || (ob == best && oa < arg)) { best = ob; arg = oa; }
+    }
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (lane == 0) { smax[warp] = best; sarg[warp] = arg; }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        for (int w = 1; w < (blockDim.x >> 5); ++w)
+            if (smax[w] > best || (smax[w] == best && sarg[w] < arg)) { best = smax[w]; arg = sarg[w]; }
+        out[blockIdx.x] = arg;
+    }
+}
+
+template <typename Kern, typename... Args>
+cudaError_t launch_pdl(Kern kern, dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = gemv_tuning().use_pdl ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kern, args...);
+}
+
+inline cudaStream_t st(void* s) { return static_cast<cudaStream_t>(s); }
+inline int done(cudaError_t e) { return e == cudaSuccess ? NVFP4R_OK : NVFP4R_ERR_CUDA; }
+
+}  // namespace
+}  // namespace nvfp4r
+
+using namespace nvfp4r;
+
+extern "C" {
+
+int nvfp4r_add_rmsnorm(const void* x, void* residual, const void* weight, void* out, int M, int H,
+                       float eps, void* stream) {
+    if (!residual || !weight || !out || M <= 0 || H <= 0) return NVFP4R_ERR_INVALID_ARGUMENT;
+    return done(launch_pdl(add_rmsnorm_kernel, dim3(M), dim3(512), 0, st(stream),
+                           static_cast<const __nv_bfloat16*>(x), static_cast<__nv_bfloat16*>(residual),
+                           static_cast<const __nv_bfloat16*>(weight), static_cast<__nv_bfloat16*>(out), H, eps));
+}
+
+int nvfp4r_qk_norm_rope_kv(const void* qkv, const void* q_weight, const void* k_weight,
+                           const int32_t* position, void* kcache, void* vcache, void* q_out, int Hq,
+                           int Hkv, int D, int Tmax, float theta, float eps, void* stream) {
+    if (!qkv || !q_weight || !k_weight || !position || !kcache || !vcache || !q_out)
+        return NVFP4R_ERR_INVALID_ARGUMENT;
+    if (D != 128) return NVFP4R_ERR_UNSUPPORTED_SHAPE;
+    const int heads = Hq + 2 * Hkv;
+    return done(launch_pdl(qk_norm_rope_kv_kernel, dim3((heads + 3) / 4), dim3(128), 0, st(stream),
+                           static_cast<const __nv_bfloat16*>(qkv), static_cast<const __nv_bfloat16*>(q_weight),
+                           static_cast<const __nv_bfloat16*>(k_weight), position,
+                           static_cast<__nv_bfloat16*>(kcache), static_cast<__nv_bfloat16*>(vcache),
+                           static_cast<__nv_bfloat16*>(q_out), Hq, Hkv, Tmax, theta, eps));
+}
+
+size_t nvfp4r_attn_decode_workspace_bytes(int Hq, int Tmax) {
+    const size_t splits = (static_cast<size_t>(Tmax) + kAttnChunk - 1) / kAttnChunk;
+    return static_cast<size_t>(Hq) * splits * (kAttnD + 4) * sizeof(float);
+}
+
+int nvfp4r_attn_decode(const void* q, const void* kcache, const void* vcache, const int32_t* seq_len,
+                       void* out, int Hq, int Hkv, int D, int Tmax, void* workspace,
+                       size_t workspace_bytes, void* stream) {
+    if (!q || !kcache || !vcache || !seq_len || !out || !workspace) return NVFP4R_ERR_INVALID_ARGUMENT;
+    if (D != 128 || Hkv <= 0 || Hq % Hkv != 0 || Hq / Hkv > 8) return NVFP4R_ERR_UNSUPPORTED_SHAPE;
+    if (workspace_bytes < nvfp4r_attn_decode_workspace_bytes(Hq, Tmax)) return NVFP4R_ERR_INVALID_ARGUMENT;
+    const int splits = (Tmax + kAttnChunk - 1) / kAttnChunk;
+    const size_t smem = 2 * kAttnChunk * kAttnPitch + 8 * kAttnD * 4 + 8 * kAttnChunk * 4;
+    static bool attr_done = false;
+    if (!attr_done) {
+        cudaError_t e = cudaFuncSetAttribute(attn_decode_partial_kernel,
+                                             cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+        if (e != cudaSuccess) return NVFP4R_ERR_CUDA;
+        attr_done = true;
+    }
+    cudaError_t e = launch_pdl(attn_decode_partial_kernel, dim3(Hkv, splits), dim3(256), smem, st(stream),
+                               static_cast<const __nv_bfloat16*>(q), static_cast<const __nv_bfloat16*>(kcache),
+                               static_cast<const __nv_bfloat16*>(vcache), seq_len,
+                               static_cast<float*>(workspace), Hq, Hkv, Tmax, rsqrtf(static_cast<float>(D)));
+    if (e != cudaSuccess) return NVFP4R_ERR_CUDA;
+    return done(launch_pdl(attn_decode_combine_kernel, dim3((Hq + 3) / 4), dim3(128), 0, st(stream),
+                           static_cast<const float*>(workspace), static_cast<__nv_bfloat16*>(out), Hq, splits));
+}
+
+int nvfp4r_silu_mul(const void* gate_up, void* out, int M, int I, void* stream) {
+    if (!gate_up || !out || M <= 0 || I <= 0) return NVFP4R_ERR_INVALID_ARGUMENT;
+    const int64_t total = static_cast<int64_t>(M) * I;
+    return done(launch_pdl(silu_mul_kernel, dim3(static_cast<unsigned>((total + 255) / 256)), dim3(256), 0,
+                           st(stream), static_cast<const __nv_bfloat16*>(gate_up),
+                           static_cast<__nv_bfloat16*>(out), M, I));
+}
+
+int nvfp4r_lm_head(const void* x, const void* weight, float* logits, int V, int H, void* stream) {
+    if (!x || !weight || !logits || V <= 0 || H <= 0) return NVFP4R_ERR_INVALID_ARGUMENT;
+    if (H % 256 != 0 || H > 12288) return NVFP4R_ERR_UNSUPPORTED_SHAPE;
+    const int grid = device_sm_count() * 4;
+    return done(launch_pdl(lm_head_kernel, dim3(grid), dim3(256), static_cast<size_t>(H) * 4, st(stream),
+                           static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(weight),
+                           logits, V, H));
+}
+
+int nvfp4r_argmax(const float* logits, int64_t row_stride, int B, int V, int32_t* out, void* stream) {
+    if (!logits || !out || B <= 0 || V <= 0) return NVFP4R_ERR_INVALID_ARGUMENT;
+    return done(launch_pdl(argmax_kernel, dim3(B), dim3(1024), 0, st(stream), logits, row_stride, V, out));
+}
+
+}  // extern "C"

@@ -14,4 +14,4 @@ FALLBACK_BACKEND = os.environ.get("NVFP4R_FALLBACK_BACKEND", "none").lower()
 # B200 (L2-cold weights, CUDA-graph replay): the GEMV's shorter fixed latency wins only
 # for the smallest batches on weights of at most this many bytes; everything else goes
 # to the tensor cores. Index = M.
-GEMV_MAX_WEIGHT_BYTES = {1: 30_000_000, 2: 10_000_000}
+GEMV_MAX_WEIGHT_BYTES = {1: 16_000_000, 2: 10_000_000}

@@ -1,0 +1,84 @@
+"""No GPU needed: the C-ABI library loads, exports every symbol the public header
+declares, the ctypes table matches the header, and the Python surface of the reference's
+``nvfp4r`` package (enable/disable/configure/status) behaves as the reference's does."""
+
+from __future__ import annotations
+
+import ctypes
+import os
+import re
+from pathlib import Path
+
+REPO = Path(__file__).resolve().parent.parent
+HEADER = REPO / "include" / "nvfp4r_b200.h"
+
+
+def _declared():
+    text = HEADER.read_text()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"NVFP4R_API\s+[\w\s\*]+?\b(nvfp4r_\w+)\s*\(", text)))
+
+
+def test_library_exports_every_declared_symbol():
+    from reset_b200 import _lib
+    names = _declared()
+    assert len(names) >= 25
+    raw = ctypes.CDLL(str(_lib.LIB_PATH))
+    missing = [n for n in names if not hasattr(raw, n)]
+    assert not missing, missing
+    # the ctypes prototypes cover the header and nothing else
+    assert sorted(_lib.PROTOTYPES) == names
+    lib = _lib.lib()
+    assert lib.nvfp4r_version() >= 1
+    assert lib.nvfp4r_status_string(0) == b"ok" and lib.nvfp4r_status_string(-2) == b"unsupported shape"
+
+
+def test_host_side_sizes_without_a_gpu():
+    from reset_b200 import _lib
+    lib = _lib.lib()
+    assert lib.nvfp4r_packed_weight_bytes(4096, 4096) == 4096 * 4096 * 9 // 16
+    assert lib.nvfp4r_packed_weight_bytes(100, 4096) == 0
+    assert lib.nvfp4r_reset_workspace_bytes(8) == 8 * 656
+    assert lib.nvfp4r_attn_decode_workspace_bytes(64, 2048) == 64 * 16 * 132 * 4
+    assert ctypes.sizeof(_lib.ResetState) == 64 * 8 + 16 + 8 + 16
+    # argument checks come before any CUDA call
+    assert lib.nvfp4r_quant(None, 0, 1, 16, None, None, None, 0, 0, None) == -1
+    assert lib.nvfp4r_reset_step_static(None, 0, 1, 8, None, None, None, None, None, None, None, None) == -1
+
+
+def test_enable_disable_configure_status(monkeypatch):
+    monkeypatch.delenv("VLLM_NVFP4_GEMM_BACKEND", raising=False)
+    from reset_b200 import nvfp4r
+    from reset_b200.nvfp4r import _config
+    saved = (_config.GEMV_MAX_M, _config.ENABLE_GEMM_PATH, _config.GEMM_PAD_MAX_M, _config.FALLBACK_BACKEND)
+    try:
+        assert set(nvfp4r.status()) == {"active", "gemv_max_m", "enable_gemm", "gemm_pad_max_m", "fallback_backend"}
+        assert nvfp4r.status()["active"] is False
+        os.environ["VLLM_NVFP4_GEMM_BACKEND"] = "nvfp4r"      # what enable() sets
+        assert nvfp4r.status()["active"] is True
+        nvfp4r.disable()
+        assert "VLLM_NVFP4_GEMM_BACKEND" not in os.environ
+        nvfp4r.configure(gemv_max_m=1, enable_gemm=False, gemm_pad_max_m=31, fallback_backend="CUTLASS")
+        st = nvfp4r.status()
+        assert (st["gemv_max_m"], st["enable_gemm"], st["gemm_pad_max_m"], st["fallback_backend"]) == \
+               (1, False, 31, "cutlass")
+        assert set(nvfp4r.__all__) >= {"gemv", "gemm", "enable", "disable", "configure", "status"}
+    finally:
+        (_config.GEMV_MAX_M, _config.ENABLE_GEMM_PATH, _config.GEMM_PAD_MAX_M, _config.FALLBACK_BACKEND) = saved
+
+
+def test_crossover_rule():
+    from reset_b200.nvfp4r.ops import use_gemv
+    assert use_gemv(1, 4096, 4096, 2) and use_gemv(2, 4096, 4096, 2)
+    assert not use_gemv(1, 24576, 4096, 2) and not use_gemv(4, 4096, 4096, 2)
+    assert not use_gemv(1, 4096, 4096, 0)                     # gemv_max_m = 0 disables the GEMV
+
+
+def test_ops_are_registered_with_the_reference_schemas():
+    import torch
+    from reset_b200 import nvfp4r  # noqa: F401
+    gemv = torch.ops.nvfp4r.gemv.default._schema
+    gemm = torch.ops.nvfp4r.gemm.default._schema
+    assert str(gemv) == ("nvfp4r::gemv(Tensor weight, Tensor weight_scale, Tensor x, Tensor x_scale, "
+                         "Tensor(a!) out, float alpha=1.) -> ()")
+    assert str(gemm) == "nvfp4r::gemm(Tensor A, Tensor B, Tensor SFA, Tensor SFB, Tensor(a!) C, float alpha=1.) -> ()"

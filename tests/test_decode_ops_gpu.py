@@ -1,0 +1,140 @@
+"""The batch-1 decode-step operators around the linears, against plain PyTorch fp32
+references of the same operations (tolerances are bf16 output rounding), and the whole
+step: CUDA-graph replay equals eager execution bit for bit."""
+
+from __future__ import annotations
+
+import math
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def lib():
+    from reset_b200 import _lib
+    return _lib
+
+
+def _s():
+    return torch.cuda.current_stream().cuda_stream
+
+
+def test_add_rmsnorm(lib):
+    H = 5120
+    g = torch.Generator(device="cuda").manual_seed(0)
+    x = torch.randn(1, H, device="cuda", generator=g).to(torch.bfloat16)
+    res = torch.randn(1, H, device="cuda", generator=g).to(torch.bfloat16)
+    w = (1 + 0.1 * torch.randn(H, device="cuda", generator=g)).to(torch.bfloat16)
+    out = torch.empty_like(x)
+    r = res.clone()
+    lib.check(lib.lib().nvfp4r_add_rmsnorm(x.data_ptr(), r.data_ptr(), w.data_ptr(), out.data_ptr(), 1, H,
+                                           1e-6, _s()), "add_rmsnorm")
+    want_res = (res.float() + x.float()).to(torch.bfloat16)
+    assert torch.equal(r, want_res)
+    f = want_res.float()
+    want = f * torch.rsqrt(f.pow(2).mean(-1, keepdim=True) + 1e-6) * w.float()
+    assert torch.allclose(out.float(), want, rtol=2e-2, atol=2e-2)
+    # x == NULL: residual untouched
+    r2 = res.clone()
+    lib.check(lib.lib().nvfp4r_add_rmsnorm(None, r2.data_ptr(), w.data_ptr(), out.data_ptr(), 1, H, 1e-6, _s()), "n")
+    assert torch.equal(r2, res)
+
+
+def _rope_ref(v, pos, theta):
+    D = v.shape[-1]
+    half = D // 2
+    freq = theta ** (-torch.arange(0, half, device=v.device, dtype=torch.float32) * 2 / D)
+    ang = pos * freq
+    c, s = torch.cos(ang), torch.sin(ang)
+    a, b = v[..., :half], v[..., half:]
+    return torch.cat([a * c - b * s, b * c + a * s], dim=-1)
+
+
+def test_qk_norm_rope_kv_and_attention(lib):
+    Hq, Hkv, D, T = 16, 2, 128, 512
+    pos = 300
+    g = torch.Generator(device="cuda").manual_seed(1)
+    qkv = torch.randn(1, (Hq + 2 * Hkv) * D, device="cuda", generator=g).to(torch.bfloat16)
+    qw = (1 + 0.1 * torch.randn(D, device="cuda", generator=g)).to(torch.bfloat16)
+    kw = (1 + 0.1 * torch.randn(D, device="cuda", generator=g)).to(torch.bfloat16)
+    kc = (torch.randn(Hkv, T, D, device="cuda", generator=g) * 0.5).to(torch.bfloat16)
+    vc = (torch.randn(Hkv, T, D, device="cuda", generator=g) * 0.5).to(torch.bfloat16)
+    kc0, vc0 = kc.clone(), vc.clone()
+    position = torch.tensor([pos], dtype=torch.int32, device="cuda")
+    q = torch.empty(1, Hq * D, dtype=torch.bfloat16, device="cuda")
+    lib.check(lib.lib().nvfp4r_qk_norm_rope_kv(qkv.data_ptr(), qw.data_ptr(), kw.data_ptr(), position.data_ptr(),
+                                               kc.data_ptr(), vc.data_ptr(), q.data_ptr(), Hq, Hkv, D, T, 1e6,
+                                               1e-6, _s()), "qk")
+    heads = qkv.float().view(Hq + 2 * Hkv, D)
+
+    def norm(h, w):
+        return (h * torch.rsqrt(h.pow(2).mean(-1, keepdim=True) + 1e-6) * w.float()).to(torch.bfloat16).float()
+    q_ref = _rope_ref(norm(heads[:Hq], qw), pos, 1e6)
+    k_ref = _rope_ref(norm(heads[Hq:Hq + Hkv], kw), pos, 1e6)
+    assert torch.allclose(q.float().view(Hq, D), q_ref, rtol=2e-2, atol=2e-2)
+    assert torch.allclose(kc[:, pos].float(), k_ref, rtol=2e-2, atol=2e-2)
+    assert torch.equal(vc[:, pos], heads[Hq + Hkv:].to(torch.bfloat16))
+    mask = torch.ones(T, dtype=torch.bool, device="cuda")
+    mask[pos] = False
+    assert torch.equal(kc[:, mask], kc0[:, mask]) and torch.equal(vc[:, mask], vc0[:, mask])
+
+    for seq in (pos + 1, 129, 128, 5, T):
+        seq_len = torch.tensor([seq], dtype=torch.int32, device="cuda")
+        n = lib.lib().nvfp4r_attn_decode_workspace_bytes(Hq, T)
+        ws = torch.zeros(n // 4 + 1, dtype=torch.float32, device="cuda")
+        out = torch.empty(1, Hq * D, dtype=torch.bfloat16, device="cuda")
+        lib.check(lib.lib().nvfp4r_attn_decode(q.data_ptr(), kc.data_ptr(), vc.data_ptr(), seq_len.data_ptr(),
+                                               out.data_ptr(), Hq, Hkv, D, T, ws.data_ptr(), ws.numel() * 4, _s()),
+                  "attn")
+        qf = q.float().view(Hkv, Hq // Hkv, D)
+        kf, vf = kc[:, :seq].float(), vc[:, :seq].float()
+        sc = torch.einsum("hgd,htd->hgt", qf, kf) / math.sqrt(D)
+        want = torch.einsum("hgt,htd->hgd", torch.softmax(sc, -1), vf).reshape(1, Hq * D)
+        assert torch.allclose(out.float(), want, rtol=2e-2, atol=1e-2), seq
+
+
+def test_silu_mul_lm_head_argmax(lib):
+    g = torch.Generator(device="cuda").manual_seed(2)
+    I = 3072
+    gu = torch.randn(2, 2 * I, device="cuda", generator=g).to(torch.bfloat16)
+    out = torch.empty(2, I, dtype=torch.bfloat16, device="cuda")
+    lib.check(lib.lib().nvfp4r_silu_mul(gu.data_ptr(), out.data_ptr(), 2, I, _s()), "silu")
+    want = torch.nn.functional.silu(gu[:, :I].float()) * gu[:, I:].float()
+    assert torch.allclose(out.float(), want, rtol=2e-2, atol=2e-2)
+
+    V, H = 5000, 1024
+    x = torch.randn(1, H, device="cuda", generator=g).to(torch.bfloat16)
+    W = (torch.randn(V, H, device="cuda", generator=g) * 0.05).to(torch.bfloat16)
+    logits = torch.empty(1, V, dtype=torch.float32, device="cuda")
+    lib.check(lib.lib().nvfp4r_lm_head(x.data_ptr(), W.data_ptr(), logits.data_ptr(), V, H, _s()), "lm_head")
+    assert torch.allclose(logits, x.float() @ W.float().T, rtol=1e-4, atol=1e-4)
+
+    tok = torch.zeros(1, dtype=torch.int32, device="cuda")
+    lib.check(lib.lib().nvfp4r_argmax(logits.data_ptr(), V, 1, V, tok.data_ptr(), _s()), "argmax")
+    assert int(tok.item()) == int(torch.argmax(logits[0]).item())
+    flat = torch.zeros(2, 64, device="cuda")
+    flat[1, 7] = 1.0
+    flat[1, 9] = 1.0
+    toks = torch.zeros(2, dtype=torch.int32, device="cuda")
+    lib.check(lib.lib().nvfp4r_argmax(flat.data_ptr(), 64, 2, 64, toks.data_ptr(), _s()), "argmax")
+    assert toks.tolist() == [0, 7]                       # first index among equals
+
+
+def test_decode_step_graph_equals_eager():
+    from reset_b200.decode import DecodeConfig, DecodeStep
+    cfg = DecodeConfig("tiny", layers=3, hidden=1024, q_heads=8, kv_heads=2, head_dim=128,
+                       intermediate=2048, vocab=4096, context=256)
+    m = DecodeStep(cfg, "cuda", seed=3)
+    m.step()
+    torch.cuda.synchronize()
+    eager_logits, eager_tok = m.logits_local.clone(), int(m.token.item())
+    assert torch.isfinite(eager_logits).all()
+    m.capture()
+    m.logits_local.zero_()
+    m.replay()
+    torch.cuda.synchronize()
+    assert torch.equal(m.logits_local, eager_logits) and int(m.token.item()) == eager_tok
+    assert m.bytes_per_step() > 0
