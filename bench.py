@@ -147,6 +147,11 @@ def run_ours(args, rank, world, local_rank):
     tp = world
     if world > 1:
         dist.init_process_group("nccl", device_id=device)
+    if args.decode_only:
+        out = run_decode(args, rank, world, device)
+        if world > 1:
+            dist.destroy_process_group()
+        return {"decode": out} if rank == 0 else None
     shards = build_weights(rank, tp, device, nvfp4r)
     host_x = make_inputs(shards, device, seed=7)
     pinned_x = {k: v.pin_memory() for k, v in host_x.items()}
@@ -286,6 +291,8 @@ def run_ours(args, rank, world, local_rank):
                                           "gbs": round(linear_bytes(n, k, M) / us / 1e3, 1)}
 
     # free the linear-set weights before the model benchmark
+    h2d_bytes = sum(M * k * 2 for _, n, k, _, _ in shards for M in M_VALUES)
+    d2h_bytes = sum(M * n * 2 for _, n, k, _, _ in shards for M in M_VALUES)
     del g_res, g_e2e, shards
     torch.cuda.empty_cache()
     decode = None if args.no_decode else run_decode(args, rank, world, device)
@@ -314,8 +321,7 @@ def run_ours(args, rank, world, local_rank):
                    "launch": "CUDA-graph replay, one graph per step",
                    "parallelism": f"tp{world}"},
         "e2e": {"value": round(gbs_e2e, 1), "unit": "GB/s",
-                "h2d_bytes_per_step": sum(M * k * 2 for _, n, k, _, _ in shards for M in M_VALUES),
-                "d2h_bytes_per_step": sum(M * n * 2 for _, n, k, _, _ in shards for M in M_VALUES)},
+                "h2d_bytes_per_step": h2d_bytes, "d2h_bytes_per_step": d2h_bytes},
         "gpu_launches": timed_launches,
         "clocks": clocks,
         "roofline": {"bound": "hbm", "achieved": round(gbs / world, 1), "peak": peak, "unit": "GB/s",
@@ -338,9 +344,20 @@ def run_decode(args, rank, world, device):
     an NCCL all-reduce after o_proj and down_proj."""
     import torch.distributed as dist
 
+    import dataclasses
+
     from reset_b200.decode import QWEN3_32B, DecodeStep
 
-    model = DecodeStep(QWEN3_32B, device, rank=rank, world=world, seed=11)
+    cfg = QWEN3_32B
+    if args.decode_layers:                     # fewer layers of the same geometry: profiler captures
+        cfg = dataclasses.replace(cfg, layers=args.decode_layers, name=f"{cfg.name} ({args.decode_layers} layers)")
+    model = DecodeStep(cfg, device, rank=rank, world=world, seed=11)
+    if args.decode_eager:
+        for _ in range(args.decode_steps):
+            model.step()
+        torch.cuda.synchronize()
+        del model
+        return {"model": cfg.name, "mode": "eager (profiling)", "steps": args.decode_steps}
     model.capture()
     for _ in range(3):
         model.replay()
@@ -360,7 +377,7 @@ def run_decode(args, rank, world, device):
     ms_tok = float(ms.item()) / steps
     peak, kind = measured_peak()
     bytes_rank = model.bytes_per_step()
-    out = {"model": QWEN3_32B.name, "batch": 1, "context": QWEN3_32B.context, "tp": world,
+    out = {"model": cfg.name, "batch": 1, "context": cfg.context, "tp": world,
            "tok_s": round(1e3 / ms_tok, 1), "ms_per_token": round(ms_tok, 4), "steps": steps,
            "hbm_bytes_per_token_per_gpu": bytes_rank,
            "roofline_tok_s": round(peak * 1e9 / bytes_rank, 1),
@@ -449,6 +466,9 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-decode", action="store_true", help="skip the Qwen3-32B decode-step measurement")
     ap.add_argument("--decode-steps", type=int, default=30)
+    ap.add_argument("--decode-only", action="store_true", help="only the decode-step measurement")
+    ap.add_argument("--decode-layers", type=int, default=0, help="override the layer count (profiling)")
+    ap.add_argument("--decode-eager", action="store_true", help="run the decode steps eagerly (profiling)")
     ap.add_argument("--case", default="", help="profile one pair, e.g. gate_up_proj:1 (eager launches)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
