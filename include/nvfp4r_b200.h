@@ -182,6 +182,33 @@ NVFP4R_API int nvfp4r_linear_packed(const void* x, int64_t x_row_stride, int M, 
                                     const float* global_scale_inv, const void* packed, int N,
                                     float alpha, void* out, int out_dtype, int rcp_mode,
                                     void* workspace, size_t workspace_bytes, void* stream);
+/* The same linear with the operator that PRODUCES its input fused into the prologue, so
+ * that the bf16 activation never makes a round trip through HBM and one launch
+ * disappears per fusion. The reference names this as its own end goal
+ * (kernels/python/nvfp4r/__init__.py:3-5) and its adapter notes the neighbouring vLLM ops
+ * (rms_norm, fused_add_rms, silu_and_mul; vllm_integration.py:129-130).
+ *   NVFP4R_PROLOGUE_ADD_RMSNORM  input = RMSNorm(residual_in + delta) * norm_weight, all
+ *       bf16 with bf16 rounding after the add and after the scaling as the separate ops do;
+ *       residual_in + delta is also written to residual_out (must not alias residual_in);
+ *       delta may be NULL; `x` is ignored; K is the hidden size.
+ *   NVFP4R_PROLOGUE_SILU_MUL     input[m,k] = silu(x[m,k]) * x[m,K+k], x = [M, 2K] (gate|up).
+ * `pro` is a HOST pointer, read during the call. */
+typedef enum nvfp4r_prologue_kind {
+    NVFP4R_PROLOGUE_NONE = 0, NVFP4R_PROLOGUE_ADD_RMSNORM = 1, NVFP4R_PROLOGUE_SILU_MUL = 2
+} nvfp4r_prologue_kind;
+typedef struct nvfp4r_prologue {
+    int kind;
+    float eps;
+    const void* delta;
+    const void* residual_in;
+    void* residual_out;
+    const void* norm_weight;
+} nvfp4r_prologue;
+NVFP4R_API int nvfp4r_linear_packed_ex(const nvfp4r_prologue* pro, const void* x, int64_t x_row_stride,
+                                       int M, int K, const float* global_scale_inv, const void* packed,
+                                       int N, float alpha, void* out, int out_dtype, int rcp_mode,
+                                       void* workspace, size_t workspace_bytes, void* stream);
+
 /* Debug/tuning: force the K split of the packed linear (0 = automatic). */
 NVFP4R_API int nvfp4r_set_packed_tuning(int splits);
 

@@ -39,6 +39,13 @@ class ResetDecision(C.Structure):
                 ("temp", C.c_double), ("boundary", C.c_int32), ("high_step", C.c_int32)]
 
 
+class Prologue(C.Structure):
+    _fields_ = [("kind", C.c_int), ("eps", C.c_float), ("delta", C.c_void_p),
+                ("residual_in", C.c_void_p), ("residual_out", C.c_void_p), ("norm_weight", C.c_void_p)]
+
+
+PROLOGUE_NONE, PROLOGUE_ADD_RMSNORM, PROLOGUE_SILU_MUL = 0, 1, 2
+
 _vp, _i, _i64, _f, _sz = C.c_void_p, C.c_int, C.c_int64, C.c_float, C.c_size_t
 
 # name -> (restype, argtypes); every symbol include/nvfp4r_b200.h declares
@@ -57,6 +64,8 @@ PROTOTYPES = {
     "nvfp4r_linear_packed_workspace_bytes": (_sz, [_i, _i, _i]),
     "nvfp4r_pack_weight": (_i, [_vp, _vp, _vp, _i, _i, _vp]),
     "nvfp4r_linear_packed": (_i, [_vp, _i64, _i, _i, _vp, _vp, _i, _f, _vp, _i, _i, _vp, _sz, _vp]),
+    "nvfp4r_linear_packed_ex": (_i, [C.POINTER(Prologue), _vp, _i64, _i, _i, _vp, _vp, _i, _f, _vp, _i, _i,
+                                     _vp, _sz, _vp]),
     "nvfp4r_set_packed_tuning": (_i, [_i]),
     "nvfp4r_gemm": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _f, _i, _i, _vp, _sz, _vp]),
     "nvfp4r_unswizzle_blockscale": (_i, [_vp, _vp, _i, _i, _vp]),

@@ -183,6 +183,48 @@ def linear_packed(x: torch.Tensor, global_scale_inv: torch.Tensor, packed: torch
     return out
 
 
+def linear_packed_rmsnorm(delta, residual_in: torch.Tensor, residual_out: torch.Tensor,
+                          norm_weight: torch.Tensor, eps: float, global_scale_inv: torch.Tensor,
+                          packed: torch.Tensor, N: int, alpha: float, workspace: torch.Tensor,
+                          out_dtype: torch.dtype = torch.bfloat16, rcp_mode: int = L.RCP_APPROX,
+                          out: torch.Tensor | None = None) -> torch.Tensor:
+    """residual_out = residual_in + delta; out = linear(RMSNorm(residual_out) * norm_weight),
+    one launch. All activations bf16 [M, K]."""
+    _need_cuda(residual_in, residual_out, norm_weight, global_scale_inv, packed, workspace, delta)
+    M, K = residual_in.shape
+    if out is None:
+        out = torch.empty((M, N), dtype=out_dtype, device=residual_in.device)
+    pro = L.Prologue(L.PROLOGUE_ADD_RMSNORM, float(eps), None if delta is None else delta.data_ptr(),
+                     residual_in.data_ptr(), residual_out.data_ptr(), norm_weight.data_ptr())
+    with torch.cuda.device(residual_in.device):
+        st = L.lib().nvfp4r_linear_packed_ex(C.byref(pro), None, 0, M, K, global_scale_inv.data_ptr(),
+                                             packed.data_ptr(), N, float(alpha), out.data_ptr(),
+                                             _DTYPE_CODE[out.dtype], rcp_mode, workspace.data_ptr(),
+                                             workspace.numel() * workspace.element_size(), _stream())
+    L.check(st, "nvfp4r_linear_packed_ex")
+    return out
+
+
+def linear_packed_silu(gate_up: torch.Tensor, global_scale_inv: torch.Tensor, packed: torch.Tensor, N: int,
+                       alpha: float, workspace: torch.Tensor, out_dtype: torch.dtype = torch.bfloat16,
+                       rcp_mode: int = L.RCP_APPROX, out: torch.Tensor | None = None) -> torch.Tensor:
+    """out = linear(silu(gate) * up) with gate_up = [M, 2K] bf16, one launch."""
+    _need_cuda(gate_up, global_scale_inv, packed, workspace)
+    M, K2 = gate_up.shape
+    K = K2 // 2
+    if out is None:
+        out = torch.empty((M, N), dtype=out_dtype, device=gate_up.device)
+    pro = L.Prologue(L.PROLOGUE_SILU_MUL, 0.0, None, None, None, None)
+    with torch.cuda.device(gate_up.device):
+        st = L.lib().nvfp4r_linear_packed_ex(C.byref(pro), gate_up.data_ptr(), gate_up.stride(0), M, K,
+                                             global_scale_inv.data_ptr(), packed.data_ptr(), N, float(alpha),
+                                             out.data_ptr(), _DTYPE_CODE[out.dtype], rcp_mode,
+                                             workspace.data_ptr(), workspace.numel() * workspace.element_size(),
+                                             _stream())
+    L.check(st, "nvfp4r_linear_packed_ex")
+    return out
+
+
 def unswizzle_blockscale(swizzled: torch.Tensor, rows: int, K: int) -> torch.Tensor:
     _need_cuda(swizzled)
     sw = _u8(swizzled).contiguous()

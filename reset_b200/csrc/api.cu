@@ -212,15 +212,12 @@ int nvfp4r_linear_tc(const void* x, int64_t x_row_stride, int M, int K, const fl
     return e == cudaSuccess ? NVFP4R_OK : cuda_fail(e, "linear_tc launch");
 }
 
+// Diagnostics, not part of the public header: the %globaltimer time line of CTA 0 of the
+// last four packed-linear launches (enabled by bit 8 of nvfp4r_set_packed_tuning).
 NVFP4R_API int nvfp4r_debug_read_trace(unsigned long long* out16) {
     cudaDeviceSynchronize();
     return nvfp4r::read_packed_trace(out16) == cudaSuccess ? 0 : -4;
 }
-NVFP4R_API int nvfp4r_debug_read_prof(long long* out8) {
-    cudaDeviceSynchronize();
-    return nvfp4r::read_tc_prof(out8) == cudaSuccess ? 0 : -4;
-}
-
 size_t nvfp4r_packed_weight_bytes(int N, int K) {
     if (N <= 0 || K <= 0 || N % 128 || K % 256) return 0;
     return nvfp4r::packed_weight_bytes(N, K);
@@ -268,6 +265,53 @@ int nvfp4r_linear_packed(const void* x, int64_t x_row_stride, int M, int K, cons
     return e == cudaSuccess ? NVFP4R_OK : cuda_fail(e, "linear_packed launch");
 }
 
+int nvfp4r_linear_packed_ex(const nvfp4r_prologue* pro, const void* x, int64_t x_row_stride, int M, int K,
+                            const float* gs, const void* packed, int N, float alpha, void* out,
+                            int out_dtype, int rcp_mode, void* workspace, size_t workspace_bytes,
+                            void* stream) {
+    if (!pro) return fail(NVFP4R_ERR_INVALID_ARGUMENT, "linear_packed_ex: null prologue");
+    if (pro->kind == NVFP4R_PROLOGUE_NONE)
+        return nvfp4r_linear_packed(x, x_row_stride, M, K, gs, packed, N, alpha, out, out_dtype, rcp_mode,
+                                    workspace, workspace_bytes, stream);
+    if (pro->kind != NVFP4R_PROLOGUE_ADD_RMSNORM && pro->kind != NVFP4R_PROLOGUE_SILU_MUL)
+        return fail(NVFP4R_ERR_INVALID_ARGUMENT, "linear_packed_ex: bad prologue kind");
+    if (!gs || !packed || !out) return fail(NVFP4R_ERR_INVALID_ARGUMENT, "linear_packed_ex: null pointer");
+    if (rcp_mode != NVFP4R_RCP_EXACT && rcp_mode != NVFP4R_RCP_APPROX)
+        return fail(NVFP4R_ERR_INVALID_ARGUMENT, "linear_packed_ex: bad rcp_mode");
+    if (M < 0 || N < 0 || K <= 0) return fail(NVFP4R_ERR_INVALID_ARGUMENT, "linear_packed_ex: bad sizes");
+    if (out_dtype < NVFP4R_BF16 || out_dtype > NVFP4R_F32)
+        return fail(NVFP4R_ERR_INVALID_ARGUMENT, "linear_packed_ex: bad out_dtype");
+    if (N % 128 != 0 || K % 256 != 0)
+        return fail(NVFP4R_ERR_UNSUPPORTED_SHAPE, "linear_packed_ex: N % 128 == 0 and K % 256 == 0 required");
+    if (M == 0 || N == 0) return NVFP4R_OK;
+    if (!workspace || workspace_bytes < nvfp4r_linear_packed_workspace_bytes(M, N, K) || !aligned(workspace, 16))
+        return fail(NVFP4R_ERR_INVALID_ARGUMENT, "linear_packed_ex: workspace missing, too small or misaligned");
+    nvfp4r::PackedLinearArgs g = {};
+    g.packed = packed; g.gs = gs; g.rcp_mode = rcp_mode;
+    g.out = out; g.out_dtype = out_dtype; g.M = M; g.N = N; g.K = K; g.alpha = alpha; g.workspace = workspace;
+    g.pro_kind = pro->kind;
+    if (pro->kind == NVFP4R_PROLOGUE_ADD_RMSNORM) {
+        if (!pro->residual_in || !pro->residual_out || !pro->norm_weight)
+            return fail(NVFP4R_ERR_INVALID_ARGUMENT, "linear_packed_ex: RMSNorm prologue needs residual_in/out and norm_weight");
+        if (pro->residual_in == pro->residual_out)
+            return fail(NVFP4R_ERR_INVALID_ARGUMENT, "linear_packed_ex: residual_out must not alias residual_in");
+        if (!aligned(pro->residual_in, 16) || !aligned(pro->residual_out, 16) || !aligned(pro->norm_weight, 16) ||
+            (pro->delta && !aligned(pro->delta, 16)))
+            return fail(NVFP4R_ERR_ALIGNMENT, "linear_packed_ex: prologue tensors need 16-byte alignment");
+        g.delta = pro->delta; g.residual_in = pro->residual_in; g.residual_out = pro->residual_out;
+        g.norm_w = pro->norm_weight; g.eps = pro->eps;
+        g.xb = pro->residual_in; g.xb_stride = K;
+    } else {
+        if (!x || !aligned(x, 16) || (x_row_stride % 8) || x_row_stride < 2 * static_cast<int64_t>(K))
+            return fail(NVFP4R_ERR_INVALID_ARGUMENT, "linear_packed_ex: SiLU prologue needs x = [M, 2K] gate|up, 16-byte aligned");
+        g.xb = x; g.xb_stride = x_row_stride;
+    }
+    const char* why = nullptr;
+    cudaError_t e = nvfp4r::launch_linear_packed(g, as_stream(stream), &why);
+    if (why != nullptr) return fail(NVFP4R_ERR_UNSUPPORTED_SHAPE, why);
+    return e == cudaSuccess ? NVFP4R_OK : cuda_fail(e, "linear_packed_ex launch");
+}
+
 int nvfp4r_set_packed_tuning(int splits) {
     if (splits < 0 || (splits & 0xff) > 64 || splits >= 2048) return fail(NVFP4R_ERR_INVALID_ARGUMENT, "packed tuning: splits 0..64");
     nvfp4r::set_packed_tuning(splits);
@@ -275,7 +319,7 @@ int nvfp4r_set_packed_tuning(int splits) {
 }
 
 int nvfp4r_set_gemm_tuning(int splits, int stages) {
-    if (splits < 0 || splits > 16 || stages < 0 || (stages & 0xff) > 10)
+    if (splits < 0 || splits > 16 || stages < 0 || stages > 10)
         return fail(NVFP4R_ERR_INVALID_ARGUMENT, "gemm tuning: splits 0..16, stages 0..10");
     nvfp4r::set_tc_tuning(splits, stages);
     return NVFP4R_OK;

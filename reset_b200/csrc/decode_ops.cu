@@ -42,20 +42,27 @@ add_rmsnorm_kernel(const __nv_bfloat16* __restrict__ x, __nv_bfloat16* __restric
     __shared__ float red[16];
     pdl_wait_prior();
     const int64_t row = blockIdx.x;
+    constexpr int kMaxPerThread = 32;                          // H <= 512 * 32
+    float keep[kMaxPerThread];
     float ss = 0.0f;
-    for (int i = threadIdx.x; i < H; i += blockDim.x) {
-        float v = __bfloat162float(residual[row * H + i]);
-        if (x != nullptr) {
-            v += __bfloat162float(x[row * H + i]);
-            v = __bfloat162float(__float2bfloat16_rn(v));      // the residual stream is bf16
-            residual[row * H + i] = __float2bfloat16_rn(v);
+#pragma unroll
+    for (int j = 0; j < kMaxPerThread; ++j) {
+        const int i = threadIdx.x + j * 512;
+        if (i < H) {
+            float v = __bfloat162float(residual[row * H + i]);
+            if (x != nullptr) {
+                v = __bfloat162float(__float2bfloat16_rn(v + __bfloat162float(x[row * H + i])));
+                residual[row * H + i] = __float2bfloat16_rn(v);   // the residual stream is bf16
+            }
+            keep[j] = v;
+            ss += v * v;
         }
-        ss += v * v;
     }
     const float inv = rsqrtf(block_sum_f(ss, red) / static_cast<float>(H) + eps);
-    for (int i = threadIdx.x; i < H; i += blockDim.x) {
-        const float v = __bfloat162float(residual[row * H + i]);
-        out[row * H + i] = __float2bfloat16_rn(v * inv * __bfloat162float(weight[i]));
+#pragma unroll
+    for (int j = 0; j < kMaxPerThread; ++j) {
+        const int i = threadIdx.x + j * 512;
+        if (i < H) out[row * H + i] = __float2bfloat16_rn(keep[j] * inv * __bfloat162float(weight[i]));
     }
     pdl_launch_dependents();
 }
@@ -270,19 +277,15 @@ lm_head_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restr
     pdl_launch_dependents();
 }
 
-// Row arg-max (lowest index among equal values), one CTA per row.
-__global__ void __launch_bounds__(1024)
-argmax_kernel(const float* __restrict__ logits, int64_t row_stride, int V, int* __restrict__ out) {
-    __shared__ float smax[32];
-    __shared__ int sarg[32];
-    pdl_wait_prior();
-    const float* row = logits + blockIdx.x * row_stride;
-    float best = -INFINITY;
-    int arg = 0x7fffffff;
-    for (int i = threadIdx.x; i < V; i += blockDim.x) {
-        const float v = row[i];
-        if (v > best) { best = v; arg = i; }
-    }
+// Row arg-max (lowest index among equal values) in two stages: kArgmaxParts CTAs per row
+// each reduce a slice into a (value, index) pair kept in a small static device array, then
+// one CTA per row reduces the pairs.
+constexpr int kArgmaxParts = 64;
+constexpr int kArgmaxMaxRows = 256;
+__device__ float g_argmax_val[kArgmaxMaxRows * kArgmaxParts];
+__device__ int g_argmax_idx[kArgmaxMaxRows * kArgmaxParts];
+
+__device__ __forceinline__ void argmax_block_reduce(float& best, int& arg, float* smax, int* sarg) {
 #pragma unroll
     for (int s = 16; s > 0; s >>= 1) {
         const float ob = __shfl_xor_sync(0xffffffffu, best, s);
@@ -292,11 +295,42 @@ argmax_kernel(const float* __restrict__ logits, int64_t row_stride, int V, int* 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     if (lane == 0) { smax[warp] = best; sarg[warp] = arg; }
     __syncthreads();
-    if (threadIdx.x == 0) {
+    if (threadIdx.x == 0)
         for (int w = 1; w < (blockDim.x >> 5); ++w)
             if (smax[w] > best || (smax[w] == best && sarg[w] < arg)) { best = smax[w]; arg = sarg[w]; }
-        out[blockIdx.x] = arg;
+}
+
+__global__ void __launch_bounds__(256)
+argmax_partial_kernel(const float* __restrict__ logits, int64_t row_stride, int V) {
+    __shared__ float smax[8];
+    __shared__ int sarg[8];
+    pdl_wait_prior();
+    const float* row = logits + blockIdx.y * row_stride;
+    const int per = (V + kArgmaxParts - 1) / kArgmaxParts;
+    const int lo = blockIdx.x * per, hi = min(V, lo + per);
+    float best = -INFINITY;
+    int arg = 0x7fffffff;
+    for (int i = lo + threadIdx.x; i < hi; i += blockDim.x) {
+        const float v = row[i];
+        if (v > best) { best = v; arg = i; }
     }
+    argmax_block_reduce(best, arg, smax, sarg);
+    if (threadIdx.x == 0) {
+        g_argmax_val[blockIdx.y * kArgmaxParts + blockIdx.x] = best;
+        g_argmax_idx[blockIdx.y * kArgmaxParts + blockIdx.x] = arg;
+    }
+    pdl_launch_dependents();
+}
+
+__global__ void __launch_bounds__(64)
+argmax_final_kernel(int* __restrict__ out) {
+    __shared__ float smax[2];
+    __shared__ int sarg[2];
+    pdl_wait_prior();
+    float best = g_argmax_val[blockIdx.x * kArgmaxParts + threadIdx.x];
+    int arg = g_argmax_idx[blockIdx.x * kArgmaxParts + threadIdx.x];
+    argmax_block_reduce(best, arg, smax, sarg);
+    if (threadIdx.x == 0) out[blockIdx.x] = arg;
 }
 
 template <typename Kern, typename... Args>
@@ -327,6 +361,7 @@ extern "C" {
 int nvfp4r_add_rmsnorm(const void* x, void* residual, const void* weight, void* out, int M, int H,
                        float eps, void* stream) {
     if (!residual || !weight || !out || M <= 0 || H <= 0) return NVFP4R_ERR_INVALID_ARGUMENT;
+    if (H > 512 * 32) return NVFP4R_ERR_UNSUPPORTED_SHAPE;
     return done(launch_pdl(add_rmsnorm_kernel, dim3(M), dim3(512), 0, st(stream),
                            static_cast<const __nv_bfloat16*>(x), static_cast<__nv_bfloat16*>(residual),
                            static_cast<const __nv_bfloat16*>(weight), static_cast<__nv_bfloat16*>(out), H, eps));
@@ -394,7 +429,11 @@ int nvfp4r_lm_head(const void* x, const void* weight, float* logits, int V, int 
 
 int nvfp4r_argmax(const float* logits, int64_t row_stride, int B, int V, int32_t* out, void* stream) {
     if (!logits || !out || B <= 0 || V <= 0) return NVFP4R_ERR_INVALID_ARGUMENT;
-    return done(launch_pdl(argmax_kernel, dim3(B), dim3(1024), 0, st(stream), logits, row_stride, V, out));
+    if (B > kArgmaxMaxRows) return NVFP4R_ERR_UNSUPPORTED_SHAPE;
+    cudaError_t e = launch_pdl(argmax_partial_kernel, dim3(kArgmaxParts, B), dim3(256), 0, st(stream), logits,
+                               row_stride, V);
+    if (e != cudaSuccess) return NVFP4R_ERR_CUDA;
+    return done(launch_pdl(argmax_final_kernel, dim3(B), dim3(kArgmaxParts), 0, st(stream), out));
 }
 
 }  // extern "C"

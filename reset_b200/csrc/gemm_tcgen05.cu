@@ -66,13 +66,11 @@ struct alignas(64) TcParams {
     float alpha;
     int tiles, splits, iters;  // N/128, K-parts per tile, K/256
     int stages;
-    int debug;                 // timing experiments only: bit0 no SFB cp, bit1 no SFA cp, bit2 no MMA
     float* partials;           // [tiles][splits][BN][128] fp32
     unsigned* tickets;         // [tiles]
 };
 
 __device__ int g_tc_status = 0;
-__device__ long long g_tc_prof[8];   // timing experiments (debug bit 3), CTA 0 only
 
 using namespace tc;
 
@@ -215,17 +213,11 @@ linear_tc_kernel(const __grid_constant__ TcParams p) {
     if (warp == 0) {
         // ---------------- producer -------------------------------------------------------
         if (lane == 0) {
-            long long t_wait = 0, t_issue = 0;
             for (int i = issued; i < total; ++i) {
                 const int s = i % p.stages;
-                const long long c0 = clock64();
                 if (!wf.wait(bar_empty + 8 * s, ((i / p.stages) - 1) & 1)) break;
-                const long long c1 = clock64();
                 issue(i);
-                const long long c2 = clock64();
-                t_wait += c1 - c0; t_issue += c2 - c1;
             }
-            if ((p.debug & 8) && c == 0) { g_tc_prof[0] = t_wait; g_tc_prof[1] = t_issue; g_tc_prof[6] = total - issued; }
         }
     } else if (warp == 1) {
         // ---------------- MMA issuer -----------------------------------------------------
@@ -233,8 +225,6 @@ linear_tc_kernel(const __grid_constant__ TcParams p) {
             constexpr uint32_t idesc = (1u << 7) | (1u << 10) | (static_cast<uint32_t>(BN >> 3) << 17) |
                                        (static_cast<uint32_t>(kTileRows >> 7) << 27);
             int i = 0;
-            long long t_wait = 0, t_issue = 0;
-            const long long t_begin = clock64();
             for (int ti = 0; ti < my_tiles && !wf.failed; ++ti) {
                 const int buf = ti & 1;
                 if (ti >= 2 && !wf.wait(bar_accempty + 8 * buf, ((ti >> 1) - 1) & 1)) break;
@@ -242,10 +232,7 @@ linear_tc_kernel(const __grid_constant__ TcParams p) {
                 const uint32_t d_tmem = tmem + buf * BN;
                 for (int j = 0; j < n_it; ++j, ++i) {
                     const int s = i % p.stages;
-                    const long long c0 = clock64();
                     if (!wf.wait(bar_full + 8 * s, (i / p.stages) & 1)) break;
-                    const long long c1 = clock64();
-                    t_wait += c1 - c0;
                     tc_fence_after();
                     const uint32_t a_smem = ring + s * kStageBytes;
                     const uint32_t sfa_smem = a_smem + kStageA;
@@ -253,21 +240,19 @@ linear_tc_kernel(const __grid_constant__ TcParams p) {
                     const uint32_t sfb_smem = b_sf + j * 4 * 512;
 #pragma unroll
                     for (int k = 0; k < 4; ++k) {
-                        if (!(p.debug & 2)) tc_cp_scales(tmem + kColSFA + 4 * k, desc_scales(sfa_smem + k * 512));
-                        if (!(p.debug & 1)) tc_cp_scales(tmem + kColSFB + 4 * k, desc_scales(sfb_smem + k * 512));
+                        tc_cp_scales(tmem + kColSFA + 4 * k, desc_scales(sfa_smem + k * 512));
+                        tc_cp_scales(tmem + kColSFB + 4 * k, desc_scales(sfb_smem + k * 512));
                     }
 #pragma unroll
                     for (int k = 0; k < 4; ++k) {
-                        if (!(p.debug & 4)) tc_mma_nvf4(d_tmem, desc_operand(a_smem + k * 32), desc_operand(b_smem + k * 32),
+                        tc_mma_nvf4(d_tmem, desc_operand(a_smem + k * 32), desc_operand(b_smem + k * 32),
                                     idesc, tmem + kColSFA + 4 * k, tmem + kColSFB + 4 * k,
                                     (j > 0 || k > 0) ? 1u : 0u);
                     }
                     tc_commit(bar_empty + 8 * s);
-                    t_issue += clock64() - c1;
                 }
                 tc_commit(bar_accfull + 8 * buf);
             }
-            if ((p.debug & 8) && c == 0) { g_tc_prof[2] = t_wait; g_tc_prof[3] = t_issue; g_tc_prof[4] = clock64() - t_begin; g_tc_prof[5] = total; }
         }
     } else {
         // ---------------- epilogue (warps 2..5) ------------------------------------------
@@ -403,7 +388,7 @@ bool weight_map(const void* w, int N, int K, CUtensorMap* out) {
 }
 
 struct Plan { int splits, stages, grid, bn; size_t smem; };
-int g_force_splits = 0, g_force_stages = 0, g_debug = 0;
+int g_force_splits = 0, g_force_stages = 0;
 
 // Choose the K split: smallest number of parts whose unit count fills the SMs well and
 // whose per-CTA activation footprint leaves room for a deep ring.
@@ -485,7 +470,6 @@ cudaError_t launch_linear_tc(const TcLinearArgs& g, cudaStream_t stream, const c
         p.splits = plan.splits;
         p.iters = g.K / kBK;
         p.stages = plan.stages;
-        p.debug = g_debug;
         const size_t tickets = (static_cast<size_t>(p.tiles) * sizeof(unsigned) + 255) / 256 * 256;
         p.tickets = static_cast<unsigned*>(g.workspace);
         p.partials = reinterpret_cast<float*>(static_cast<uint8_t*>(g.workspace) + tickets);
@@ -518,14 +502,8 @@ cudaError_t launch_linear_tc(const TcLinearArgs& g, cudaStream_t stream, const c
 }
 
 void set_tc_tuning(int splits, int stages) {
-    g_debug = stages >> 8;
-    stages &= 0xff;
     g_force_splits = splits;
     g_force_stages = stages;
-}
-
-cudaError_t read_tc_prof(long long* out8) {
-    return cudaMemcpyFromSymbol(out8, g_tc_prof, 8 * sizeof(long long));
 }
 
 cudaError_t read_and_clear_tc_status(int* flag) {

@@ -74,7 +74,6 @@ size_t gemm_workspace_bytes(int M, int N, int K);
 // kernel handles.
 cudaError_t launch_linear_tc(const TcLinearArgs& g, cudaStream_t stream, const char** why);
 cudaError_t read_and_clear_tc_status(int* flag);
-cudaError_t read_tc_prof(long long* out8);
 // 0 = automatic
 void set_tc_tuning(int splits, int stages);
 
@@ -90,6 +89,13 @@ struct PackedLinearArgs {
     int M, N, K;
     float alpha;
     void* workspace;
+    // fused prologue: 0 none, 1 add + RMSNorm, 2 SiLU * up
+    int pro_kind;
+    const void* delta;
+    const void* residual_in;
+    void* residual_out;
+    const void* norm_w;
+    float eps;
 };
 size_t packed_weight_bytes(int N, int K);
 size_t packed_workspace_bytes(int M, int N, int K);

@@ -60,6 +60,13 @@ struct PackedParams {
     int tiles, splits, kblocks;
     float* partials;
     unsigned* tickets;
+    // fused prologue (what produces the bf16 activations that get quantized)
+    int pro_kind;                  // 0: xb as is; 1: RMSNorm(residual_in + delta) * norm_w; 2: silu(g) * u
+    const void* delta;             // kind 1: bf16 [M, K] or nullptr
+    const void* residual_in;       // kind 1: bf16 [M, K]
+    void* residual_out;            // kind 1: bf16 [M, K], receives residual_in + delta
+    const void* norm_w;            // kind 1: bf16 [K]
+    float eps;
 };
 
 __device__ int g_packed_status = 0;
@@ -93,6 +100,25 @@ pack_weight_kernel(const uint8_t* __restrict__ w, const uint8_t* __restrict__ sf
         *reinterpret_cast<uint32_t*>(dst + kCodesBytes + unit * 512 + (row % 32) * 16 + (row / 32) * 4) = s4;
     }
 }
+
+// ---- bf16 vector helpers for the fused prologues ----------------------------------------
+__device__ __forceinline__ void unpack8(const uint4& v, float f[8]) {
+    const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        f[2 * i] = __uint_as_float(w[i] << 16);
+        f[2 * i + 1] = __uint_as_float(w[i] & 0xFFFF0000u);
+    }
+}
+__device__ __forceinline__ uint32_t pack2_bf16(float a, float b) {
+    const __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+    return *reinterpret_cast<const uint32_t*>(&h);
+}
+__device__ __forceinline__ uint4 pack8(const float f[8]) {
+    return make_uint4(pack2_bf16(f[0], f[1]), pack2_bf16(f[2], f[3]), pack2_bf16(f[4], f[5]),
+                      pack2_bf16(f[6], f[7]));
+}
+__device__ __forceinline__ float round_bf16(float v) { return __bfloat162float(__float2bfloat16_rn(v)); }
 
 // ---- thread-block cluster helpers (split-K reduction through distributed shared memory)
 __device__ __forceinline__ uint32_t cluster_rank() {
@@ -253,36 +279,109 @@ linear_packed_kernel(const __grid_constant__ PackedParams p) {
         const QuantScales qe = make_quant_scales<kRcpExact>(gs);
         const QuantScales qa = make_quant_scales<kRcpApprox>(gs);
         const __nv_bfloat16* xb = static_cast<const __nv_bfloat16*>(p.xb);
-        // four blocks per thread per round: all eight 16-byte loads are issued before any
-        // of the arithmetic, so a round costs one memory round trip
         const int n_items = p.M * blocks;
-        for (int i0 = tid; i0 < n_items; i0 += 4 * kThreadsP) {
-            uint4 lo[4], hi[4];
+        auto quantize_store = [&](int m, int blk, const uint4& lo, const uint4& hi) {
+            uint32_t cw[2];
+            const uint32_t sf = (p.rcp_mode == kRcpExact) ? quantize_block16<kRcpExact>(lo, hi, qe, cw)
+                                                          : quantize_block16<kRcpApprox>(lo, hi, qa, cw);
+            *reinterpret_cast<uint2*>(b_tile_g + (blk >> 4) * (BN * 128) + swz128(m, (blk & 15) * 8)) =
+                make_uint2(cw[0], cw[1]);
+            b_sf_g[(blk >> 2) * kSfbStride + m * 16 + (blk & 3)] = static_cast<uint8_t>(sf);
+        };
+        if (p.pro_kind == 0) {
+            // four blocks per thread per round: all eight 16-byte loads are issued before any
+            // of the arithmetic, so a round costs one memory round trip
+            for (int i0 = tid; i0 < n_items; i0 += 4 * kThreadsP) {
+                uint4 lo[4], hi[4];
 #pragma unroll
-            for (int u = 0; u < 4; ++u) {
-                const int i = i0 + u * kThreadsP;
-                if (i < n_items) {
-                    const int m = i / blocks, blk = i - m * blocks;
-                    const uint4* src = reinterpret_cast<const uint4*>(
-                        xb + (p.m0 + m) * p.xb_stride + static_cast<int64_t>(blk0 + blk) * 16);
-                    lo[u] = __ldg(src);
-                    hi[u] = __ldg(src + 1);
+                for (int u = 0; u < 4; ++u) {
+                    const int i = i0 + u * kThreadsP;
+                    if (i < n_items) {
+                        const int m = i / blocks, blk = i - m * blocks;
+                        const uint4* src = reinterpret_cast<const uint4*>(
+                            xb + (p.m0 + m) * p.xb_stride + static_cast<int64_t>(blk0 + blk) * 16);
+                        lo[u] = __ldg(src);
+                        hi[u] = __ldg(src + 1);
+                    }
+                }
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                    const int i = i0 + u * kThreadsP;
+                    if (i < n_items) quantize_store(i / blocks, i % blocks, lo[u], hi[u]);
                 }
             }
+        } else if (p.pro_kind == 2) {
+            // activation = bf16(silu(gate) * up), gate_up row = [gate (K) | up (K)]
+            for (int i = tid; i < n_items; i += kThreadsP) {
+                const int m = i / blocks, blk = i - m * blocks;
+                const __nv_bfloat16* row = xb + (p.m0 + m) * p.xb_stride + static_cast<int64_t>(blk0 + blk) * 16;
+                const uint4 g0 = __ldg(reinterpret_cast<const uint4*>(row));
+                const uint4 g1 = __ldg(reinterpret_cast<const uint4*>(row) + 1);
+                const uint4 u0 = __ldg(reinterpret_cast<const uint4*>(row + p.K));
+                const uint4 u1 = __ldg(reinterpret_cast<const uint4*>(row + p.K) + 1);
+                float g[16], u[16];
+                unpack8(g0, g); unpack8(g1, g + 8); unpack8(u0, u); unpack8(u1, u + 8);
 #pragma unroll
-            for (int u = 0; u < 4; ++u) {
-                const int i = i0 + u * kThreadsP;
-                if (i < n_items) {
-                    const int m = i / blocks, blk = i - m * blocks;
-                    uint32_t cw[2];
-                    const uint32_t sf = (p.rcp_mode == kRcpExact)
-                                            ? quantize_block16<kRcpExact>(lo[u], hi[u], qe, cw)
-                                            : quantize_block16<kRcpApprox>(lo[u], hi[u], qa, cw);
-                    *reinterpret_cast<uint2*>(b_tile_g + (blk >> 4) * (BN * 128) + swz128(m, (blk & 15) * 8)) =
-                        make_uint2(cw[0], cw[1]);
-                    b_sf_g[(blk >> 2) * kSfbStride + m * 16 + (blk & 3)] = static_cast<uint8_t>(sf);
-                }
+                for (int j = 0; j < 16; ++j) g[j] = g[j] / (1.0f + __expf(-g[j])) * u[j];
+                quantize_store(m, blk, pack8(g), pack8(g + 8));
             }
+        } else {
+            // activation = bf16( bf16(residual + delta) * rsqrt(mean_sq + eps) * norm_w ).
+            // Every CTA needs the row's mean square over the whole K: it is recomputed
+            // here from L2 (2 x 2K bytes per row) instead of being passed between kernels.
+            float* red = reinterpret_cast<float*>(recv_g);            // reduction buffer is free now
+            const __nv_bfloat16* rin = static_cast<const __nv_bfloat16*>(p.residual_in);
+            const __nv_bfloat16* dl = static_cast<const __nv_bfloat16*>(p.delta);
+            const __nv_bfloat16* nw = static_cast<const __nv_bfloat16*>(p.norm_w);
+            __nv_bfloat16* rout = static_cast<__nv_bfloat16*>(p.residual_out);
+            for (int m = 0; m < p.M; ++m) {
+                const int64_t base = static_cast<int64_t>(p.m0 + m) * p.K;
+                float ss = 0.0f;
+                for (int c8 = tid; c8 < p.K / 8; c8 += kThreadsP) {
+                    float r[8], d[8];
+                    unpack8(__ldg(reinterpret_cast<const uint4*>(rin + base) + c8), r);
+                    if (dl != nullptr) {
+                        unpack8(__ldg(reinterpret_cast<const uint4*>(dl + base) + c8), d);
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) r[j] = round_bf16(r[j] + d[j]);
+                    }
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) ss += r[j] * r[j];
+                }
+#pragma unroll
+                for (int sft = 16; sft > 0; sft >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, sft);
+                if (lane == 0) red[m * 8 + warp] = ss;
+            }
+            __syncthreads();
+            const bool writer = (rank_in_part == 0);                  // one CTA per K part writes the residual
+            for (int i = tid; i < n_items; i += kThreadsP) {
+                const int m = i / blocks, blk = i - m * blocks;
+                float tot = 0.0f;
+#pragma unroll
+                for (int w = 0; w < kThreadsP / kWarp; ++w) tot += red[m * 8 + w];
+                const float inv = rsqrtf(tot / static_cast<float>(p.K) + p.eps);
+                const int64_t off = static_cast<int64_t>(p.m0 + m) * p.K + static_cast<int64_t>(blk0 + blk) * 16;
+                float r[16], d[16], w16[16];
+                unpack8(__ldg(reinterpret_cast<const uint4*>(rin + off)), r);
+                unpack8(__ldg(reinterpret_cast<const uint4*>(rin + off) + 1), r + 8);
+                if (dl != nullptr) {
+                    unpack8(__ldg(reinterpret_cast<const uint4*>(dl + off)), d);
+                    unpack8(__ldg(reinterpret_cast<const uint4*>(dl + off) + 1), d + 8);
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) r[j] = round_bf16(r[j] + d[j]);
+                }
+                if (writer) {
+                    *reinterpret_cast<uint4*>(rout + off) = pack8(r);
+                    *(reinterpret_cast<uint4*>(rout + off) + 1) = pack8(r + 8);
+                }
+                const int64_t koff = static_cast<int64_t>(blk0 + blk) * 16;
+                unpack8(__ldg(reinterpret_cast<const uint4*>(nw + koff)), w16);
+                unpack8(__ldg(reinterpret_cast<const uint4*>(nw + koff) + 1), w16 + 8);
+#pragma unroll
+                for (int j = 0; j < 16; ++j) r[j] = r[j] * inv * w16[j];
+                quantize_store(m, blk, pack8(r), pack8(r + 8));
+            }
+            __syncthreads();                                          // red is handed back to the reduction
         }
         // Rows M..BN-1 of the operand are never written: whatever they hold only reaches
         // accumulator columns that are not stored.
@@ -556,6 +655,12 @@ cudaError_t launch_linear_packed(const PackedLinearArgs& g, cudaStream_t stream,
         p.tiles = g.N / kTileRows;
         p.splits = plan.splits;
         p.kblocks = g.K / kBlockK;
+        p.pro_kind = g.pro_kind;
+        p.delta = g.delta;
+        p.residual_in = g.residual_in;
+        p.residual_out = g.residual_out;
+        p.norm_w = g.norm_w;
+        p.eps = g.eps;
         const size_t tickets = (static_cast<size_t>(p.tiles) * sizeof(unsigned) + 255) / 256 * 256;
         p.tickets = static_cast<unsigned*>(g.workspace);
         p.partials = reinterpret_cast<float*>(static_cast<uint8_t*>(g.workspace) + tickets);

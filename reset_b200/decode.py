@@ -40,40 +40,69 @@ QWEN3_8B = DecodeConfig("Qwen3-8B", 36, 4096, 32, 8, 128, 12288, 151936)
 
 class _Linear:
     """One NVFP4 linear shard: packed weight for the tensor-core kernel, flat weight for the
-    CUDA-core GEMV where the measured crossover can choose it."""
+    CUDA-core GEMV where the measured crossover can choose it. Calls go through the C ABI with
+    caller-owned output buffers (nothing is allocated inside a step)."""
 
-    def __init__(self, N: int, K: int, device, gen, max_m: int = 1):
-        self.N, self.K = N, K
+    def __init__(self, N: int, K: int, device, gen, workspace: "Workspace"):
+        self.N, self.K, self.ws = N, K, workspace
         w = torch.randint(0, 256, (N, K // 2), dtype=torch.uint8, device=device, generator=gen)
         s = torch.randint(0x20, 0x38, (N, K // 16), dtype=torch.uint8, device=device, generator=gen)
         self.packed = capi.pack_weight(w, s) if (N % 128 == 0 and K % 256 == 0) else None
-        keep_flat = self.packed is None or any(nvops.use_gemv(m, N, K, 2) for m in range(1, max_m + 1))
-        self.w, self.s = (w, s) if keep_flat else (None, None)
+        self.use_gemv = self.packed is None or nvops.use_gemv(1, N, K, 2)
+        self.w, self.s = (w, s) if self.use_gemv else (None, None)
         self.gs_inv = torch.tensor([64.0], dtype=torch.float32, device=device)
         self.alpha = 1.0
+        if self.packed is not None:
+            workspace.reserve(L.lib().nvfp4r_linear_packed_workspace_bytes(1, N, K))
 
     def calibrate(self, x: torch.Tensor) -> None:
         """Pick alpha so that the output has unit RMS on a sample input (keeps the random
         model's activations finite; done once, outside any timed region)."""
-        y = self(x).float()
-        rms = float(y.pow(2).mean().sqrt().item())
+        out = torch.empty((x.shape[0], self.N), dtype=torch.bfloat16, device=x.device)
+        self.plain(x, out)
+        rms = float(out.float().pow(2).mean().sqrt().item())
         if rms > 0 and rms == rms:
             self.alpha = 1.0 / rms
 
-    def __call__(self, x: torch.Tensor) -> torch.Tensor:
-        return nvops.linear_auto(x, self.gs_inv, self.w, self.s, self.packed, self.N, self.alpha,
-                                 torch.bfloat16, L.RCP_APPROX)
+    def plain(self, x: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+        if self.use_gemv:
+            return capi.linear(x, self.gs_inv, self.w, self.s, self.alpha, out=out, rcp_mode=L.RCP_APPROX)
+        return capi.linear_packed(x, self.gs_inv, self.packed, self.N, self.alpha, self.ws.buf,
+                                  rcp_mode=L.RCP_APPROX, out=out)
+
+    def after_rmsnorm(self, delta, res_in, res_out, norm_w, eps, out):
+        return capi.linear_packed_rmsnorm(delta, res_in, res_out, norm_w, eps, self.gs_inv, self.packed,
+                                          self.N, self.alpha, self.ws.buf, rcp_mode=L.RCP_APPROX, out=out)
+
+    def after_silu_mul(self, gate_up, out):
+        return capi.linear_packed_silu(gate_up, self.gs_inv, self.packed, self.N, self.alpha, self.ws.buf,
+                                       rcp_mode=L.RCP_APPROX, out=out)
 
     def weight_bytes(self) -> int:
         return self.N * self.K * 9 // 16
 
 
+class Workspace:
+    """One zero-initialised split-K scratch shared by all linears of a step (their launches
+    are ordered on one stream)."""
+
+    def __init__(self, device):
+        self.device, self.bytes, self.buf = device, 0, None
+
+    def reserve(self, n: int) -> None:
+        self.bytes = max(self.bytes, int(n))
+
+    def allocate(self) -> None:
+        self.buf = torch.zeros((self.bytes + 15) // 16 * 2 + 2, dtype=torch.int64, device=self.device)
+
+
 class DecodeStep:
     def __init__(self, cfg: DecodeConfig, device, rank: int = 0, world: int = 1, seed: int = 0,
-                 process_group=None):
+                 process_group=None, fused: bool = True):
         if cfg.q_heads % world or cfg.kv_heads % world or cfg.intermediate % world or cfg.vocab % world:
             raise ValueError("tensor-parallel degree must divide heads, intermediate and vocab")
         self.cfg, self.device, self.rank, self.world, self.pg = cfg, torch.device(device), rank, world, process_group
+        self.ws = Workspace(self.device)
         gen = torch.Generator(device=self.device).manual_seed(seed + 1000 * rank)
         D, H = cfg.head_dim, cfg.hidden
         self.hq, self.hkv = cfg.q_heads // world, cfg.kv_heads // world
@@ -82,10 +111,10 @@ class DecodeStep:
         self.layers = []
         for _ in range(cfg.layers):
             self.layers.append({
-                "qkv": _Linear((self.hq + 2 * self.hkv) * D, H, self.device, gen),
-                "o": _Linear(H, self.hq * D, self.device, gen),
-                "gate_up": _Linear(2 * inter, H, self.device, gen),
-                "down": _Linear(H, inter, self.device, gen),
+                "qkv": _Linear((self.hq + 2 * self.hkv) * D, H, self.device, gen, self.ws),
+                "o": _Linear(H, self.hq * D, self.device, gen, self.ws),
+                "gate_up": _Linear(2 * inter, H, self.device, gen, self.ws),
+                "down": _Linear(H, inter, self.device, gen, self.ws),
                 "ln1": torch.ones(H, **bf), "ln2": torch.ones(H, **bf),
                 "qn": torch.ones(D, **bf), "kn": torch.ones(D, **bf),
                 "k": (torch.randn(self.hkv, cfg.context, D, device=self.device, generator=gen) * 0.5).to(torch.bfloat16),
@@ -99,8 +128,16 @@ class DecodeStep:
         self.position = torch.tensor([cfg.context - 1], dtype=torch.int32, device=self.device)
         self.seq_len = torch.tensor([cfg.context], dtype=torch.int32, device=self.device)
         self.token = torch.zeros(1, dtype=torch.int32, device=self.device)
-        self.residual = torch.zeros(1, H, **bf)
+        self.ws.allocate()
+        self.res = [torch.zeros(1, H, **bf), torch.zeros(1, H, **bf)]     # ping-pong residual stream
+        self.residual = self.res[0]
         self.normed = torch.zeros(1, H, **bf)
+        self.qkv_out = torch.zeros(1, (self.hq + 2 * self.hkv) * D, **bf)
+        self.o_out = torch.zeros(1, H, **bf)
+        self.gu_out = torch.zeros(1, 2 * inter, **bf)
+        self.down_out = torch.zeros(1, H, **bf)
+        probe = self.layers[0]
+        self.fused = bool(fused) and all(probe[n].packed is not None for n in ("qkv", "gate_up", "down"))
         self.q = torch.zeros(1, self.hq * D, **bf)
         self.attn = torch.zeros(1, self.hq * D, **bf)
         self.act = torch.zeros(1, inter, **bf)
@@ -115,8 +152,8 @@ class DecodeStep:
     def _stream(self) -> int:
         return torch.cuda.current_stream().cuda_stream
 
-    def _add_rmsnorm(self, x, weight):
-        L.check(L.lib().nvfp4r_add_rmsnorm(None if x is None else x.data_ptr(), self.residual.data_ptr(),
+    def _add_rmsnorm(self, x, residual, weight):
+        L.check(L.lib().nvfp4r_add_rmsnorm(None if x is None else x.data_ptr(), residual.data_ptr(),
                                            weight.data_ptr(), self.normed.data_ptr(), 1, self.cfg.hidden,
                                            self.cfg.eps, self._stream()), "add_rmsnorm")
 
@@ -139,24 +176,38 @@ class DecodeStep:
 
     # -- the step ---------------------------------------------------------------------
     def step(self) -> None:
-        """One token: embedding row -> all layers -> logits -> arg-max into ``self.token``."""
+        """One token: embedding row -> all layers -> logits -> arg-max into ``self.token``.
+        With ``fused`` the two RMSNorms and the SiLU*up of a layer run inside the prologue of
+        the linear that consumes them (7 launches per layer instead of 10)."""
         c = self.cfg
         lib = L.lib()
-        self.residual.copy_(self.embed[:1])
-        x = None
+        cur = 0
+        self.res[0].copy_(self.embed[:1])
+        x = None                                            # output of the previous row-parallel linear
         for layer in self.layers:
-            self._add_rmsnorm(x, layer["ln1"])
-            qkv = layer["qkv"](self.normed)
-            self._attention(layer, qkv)
-            x = layer["o"](self.attn)
-            self._all_reduce(x)
-            self._add_rmsnorm(x, layer["ln2"])
-            gu = layer["gate_up"](self.normed)
-            L.check(lib.nvfp4r_silu_mul(gu.data_ptr(), self.act.data_ptr(), 1, self.act.shape[1], self._stream()),
-                    "silu_mul")
-            x = layer["down"](self.act)
-            self._all_reduce(x)
-        self._add_rmsnorm(x, self.final_ln)
+            if self.fused:
+                layer["qkv"].after_rmsnorm(x, self.res[cur], self.res[1 - cur], layer["ln1"], c.eps, self.qkv_out)
+                cur = 1 - cur
+            else:
+                self._add_rmsnorm(x, self.res[cur], layer["ln1"])
+                layer["qkv"].plain(self.normed, self.qkv_out)
+            self._attention(layer, self.qkv_out)
+            layer["o"].plain(self.attn, self.o_out)
+            self._all_reduce(self.o_out)
+            if self.fused:
+                layer["gate_up"].after_rmsnorm(self.o_out, self.res[cur], self.res[1 - cur], layer["ln2"], c.eps,
+                                               self.gu_out)
+                cur = 1 - cur
+                layer["down"].after_silu_mul(self.gu_out, self.down_out)
+            else:
+                self._add_rmsnorm(self.o_out, self.res[cur], layer["ln2"])
+                layer["gate_up"].plain(self.normed, self.gu_out)
+                L.check(lib.nvfp4r_silu_mul(self.gu_out.data_ptr(), self.act.data_ptr(), 1, self.act.shape[1],
+                                            self._stream()), "silu_mul")
+                layer["down"].plain(self.act, self.down_out)
+            self._all_reduce(self.down_out)
+            x = self.down_out
+        self._add_rmsnorm(x, self.res[cur], self.final_ln)
         L.check(lib.nvfp4r_lm_head(self.normed.data_ptr(), self.lm_head.data_ptr(), self.logits_local.data_ptr(),
                                    self.vocab_local, c.hidden, self._stream()), "lm_head")
         if self.world > 1:
@@ -203,4 +254,4 @@ class DecodeStep:
         return lin + kv + self.vocab_local * c.hidden * 2
 
     def kernels_per_step(self) -> int:
-        return self.cfg.layers * 10 + 4
+        return self.cfg.layers * (7 if self.fused else 10) + 5

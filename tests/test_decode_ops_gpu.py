@@ -137,4 +137,10 @@ def test_decode_step_graph_equals_eager():
     m.replay()
     torch.cuda.synchronize()
     assert torch.equal(m.logits_local, eager_logits) and int(m.token.item()) == eager_tok
-    assert m.bytes_per_step() > 0
+    assert m.bytes_per_step() > 0 and m.fused
+    # the unfused step (separate RMSNorm / SiLU kernels) computes the same model
+    u = DecodeStep(cfg, "cuda", seed=3, fused=False)
+    u.step()
+    torch.cuda.synchronize()
+    a, b = eager_logits.float(), u.logits_local.float()
+    assert (a - b).norm() / b.norm() < 5e-2

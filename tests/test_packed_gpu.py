@@ -162,3 +162,76 @@ def test_linear_packed_cluster_reduction_variant(capi, splits):
     torch.cuda.synchronize()
     assert torch.equal(a, b)
     assert torch.equal(a, ref)          # same parts added in the same order
+
+
+@pytest.mark.parametrize("M,with_delta", [(1, True), (1, False), (5, True)])
+def test_fused_add_rmsnorm_prologue(capi, M, with_delta):
+    """linear(RMSNorm(residual + delta) * w) in one launch vs the separate operators: the
+    residual stream is bit-identical; the linear output agrees up to the bf16 roundings
+    that a different summation order of the mean square can flip (a handful of codes)."""
+    from reset_b200 import _lib
+    N, K = 1536, 5120
+    w, ws = onv.random_nvfp4((N,), K, seed=21)
+    packed = capi.pack_weight(cuda(w), cuda(ws))
+    g = torch.Generator(device="cuda").manual_seed(22)
+    res = torch.randn(M, K, device="cuda", generator=g).to(torch.bfloat16)
+    delta = torch.randn(M, K, device="cuda", generator=g).to(torch.bfloat16) if with_delta else None
+    nw = (1 + 0.1 * torch.randn(K, device="cuda", generator=g)).to(torch.bfloat16)
+    gs = torch.tensor([40.0], dtype=torch.float32, device="cuda")
+    wksp = capi.packed_workspace(M, N, K, "cuda")
+    res_out = torch.zeros_like(res)
+    fused = capi.linear_packed_rmsnorm(delta, res, res_out, nw, 1e-6, gs, packed, N, 0.5, wksp,
+                                       out_dtype=torch.float32, rcp_mode=_lib.RCP_EXACT)
+    torch.cuda.synchronize()
+    want_res = (res.float() + delta.float()).to(torch.bfloat16) if with_delta else res
+    assert torch.equal(res_out, want_res)
+    f = want_res.float()
+    normed = (f * torch.rsqrt(f.pow(2).mean(-1, keepdim=True) + 1e-6) * nw.float()).to(torch.bfloat16)
+    xc, xsf = onv.quantize_nvfp4(normed.float().cpu().numpy(), 40.0)
+    exact = onv.linear_f64(w, ws, xc, xsf, alpha=0.5)
+    assert rel_l2(fused.cpu().numpy(), exact) <= 5e-3
+    # and against the unfused kernels of this library
+    normed2 = torch.empty_like(res)
+    r2 = res.clone()
+    lib = _lib.lib()
+    _lib.check(lib.nvfp4r_add_rmsnorm(None if delta is None else delta.data_ptr(), r2.data_ptr(), nw.data_ptr(),
+                                      normed2.data_ptr(), M, K, 1e-6, torch.cuda.current_stream().cuda_stream), "n")
+    unfused = capi.linear_packed(normed2, gs, packed, N, 0.5, wksp, out_dtype=torch.float32)
+    torch.cuda.synchronize()
+    assert torch.equal(r2, res_out)
+    assert rel_l2(fused.cpu().numpy(), unfused.cpu().numpy()) <= 5e-3
+
+
+@pytest.mark.parametrize("M", [1, 4])
+def test_fused_silu_mul_prologue(capi, M):
+    from reset_b200 import _lib
+    N, K = 1024, 3072
+    w, ws = onv.random_nvfp4((N,), K, seed=23)
+    packed = capi.pack_weight(cuda(w), cuda(ws))
+    g = torch.Generator(device="cuda").manual_seed(24)
+    gu = torch.randn(M, 2 * K, device="cuda", generator=g).to(torch.bfloat16)
+    gs = torch.tensor([30.0], dtype=torch.float32, device="cuda")
+    wksp = capi.packed_workspace(M, N, K, "cuda")
+    fused = capi.linear_packed_silu(gu, gs, packed, N, 1.0, wksp, out_dtype=torch.float32,
+                                    rcp_mode=_lib.RCP_EXACT)
+    act = torch.empty(M, K, dtype=torch.bfloat16, device="cuda")
+    _lib.check(_lib.lib().nvfp4r_silu_mul(gu.data_ptr(), act.data_ptr(), M, K,
+                                          torch.cuda.current_stream().cuda_stream), "silu")
+    unfused = capi.linear_packed(act, gs, packed, N, 1.0, wksp, out_dtype=torch.float32)
+    torch.cuda.synchronize()
+    assert torch.equal(fused, unfused)          # same arithmetic, same roundings
+    ref_act = (torch.nn.functional.silu(gu[:, :K].float()) * gu[:, K:].float()).to(torch.bfloat16)
+    xc, xsf = onv.quantize_nvfp4(ref_act.float().cpu().numpy(), 30.0)
+    assert rel_l2(fused.cpu().numpy(), onv.linear_f64(w, ws, xc, xsf)) <= 5e-3
+
+
+def test_fused_prologue_argument_checks(capi):
+    from reset_b200 import _lib
+    w, ws = onv.random_nvfp4((128,), 256, seed=1)
+    packed = capi.pack_weight(cuda(w), cuda(ws))
+    res = torch.zeros(1, 256, dtype=torch.bfloat16, device="cuda")
+    nw = torch.ones(256, dtype=torch.bfloat16, device="cuda")
+    gs = torch.tensor([1.0], dtype=torch.float32, device="cuda")
+    wk = capi.packed_workspace(1, 128, 256, "cuda")
+    with pytest.raises(_lib.Nvfp4rError):
+        capi.linear_packed_rmsnorm(None, res, res, nw, 1e-6, gs, packed, 128, 1.0, wk)   # aliasing
