@@ -137,6 +137,14 @@ def make_inputs(shards, device, seed):
     return xs
 
 
+_T0 = time.perf_counter()
+
+
+def stage(rank: int, what: str) -> None:
+    """Progress line on stderr (the JSON line on stdout stays alone)."""
+    print(f"[bench rank {rank} +{time.perf_counter() - _T0:.1f}s] {what}", file=sys.stderr, flush=True)
+
+
 def run_ours(args, rank, world, local_rank):
     import torch.distributed as dist
 
@@ -149,10 +157,10 @@ def run_ours(args, rank, world, local_rank):
         dist.init_process_group("nccl", device_id=device)
     if args.decode_only:
         out = run_decode(args, rank, world, device)
-        if world > 1:
-            dist.destroy_process_group()
         return {"decode": out} if rank == 0 else None
+    stage(rank, "process group up" if world > 1 else "device ready")
     shards = build_weights(rank, tp, device, nvfp4r)
+    stage(rank, "weights built")
     host_x = make_inputs(shards, device, seed=7)
     pinned_x = {k: v.pin_memory() for k, v in host_x.items()}
     dev_x = {k: v.to(device) for k, v in host_x.items()}
@@ -247,6 +255,7 @@ def run_ours(args, rank, world, local_rank):
 
     sampler = ClockSampler(local_rank) if rank == 0 else None
     g_res = capture_phases(step_resident)
+    stage(rank, "resident graphs captured")
     # keep the GPU busy long enough before the timed region for clock samples to exist
     t_end = time.perf_counter() + 0.4
     while time.perf_counter() < t_end:
@@ -255,9 +264,11 @@ def run_ours(args, rank, world, local_rank):
         torch.cuda.synchronize()
     ms_total = timed(g_res, args.steps, args.warmup)
     timed_launches = args.steps * 16
+    stage(rank, "resident timed")
     g_e2e = capture_phases(step_e2e)
     ms_e2e = timed(g_e2e, args.steps, max(3, args.warmup))
     clocks = sampler.stop() if sampler else None
+    stage(rank, "e2e timed")
 
     # per-(linear, M) latency table: each pair alone, CUDA-graph replay of two passes over
     # its weight copies (so every launch still reads a cold weight)
@@ -296,10 +307,9 @@ def run_ours(args, rank, world, local_rank):
     del g_res, g_e2e, shards
     torch.cuda.empty_cache()
     decode = None if args.no_decode else run_decode(args, rank, world, device)
+    stage(rank, "decode done")
 
     if rank != 0:
-        if world > 1:
-            dist.destroy_process_group()
         return None
     peak, peak_kind = measured_peak()
     bytes_step = step_bytes()
@@ -333,8 +343,6 @@ def run_ours(args, rank, world, local_rank):
     }
     if world == 1:
         line["cpu_baseline"] = cpu_baseline(sample_repeats=2)
-    if world > 1:
-        dist.destroy_process_group()
     return line
 
 
@@ -470,7 +478,12 @@ def main():
     ap.add_argument("--decode-layers", type=int, default=0, help="override the layer count (profiling)")
     ap.add_argument("--decode-eager", action="store_true", help="run the decode steps eagerly (profiling)")
     ap.add_argument("--case", default="", help="profile one pair, e.g. gate_up_proj:1 (eager launches)")
+    ap.add_argument("--watchdog", type=int, default=1200,
+                    help="seconds after which every rank dumps its Python stacks to stderr and exits")
     args = ap.parse_args()
+    if args.watchdog > 0:
+        import faulthandler
+        faulthandler.dump_traceback_later(args.watchdog, exit=True)
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -483,6 +496,17 @@ def main():
         line = run_ours(args, rank, world, local_rank)
     if line is not None:
         print(json.dumps(line), flush=True)
+    if world > 1 and args.impl == "ours":
+        # Leave without tearing the communicator down: NCCL's destroy waits for every CUDA
+        # graph that captured a collective, and graph objects die in interpreter-defined
+        # order. All ranks meet once more, then exit.
+        import torch.distributed as dist
+        torch.cuda.synchronize()
+        dist.barrier()
+        torch.cuda.synchronize()
+        sys.stdout.flush()
+        sys.stderr.flush()
+        os._exit(0)
 
 
 if __name__ == "__main__":
