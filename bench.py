@@ -396,6 +396,189 @@ def run_decode(args, rank, world, device):
     return out
 
 
+
+# ------------------------------------------------------- secondary measurements
+
+def _graph_us(fn, reps: int, device, samples: int = 7) -> float:
+    """Median microseconds per call of `fn`, `reps` calls per CUDA-graph replay."""
+    side = torch.cuda.Stream(device=device)
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        for _ in range(reps):
+            fn()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=side):
+            for _ in range(reps):
+                fn()
+    torch.cuda.current_stream().wait_stream(side)
+    g.replay()
+    torch.cuda.synchronize()
+    ts = []
+    for _ in range(samples):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        g.replay()
+        e1.record()
+        torch.cuda.synchronize()
+        ts.append(e0.elapsed_time(e1) / reps * 1e3)
+    return sorted(ts)[len(ts) // 2]
+
+
+SWEEP_SHAPES = {
+    "qwen3-14b": [("qkv_proj", 7168, 5120), ("o_proj", 5120, 5120), ("gate_up_proj", 34816, 5120),
+                  ("down_proj", 5120, 17408)],
+    "qwen3-8b": [(n, N, K) for n, N, K, _ in LINEARS],
+    "qwen3-32b": [("qkv_proj", 10240, 5120), ("o_proj", 5120, 8192), ("gate_up_proj", 51200, 5120),
+                  ("down_proj", 5120, 25600)],
+}
+
+
+def run_sweep(args):
+    """M sweep 1..16 over one model's four linear shapes (BASELINE config 4): the fused
+    quantize + CUDA-core GEMV, the fused quantize + tcgen05 packed linear, and, when the
+    installed vLLM's operators load, its `scaled_fp4_quant` + `cutlass_scaled_fp4_mm` pair.
+    Every launch reads a weight copy that has left L2 (copies total > 1 GB)."""
+    from reset_b200 import capi, nvfp4r
+
+    device = torch.device("cuda", 0)
+    torch.cuda.set_device(device)
+    try:
+        import vllm._custom_ops as vops
+    except Exception:
+        vops = None
+    peak, _ = measured_peak()
+    gen = torch.Generator(device=device).manual_seed(3)
+    gs = torch.tensor([100.0], dtype=torch.float32, device=device)
+    alpha_t = torch.tensor([1.0], dtype=torch.float32, device=device)
+    Ms = [int(m) for m in args.sweep_m.split(",")]
+    out = {"sweep": args.sweep, "unit": "us per linear incl. activation quantization", "peak_gbs": peak,
+           "l2": "weight copies cycled, > 1 GB between reuses", "shapes": {}}
+    for name, N, K in SWEEP_SHAPES[args.sweep]:
+        copies = int(1.1e9 // (N * K * 9 // 16)) + 1
+        ws = []
+        for _ in range(copies):
+            w = torch.randint(0, 256, (N, K // 2), dtype=torch.uint8, device=device, generator=gen)
+            s = torch.randint(1, 0x38, (N, K // 16), dtype=torch.uint8, device=device, generator=gen)
+            ws.append((w, s, capi.pack_weight(w, s), capi.swizzle_blockscale(s) if vops else None))
+        wksp = capi.packed_workspace(16, N, K, device)
+        rows = {}
+        for M in Ms:
+            x = torch.randn(M, K, device=device, generator=gen).to(torch.bfloat16)
+            o = torch.empty(M, N, dtype=torch.bfloat16, device=device)
+            st = {"i": 0}
+
+            def nxt():
+                st["i"] += 1
+                return ws[st["i"] % copies]
+
+            def f_gemv():
+                w, s, _, _ = nxt()
+                capi.linear(x, gs, w, s, 1.0, out=o, rcp_mode=1)
+
+            def f_tc():
+                _, _, p, _ = nxt()
+                capi.linear_packed(x, gs, p, N, 1.0, wksp, rcp_mode=1, out=o)
+
+            def f_vllm():
+                w, _, _, ssw = nxt()
+                c, sf = vops.scaled_fp4_quant(x, gs)
+                vops.cutlass_scaled_fp4_mm(c, w, sf, ssw.view(torch.float8_e4m3fn), alpha_t, torch.bfloat16)
+
+            r = {}
+            if M <= 16:
+                r["gemv_us"] = round(_graph_us(f_gemv, 2 * copies, device), 2)
+            r["tcgen05_us"] = round(_graph_us(f_tc, 2 * copies, device), 2)
+            if vops is not None:
+                try:
+                    r["vllm_cutlass_us"] = round(_graph_us(f_vllm, 2 * copies, device), 2)
+                except Exception as e:  # library kernel unavailable for this shape/build
+                    r["vllm_cutlass_error"] = str(e).splitlines()[0][:160]
+                    torch.cuda.synchronize()
+            best = min(v for k, v in r.items() if k in ("gemv_us", "tcgen05_us"))
+            r["best_pct_of_peak"] = round(100.0 * linear_bytes(N, K, M) / best / 1e3 / peak, 1)
+            r["chosen"] = "gemv" if nvfp4r.ops.use_gemv(M, N, K, nvfp4r.status()["gemv_max_m"]) else "tcgen05"
+            rows[str(M)] = r
+        out["shapes"][f"{name} ({N}x{K})"] = rows
+        del ws
+        torch.cuda.empty_cache()
+    return out
+
+
+def run_reset_loop(args):
+    """ReSET decode loop (BASELINE config 2): vocab 151936, batch 1..8, a delimiter every 40-120
+    tokens, t_high 1.0 / t_low 0.1 / tau_0 0.5505 / w 32. GPU: one fused step per token for the
+    whole batch (three launches), CUDA-graph replay over a pool of distinct logits buffers larger
+    than L2, restored before every replay because the step divides in place. CPU: the oracle's
+    per-request processor (the reference's algorithm) on the host cores, same logits."""
+    import ctypes as C
+
+    import numpy as np
+
+    from oracle import reset_policy as orp
+    from reset_b200 import _lib, capi
+
+    device = torch.device("cuda", 0)
+    torch.cuda.set_device(device)
+    V, steps = 151936, args.reset_steps
+    out = {"reset_loop": {"vocab": V, "steps": steps, "unit": "us per decode step (whole batch)"}}
+    delim = V - 5
+    for B in (1, 2, 4, 8):
+        pool_n = max(8, int(300e6 // (B * V * 4)))
+        pristine = torch.randn(pool_n, B, V, device=device, generator=torch.Generator(device=device).manual_seed(B)) * 3.0
+        pristine[:, :, 17] += 12.0
+        pool = pristine.clone()
+        states = torch.zeros(B * C.sizeof(_lib.ResetState), dtype=torch.uint8, device=device)
+        ws = capi.reset_workspace(B, device)
+        params = _lib.ResetParams(1.0, 0.1, 0.5505, 32, 0)
+        bm = torch.zeros((V + 31) // 32, dtype=torch.int32, device=device)
+        bm[delim // 32] = 1 << (delim % 32)
+        nl = torch.zeros_like(bm)
+        streams = np.stack([orp.synthetic_token_stream(pool_n + 2, delim, V, 7 + b) for b in range(B)])
+        last = [torch.from_numpy(np.ascontiguousarray(streams[:, t:t + 2]).astype(np.int32)).to(device)
+                for t in range(pool_n)]
+
+        def one_pass():
+            for t in range(pool_n):
+                capi.reset_step(pool[t], states, params, last_ids=last[t], nl_bitmap=nl, dnl_bitmap=bm,
+                                workspace=ws)
+
+        side = torch.cuda.Stream(device=device)
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            one_pass()
+            pool.copy_(pristine)
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, stream=side):
+                one_pass()
+        torch.cuda.current_stream().wait_stream(side)
+        ts = []
+        for _ in range(max(3, steps // pool_n)):
+            pool.copy_(pristine)
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            g.replay()
+            e1.record()
+            torch.cuda.synchronize()
+            ts.append(e0.elapsed_time(e1) / pool_n * 1e3)
+        gpu_us = sorted(ts)[len(ts) // 2]
+        # CPU: the per-request processor, one call per row per step
+        host = pristine[: min(pool_n, 24)].cpu()
+        pols = [orp.ResetPolicy(1.0, 0.1, 0.5505, 32, frozenset(), frozenset([delim])) for _ in range(B)]
+        t0 = time.perf_counter()
+        for t in range(host.shape[0]):
+            for b in range(B):
+                pols[b](streams[b][: t + 2].tolist(), host[t, b])
+        cpu_us = (time.perf_counter() - t0) / host.shape[0] * 1e6
+        out["reset_loop"][f"B{B}"] = {"gpu_us": round(gpu_us, 2), "cpu_oracle_us": round(cpu_us, 1),
+                                      "speedup": round(cpu_us / gpu_us, 1),
+                                      "gbs": round(2 * B * V * 4 / gpu_us / 1e3, 1),
+                                      "logits_pool_mb": round(pool_n * B * V * 4 / 1e6)}
+        del pool, pristine, g
+        torch.cuda.empty_cache()
+    out["reset_loop"]["cpu_threads"] = torch.get_num_threads()
+    return out
+
 # ---------------------------------------------------------------------- reference / CPU
 
 def _cpu_pass(weights, xs, gs_inv):
@@ -478,6 +661,11 @@ def main():
     ap.add_argument("--decode-layers", type=int, default=0, help="override the layer count (profiling)")
     ap.add_argument("--decode-eager", action="store_true", help="run the decode steps eagerly (profiling)")
     ap.add_argument("--case", default="", help="profile one pair, e.g. gate_up_proj:1 (eager launches)")
+    ap.add_argument("--sweep", default="", choices=["", *SWEEP_SHAPES],
+                    help="M sweep over one model's linear shapes: GEMV vs tcgen05 vs the installed vLLM pair")
+    ap.add_argument("--sweep-m", default="1,2,3,4,6,8,12,16")
+    ap.add_argument("--reset-loop", action="store_true", help="ReSET decode-loop step time vs the CPU oracle")
+    ap.add_argument("--reset-steps", type=int, default=256)
     ap.add_argument("--watchdog", type=int, default=1200,
                     help="seconds after which every rank dumps its Python stacks to stderr and exits")
     args = ap.parse_args()
@@ -490,6 +678,10 @@ def main():
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     if args.impl == "reference":
         line = run_reference(args, rank, world)
+    elif args.sweep or args.reset_loop:
+        if world > 1:
+            raise SystemExit("bench.py: --sweep / --reset-loop are single-GPU measurements")
+        line = run_sweep(args) if args.sweep else run_reset_loop(args)
     else:
         if not torch.cuda.is_available():
             raise SystemExit("bench.py: no CUDA device (there is no CPU fallback for the product path)")

@@ -169,8 +169,11 @@ NVFP4R_API int nvfp4r_linear_tc(const void* x, int64_t x_row_stride, int M, int 
  *                                      (packed 16-byte aligned; N % 128 == 0, K % 256 == 0)
  *   nvfp4r_linear_packed               out[M,N] = alpha * quant(x)[M,K] . W^T, same
  *                                      arithmetic and rcp_mode meaning as nvfp4r_linear;
- *                                      workspace >= nvfp4r_linear_packed_workspace_bytes,
- *                                      zeroed before first use, left ready for the next call
+ *                                      workspace >= nvfp4r_linear_packed_workspace_bytes(M,..)
+ *                                      (grows with M), 16-byte aligned, ALL ZERO before the
+ *                                      first use; every call leaves it all zero again, so
+ *                                      linears of any shape may share one workspace as long
+ *                                      as their launches are ordered on one stream
  * Stands in for the whole of `_nvfp4r_linear_impl` for decode-sized M
  * (vllm_integration.py:165-274) in one launch per 32 rows.
  * ------------------------------------------------------------------------- */

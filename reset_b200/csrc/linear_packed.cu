@@ -13,18 +13,26 @@
 // ONE 1-D bulk copy of 18 or 36 KB: perfectly sequential DRAM reads, one TMA instruction
 // and one mbarrier transaction per 36 KB, no tensor map.
 //
-// Why this shape (measured on B200, see the profile notes of this kernel):
+// Why this shape (measured on B200):
 //   * a thread that issues bulk copies is held ~190 cycles per copy and the MMA thread
-//     spends ~550 cycles per stage on barrier wait + commit regardless of the work in it,
-//     so stages must be few and large;
+//     spends some hundred cycles per stage on barrier wait + commit regardless of the work
+//     in it, so stages must be few and large;
 //   * shared memory per CTA stays under half an SM (two 36 KB stages + the activations of
 //     a K part of at most 2048 elements) so that the CTA of the NEXT linear, launched with
 //     programmatic stream serialization, becomes resident while this one still runs and
 //     starts pulling its own weights at once;
+//   * every phase of a decode-sized launch runs ONCE per CTA, so its instructions are
+//     fetched cold: straight-line code that runs once costs about 8 cycles per instruction
+//     (measured: 15 KB of unrolled epilogue took 4 us). The kernel is therefore written for
+//     small code: loops are not unrolled unless that removes a memory round trip, there is
+//     one quantizer instance, and accumulators are read from tensor memory four tokens at
+//     a time instead of into a register image of the whole tile;
 //   * the activation block scales are copied into tensor memory once per kernel and stay
 //     there (128 columns), the weight scales ride with each stage.
 //
-// Persistent CTAs (one per SM), roles and split-K protocol as in gemm_tcgen05.cu.
+// Grid: persistent CTAs, two per SM. CTA c works on K part c % S of tiles
+// c / S, c / S + G/S, ... Roles: warp 0 = bulk-copy producer, warp 1 = MMA issuer,
+// warps 2-5 = epilogue (one TMEM lane quadrant each).
 #include "kernels.h"
 #include "quant_core.cuh"
 #include "tcgen05_ptx.cuh"
@@ -44,11 +52,11 @@ constexpr int kStageBytes = kBlocksPerStage * kBlockBytes;  // 36864
 constexpr int kStages = 2;
 constexpr int kMaxPartBlocks = 8;                           // K part <= 2048 elements
 constexpr int kThreadsP = 192;
-constexpr int kEpilogueThreads = 128;
+constexpr int kWarpsP = kThreadsP / 32;
 
 struct PackedParams {
     const uint8_t* packed;
-    const void* xb;            // bf16 [M, K]
+    const void* xb;            // bf16 [M, K] (prologue 0) or [M, 2K] (prologue 2)
     int64_t xb_stride;
     const float* gs;
     int rcp_mode;
@@ -57,9 +65,10 @@ struct PackedParams {
     int64_t ldc;               // elements between tokens in out
     int M, m0, N, K;
     float alpha;
-    int tiles, splits, kblocks;
-    float* partials;
-    unsigned* tickets;
+    // work split, computed on the host: S parts of kb_q or kb_q + 1 K blocks (the first
+    // kb_r parts have one more), ctas_per_part CTAs per part
+    int tiles, splits, kblocks, ctas_per_part, kb_q, kb_r;
+    unsigned long long* slots; // split-K hand-over slots {flag:32 | fp32 bits:32}, all zero between launches
     // fused prologue (what produces the bf16 activations that get quantized)
     int pro_kind;                  // 0: xb as is; 1: RMSNorm(residual_in + delta) * norm_w; 2: silu(g) * u
     const void* delta;             // kind 1: bf16 [M, K] or nullptr
@@ -70,21 +79,23 @@ struct PackedParams {
 };
 
 __device__ int g_packed_status = 0;
-// Optional time line of CTA 0 (nanoseconds of %globaltimer), filled when g_packed_trace != 0.
+// Optional time line (nanoseconds of %globaltimer) of eight consecutive CTAs, filled when
+// g_packed_trace != 0: CTAs base .. base+7 with base = g_packed_trace - 1 (a multiple of 8),
+// the last four launches each.
 __device__ int g_packed_trace = 0;
-__device__ unsigned long long g_packed_times[4 * 16];
-__device__ unsigned g_packed_launch = 0;
+__device__ unsigned long long g_packed_times[8 * 4 * 16];
+__device__ unsigned g_packed_launch[8] = {};
 __device__ __forceinline__ unsigned long long gtime() {
     unsigned long long t;
     asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
     return t;
 }
-#define TRACE(slot) do { if (trace) g_packed_times[(launch_id & 3) * 16 + (slot)] = gtime(); } while (0)
+#define TRACE(slot) do { if (trace) g_packed_times[((blockIdx.x & 7) * 4 + (launch_id & 3)) * 16 + (slot)] = gtime(); } while (0)
 
 // ---- one-time re-layout ----------------------------------------------------------
 
-// One thread moves one 16-byte unit of codes; the first K/256*... threads of each block
-// also move the scales. grid = (K/256, N/128), block = 1024 threads (128 rows x 8 units).
+// One thread moves one 16-byte unit of codes; the threads with unit < 4 also move four
+// scale bytes. grid = (K/256, N/128), block = 1024 threads (128 rows x 8 units).
 __global__ void __launch_bounds__(1024)
 pack_weight_kernel(const uint8_t* __restrict__ w, const uint8_t* __restrict__ sf_flat,
                    uint8_t* __restrict__ packed, int N, int K) {
@@ -120,85 +131,103 @@ __device__ __forceinline__ uint4 pack8(const float f[8]) {
 }
 __device__ __forceinline__ float round_bf16(float v) { return __bfloat162float(__float2bfloat16_rn(v)); }
 
-// ---- thread-block cluster helpers (split-K reduction through distributed shared memory)
-__device__ __forceinline__ uint32_t cluster_rank() {
-    uint32_t r;
-    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
-    return r;
-}
-__device__ __forceinline__ uint32_t map_to_rank(uint32_t smem_addr, uint32_t rank) {
-    uint32_t r;
-    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_addr), "r"(rank));
-    return r;
-}
-__device__ __forceinline__ void st_cluster_f32(uint32_t addr, float v) {
-    asm volatile("st.shared::cluster.f32 [%0], %1;" :: "r"(addr), "f"(v) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive_remote(uint32_t cluster_addr) {
-    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" :: "r"(cluster_addr) : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait_cluster(uint32_t bar, uint32_t parity) {
-    uint32_t ok;
-    asm volatile("{\n\t.reg .pred p;\n\t"
-                 "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
-                 "selp.u32 %0, 1, 0, p;\n\t}"
-                 : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
-    return ok != 0;
-}
-__device__ __forceinline__ bool mbar_wait_cluster_bounded(uint32_t bar, uint32_t parity) {
-    for (uint32_t i = 0; i < 20000000u; ++i)
-        if (mbar_try_wait_cluster(bar, parity)) return true;
-    return false;
-}
-__device__ __forceinline__ void cluster_sync_all() {
-    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+__device__ __forceinline__ void tmem_ld4(uint32_t taddr, float v[4]) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x4.b32 {%0,%1,%2,%3}, [%4];"
+                 : "=f"(v[0]), "=f"(v[1]), "=f"(v[2]), "=f"(v[3]) : "r"(taddr) : "memory");
 }
 
-__device__ __forceinline__ unsigned ticket_acq_rel(unsigned* addr) {
-    unsigned old;
-    asm volatile("atom.add.acq_rel.gpu.global.u32 %0, [%1], 1;" : "=r"(old) : "l"(addr) : "memory");
-    return old;
+// ---- split-K hand-over through self-validating 8-byte slots ------------------------------
+// A K part that is not part 0 publishes every partial value as ONE 64-bit store
+// {flag = 1 : fp32 bits}; the CTA of part 0 polls the slots, adds the values in part order
+// and writes zeros back, so the scratch is all-zero again when the kernel ends. A 64-bit
+// scalar access is single-copy atomic, so a slot is either still zero or complete: no
+// fence, no ticket, one store latency plus one load latency on the critical path. All CTAs
+// of the grid are resident at once (the grid never exceeds two CTAs per SM), so the part
+// the poll waits for is running; the poll is bounded all the same.
+__device__ __forceinline__ void slot_store(unsigned long long* p, float v) {
+    const unsigned long long w = (1ull << 32) | static_cast<unsigned long long>(__float_as_uint(v));
+    asm volatile("st.relaxed.gpu.global.u64 [%0], %1;" :: "l"(p), "l"(w) : "memory");
+}
+__device__ __forceinline__ unsigned long long slot_load(const unsigned long long* p) {
+    unsigned long long w;
+    asm volatile("ld.relaxed.gpu.global.u64 %0, [%1];" : "=l"(w) : "l"(p) : "memory");
+    return w;
+}
+constexpr uint32_t kSlotPollLimit = 4000000u;      // polls per group before giving up (~ a second)
+
+// Adds to v[0..cnt) the values of parts 1..S-1 for tokens m_first .. m_first+cnt-1 of this
+// thread's weight row, in part order; GP parts x TJ tokens are polled together (all loads in
+// flight at once: one round trip per group). `base` points at the slot of (part 1, token 0,
+// this row); M is the launch's token count; cnt <= TJ.
+template <int GP, int TJ>
+__device__ __forceinline__ bool slots_gather(unsigned long long* base, int S, int M, int m_first, int cnt,
+                                             float* v) {
+    const int64_t part_stride = static_cast<int64_t>(M) * kTileRows;
+#pragma unroll 1
+    for (int s0 = 1; s0 < S; s0 += GP) {
+        unsigned long long w[GP][TJ];
+        unsigned long long* ps = base + (static_cast<int64_t>(s0 - 1) * M + m_first) * kTileRows;
+#pragma unroll
+        for (int g = 0; g < GP; ++g)
+#pragma unroll
+            for (int j = 0; j < TJ; ++j)
+                if (s0 + g < S && j < cnt) w[g][j] = slot_load(ps + g * part_stride + j * kTileRows);
+        for (uint32_t it = 0;; ++it) {
+            bool all = true;
+#pragma unroll
+            for (int g = 0; g < GP; ++g)
+#pragma unroll
+                for (int j = 0; j < TJ; ++j)
+                    if (s0 + g < S && j < cnt && (w[g][j] >> 32) != 1ull) {
+                        w[g][j] = slot_load(ps + g * part_stride + j * kTileRows);
+                        all = false;
+                    }
+            if (all) break;
+            if (it > kSlotPollLimit) return false;
+        }
+#pragma unroll
+        for (int g = 0; g < GP; ++g)
+#pragma unroll
+            for (int j = 0; j < TJ; ++j)
+                if (s0 + g < S && j < cnt) {
+                    v[j] += __uint_as_float(static_cast<uint32_t>(w[g][j]));
+                    ps[g * part_stride + j * kTileRows] = 0ull;
+                }
+    }
+    return true;
 }
 
 // ---- the linear ---------------------------------------------------------------------
 
-// kCluster: the S CTAs that share a tile form a thread-block cluster (cluster rank = K
-// part) and reduce their partial tiles through distributed shared memory: every CTA owns
-// 128/S rows of the tile, receives the other parts' values for those rows with
-// st.shared::cluster + a remote mbarrier arrive, adds them in part order and stores.
-// Without it (S == 1, or S not a cluster size) partials go through global scratch and a
-// ticket.
-template <int BN, bool kCluster>
+template <int BN>
 __global__ void __launch_bounds__(kThreadsP, 2)
 linear_packed_kernel(const __grid_constant__ PackedParams p) {
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t* smem = smem_raw + (smem_base - smem_u32(smem_raw));
 
-    __shared__ __align__(8) uint64_t bars[2 * kStages + 6];
+    __shared__ __align__(8) uint64_t bars[2 * kStages + 4 + kMaxPartBlocks / kBlocksPerStage];
     __shared__ uint32_t s_tmem;
-    __shared__ int s_last;
-
-    const int tid = threadIdx.x, warp = tid / kWarp, lane = tid % kWarp;
-    const bool trace = (g_packed_trace != 0) && blockIdx.x == 0 && lane == 0;
+    __shared__ float s_red[32 * 8];                    // RMSNorm: per token, per warp sum of squares
     __shared__ unsigned s_launch_id;
-    if (g_packed_trace != 0 && blockIdx.x == 0) {
-        if (tid == 0) s_launch_id = atomicAdd(&g_packed_launch, 1u);
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const bool traced_cta = (g_packed_trace != 0) && (static_cast<int>(blockIdx.x) >> 3) == ((g_packed_trace - 1) >> 3);
+    const bool trace = traced_cta && lane == 0;
+    if (traced_cta) {
+        if (tid == 0) s_launch_id = atomicAdd(&g_packed_launch[blockIdx.x & 7], 1u);
         __syncthreads();
     }
-    const unsigned launch_id = (g_packed_trace != 0 && blockIdx.x == 0) ? s_launch_id : 0u;
+    const unsigned launch_id = traced_cta ? s_launch_id : 0u;
     if (warp == 0) TRACE(0);
+
     const int S = p.splits;
-    const int ctas_per_part = gridDim.x / S;           // CTAs beyond S * ctas_per_part idle
-    const int c = blockIdx.x;
-    const bool active = c < S * ctas_per_part;
-    const int part = c % S, rank_in_part = c / S;
-    const int kb0 = static_cast<int>((static_cast<int64_t>(p.kblocks) * part) / S);
-    const int kb1 = static_cast<int>((static_cast<int64_t>(p.kblocks) * (part + 1)) / S);
-    const int nkb = kb1 - kb0;                                        // <= kMaxPartBlocks
+    const int rank = static_cast<int>(blockIdx.x) / S, part = static_cast<int>(blockIdx.x) - rank * S;
+    const int kb0 = part * p.kb_q + min(part, p.kb_r);
+    const int nkb = p.kb_q + (part < p.kb_r ? 1 : 0);                   // 1 .. kMaxPartBlocks
     const int stages_per_tile = (nkb + kBlocksPerStage - 1) / kBlocksPerStage;
-    const int my_tiles = (active && rank_in_part < p.tiles)
-                             ? (p.tiles - rank_in_part + ctas_per_part - 1) / ctas_per_part : 0;
+    const int cpp = p.ctas_per_part;
+    const int my_tiles = (rank < cpp && rank < p.tiles) ? (p.tiles - rank + cpp - 1) / cpp : 0;
     const int total = my_tiles * stages_per_tile;
 
     const uint32_t ring = smem_base;
@@ -206,114 +235,136 @@ linear_packed_kernel(const __grid_constant__ PackedParams p) {
     // activation scale chunks: tcgen05.cp reads 32 rows x 16 B per chunk, but only rows
     // < BN matter, so with BN == 16 consecutive chunks overlap by half (stride 256 B)
     constexpr int kSfbStride = (BN == 16) ? 256 : 512;
-    constexpr int kSfbBytes = kMaxPartBlocks * 4 * kSfbStride + 256;
     const uint32_t b_sf = b_tile + kMaxPartBlocks * (BN * 128);
     uint8_t* b_tile_g = smem + kStages * kStageBytes;
     uint8_t* b_sf_g = b_tile_g + kMaxPartBlocks * (BN * 128);
-    // cluster reduction: values received for the rows this CTA owns, [part][token][row]
-    const uint32_t recv = b_sf + kSfbBytes;
-    float* recv_g = reinterpret_cast<float*>(b_sf_g + kSfbBytes);
 
     const uint32_t bar_full = smem_u32(&bars[0]);
     const uint32_t bar_empty = smem_u32(&bars[kStages]);
     const uint32_t bar_accfull = smem_u32(&bars[2 * kStages]);
     const uint32_t bar_accempty = smem_u32(&bars[2 * kStages + 2]);
-    const uint32_t bar_redfull = smem_u32(&bars[2 * kStages + 4]);
-    const uint32_t bar_redfree = smem_u32(&bars[2 * kStages + 5]);
+    const uint32_t bar_sfb = smem_u32(&bars[2 * kStages + 4]);       // one per stage of the K part, used once
 
     constexpr uint32_t kTmemCols = 256;
-    constexpr uint32_t kColSFA = 2 * BN;                              // 16 columns per block in a stage
-    constexpr uint32_t kColSFB = kColSFA + 16 * kBlocksPerStage;      // likewise for the activations
-    constexpr uint32_t kColSFBres = kColSFB + 16 * kBlocksPerStage;   // 16 per block of the K part
+    constexpr uint32_t kColSFA = 2 * BN;                              // 16 columns per block of a stage
+    constexpr uint32_t kColSFB = kColSFA + 16 * kBlocksPerStage;      // 16 per block of the K part
 
-    if (warp == 0 && lane == 0) {
-        for (int s = 0; s < kStages; ++s) {
-            mbar_init(bar_full + 8 * s, 1);
-            mbar_init(bar_empty + 8 * s, 1);
-        }
-        for (int b = 0; b < 2; ++b) {
-            mbar_init(bar_accfull + 8 * b, 1);
-            mbar_init(bar_accempty + 8 * b, kEpilogueThreads / kWarp);
-        }
-        if (kCluster) {
-            mbar_init(bar_redfull, (S - 1) * (kTileRows / S));   // one arrival per sending thread
-            mbar_init(bar_redfree, S - 1);                       // one arrival per peer CTA
-        }
+    // producer state (thread 0 only): next stage = K-block pair p_j of this CTA's p_ti-th tile
+    int issued = 0, p_ti = 0, p_j = 0;
+    const uint64_t policy = l2_policy_evict_first();
+    auto issue_next = [&]() {
+        const int tile = rank + p_ti * cpp;
+        const int s = issued & (kStages - 1);
+        const int nb = min(kBlocksPerStage, nkb - p_j * kBlocksPerStage);
+        const uint32_t bytes = static_cast<uint32_t>(nb) * kBlockBytes;
+        mbar_expect_tx(bar_full + 8 * s, bytes);
+        bulk_g2s(ring + s * kStageBytes,
+                 p.packed + (static_cast<int64_t>(tile) * p.kblocks + kb0 + p_j * kBlocksPerStage) * kBlockBytes,
+                 bytes, bar_full + 8 * s, policy);
+        ++issued;
+        if (++p_j == stages_per_tile) { p_j = 0; ++p_ti; }
+    };
+
+    // The weights do not depend on the previous kernel: thread 0 arms the barriers and starts
+    // the first stages before anything else happens in this CTA.
+    if (tid == 0) {
+#pragma unroll 1
+        for (int i = 0; i < 2 * kStages + 4 + kMaxPartBlocks / kBlocksPerStage; ++i)   // accempty: one arrival per epilogue warp
+            mbar_init(bar_full + 8 * i, (i >= 2 * kStages + 2 && i < 2 * kStages + 4) ? 4u : 1u);
         mbar_fence_init();
+#pragma unroll 1
+        while (issued < total && issued < kStages) issue_next();
     }
     if (warp == 1) tmem_alloc(smem_u32(&s_tmem), kTmemCols);
+    if (warp == 0) TRACE(1);
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem = s_tmem;
-
-    const uint64_t policy = l2_policy_evict_first();
-    auto stage_blocks = [&](int j) { return min(kBlocksPerStage, nkb - j * kBlocksPerStage); };
-    auto issue = [&](int i) {                          // stage i of this CTA's sequence
-        const int ti = i / stages_per_tile, j = i - ti * stages_per_tile;
-        const int tile = rank_in_part + ti * ctas_per_part;
-        const int s = i % kStages;
-        const uint32_t bytes = static_cast<uint32_t>(stage_blocks(j)) * kBlockBytes;
-        mbar_expect_tx(bar_full + 8 * s, bytes);
-        bulk_g2s(ring + s * kStageBytes,
-                 p.packed + (static_cast<int64_t>(tile) * p.kblocks + kb0 + j * kBlocksPerStage) * kBlockBytes,
-                 bytes, bar_full + 8 * s, policy);
-    };
-
-    int issued = 0;
-    if (warp == 0 && lane == 0) {
-        const int first = min(kStages, total);
-        for (; issued < first; ++issued) issue(issued);
-    }
-    if (warp == 0) TRACE(1);
     pdl_launch_dependents();
-    if (kCluster) cluster_sync_all();      // every CTA's reduction barriers are initialised
     pdl_wait_prior();
     if (warp == 0) TRACE(2);
 
     // ---- prologue: quantize this part's activations into operand layout --------------
-    if (active) {
+    if (my_tiles > 0) {
         const int blk0 = kb0 * (kBlockK / 16);
         const int blocks = nkb * (kBlockK / 16);
-        const float gs = __ldg(p.gs);
-        const QuantScales qe = make_quant_scales<kRcpExact>(gs);
-        const QuantScales qa = make_quant_scales<kRcpApprox>(gs);
-        const __nv_bfloat16* xb = static_cast<const __nv_bfloat16*>(p.xb);
         const int n_items = p.M * blocks;
-        auto quantize_store = [&](int m, int blk, const uint4& lo, const uint4& hi) {
-            uint32_t cw[2];
-            const uint32_t sf = (p.rcp_mode == kRcpExact) ? quantize_block16<kRcpExact>(lo, hi, qe, cw)
-                                                          : quantize_block16<kRcpApprox>(lo, hi, qa, cw);
-            *reinterpret_cast<uint2*>(b_tile_g + (blk >> 4) * (BN * 128) + swz128(m, (blk & 15) * 8)) =
-                make_uint2(cw[0], cw[1]);
-            b_sf_g[(blk >> 2) * kSfbStride + m * 16 + (blk & 3)] = static_cast<uint8_t>(sf);
-        };
-        if (p.pro_kind == 0) {
-            // four blocks per thread per round: all eight 16-byte loads are issued before any
-            // of the arithmetic, so a round costs one memory round trip
-            for (int i0 = tid; i0 < n_items; i0 += 4 * kThreadsP) {
-                uint4 lo[4], hi[4];
+        const bool exact = (p.rcp_mode == kRcpExact);
+        const float gs = __ldg(p.gs);
+        const QuantScales q = exact ? make_quant_scales<kRcpExact>(gs) : make_quant_scales<kRcpApprox>(gs);
+        const __nv_bfloat16* xb = static_cast<const __nv_bfloat16*>(p.xb);
+        const __nv_bfloat16* rin = static_cast<const __nv_bfloat16*>(p.residual_in);
+        const __nv_bfloat16* dl = static_cast<const __nv_bfloat16*>(p.delta);
+        const int kind = p.pro_kind;
+
+        if (kind == 1) {
+            // Every CTA needs each row's mean square over the whole K: recomputed here from
+            // L2 (2 x 2K bytes per row) instead of being passed between kernels. Four 16-byte
+            // chunks per thread are loaded before any arithmetic: one round trip for K <= 6144.
+#pragma unroll 1
+            for (int m = 0; m < p.M; ++m) {
+                const int64_t base = static_cast<int64_t>(p.m0 + m) * p.K;
+                float ss = 0.0f;
+#pragma unroll 1
+                for (int c0 = tid; c0 < p.K / 8; c0 += 4 * kThreadsP) {
+                    uint4 r4[4], d4[4];
 #pragma unroll
-                for (int u = 0; u < 4; ++u) {
-                    const int i = i0 + u * kThreadsP;
-                    if (i < n_items) {
-                        const int m = i / blocks, blk = i - m * blocks;
-                        const uint4* src = reinterpret_cast<const uint4*>(
-                            xb + (p.m0 + m) * p.xb_stride + static_cast<int64_t>(blk0 + blk) * 16);
-                        lo[u] = __ldg(src);
-                        hi[u] = __ldg(src + 1);
+                    for (int u = 0; u < 4; ++u) {
+                        const int c8 = c0 + u * kThreadsP;
+                        if (c8 < p.K / 8) {
+                            r4[u] = __ldg(reinterpret_cast<const uint4*>(rin + base) + c8);
+                            if (dl != nullptr) d4[u] = __ldg(reinterpret_cast<const uint4*>(dl + base) + c8);
+                        }
+                    }
+#pragma unroll
+                    for (int u = 0; u < 4; ++u) {
+                        if (c0 + u * kThreadsP < p.K / 8) {
+                            float r[8], d[8];
+                            unpack8(r4[u], r);
+                            if (dl != nullptr) {
+                                unpack8(d4[u], d);
+#pragma unroll
+                                for (int j = 0; j < 8; ++j) r[j] = round_bf16(r[j] + d[j]);
+                            }
+#pragma unroll
+                            for (int j = 0; j < 8; ++j) ss += r[j] * r[j];
+                        }
                     }
                 }
 #pragma unroll
-                for (int u = 0; u < 4; ++u) {
-                    const int i = i0 + u * kThreadsP;
-                    if (i < n_items) quantize_store(i / blocks, i % blocks, lo[u], hi[u]);
-                }
+                for (int sft = 16; sft > 0; sft >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, sft);
+                if (lane == 0) s_red[m * 8 + warp] = ss;
             }
-        } else if (p.pro_kind == 2) {
-            // activation = bf16(silu(gate) * up), gate_up row = [gate (K) | up (K)]
-            for (int i = tid; i < n_items; i += kThreadsP) {
-                const int m = i / blocks, blk = i - m * blocks;
+            __syncthreads();
+        }
+
+        // One 16-element block per thread per round. Prologue 0 prefetches the next round's
+        // block while the current one is quantized.
+        uint4 nlo = make_uint4(0, 0, 0, 0), nhi = nlo;
+        auto src0 = [&](int i) {
+            const int m = i / blocks, blk = i - m * blocks;
+            return reinterpret_cast<const uint4*>(xb + (p.m0 + m) * p.xb_stride + static_cast<int64_t>(blk0 + blk) * 16);
+        };
+        if (kind == 0 && tid < n_items) {
+            const uint4* s0 = src0(tid);
+            nlo = __ldg(s0);
+            nhi = __ldg(s0 + 1);
+        }
+#pragma unroll 1
+        for (int i = tid; i < n_items; i += kThreadsP) {
+            const int m = i / blocks, blk = i - m * blocks;
+            uint4 lo, hi;
+            if (kind == 0) {
+                lo = nlo;
+                hi = nhi;
+                if (i + kThreadsP < n_items) {
+                    const uint4* s0 = src0(i + kThreadsP);
+                    nlo = __ldg(s0);
+                    nhi = __ldg(s0 + 1);
+                }
+            } else if (kind == 2) {
+                // activation = bf16(silu(gate) * up), gate_up row = [gate (K) | up (K)]
                 const __nv_bfloat16* row = xb + (p.m0 + m) * p.xb_stride + static_cast<int64_t>(blk0 + blk) * 16;
                 const uint4 g0 = __ldg(reinterpret_cast<const uint4*>(row));
                 const uint4 g1 = __ldg(reinterpret_cast<const uint4*>(row) + 1);
@@ -323,65 +374,47 @@ linear_packed_kernel(const __grid_constant__ PackedParams p) {
                 unpack8(g0, g); unpack8(g1, g + 8); unpack8(u0, u); unpack8(u1, u + 8);
 #pragma unroll
                 for (int j = 0; j < 16; ++j) g[j] = g[j] / (1.0f + __expf(-g[j])) * u[j];
-                quantize_store(m, blk, pack8(g), pack8(g + 8));
-            }
-        } else {
-            // activation = bf16( bf16(residual + delta) * rsqrt(mean_sq + eps) * norm_w ).
-            // Every CTA needs the row's mean square over the whole K: it is recomputed
-            // here from L2 (2 x 2K bytes per row) instead of being passed between kernels.
-            float* red = reinterpret_cast<float*>(recv_g);            // reduction buffer is free now
-            const __nv_bfloat16* rin = static_cast<const __nv_bfloat16*>(p.residual_in);
-            const __nv_bfloat16* dl = static_cast<const __nv_bfloat16*>(p.delta);
-            const __nv_bfloat16* nw = static_cast<const __nv_bfloat16*>(p.norm_w);
-            __nv_bfloat16* rout = static_cast<__nv_bfloat16*>(p.residual_out);
-            for (int m = 0; m < p.M; ++m) {
-                const int64_t base = static_cast<int64_t>(p.m0 + m) * p.K;
-                float ss = 0.0f;
-                for (int c8 = tid; c8 < p.K / 8; c8 += kThreadsP) {
-                    float r[8], d[8];
-                    unpack8(__ldg(reinterpret_cast<const uint4*>(rin + base) + c8), r);
-                    if (dl != nullptr) {
-                        unpack8(__ldg(reinterpret_cast<const uint4*>(dl + base) + c8), d);
-#pragma unroll
-                        for (int j = 0; j < 8; ++j) r[j] = round_bf16(r[j] + d[j]);
-                    }
-#pragma unroll
-                    for (int j = 0; j < 8; ++j) ss += r[j] * r[j];
-                }
-#pragma unroll
-                for (int sft = 16; sft > 0; sft >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, sft);
-                if (lane == 0) red[m * 8 + warp] = ss;
-            }
-            __syncthreads();
-            const bool writer = (rank_in_part == 0);                  // one CTA per K part writes the residual
-            for (int i = tid; i < n_items; i += kThreadsP) {
-                const int m = i / blocks, blk = i - m * blocks;
-                float tot = 0.0f;
-#pragma unroll
-                for (int w = 0; w < kThreadsP / kWarp; ++w) tot += red[m * 8 + w];
-                const float inv = rsqrtf(tot / static_cast<float>(p.K) + p.eps);
-                const int64_t off = static_cast<int64_t>(p.m0 + m) * p.K + static_cast<int64_t>(blk0 + blk) * 16;
-                float r[16], d[16], w16[16];
-                unpack8(__ldg(reinterpret_cast<const uint4*>(rin + off)), r);
-                unpack8(__ldg(reinterpret_cast<const uint4*>(rin + off) + 1), r + 8);
+                lo = pack8(g);
+                hi = pack8(g + 8);
+            } else {
+                // activation = bf16( bf16(residual + delta) * rsqrt(mean_sq + eps) * norm_w );
+                // the CTAs of rank 0 (one per K part) also write the new residual
+                const __nv_bfloat16* nw = static_cast<const __nv_bfloat16*>(p.norm_w);
+                __nv_bfloat16* rout = static_cast<__nv_bfloat16*>(p.residual_out);
+                const int64_t koff = static_cast<int64_t>(blk0 + blk) * 16;
+                const int64_t off = static_cast<int64_t>(p.m0 + m) * p.K + koff;
+                const uint4 r0 = __ldg(reinterpret_cast<const uint4*>(rin + off));
+                const uint4 r1 = __ldg(reinterpret_cast<const uint4*>(rin + off) + 1);
+                const uint4 w0 = __ldg(reinterpret_cast<const uint4*>(nw + koff));
+                const uint4 w1 = __ldg(reinterpret_cast<const uint4*>(nw + koff) + 1);
+                float r[16], t[16];
+                unpack8(r0, r); unpack8(r1, r + 8);
                 if (dl != nullptr) {
-                    unpack8(__ldg(reinterpret_cast<const uint4*>(dl + off)), d);
-                    unpack8(__ldg(reinterpret_cast<const uint4*>(dl + off) + 1), d + 8);
+                    const uint4 d0 = __ldg(reinterpret_cast<const uint4*>(dl + off));
+                    const uint4 d1 = __ldg(reinterpret_cast<const uint4*>(dl + off) + 1);
+                    unpack8(d0, t); unpack8(d1, t + 8);
 #pragma unroll
-                    for (int j = 0; j < 16; ++j) r[j] = round_bf16(r[j] + d[j]);
+                    for (int j = 0; j < 16; ++j) r[j] = round_bf16(r[j] + t[j]);
                 }
-                if (writer) {
+                if (rank == 0) {
                     *reinterpret_cast<uint4*>(rout + off) = pack8(r);
                     *(reinterpret_cast<uint4*>(rout + off) + 1) = pack8(r + 8);
                 }
-                const int64_t koff = static_cast<int64_t>(blk0 + blk) * 16;
-                unpack8(__ldg(reinterpret_cast<const uint4*>(nw + koff)), w16);
-                unpack8(__ldg(reinterpret_cast<const uint4*>(nw + koff) + 1), w16 + 8);
+                float tot = 0.0f;
 #pragma unroll
-                for (int j = 0; j < 16; ++j) r[j] = r[j] * inv * w16[j];
-                quantize_store(m, blk, pack8(r), pack8(r + 8));
+                for (int w = 0; w < kWarpsP; ++w) tot += s_red[m * 8 + w];
+                const float inv = rsqrtf(tot / static_cast<float>(p.K) + p.eps);
+                unpack8(w0, t); unpack8(w1, t + 8);
+#pragma unroll
+                for (int j = 0; j < 16; ++j) r[j] = r[j] * inv * t[j];
+                lo = pack8(r);
+                hi = pack8(r + 8);
             }
-            __syncthreads();                                          // red is handed back to the reduction
+            uint32_t cw[2];
+            const uint32_t sf = quantize_block16_rt(lo, hi, q, exact, cw);
+            *reinterpret_cast<uint2*>(b_tile_g + (blk >> 4) * (BN * 128) + swz128(m, (blk & 15) * 8)) =
+                make_uint2(cw[0], cw[1]);
+            b_sf_g[(blk >> 2) * kSfbStride + m * 16 + (blk & 3)] = static_cast<uint8_t>(sf);
         }
         // Rows M..BN-1 of the operand are never written: whatever they hold only reaches
         // accumulator columns that are not stored.
@@ -391,183 +424,139 @@ linear_packed_kernel(const __grid_constant__ PackedParams p) {
     if (warp == 0) TRACE(3);
 
     WaitFail wf;
-    if (warp == 0) {
+    if (tid == 0) {
         // ---------------- producer -------------------------------------------------------
-        if (lane == 0) {
-            for (int i = issued; i < total; ++i) {
-                const int s = i % kStages;
-                if (!wf.wait(bar_empty + 8 * s, ((i / kStages) - 1) & 1)) break;
-                issue(i);
-            }
+#pragma unroll 1
+        while (issued < total) {
+            const int s = issued & (kStages - 1);
+            if (!wf.wait(bar_empty + 8 * s, ((issued / kStages) - 1) & 1)) break;
+            issue_next();
         }
-    } else if (warp == 1) {
+    } else if (tid == 32 && my_tiles > 0) {
         // ---------------- MMA issuer -----------------------------------------------------
-        if (lane == 0 && my_tiles > 0) {
-            constexpr uint32_t idesc = (1u << 7) | (1u << 10) | (static_cast<uint32_t>(BN >> 3) << 17) |
-                                       (static_cast<uint32_t>(kTileRows >> 7) << 27);
-            // A CTA that walks several tiles copies the activation scales into tensor
-            // memory once; a single-tile CTA copies them with the stage that uses them.
-            const bool sfb_resident = my_tiles >= 2;
-            if (sfb_resident)
-                for (int ch = 0; ch < nkb * 4; ++ch)
-                    tc_cp_scales(tmem + kColSFBres + 4 * ch, desc_scales(b_sf + ch * kSfbStride));
-            int i = 0;
-            for (int ti = 0; ti < my_tiles && !wf.failed; ++ti) {
-                const int buf = ti & 1;
-                if (ti >= 2 && !wf.wait(bar_accempty + 8 * buf, ((ti >> 1) - 1) & 1)) break;
+        constexpr uint32_t idesc = (1u << 7) | (1u << 10) | (static_cast<uint32_t>(BN >> 3) << 17) |
+                                   (static_cast<uint32_t>(kTileRows >> 7) << 27);
+        int i = 0;
+#pragma unroll 1
+        for (int ti = 0; ti < my_tiles && !wf.failed; ++ti) {
+            const int buf = ti & 1;
+            if (ti >= 2 && !wf.wait(bar_accempty + 8 * buf, ((ti >> 1) - 1) & 1)) break;
+            tc_fence_after();
+            const uint32_t d_tmem = tmem + buf * BN;
+#pragma unroll 1
+            for (int j = 0; j < stages_per_tile; ++j, ++i) {
+                const int s = i & (kStages - 1);
+                if (!wf.wait(bar_full + 8 * s, (i / kStages) & 1)) break;
+                if (i == 0) TRACE(4);
+                // the activation scales of this stage's blocks are in tensor memory (first tile only)
+                if (ti == 0 && !wf.wait(bar_sfb + 8 * j, 0)) break;
                 tc_fence_after();
-                const uint32_t d_tmem = tmem + buf * BN;
-                for (int j = 0; j < stages_per_tile; ++j, ++i) {
-                    const int s = i % kStages;
-                    if (!wf.wait(bar_full + 8 * s, (i / kStages) & 1)) break;
-                    if (i == 0) TRACE(4);
-                    tc_fence_after();
-                    const int nb = stage_blocks(j);
-                    for (int b = 0; b < nb; ++b) {
-                        const uint32_t a_smem = ring + s * kStageBytes + b * kBlockBytes;
-                        const int blk = j * kBlocksPerStage + b;              // block within the part
-                        const uint32_t b_smem = b_tile + blk * (BN * 128);
-#pragma unroll
-                        for (int k = 0; k < 4; ++k) {
-                            tc_cp_scales(tmem + kColSFA + 16 * b + 4 * k,
-                                         desc_scales(a_smem + kCodesBytes + k * 512));
-                            if (!sfb_resident)
-                                tc_cp_scales(tmem + kColSFB + 16 * b + 4 * k,
-                                             desc_scales(b_sf + (blk * 4 + k) * kSfbStride));
-                        }
-                        const uint32_t sfb_col = sfb_resident ? kColSFBres + 16 * blk : kColSFB + 16 * b;
-#pragma unroll
-                        for (int k = 0; k < 4; ++k)
-                            tc_mma_nvf4(d_tmem, desc_operand(a_smem + k * 32), desc_operand(b_smem + k * 32),
-                                        idesc, tmem + kColSFA + 16 * b + 4 * k,
-                                        tmem + sfb_col + 4 * k, (blk > 0 || k > 0) ? 1u : 0u);
+                const int nb = min(kBlocksPerStage, nkb - j * kBlocksPerStage);
+#pragma unroll 1
+                for (int b = 0; b < nb; ++b) {
+                    const uint32_t a_smem = ring + s * kStageBytes + b * kBlockBytes;
+                    const int blk = j * kBlocksPerStage + b;              // block within the part
+                    const uint64_t a_desc = desc_operand(a_smem);
+                    const uint64_t b_desc = desc_operand(b_tile + blk * (BN * 128));
+                    const uint64_t sfa_desc = desc_scales(a_smem + kCodesBytes);
+                    const uint32_t sfa_col = tmem + kColSFA + 16 * b;
+                    const uint32_t sfb_col = tmem + kColSFB + 16 * blk;
+#pragma unroll 1
+                    for (int k = 0; k < 4; ++k) {
+                        // descriptors advance by (bytes >> 4): 512 B per scale chunk, 32 B per K64 of codes
+                        tc_cp_scales(sfa_col + 4 * k, sfa_desc + 32 * k);
+                        tc_mma_nvf4(d_tmem, a_desc + 2 * k, b_desc + 2 * k, idesc, sfa_col + 4 * k,
+                                    sfb_col + 4 * k, (blk | k) != 0 ? 1u : 0u);
                     }
-                    tc_commit(bar_empty + 8 * s);
                 }
-                tc_commit(bar_accfull + 8 * buf);
-                if (ti == 0) TRACE(5);
+                tc_commit(bar_empty + 8 * s);
             }
-            TRACE(6);
+            tc_commit(bar_accfull + 8 * buf);
+            if (ti == 0) TRACE(5);
         }
-    } else {
+        TRACE(6);
+    } else if (warp >= 2) {
         // ---------------- epilogue (warps 2..5) ------------------------------------------
-        const int q = warp & 3;
+        const int q = warp & 3;                                   // TMEM lane quadrant of this warp
         const int row_in_tile = q * 32 + lane;
-        const int et = tid - 2 * kWarp;
+        if (tid == 64 && my_tiles > 0) {
+            // activation scales of the whole K part go into tensor memory once, issued from
+            // this thread so that they overlap the MMA thread's weight-scale copies; one
+            // commit per stage of the K part
+            const uint64_t d0 = desc_scales(b_sf);
+#pragma unroll 1
+            for (int j = 0; j < stages_per_tile; ++j) {
+                const int c0 = j * kBlocksPerStage * 4, c1 = min(nkb * 4, c0 + kBlocksPerStage * 4);
+#pragma unroll 1
+                for (int ch = c0; ch < c1; ++ch)
+                    tc_cp_scales(tmem + kColSFB + 4 * ch, d0 + ch * (kSfbStride >> 4));
+                tc_commit(bar_sfb + 8 * j);
+            }
+        }
+        __syncwarp();
+#pragma unroll 1
         for (int ti = 0; ti < my_tiles; ++ti) {
             const int buf = ti & 1;
-            const int tile = rank_in_part + ti * ctas_per_part;
+            const int tile = rank + ti * cpp;
             if (!wf.wait(bar_accfull + 8 * buf, (ti >> 1) & 1)) break;
             if (warp == 2 && ti == 0) TRACE(7);
             if (warp == 2 && ti == my_tiles - 1) TRACE(8);
             tc_fence_after();
-            float acc[BN];
-#pragma unroll
-            for (int h = 0; h < BN / 16; ++h)
-                tmem_ld16(tmem + (static_cast<uint32_t>(q * 32) << 16) + buf * BN + h * 16, &acc[h * 16]);
-            tmem_ld_wait();
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(bar_accempty + 8 * buf);
-
+            const uint32_t taddr = tmem + (static_cast<uint32_t>(q * 32) << 16) + buf * BN;
             const int64_t n = static_cast<int64_t>(tile) * kTileRows + row_in_tile;
-            auto store = [&](int m, float v) {
-                const int64_t idx = (p.m0 + m) * p.ldc + n;
-                v *= p.alpha;
-                if (p.out_dtype == 0) static_cast<__nv_bfloat16*>(p.out)[idx] = __float2bfloat16_rn(v);
-                else if (p.out_dtype == 1) static_cast<__half*>(p.out)[idx] = __float2half_rn(v);
-                else static_cast<float*>(p.out)[idx] = v;
-            };
-            if (S == 1) {
+            unsigned long long* tile_slots =
+                p.slots + static_cast<int64_t>(tile) * (S - 1) * p.M * kTileRows + row_in_tile;
+#pragma unroll 1
+            for (int mf = 0; mf < p.M; mf += 4) {
+                const int cnt = min(4, p.M - mf);
+                float v[4];
+                tmem_ld4(taddr + mf, v);
+                tmem_ld_wait();
+                if (part != 0) {
+                    unsigned long long* dst = tile_slots + (static_cast<int64_t>(part - 1) * p.M + mf) * kTileRows;
 #pragma unroll
-                for (int m = 0; m < BN; ++m)
-                    if (m < p.M) store(m, acc[m]);
-            } else if (kCluster) {
-                // reduce-scatter over the cluster: rows [o*R, (o+1)*R) of the tile belong to
-                // the CTA of rank o; recv[part][token][row - o*R] in the owner's shared memory
-                const int R = kTileRows / S;
-                const int owner = row_in_tile / R, r_local = row_in_tile - owner * R;
-                if (ti >= 1) {                              // peers have read tile ti-1's values
-                    if (!mbar_wait_cluster_bounded(bar_redfree, (ti - 1) & 1)) wf.failed = true;
-                }
-                if (owner != part) {
-                    const uint32_t dst = map_to_rank(recv, owner) +
-                                         static_cast<uint32_t>((part * BN * R + r_local) * 4);
-#pragma unroll
-                    for (int m = 0; m < BN; ++m)
-                        if (m < p.M) st_cluster_f32(dst + m * R * 4, acc[m]);
-                    mbar_arrive_remote(map_to_rank(bar_redfull, owner));
+                    for (int j = 0; j < 4; ++j)
+                        if (j < cnt) slot_store(dst + j * kTileRows, v[j]);
                 } else {
-                    if (!mbar_wait_cluster_bounded(bar_redfull, ti & 1)) wf.failed = true;
+                    if (S > 1) {
+                        const bool ok = cnt == 1 ? slots_gather<8, 1>(tile_slots, S, p.M, mf, cnt, v)
+                                                 : slots_gather<4, 4>(tile_slots, S, p.M, mf, cnt, v);
+                        if (!ok) wf.failed = true;
+                    }
 #pragma unroll
-                    for (int m = 0; m < BN; ++m) {
-                        if (m < p.M) {
-                            float v = 0.0f;
-                            for (int s = 0; s < S; ++s)     // part order: deterministic
-                                v += (s == part) ? acc[m] : recv_g[(s * BN + m) * R + r_local];
-                            store(m, v);
+                    for (int j = 0; j < 4; ++j) {
+                        if (j < cnt) {
+                            const int64_t idx = (p.m0 + mf + j) * p.ldc + n;
+                            const float o = v[j] * p.alpha;
+                            if (p.out_dtype == 0) static_cast<__nv_bfloat16*>(p.out)[idx] = __float2bfloat16_rn(o);
+                            else if (p.out_dtype == 1) static_cast<__half*>(p.out)[idx] = __float2half_rn(o);
+                            else static_cast<float*>(p.out)[idx] = o;
                         }
                     }
                 }
-                named_barrier(1, kEpilogueThreads);         // this CTA's owners are done reading
-                if (et == 0)
-                    for (int r = 0; r < S; ++r)
-                        if (r != part) mbar_arrive_remote(map_to_rank(bar_redfree, r));
-            } else {
-                float* slot = p.partials + (static_cast<int64_t>(tile) * S + part) * (BN * kTileRows);
-#pragma unroll
-                for (int m = 0; m < BN; ++m)
-                    if (m < p.M) __stcg(slot + m * kTileRows + row_in_tile, acc[m]);
-                // The CTA barrier orders every thread's partial stores before thread 0's
-                // release; the acquire side is the same atomic followed by the second barrier.
-                named_barrier(1, kEpilogueThreads);
-                if (et == 0) {
-                    const unsigned t = ticket_acq_rel(p.tickets + tile);
-                    s_last = (t == static_cast<unsigned>(S) - 1u) ? 1 : 0;
-                    if (s_last) p.tickets[tile] = 0u;
-                }
-                named_barrier(1, kEpilogueThreads);
-                if (s_last) {
-                    // all loads first (independent, many in flight), parts added in part order
-                    const float* base = p.partials + static_cast<int64_t>(tile) * S * (BN * kTileRows);
-#pragma unroll
-                    for (int m = 0; m < BN; ++m) acc[m] = 0.0f;
-                    for (int s = 0; s < S; ++s) {
-#pragma unroll
-                        for (int m = 0; m < BN; ++m)
-                            if (m < p.M)
-                                acc[m] += __ldcg(base + s * (BN * kTileRows) + m * kTileRows + row_in_tile);
-                    }
-#pragma unroll
-                    for (int m = 0; m < BN; ++m)
-                        if (m < p.M) store(m, acc[m]);
-                }
-                named_barrier(1, kEpilogueThreads);
             }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar_accempty + 8 * buf);
         }
+        if (warp == 2) TRACE(9);
     }
 
-    if (warp == 2) TRACE(9);
     if (wf.failed && lane == 0) atomicExch(&g_packed_status, 1);
     tc_fence_before();
     __syncthreads();
-    // no CTA leaves while a peer may still write to its shared memory or its barriers
-    if (kCluster) cluster_sync_all();
     if (warp == 1) {
         tc_fence_after();
         tmem_dealloc(tmem, kTmemCols);
     }
 }
 
-struct PackedPlan { int splits, grid, bn; size_t smem; bool cluster; };
-// Off by default: measured slower than the ticket path on B200 (cluster scheduling
-// granularity and lock-step between the CTAs of a cluster); kept selectable for study.
-int g_packed_use_cluster = 0;
+struct PackedPlan { int splits, grid, bn; size_t smem; };
 int g_force_packed_splits = 0;
 int g_packed_ctas_per_sm = 2;
 
 // Parts of at most kMaxPartBlocks K blocks; among the admissible split counts take the
-// one that keeps the most SMs busy (fewer parts on a tie).
+// one with the smallest estimated time.
 bool plan_packed(int M, int N, int K, PackedPlan* plan) {
     const int bn = M <= 16 ? 16 : 32;
     const int per_sm = (bn == 16 && g_packed_ctas_per_sm == 2) ? 2 : 1;
@@ -577,16 +566,14 @@ bool plan_packed(int M, int N, int K, PackedPlan* plan) {
     if (min_s > G) return false;
     // Estimated time of a split count, fitted to sweeps on B200: the CTAs make
     // ceil(units / G) rounds; a round streams one unit (largest K part) at the per-CTA share
-    // of HBM bandwidth and pays about a microsecond for the partial-sum hand-over.
+    // of HBM bandwidth and pays a fraction of a microsecond for the partial-sum hand-over.
     int best = -1;
     double best_score = 1e30;
     const double kb_per_us = 6400.0 * 1000.0 / 1024.0 / G;      // KB per microsecond per CTA
     for (int s = min_s; s <= kblocks && s <= G && s <= 64; ++s) {
-        const bool clusterable = (s == 2 || s == 4 || s == 8);
-        if (g_packed_use_cluster && min_s <= 8 && s > 1 && !clusterable) continue;
-        const int rounds = (tiles * s + G - 1) / G;
+        const int rounds = (tiles + G / s - 1) / (G / s);
         const int unit_blocks = (kblocks + s - 1) / s;
-        const double score = rounds * (unit_blocks * 18.0 / kb_per_us + (s > 1 ? 1.0 : 0.3)) + 0.01 * s;
+        const double score = rounds * (unit_blocks * 18.0 / kb_per_us + (s > 1 ? 0.6 : 0.3)) + 0.01 * s;
         if (score < best_score) { best_score = score; best = s; }
     }
     if (g_force_packed_splits >= min_s && g_force_packed_splits <= kblocks && g_force_packed_splits <= G)
@@ -594,14 +581,10 @@ bool plan_packed(int M, int N, int K, PackedPlan* plan) {
     if (best < 0) return false;
     plan->splits = best;
     plan->bn = bn;
-    plan->cluster = g_packed_use_cluster && (best == 2 || best == 4 || best == 8);
-    // whole clusters only; never more CTAs than there is work
-    int clusters = G / best;
-    if (clusters > tiles) clusters = tiles;
-    plan->grid = plan->cluster ? clusters * best : G;
+    plan->grid = G;
     const int sfb_stride = bn == 16 ? 256 : 512;
     plan->smem = static_cast<size_t>(kStages) * kStageBytes + kMaxPartBlocks * (bn * 128) +
-                 (kMaxPartBlocks * 4 * sfb_stride + 256) + static_cast<size_t>(bn) * kTileRows * 4 + 1024;
+                 (kMaxPartBlocks * 4 * sfb_stride + 256) + 1024;
     return true;
 }
 
@@ -616,9 +599,9 @@ size_t packed_workspace_bytes(int M, int N, int K) {
     PackedPlan plan;
     if (!plan_packed(M < 32 ? M : 32, N, K, &plan)) return 16;
     const size_t tiles = N / kTileRows;
-    const size_t tickets = (tiles * sizeof(unsigned) + 255) / 256 * 256;
-    const size_t partials = plan.splits > 1 ? tiles * plan.splits * plan.bn * kTileRows * sizeof(float) : 0;
-    return tickets + partials + 256;
+    const size_t m = M < 32 ? M : 32;
+    const size_t slots = plan.splits > 1 ? tiles * (plan.splits - 1) * m * kTileRows * sizeof(unsigned long long) : 0;
+    return slots + 256;
 }
 
 cudaError_t launch_pack_weight(const void* w, const void* sf_flat, void* packed, int N, int K,
@@ -655,24 +638,23 @@ cudaError_t launch_linear_packed(const PackedLinearArgs& g, cudaStream_t stream,
         p.tiles = g.N / kTileRows;
         p.splits = plan.splits;
         p.kblocks = g.K / kBlockK;
+        p.ctas_per_part = plan.grid / plan.splits;
+        p.kb_q = p.kblocks / plan.splits;
+        p.kb_r = p.kblocks % plan.splits;
         p.pro_kind = g.pro_kind;
         p.delta = g.delta;
         p.residual_in = g.residual_in;
         p.residual_out = g.residual_out;
         p.norm_w = g.norm_w;
         p.eps = g.eps;
-        const size_t tickets = (static_cast<size_t>(p.tiles) * sizeof(unsigned) + 255) / 256 * 256;
-        p.tickets = static_cast<unsigned*>(g.workspace);
-        p.partials = reinterpret_cast<float*>(static_cast<uint8_t*>(g.workspace) + tickets);
+        p.slots = static_cast<unsigned long long*>(g.workspace);
 
-        void (*kern)(PackedParams) =
-            plan.bn == 16 ? (plan.cluster ? linear_packed_kernel<16, true> : linear_packed_kernel<16, false>)
-                          : (plan.cluster ? linear_packed_kernel<32, true> : linear_packed_kernel<32, false>);
-        static bool attr_done[4][64] = {};
+        void (*kern)(PackedParams) = plan.bn == 16 ? linear_packed_kernel<16> : linear_packed_kernel<32>;
+        static bool attr_done[2][64] = {};
         int dev = 0;
         cudaError_t e = cudaGetDevice(&dev);
         if (e != cudaSuccess) return e;
-        const int ki = (plan.bn == 16 ? 0 : 1) + (plan.cluster ? 2 : 0);
+        const int ki = plan.bn == 16 ? 0 : 1;
         if (dev >= 0 && dev < 64 && !attr_done[ki][dev]) {
             e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
             if (e != cudaSuccess) return e;
@@ -683,18 +665,11 @@ cudaError_t launch_linear_packed(const PackedLinearArgs& g, cudaStream_t stream,
         cfg.blockDim = dim3(kThreadsP);
         cfg.dynamicSmemBytes = plan.smem;
         cfg.stream = stream;
-        cudaLaunchAttribute attr[2];
+        cudaLaunchAttribute attr[1];
         int na = 0;
         if (gemv_tuning().use_pdl) {
             attr[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
             attr[na].val.programmaticStreamSerializationAllowed = 1;
-            ++na;
-        }
-        if (plan.cluster) {
-            attr[na].id = cudaLaunchAttributeClusterDimension;
-            attr[na].val.clusterDim.x = static_cast<unsigned>(plan.splits);
-            attr[na].val.clusterDim.y = 1;
-            attr[na].val.clusterDim.z = 1;
             ++na;
         }
         cfg.attrs = attr;
@@ -708,13 +683,13 @@ cudaError_t launch_linear_packed(const PackedLinearArgs& g, cudaStream_t stream,
 void set_packed_tuning(int splits) {
     g_force_packed_splits = splits & 0xff;
     g_packed_ctas_per_sm = ((splits >> 9) & 1) ? 1 : 2;
-    g_packed_use_cluster = ((splits >> 10) & 1) ? 1 : 0;
-    const int trace = (splits >> 8) & 1;
+    // bit 8: record the time line of eight CTAs; bits 12..23: the first of them
+    const int trace = ((splits >> 8) & 1) ? 1 + ((splits >> 12) & 0xfff) : 0;
     cudaMemcpyToSymbol(g_packed_trace, &trace, sizeof(int));
 }
 
-cudaError_t read_packed_trace(unsigned long long* out16) {
-    return cudaMemcpyFromSymbol(out16, g_packed_times, 64 * sizeof(unsigned long long));
+cudaError_t read_packed_trace(unsigned long long* out512) {
+    return cudaMemcpyFromSymbol(out512, g_packed_times, 8 * 64 * sizeof(unsigned long long));
 }
 
 cudaError_t read_and_clear_packed_status(int* flag) {

@@ -39,9 +39,10 @@ __device__ __forceinline__ QuantScales make_quant_scales(float gs) {
 // Returns the e4m3 scale byte; codes[0] = elements 0-7, codes[1] = 8-15.
 //   amax = max|x| ; s = gs*(amax*inv6) clamped to 448 ; sf = e4m3_rne(s)
 //   r = sf == 0 ? 0 : 1/(float(sf)*gs_rcp) ; code_i = e2m1_rne(sat6(x_i*r))
-template <int kMode>
-__device__ __forceinline__ uint32_t quantize_block16(const uint4& lo, const uint4& hi,
-                                                     const QuantScales& q, uint32_t codes[2]) {
+// `exact` selects the reciprocal: IEEE division (kRcpExact) or rcp.approx.ftz (kRcpApprox);
+// `q` must have been made for the same mode.
+__device__ __forceinline__ uint32_t quantize_block16_rt(const uint4& lo, const uint4& hi,
+                                                        const QuantScales& q, bool exact, uint32_t codes[2]) {
     const uint32_t w[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
     float f[16];
     float amax = 0.0f;
@@ -56,18 +57,21 @@ __device__ __forceinline__ uint32_t quantize_block16(const uint4& lo, const uint
     s = fminf(s, 448.0f);
     const uint32_t sf_byte = f32_to_e4m3(s);
     const float sf = e4m3_to_f32(sf_byte);
+    const float denom = __fmul_rn(sf, q.gs_rcp);
     float r;
-    if (kMode == kRcpExact) {
-        const float denom = __fmul_rn(sf, q.gs_rcp);
-        r = (denom == 0.0f) ? 0.0f : __fdiv_rn(1.0f, denom);
-    } else {
-        r = (sf != 0.0f) ? rcp_approx_ftz(__fmul_rn(sf, q.gs_rcp)) : 0.0f;
-    }
+    if (exact) r = (denom == 0.0f) ? 0.0f : __fdiv_rn(1.0f, denom);
+    else r = (sf != 0.0f) ? rcp_approx_ftz(denom) : 0.0f;
 #pragma unroll
     for (int i = 0; i < 16; ++i) f[i] = __fmul_rn(f[i], r);
     codes[0] = f32x8_to_e2m1x8(&f[0]);
     codes[1] = f32x8_to_e2m1x8(&f[8]);
     return sf_byte;
+}
+
+template <int kMode>
+__device__ __forceinline__ uint32_t quantize_block16(const uint4& lo, const uint4& hi,
+                                                     const QuantScales& q, uint32_t codes[2]) {
+    return quantize_block16_rt(lo, hi, q, kMode == kRcpExact, codes);
 }
 
 // Byte offset of scale (row, col) in the 128x4-tiled layout with `cols_padded`

@@ -143,25 +143,32 @@ def test_packed_rejects_bad_shapes(capi):
         capi.pack_weight(cuda(w), cuda(ws))
 
 
-@pytest.mark.parametrize("splits", [2, 4, 8])
-def test_linear_packed_cluster_reduction_variant(capi, splits):
-    """Optional split-K through a thread-block cluster and distributed shared memory
-    (tuning bit 10) gives the same result as the default global-scratch ticket path."""
+@pytest.mark.parametrize("splits", [2, 3, 8])
+@pytest.mark.parametrize("M", [1, 5, 16])
+def test_linear_packed_forced_splits(capi, splits, M):
+    """Split-K hand-over through the self-validating slots: any forced split count gives the
+    unsplit result up to fp32 summation order, twice in a row bit-identically, and leaves the
+    workspace all zero (the contract that lets linears share one workspace)."""
     from reset_b200 import _lib
-    N, K, M = 1024, 4096, 5
+    N, K = 1024, 4096
     w, ws = onv.random_nvfp4((N,), K, seed=15)
     xb = make_activation(M, K, seed=16).cuda()
     gs = torch.tensor([80.0], dtype=torch.float32, device="cuda")
     packed = capi.pack_weight(cuda(w), cuda(ws))
-    big = torch.zeros(8 << 20, dtype=torch.int64, device="cuda")
-    _lib.check(_lib.lib().nvfp4r_set_packed_tuning(splits), "tuning")
-    ref = capi.linear_packed(xb, gs, packed, N, 1.0, big, out_dtype=torch.float32)
-    _lib.check(_lib.lib().nvfp4r_set_packed_tuning(splits | 1024), "tuning")
-    a = capi.linear_packed(xb, gs, packed, N, 1.0, big, out_dtype=torch.float32)
-    b = capi.linear_packed(xb, gs, packed, N, 1.0, big, out_dtype=torch.float32)
-    torch.cuda.synchronize()
+    big = torch.zeros(1 << 20, dtype=torch.int64, device="cuda")
+    try:
+        _lib.check(_lib.lib().nvfp4r_set_packed_tuning(2), "tuning")     # K = 4096 needs at least 2 parts
+        ref = capi.linear_packed(xb, gs, packed, N, 1.0, big, out_dtype=torch.float32)
+        _lib.check(_lib.lib().nvfp4r_set_packed_tuning(splits), "tuning")
+        a = capi.linear_packed(xb, gs, packed, N, 1.0, big, out_dtype=torch.float32)
+        b = capi.linear_packed(xb, gs, packed, N, 1.0, big, out_dtype=torch.float32)
+        torch.cuda.synchronize()
+    finally:
+        _lib.check(_lib.lib().nvfp4r_set_packed_tuning(0), "tuning")
     assert torch.equal(a, b)
-    assert torch.equal(a, ref)          # same parts added in the same order
+    assert rel_l2(a.cpu().numpy(), ref.cpu().numpy()) <= 1e-6
+    assert int(big.count_nonzero().item()) == 0
+    _lib.check(_lib.lib().nvfp4r_check_device_status(), "device status")
 
 
 @pytest.mark.parametrize("M,with_delta", [(1, True), (1, False), (5, True)])
