@@ -566,14 +566,15 @@ bool plan_packed(int M, int N, int K, PackedPlan* plan) {
     if (min_s > G) return false;
     // Estimated time of a split count, fitted to sweeps on B200: the CTAs make
     // ceil(units / G) rounds; a round streams one unit (largest K part) at the per-CTA share
-    // of HBM bandwidth and pays a fraction of a microsecond for the partial-sum hand-over.
+    // of HBM bandwidth and pays about a microsecond per tile for the pipeline restart and the
+    // partial-sum hand-over.
     int best = -1;
     double best_score = 1e30;
     const double kb_per_us = 6400.0 * 1000.0 / 1024.0 / G;      // KB per microsecond per CTA
     for (int s = min_s; s <= kblocks && s <= G && s <= 64; ++s) {
         const int rounds = (tiles + G / s - 1) / (G / s);
         const int unit_blocks = (kblocks + s - 1) / s;
-        const double score = rounds * (unit_blocks * 18.0 / kb_per_us + (s > 1 ? 0.6 : 0.3)) + 0.01 * s;
+        const double score = rounds * (unit_blocks * 18.0 / kb_per_us + (s > 1 ? 1.2 : 0.3)) + 0.01 * s;
         if (score < best_score) { best_score = score; best = s; }
     }
     if (g_force_packed_splits >= min_s && g_force_packed_splits <= kblocks && g_force_packed_splits <= G)

@@ -5,7 +5,7 @@ import os
 
 # Largest decode batch routed to the CUDA-core GEMV. The reference defaults to 2;
 # here it is the crossover measured on B200 against the tcgen05 kernel.
-GEMV_MAX_M = int(os.environ.get("NVFP4R_GEMV_MAX_M", "2"))
+GEMV_MAX_M = int(os.environ.get("NVFP4R_GEMV_MAX_M", "4"))
 GEMM_PAD_MAX_M = int(os.environ.get("NVFP4R_GEMM_PAD_MAX_M", "63"))
 ENABLE_GEMM_PATH = os.environ.get("NVFP4R_ENABLE_GEMM", "1") == "1"
 FALLBACK_BACKEND = os.environ.get("NVFP4R_FALLBACK_BACKEND", "none").lower()
@@ -14,4 +14,4 @@ FALLBACK_BACKEND = os.environ.get("NVFP4R_FALLBACK_BACKEND", "none").lower()
 # B200 (L2-cold weights, CUDA-graph replay): the GEMV's shorter fixed latency wins only
 # for the smallest batches on weights of at most this many bytes; everything else goes
 # to the tensor cores. Index = M.
-GEMV_MAX_WEIGHT_BYTES = {1: 16_000_000, 2: 10_000_000}
+GEMV_MAX_WEIGHT_BYTES = {1: 11_000_000, 2: 6_500_000, 3: 4_800_000, 4: 2_500_000}
