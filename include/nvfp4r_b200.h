@@ -349,7 +349,12 @@ NVFP4R_API int nvfp4r_check_device_status(void);
  *   nvfp4r_add_rmsnorm      residual += x (x may be NULL); out = RMSNorm(residual) * weight
  *   nvfp4r_qk_norm_rope_kv  per-head RMSNorm on q and k, rotary embedding (rotate-half) at
  *                           *position, k/v written to caches [Hkv, Tmax, D], q to q_out
- *   nvfp4r_attn_decode      GQA attention of one token over the first *seq_len cache rows
+ *   nvfp4r_attn_decode      GQA attention of one token over the first *seq_len cache rows, one
+ *                           launch; workspace >= nvfp4r_attn_decode_workspace_bytes, ZEROED
+ *                           before the first use (it holds arrival counters that every call
+ *                           leaves at zero); *seq_len must not be written by the launch that
+ *                           directly precedes this one (cache rows of earlier tokens are
+ *                           fetched before that launch is waited for)
  *   nvfp4r_silu_mul         out[m,i] = silu(gate_up[m,i]) * gate_up[m,I+i]
  *   nvfp4r_lm_head          logits[v] = W[v,:] . x, bf16 weight, fp32 logits
  *   nvfp4r_argmax           first index of the row maximum

@@ -23,6 +23,10 @@ __device__ __forceinline__ float warp_max_f(float v) {
     for (int s = 16; s > 0; s >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, s));
     return v;
 }
+__device__ __forceinline__ uint32_t pack_bf16x2(float a, float b) {
+    const __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+    return *reinterpret_cast<const uint32_t*>(&h);
+}
 __device__ __forceinline__ float block_sum_f(float v, float* red) {      // blockDim multiple of 32
     v = warp_sum_f(v);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
@@ -117,23 +121,32 @@ qk_norm_rope_kv_kernel(const __nv_bfloat16* __restrict__ qkv, const __nv_bfloat1
     pdl_launch_dependents();
 }
 
-// GQA decode attention, split over the context. CTA (kv head, split): the chunk of K and V
-// is staged in shared memory once and shared by the `group` query heads of that kv head
-// (one warp each). Partial (max, sum, acc[128]) per (q head, split) goes to scratch.
-constexpr int kAttnChunk = 128;                                // positions per CTA
+// GQA decode attention in ONE launch, split over the context. CTA (kv head, split): the
+// chunk of K and V is staged in shared memory once and shared by the `group` query heads of
+// that kv head (one warp each); the partial (max, sum, acc[128]) per (q head, split) goes to
+// scratch, and the last CTA of a kv head to arrive (atomic ticket, nothing waits) merges the
+// partials of its heads and writes the output.
+// The cache rows of earlier tokens do not depend on the kernel that precedes this one, so they
+// are fetched BEFORE griddepcontrol.wait; only the newest row (*seq_len - 1, written by
+// qk_norm_rope_kv) and q are read after it. *seq_len itself must therefore be stable since
+// before the preceding launch (it is step input, not a product of the layer).
+constexpr int kAttnChunk = 64;                                 // positions per CTA
 constexpr int kAttnD = 128;
 constexpr int kAttnPitch = kAttnD * 2 + 16;                    // bytes per staged row (bank skew)
+constexpr int kAttnRec = kAttnD + 4;                           // floats per partial record
+constexpr int kAttnLoads = kAttnChunk * (kAttnD / 8) / 256;    // 16-byte units per thread per tensor
 
 __global__ void __launch_bounds__(256)
-attn_decode_partial_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ kcache,
-                           const __nv_bfloat16* __restrict__ vcache, const int* __restrict__ seq_len,
-                           float* __restrict__ scratch, int Hq, int Hkv, int Tmax, float scale) {
-    extern __shared__ __align__(16) uint8_t sm[];
-    uint8_t* ks = sm;
-    uint8_t* vs = sm + kAttnChunk * kAttnPitch;
-    float* qs = reinterpret_cast<float*>(vs + kAttnChunk * kAttnPitch);       // [group][128]
-    float* ps = qs + 8 * kAttnD;                                               // [group][chunk]
-    pdl_wait_prior();
+attn_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ kcache,
+                   const __nv_bfloat16* __restrict__ vcache, const int* __restrict__ seq_len,
+                   float* __restrict__ scratch, unsigned* __restrict__ tickets,
+                   __nv_bfloat16* __restrict__ out, int Hq, int Hkv, int Tmax, float scale) {
+    __shared__ __align__(16) uint8_t ks[kAttnChunk * kAttnPitch];
+    __shared__ __align__(16) uint8_t vs[kAttnChunk * kAttnPitch];
+    __shared__ __align__(16) float qs[8 * kAttnD];             // [group][128]
+    __shared__ float ps[8 * kAttnChunk];                       // [group][chunk]
+    __shared__ int s_last;
+    pdl_launch_dependents();
     const int kvh = blockIdx.x, split = blockIdx.y, n_splits = gridDim.y;
     const int group = Hq / Hkv;
     const int len = *seq_len;
@@ -141,97 +154,147 @@ attn_decode_partial_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloa
     const int np = min(kAttnChunk, len - p0);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int qh = kvh * group + warp;
-    float* my = scratch + (static_cast<int64_t>(qh) * n_splits + split) * (kAttnD + 4);
-    if (np <= 0) {
-        if (warp < group && lane == 0) { my[0] = -INFINITY; my[1] = 0.0f; }
-        return;
-    }
-    for (int i = threadIdx.x; i < np * (kAttnD / 8); i += blockDim.x) {
-        const int r = i / (kAttnD / 8), u = i % (kAttnD / 8);
-        const int64_t g = (static_cast<int64_t>(kvh) * Tmax + p0 + r) * kAttnD + u * 8;
-        *reinterpret_cast<uint4*>(ks + r * kAttnPitch + u * 16) = *reinterpret_cast<const uint4*>(kcache + g);
-        *reinterpret_cast<uint4*>(vs + r * kAttnPitch + u * 16) = *reinterpret_cast<const uint4*>(vcache + g);
-    }
-    if (warp < group)
-        for (int d = lane; d < kAttnD; d += 32)
-            qs[warp * kAttnD + d] = __bfloat162float(q[static_cast<int64_t>(qh) * kAttnD + d]) * scale;
-    __syncthreads();
-    if (warp >= group) return;
-    // scores: lane handles positions lane, lane+32, ...
-    float sc[kAttnChunk / 32];
-    float mx = -INFINITY;
+    float* my = scratch + (static_cast<int64_t>(qh) * n_splits + split) * kAttnRec;
+
+    // stage the chunk: all loads of a thread are issued before the first store
+    {
+        uint4 kk[kAttnLoads], vv[kAttnLoads];
 #pragma unroll
-    for (int j = 0; j < kAttnChunk / 32; ++j) {
-        const int r = lane + 32 * j;
-        float acc = 0.0f;
-        if (r < np) {
-            const uint8_t* row = ks + r * kAttnPitch;
-#pragma unroll 4
-            for (int u = 0; u < kAttnD / 8; ++u) {
-                const uint4 kv = *reinterpret_cast<const uint4*>(row + u * 16);
-                const float4 qa = *reinterpret_cast<const float4*>(qs + warp * kAttnD + u * 8);
-                const float4 qb = *reinterpret_cast<const float4*>(qs + warp * kAttnD + u * 8 + 4);
-                const uint32_t w[4] = {kv.x, kv.y, kv.z, kv.w};
-                acc += __uint_as_float(w[0] << 16) * qa.x + __uint_as_float(w[0] & 0xFFFF0000u) * qa.y;
-                acc += __uint_as_float(w[1] << 16) * qa.z + __uint_as_float(w[1] & 0xFFFF0000u) * qa.w;
-                acc += __uint_as_float(w[2] << 16) * qb.x + __uint_as_float(w[2] & 0xFFFF0000u) * qb.y;
-                acc += __uint_as_float(w[3] << 16) * qb.z + __uint_as_float(w[3] & 0xFFFF0000u) * qb.w;
+        for (int j = 0; j < kAttnLoads; ++j) {
+            const int i = threadIdx.x + j * 256;
+            const int r = i / (kAttnD / 8), u = i % (kAttnD / 8);
+            if (r < np && p0 + r != len - 1) {
+                const int64_t g = (static_cast<int64_t>(kvh) * Tmax + p0 + r) * kAttnD + u * 8;
+                kk[j] = ldg_stream_16(kcache + g);
+                vv[j] = ldg_stream_16(vcache + g);
             }
-            mx = fmaxf(mx, acc);
-        } else {
-            acc = -INFINITY;
         }
-        sc[j] = acc;
+#pragma unroll
+        for (int j = 0; j < kAttnLoads; ++j) {
+            const int i = threadIdx.x + j * 256;
+            const int r = i / (kAttnD / 8), u = i % (kAttnD / 8);
+            if (r < np && p0 + r != len - 1) {
+                *reinterpret_cast<uint4*>(ks + r * kAttnPitch + u * 16) = kk[j];
+                *reinterpret_cast<uint4*>(vs + r * kAttnPitch + u * 16) = vv[j];
+            }
+        }
+    }
+    pdl_wait_prior();
+    if (np > 0) {
+        const int r = len - 1 - p0;                            // the newest row, if it is in this chunk
+        if (r >= 0 && r < np && threadIdx.x < 2 * (kAttnD / 8)) {
+            const int u = threadIdx.x & (kAttnD / 8 - 1);
+            const int64_t g = (static_cast<int64_t>(kvh) * Tmax + len - 1) * kAttnD + u * 8;
+            if (threadIdx.x < kAttnD / 8)
+                *reinterpret_cast<uint4*>(ks + r * kAttnPitch + u * 16) = *reinterpret_cast<const uint4*>(kcache + g);
+            else
+                *reinterpret_cast<uint4*>(vs + r * kAttnPitch + u * 16) = *reinterpret_cast<const uint4*>(vcache + g);
+        }
+        if (warp < group)
+            for (int d = lane; d < kAttnD; d += 32)
+                qs[warp * kAttnD + d] = __bfloat162float(q[static_cast<int64_t>(qh) * kAttnD + d]) * scale;
+    }
+    __syncthreads();
+    if (warp < group) {
+        if (np <= 0) {
+            if (lane == 0) { my[0] = -INFINITY; my[1] = 0.0f; }
+        } else {
+            // scores: lane handles positions lane, lane+32
+            float sc[kAttnChunk / 32];
+            float mx = -INFINITY;
+#pragma unroll
+            for (int j = 0; j < kAttnChunk / 32; ++j) {
+                const int r = lane + 32 * j;
+                float acc = -INFINITY;
+                if (r < np) {
+                    acc = 0.0f;
+                    const uint8_t* row = ks + r * kAttnPitch;
+#pragma unroll 4
+                    for (int u = 0; u < kAttnD / 8; ++u) {
+                        const uint4 kv = *reinterpret_cast<const uint4*>(row + u * 16);
+                        const float4 qa = *reinterpret_cast<const float4*>(qs + warp * kAttnD + u * 8);
+                        const float4 qb = *reinterpret_cast<const float4*>(qs + warp * kAttnD + u * 8 + 4);
+                        const uint32_t w[4] = {kv.x, kv.y, kv.z, kv.w};
+                        acc += __uint_as_float(w[0] << 16) * qa.x + __uint_as_float(w[0] & 0xFFFF0000u) * qa.y;
+                        acc += __uint_as_float(w[1] << 16) * qa.z + __uint_as_float(w[1] & 0xFFFF0000u) * qa.w;
+                        acc += __uint_as_float(w[2] << 16) * qb.x + __uint_as_float(w[2] & 0xFFFF0000u) * qb.y;
+                        acc += __uint_as_float(w[3] << 16) * qb.z + __uint_as_float(w[3] & 0xFFFF0000u) * qb.w;
+                    }
+                    mx = fmaxf(mx, acc);
+                }
+                sc[j] = acc;
+            }
+            mx = warp_max_f(mx);
+            float sum = 0.0f;
+#pragma unroll
+            for (int j = 0; j < kAttnChunk / 32; ++j) {
+                const float e = (lane + 32 * j < np) ? __expf(sc[j] - mx) : 0.0f;
+                ps[warp * kAttnChunk + lane + 32 * j] = e;
+                sum += e;
+            }
+            sum = warp_sum_f(sum);
+            __syncwarp();
+            // weighted values: lane handles dims 4*lane .. 4*lane+3
+            float o[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+#pragma unroll 4
+            for (int r = 0; r < np; ++r) {
+                const float pr = ps[warp * kAttnChunk + r];
+                const uint2 vv = *reinterpret_cast<const uint2*>(vs + r * kAttnPitch + lane * 8);
+                o[0] += pr * __uint_as_float(vv.x << 16);
+                o[1] += pr * __uint_as_float(vv.x & 0xFFFF0000u);
+                o[2] += pr * __uint_as_float(vv.y << 16);
+                o[3] += pr * __uint_as_float(vv.y & 0xFFFF0000u);
+            }
+            if (lane == 0) { my[0] = mx; my[1] = sum; }
+            __stcg(reinterpret_cast<float4*>(my + 4 + lane * 4), make_float4(o[0], o[1], o[2], o[3]));
+        }
+    }
+    // ticket: the barrier orders every warp's partial stores before thread 0's fence + atomic
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        __threadfence();
+        const unsigned t = atomicAdd(tickets + kvh, 1u);
+        s_last = (t == static_cast<unsigned>(n_splits) - 1u) ? 1 : 0;
+        if (s_last) tickets[kvh] = 0u;
+        __threadfence();
+    }
+    __syncthreads();
+    if (!s_last || warp >= group) return;
+    // merge the splits of this warp's head: lane s owns the (max, sum) of split s0 + s, the
+    // accumulator loads of a group of splits are independent of one another
+    const float* base = scratch + static_cast<int64_t>(qh) * n_splits * kAttnRec;
+    float mx = -INFINITY;
+    for (int s = lane; s < n_splits; s += 32) {
+        const float2 ms = __ldcg(reinterpret_cast<const float2*>(base + s * kAttnRec));
+        if (ms.y > 0.0f) mx = fmaxf(mx, ms.x);
     }
     mx = warp_max_f(mx);
-    float sum = 0.0f;
-#pragma unroll
-    for (int j = 0; j < kAttnChunk / 32; ++j) {
-        const float e = (lane + 32 * j < np) ? __expf(sc[j] - mx) : 0.0f;
-        ps[warp * kAttnChunk + lane + 32 * j] = e;
-        sum += e;
-    }
-    sum = warp_sum_f(sum);
-    __syncwarp();
-    // weighted values: lane handles dims 4*lane .. 4*lane+3
-    float o[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-    for (int r = 0; r < np; ++r) {
-        const float pr = ps[warp * kAttnChunk + r];
-        const uint2 vv = *reinterpret_cast<const uint2*>(vs + r * kAttnPitch + lane * 8);
-        o[0] += pr * __uint_as_float(vv.x << 16);
-        o[1] += pr * __uint_as_float(vv.x & 0xFFFF0000u);
-        o[2] += pr * __uint_as_float(vv.y << 16);
-        o[3] += pr * __uint_as_float(vv.y & 0xFFFF0000u);
-    }
-    if (lane == 0) { my[0] = mx; my[1] = sum; }
-    *reinterpret_cast<float4*>(my + 4 + lane * 4) = make_float4(o[0], o[1], o[2], o[3]);
-    pdl_launch_dependents();
-}
-
-// Merge the per-split partials of one q head (one warp per head).
-__global__ void __launch_bounds__(128)
-attn_decode_combine_kernel(const float* __restrict__ scratch, __nv_bfloat16* __restrict__ out, int Hq,
-                           int n_splits) {
-    pdl_wait_prior();
-    const int qh = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-    const int lane = threadIdx.x & 31;
-    if (qh >= Hq) return;
-    const float* base = scratch + static_cast<int64_t>(qh) * n_splits * (kAttnD + 4);
-    float mx = -INFINITY;
-    for (int s = 0; s < n_splits; ++s) mx = fmaxf(mx, base[s * (kAttnD + 4)]);
     float denom = 0.0f, o[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-    for (int s = 0; s < n_splits; ++s) {
-        const float* p = base + s * (kAttnD + 4);
-        const float w = (p[1] > 0.0f) ? __expf(p[0] - mx) : 0.0f;
-        denom += w * p[1];
-        const float4 a = *reinterpret_cast<const float4*>(p + 4 + lane * 4);
-        o[0] += w * a.x; o[1] += w * a.y; o[2] += w * a.z; o[3] += w * a.w;
+    for (int s0 = 0; s0 < n_splits; s0 += 32) {
+        float wgt = 0.0f;
+        if (s0 + lane < n_splits) {
+            const float2 ms = __ldcg(reinterpret_cast<const float2*>(base + (s0 + lane) * kAttnRec));
+            if (ms.y > 0.0f) {
+                wgt = __expf(ms.x - mx);
+                denom += wgt * ms.y;
+            }
+        }
+        const int cnt = min(32, n_splits - s0);
+#pragma unroll 8
+        for (int j = 0; j < cnt; ++j) {
+            const float w = __shfl_sync(0xffffffffu, wgt, j);
+            const float4 a = __ldcg(reinterpret_cast<const float4*>(base + (s0 + j) * kAttnRec + 4 + lane * 4));
+            // a split without positions left its record unwritten: select, do not multiply
+            o[0] += (w > 0.0f) ? w * a.x : 0.0f;
+            o[1] += (w > 0.0f) ? w * a.y : 0.0f;
+            o[2] += (w > 0.0f) ? w * a.z : 0.0f;
+            o[3] += (w > 0.0f) ? w * a.w : 0.0f;
+        }
     }
+    denom = warp_sum_f(denom);
     const float inv = 1.0f / denom;
-    __nv_bfloat16* dst = out + static_cast<int64_t>(qh) * kAttnD + lane * 4;
-#pragma unroll
-    for (int j = 0; j < 4; ++j) dst[j] = __float2bfloat16_rn(o[j] * inv);
-    pdl_launch_dependents();
+    const uint32_t lo = pack_bf16x2(o[0] * inv, o[1] * inv), hi = pack_bf16x2(o[2] * inv, o[3] * inv);
+    *reinterpret_cast<uint2*>(out + static_cast<int64_t>(qh) * kAttnD + lane * 4) = make_uint2(lo, hi);
 }
 
 // out[m, i] = silu(gate_up[m, i]) * gate_up[m, I + i]
@@ -383,7 +446,8 @@ int nvfp4r_qk_norm_rope_kv(const void* qkv, const void* q_weight, const void* k_
 
 size_t nvfp4r_attn_decode_workspace_bytes(int Hq, int Tmax) {
     const size_t splits = (static_cast<size_t>(Tmax) + kAttnChunk - 1) / kAttnChunk;
-    return static_cast<size_t>(Hq) * splits * (kAttnD + 4) * sizeof(float);
+    // partial records, then one ticket per kv head (at most Hq of them)
+    return static_cast<size_t>(Hq) * splits * kAttnRec * sizeof(float) + static_cast<size_t>(Hq) * sizeof(unsigned);
 }
 
 int nvfp4r_attn_decode(const void* q, const void* kcache, const void* vcache, const int32_t* seq_len,
@@ -393,21 +457,13 @@ int nvfp4r_attn_decode(const void* q, const void* kcache, const void* vcache, co
     if (D != 128 || Hkv <= 0 || Hq % Hkv != 0 || Hq / Hkv > 8) return NVFP4R_ERR_UNSUPPORTED_SHAPE;
     if (workspace_bytes < nvfp4r_attn_decode_workspace_bytes(Hq, Tmax)) return NVFP4R_ERR_INVALID_ARGUMENT;
     const int splits = (Tmax + kAttnChunk - 1) / kAttnChunk;
-    const size_t smem = 2 * kAttnChunk * kAttnPitch + 8 * kAttnD * 4 + 8 * kAttnChunk * 4;
-    static bool attr_done = false;
-    if (!attr_done) {
-        cudaError_t e = cudaFuncSetAttribute(attn_decode_partial_kernel,
-                                             cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
-        if (e != cudaSuccess) return NVFP4R_ERR_CUDA;
-        attr_done = true;
-    }
-    cudaError_t e = launch_pdl(attn_decode_partial_kernel, dim3(Hkv, splits), dim3(256), smem, st(stream),
-                               static_cast<const __nv_bfloat16*>(q), static_cast<const __nv_bfloat16*>(kcache),
-                               static_cast<const __nv_bfloat16*>(vcache), seq_len,
-                               static_cast<float*>(workspace), Hq, Hkv, Tmax, rsqrtf(static_cast<float>(D)));
-    if (e != cudaSuccess) return NVFP4R_ERR_CUDA;
-    return done(launch_pdl(attn_decode_combine_kernel, dim3((Hq + 3) / 4), dim3(128), 0, st(stream),
-                           static_cast<const float*>(workspace), static_cast<__nv_bfloat16*>(out), Hq, splits));
+    if (splits > 65535) return NVFP4R_ERR_UNSUPPORTED_SHAPE;
+    float* records = static_cast<float*>(workspace);
+    unsigned* tickets = reinterpret_cast<unsigned*>(records + static_cast<size_t>(Hq) * splits * kAttnRec);
+    return done(launch_pdl(attn_decode_kernel, dim3(Hkv, splits), dim3(256), 0, st(stream),
+                           static_cast<const __nv_bfloat16*>(q), static_cast<const __nv_bfloat16*>(kcache),
+                           static_cast<const __nv_bfloat16*>(vcache), seq_len, records, tickets,
+                           static_cast<__nv_bfloat16*>(out), Hq, Hkv, Tmax, rsqrtf(static_cast<float>(D))));
 }
 
 int nvfp4r_silu_mul(const void* gate_up, void* out, int M, int I, void* stream) {

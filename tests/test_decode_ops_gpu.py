@@ -94,6 +94,12 @@ def test_qk_norm_rope_kv_and_attention(lib):
         sc = torch.einsum("hgd,htd->hgt", qf, kf) / math.sqrt(D)
         want = torch.einsum("hgt,htd->hgd", torch.softmax(sc, -1), vf).reshape(1, Hq * D)
         assert torch.allclose(out.float(), want, rtol=2e-2, atol=1e-2), seq
+        # the arrival counters are back at zero: a second call on the same workspace agrees bit for bit
+        out2 = torch.empty_like(out)
+        lib.check(lib.lib().nvfp4r_attn_decode(q.data_ptr(), kc.data_ptr(), vc.data_ptr(), seq_len.data_ptr(),
+                                               out2.data_ptr(), Hq, Hkv, D, T, ws.data_ptr(), ws.numel() * 4, _s()),
+                  "attn")
+        assert torch.equal(out, out2)
 
 
 def test_silu_mul_lm_head_argmax(lib):
