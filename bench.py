@@ -139,6 +139,10 @@ def make_inputs(shards, device, seed):
 
 
 _T0 = time.perf_counter()
+# Libraries (NCCL's version banner) write to file descriptor 1; the JSON line must be alone on
+# stdout, so keep a private handle on the real stdout and point descriptor 1 at stderr.
+_STDOUT = os.fdopen(os.dup(1), "w")
+os.dup2(2, 1)
 
 
 def stage(rank: int, what: str) -> None:
@@ -168,6 +172,10 @@ def run_ours(args, rank, world, local_rank):
     gs = torch.tensor([100.0], dtype=torch.float32, device=device)
     pinned_out = {(name, M): torch.empty((M, n), dtype=torch.bfloat16).pin_memory()
                   for name, n, k, style, _ in shards for M in M_VALUES}
+    peer = None
+    if world > 1 and args.allreduce == "peer":
+        from reset_b200.comm import PeerAllReduce
+        peer = PeerAllReduce(device, max(M_VALUES) * HIDDEN)
     counters = {name: 0 for name, *_ in shards}
     path_used = {}
     gemv_max_m = nvfp4r.status()["gemv_max_m"]
@@ -178,7 +186,10 @@ def run_ours(args, rank, world, local_rank):
         out = nvfp4r.linear_auto(x, gs, w, s, packed, n, 1.0, torch.bfloat16)
         path_used[(name, M)] = "gemv" if (packed is None or nvfp4r.ops.use_gemv(M, n, k, gemv_max_m)) else "tcgen05"
         if world > 1 and style == "row":
-            dist.all_reduce(out)
+            if peer is not None:
+                peer.all_reduce_(out)
+            else:
+                dist.all_reduce(out)
         return out
 
     def step_resident():
@@ -257,12 +268,12 @@ def run_ours(args, rank, world, local_rank):
     sampler = ClockSampler(local_rank) if rank == 0 else None
     g_res = capture_phases(step_resident)
     stage(rank, "resident graphs captured")
-    # keep the GPU busy long enough before the timed region for clock samples to exist
-    t_end = time.perf_counter() + 0.4
-    while time.perf_counter() < t_end:
+    # keep the GPU busy long enough before the timed region for clock samples to exist; a FIXED
+    # number of replays, the same on every rank (the graphs contain the all-reduces)
+    for _ in range(800):
         for g in g_res:
             g.replay()
-        torch.cuda.synchronize()
+    torch.cuda.synchronize()
     ms_total = timed(g_res, args.steps, args.warmup)
     timed_launches = args.steps * 16
     stage(rank, "resident timed")
@@ -330,7 +341,9 @@ def run_ours(args, rank, world, local_rank):
                    "launches_per_step": 16, "weight_copies": WEIGHT_COPIES,
                    "l2": "every launch reads a weight copy not touched for >1 GB of traffic (inputs larger than L2)",
                    "launch": "CUDA-graph replay, one graph per step",
-                   "parallelism": f"tp{world}"},
+                   "parallelism": f"tp{world}",
+                   "allreduce": "none" if world == 1 else
+                                ("one-shot kernel over NVLink peer memory" if peer is not None else "NCCL")},
         "e2e": {"value": round(gbs_e2e, 1), "unit": "GB/s",
                 "h2d_bytes_per_step": h2d_bytes, "d2h_bytes_per_step": d2h_bytes},
         "gpu_launches": timed_launches,
@@ -360,7 +373,7 @@ def run_decode(args, rank, world, device):
     cfg = QWEN3_32B
     if args.decode_layers:                     # fewer layers of the same geometry: profiler captures
         cfg = dataclasses.replace(cfg, layers=args.decode_layers, name=f"{cfg.name} ({args.decode_layers} layers)")
-    model = DecodeStep(cfg, device, rank=rank, world=world, seed=11)
+    model = DecodeStep(cfg, device, rank=rank, world=world, seed=11, peer_allreduce=(args.allreduce == "peer"))
     if args.decode_eager:
         for _ in range(args.decode_steps):
             model.step()
@@ -391,7 +404,8 @@ def run_decode(args, rank, world, device):
            "hbm_bytes_per_token_per_gpu": bytes_rank,
            "roofline_tok_s": round(peak * 1e9 / bytes_rank, 1),
            "frac_of_hbm_roofline": round((bytes_rank / (ms_tok * 1e-3) / 1e9) / peak, 4),
-           "launch": "one CUDA graph per token", "kernels_per_token": model.kernels_per_step()}
+           "launch": "one CUDA graph per token", "kernels_per_token": model.kernels_per_step(),
+           "allreduce": "none" if world == 1 else ("peer one-shot" if model.peer is not None else "NCCL")}
     del model
     torch.cuda.empty_cache()
     return out
@@ -667,6 +681,8 @@ def main():
     ap.add_argument("--sweep-m", default="1,2,3,4,6,8,12,16")
     ap.add_argument("--reset-loop", action="store_true", help="ReSET decode-loop step time vs the CPU oracle")
     ap.add_argument("--reset-steps", type=int, default=256)
+    ap.add_argument("--allreduce", default="peer", choices=["peer", "nccl"],
+                    help="sum exchange after row-parallel linears at N > 1: this library's one-shot kernel or NCCL")
     ap.add_argument("--watchdog", type=int, default=1200,
                     help="seconds after which every rank dumps its Python stacks to stderr and exits")
     args = ap.parse_args()
@@ -687,8 +703,12 @@ def main():
         if not torch.cuda.is_available():
             raise SystemExit("bench.py: no CUDA device (there is no CPU fallback for the product path)")
         line = run_ours(args, rank, world, local_rank)
+    if args.impl == "ours" and torch.cuda.is_available():
+        from reset_b200 import _lib
+        _lib.check(_lib.lib().nvfp4r_check_device_status(), "a bounded device-side wait expired during the run")
     if line is not None:
-        print(json.dumps(line), flush=True)
+        _STDOUT.write(json.dumps(line) + "\n")
+        _STDOUT.flush()
     if world > 1 and args.impl == "ours":
         # Leave without tearing the communicator down: NCCL's destroy waits for every CUDA
         # graph that captured a collective, and graph objects die in interpreter-defined

@@ -337,6 +337,43 @@ NVFP4R_API int nvfp4r_entropy(const float* logits, int64_t row_stride, int B, in
  * ------------------------------------------------------------------------- */
 NVFP4R_API int nvfp4r_set_gemv_tuning(int ctas_per_sm, int use_pdl, int force_generic);
 
+/* ------------------------------------------------------------------------- *
+ * One-shot all-reduce (sum) of a small bf16 tensor over NVLink peer memory: the exchange
+ * after a row-parallel linear (o_proj, down_proj) under tensor parallelism, one launch per
+ * rank, no library collective. In the reference's deployment this step is vLLM's
+ * tensor_model_parallel_all_reduce inside RowParallelLinear (the reference itself only
+ * consumes the per-partition sizes, kernels/python/nvfp4r/vllm_integration.py:461-462).
+ * Every rank adds the W contributions in rank order in fp32 and rounds once, so all ranks
+ * hold identical bits.
+ *   set-up (host, once; these calls allocate / map memory, the all-reduce itself does not):
+ *     nvfp4r_peer_buffer_bytes(world, max_elems)  size of one rank's receive memory
+ *     nvfp4r_peer_alloc(bytes, &ptr, handle)      zeroed device memory + its 64-byte IPC handle
+ *     nvfp4r_peer_open(handle, &peer_ptr)         map a peer's memory (another process, same node)
+ *     nvfp4r_peer_close / nvfp4r_peer_free
+ *   nvfp4r_peer_allreduce_bf16(comm, in, out, count, mode, stream)
+ *     comm->base[r] = receive memory of rank r as seen from THIS process (own: the local
+ *     pointer); count even, <= comm->max_elems; in/out 4-byte aligned, may alias.
+ *     mode NVFP4R_PEER_PUSH | NVFP4R_PEER_GATHER (= 3) is the all-reduce; the two halves can be
+ *     launched separately (push on every rank first, then gather) where ranks share one GPU.
+ * Every rank must issue the same sequence of calls. A wait for a peer that never pushes ends
+ * after a bounded number of polls and sets the status read by nvfp4r_check_device_status.
+ * ------------------------------------------------------------------------- */
+#define NVFP4R_PEER_MAX_WORLD 8
+enum { NVFP4R_PEER_PUSH = 1, NVFP4R_PEER_GATHER = 2, NVFP4R_PEER_ALLREDUCE = 3 };
+typedef struct nvfp4r_peer_comm {
+    int world;
+    int rank;
+    size_t max_elems;
+    void* base[NVFP4R_PEER_MAX_WORLD];
+} nvfp4r_peer_comm;
+NVFP4R_API size_t nvfp4r_peer_buffer_bytes(int world, size_t max_elems);
+NVFP4R_API int nvfp4r_peer_alloc(size_t bytes, void** ptr, unsigned char* handle64);
+NVFP4R_API int nvfp4r_peer_open(const unsigned char* handle64, void** peer_ptr);
+NVFP4R_API int nvfp4r_peer_close(void* peer_ptr);
+NVFP4R_API int nvfp4r_peer_free(void* ptr);
+NVFP4R_API int nvfp4r_peer_allreduce_bf16(const nvfp4r_peer_comm* comm, const void* in, void* out,
+                                          size_t count, int mode, void* stream);
+
 /* Reads and clears the device-side time-out flag of the current device
  * (synchronises the device; diagnostics only). Returns 0, or
  * NVFP4R_ERR_DEVICE_TIMEOUT if a bounded wait inside a kernel gave up. */

@@ -46,6 +46,15 @@ class Prologue(C.Structure):
 
 PROLOGUE_NONE, PROLOGUE_ADD_RMSNORM, PROLOGUE_SILU_MUL = 0, 1, 2
 
+PEER_MAX_WORLD = 8
+PEER_PUSH, PEER_GATHER, PEER_ALLREDUCE = 1, 2, 3
+
+
+class PeerComm(C.Structure):
+    _fields_ = [("world", C.c_int), ("rank", C.c_int), ("max_elems", C.c_size_t),
+                ("base", C.c_void_p * PEER_MAX_WORLD)]
+
+
 _vp, _i, _i64, _f, _sz = C.c_void_p, C.c_int, C.c_int64, C.c_float, C.c_size_t
 
 # name -> (restype, argtypes); every symbol include/nvfp4r_b200.h declares
@@ -84,6 +93,12 @@ PROTOTYPES = {
     "nvfp4r_silu_mul": (_i, [_vp, _vp, _i, _i, _vp]),
     "nvfp4r_lm_head": (_i, [_vp, _vp, _vp, _i, _i, _vp]),
     "nvfp4r_argmax": (_i, [_vp, _i64, _i, _i, _vp, _vp]),
+    "nvfp4r_peer_buffer_bytes": (_sz, [_i, _sz]),
+    "nvfp4r_peer_alloc": (_i, [_sz, C.POINTER(C.c_void_p), C.c_char_p]),
+    "nvfp4r_peer_open": (_i, [C.c_char_p, C.POINTER(C.c_void_p)]),
+    "nvfp4r_peer_close": (_i, [_vp]),
+    "nvfp4r_peer_free": (_i, [_vp]),
+    "nvfp4r_peer_allreduce_bf16": (_i, [C.POINTER(PeerComm), _vp, _vp, _sz, _i, _vp]),
     "nvfp4r_check_device_status": (_i, []),
 }
 

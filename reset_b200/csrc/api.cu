@@ -451,8 +451,10 @@ int nvfp4r_check_device_status(void) {
     int flag3 = 0;
     if (e == cudaSuccess) e = nvfp4r::read_and_clear_tc_status(&flag2);
     if (e == cudaSuccess) e = nvfp4r::read_and_clear_packed_status(&flag3);
+    int flag4 = 0;
+    if (e == cudaSuccess) e = nvfp4r::read_and_clear_peer_status(&flag4);
     if (e != cudaSuccess) return cuda_fail(e, "device status");
-    flag |= flag2 | flag3;
+    flag |= flag2 | flag3 | flag4;
     return flag ? fail(NVFP4R_ERR_DEVICE_TIMEOUT, "a bounded device-side wait gave up") : NVFP4R_OK;
 }
 

@@ -110,6 +110,8 @@ cudaError_t read_packed_trace(unsigned long long* out16);
 // inside the kernels and clears it.
 cudaError_t read_and_clear_device_status(int* flag);
 
+cudaError_t read_and_clear_peer_status(int* flag);
+
 int device_sm_count();
 
 }  // namespace nvfp4r

@@ -3,7 +3,8 @@
 Builds random-initialised weights of the named geometry directly as NVFP4 codes + block
 scales (no bf16 master copy), shards them tensor-parallel (column: qkv, gate_up; row: o,
 down), and runs one token through all layers with this library's kernels only; the
-all-reduce after the two row-parallel linears of every layer is NCCL. The whole step is
+all-reduce after the two row-parallel linears of every layer is this library's one-shot
+kernel over peer memory (`comm.PeerAllReduce`) or, on request, NCCL. The whole step is
 captured in one CUDA graph. This is benchmark scaffolding: the reference leaves the model
 to vLLM and has no counterpart for this file.
 """
@@ -98,7 +99,7 @@ class Workspace:
 
 class DecodeStep:
     def __init__(self, cfg: DecodeConfig, device, rank: int = 0, world: int = 1, seed: int = 0,
-                 process_group=None, fused: bool = True):
+                 process_group=None, fused: bool = True, peer_allreduce: bool = True):
         if cfg.q_heads % world or cfg.kv_heads % world or cfg.intermediate % world or cfg.vocab % world:
             raise ValueError("tensor-parallel degree must divide heads, intermediate and vocab")
         self.cfg, self.device, self.rank, self.world, self.pg = cfg, torch.device(device), rank, world, process_group
@@ -146,6 +147,11 @@ class DecodeStep:
         n = L.lib().nvfp4r_attn_decode_workspace_bytes(self.hq, cfg.context)
         self.attn_ws = torch.zeros((n + 3) // 4, dtype=torch.float32, device=self.device)
         self.graph = None
+        # the sum exchange after o_proj / down_proj: one-shot kernel over peer memory, or NCCL
+        self.peer = None
+        if world > 1 and peer_allreduce:
+            from .comm import PeerAllReduce
+            self.peer = PeerAllReduce(self.device, H, group=process_group)
         self._calibrate()
 
     # -- thin wrappers over the C ABI ------------------------------------------------
@@ -171,7 +177,9 @@ class DecodeStep:
                                        self.attn_ws.numel() * 4, self._stream()), "attn_decode")
 
     def _all_reduce(self, t):
-        if self.world > 1:
+        if self.peer is not None:
+            self.peer.all_reduce_(t)
+        elif self.world > 1:
             torch.distributed.all_reduce(t, group=self.pg)
 
     # -- the step ---------------------------------------------------------------------

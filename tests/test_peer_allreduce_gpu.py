@@ -1,0 +1,127 @@
+"""One-shot peer-memory all-reduce (`nvfp4r_peer_allreduce_bf16`).
+
+On one GPU the ranks are emulated without any kernel waiting for another: every rank's PUSH
+half runs first, then every rank's GATHER half (all data is in place when a gather starts).
+With two or more GPUs the real thing runs as one process per GPU (spawned children), checked
+against the rank-ordered fp32 sum and against NCCL."""
+
+import ctypes as C
+import os
+import subprocess
+import sys
+from pathlib import Path
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+REPO = Path(__file__).resolve().parents[1]
+
+
+def _expected(parts):
+    acc = torch.zeros_like(parts[0], dtype=torch.float32)
+    for p in parts:                                   # rank order, fp32, one rounding
+        acc += p.float()
+    return acc.to(torch.bfloat16)
+
+
+@pytest.mark.parametrize("world", [2, 3, 8])
+def test_emulated_ranks_on_one_gpu(world):
+    from reset_b200 import _lib as L
+    lib = L.lib()
+    max_elems = 5120 * 2
+    nbytes = lib.nvfp4r_peer_buffer_bytes(world, max_elems)
+    assert nbytes == 256 + 2 * world * (max_elems // 2) * 8
+    ptrs = []
+    for _ in range(world):
+        p, h = C.c_void_p(), C.create_string_buffer(64)
+        L.check(lib.nvfp4r_peer_alloc(nbytes, C.byref(p), h), "alloc")
+        ptrs.append(p)
+    try:
+        comms = []
+        for r in range(world):
+            c = L.PeerComm()
+            c.world, c.rank, c.max_elems = world, r, max_elems
+            for k in range(world):
+                c.base[k] = ptrs[k].value
+            comms.append(c)
+        g = torch.Generator(device="cuda").manual_seed(world)
+        stream = torch.cuda.current_stream().cuda_stream
+        for call, count in enumerate([5120, 2, max_elems, 5120, 4096]):        # parity flips every call
+            parts = [torch.randn(count, device="cuda", generator=g).to(torch.bfloat16) for _ in range(world)]
+            outs = [torch.empty_like(p) for p in parts]
+            for r in range(world):
+                L.check(lib.nvfp4r_peer_allreduce_bf16(C.byref(comms[r]), parts[r].data_ptr(), outs[r].data_ptr(),
+                                                       count, L.PEER_PUSH, stream), "push")
+            for r in range(world):
+                L.check(lib.nvfp4r_peer_allreduce_bf16(C.byref(comms[r]), parts[r].data_ptr(), outs[r].data_ptr(),
+                                                       count, L.PEER_GATHER, stream), "gather")
+            torch.cuda.synchronize()
+            want = _expected(parts)
+            for r in range(world):
+                assert torch.equal(outs[r], want), (call, r)
+        L.check(lib.nvfp4r_check_device_status(), "device status")
+        # argument checks
+        x = torch.zeros(6, dtype=torch.bfloat16, device="cuda")
+        assert lib.nvfp4r_peer_allreduce_bf16(C.byref(comms[0]), x.data_ptr(), x.data_ptr(), 5, 3, stream) != 0
+        assert lib.nvfp4r_peer_allreduce_bf16(C.byref(comms[0]), x.data_ptr(), x.data_ptr(), max_elems + 2, 3, stream) != 0
+        assert lib.nvfp4r_peer_allreduce_bf16(C.byref(comms[0]), x.data_ptr(), x.data_ptr(), 6, 0, stream) != 0
+    finally:
+        torch.cuda.synchronize()
+        for p in ptrs:
+            lib.nvfp4r_peer_free(p)
+
+
+_CHILD = r"""
+import os, sys
+sys.path.insert(0, os.environ["REPO"])
+import torch, torch.distributed as dist
+rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+dev = torch.device("cuda", rank); torch.cuda.set_device(dev)
+dist.init_process_group("nccl", device_id=dev)
+from reset_b200.comm import PeerAllReduce
+from reset_b200 import _lib as L
+ar = PeerAllReduce(dev, 8 * 5120)
+ok = True
+for call, count in enumerate([5120, 2, 8 * 5120, 5120, 10240, 5120]):
+    parts = [torch.randn(count, device=dev, generator=torch.Generator(device=dev).manual_seed(100 * call + r)).to(torch.bfloat16)
+             for r in range(world)]
+    acc = torch.zeros(count, device=dev)
+    for p in parts: acc += p.float()
+    want = acc.to(torch.bfloat16)
+    mine = parts[rank].clone()
+    ar.all_reduce_(mine)
+    nccl = parts[rank].clone(); dist.all_reduce(nccl)
+    torch.cuda.synchronize()
+    ok = ok and torch.equal(mine, want) and torch.allclose(mine.float(), nccl.float(), rtol=1e-2, atol=1e-2)
+# graph capture and replay (the call counter advances on the device)
+x = torch.ones(5120, device=dev, dtype=torch.bfloat16) * (rank + 1)
+buf = x.clone()
+s = torch.cuda.Stream(); s.wait_stream(torch.cuda.current_stream())
+with torch.cuda.stream(s):
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g, stream=s):
+        buf.copy_(x); ar.all_reduce_(buf)
+        buf.copy_(x); ar.all_reduce_(buf); ar.all_reduce_(buf)
+torch.cuda.current_stream().wait_stream(s)
+for _ in range(5): g.replay()
+torch.cuda.synchronize()
+tot = world * (world + 1) // 2
+ok = ok and bool((buf.float() == tot * world).all())
+L.check(L.lib().nvfp4r_check_device_status(), "status")
+flag = torch.tensor([1 if ok else 0], device=dev); dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+dist.barrier(); torch.cuda.synchronize()
+print("PEER_OK" if int(flag.item()) == 1 else "PEER_MISMATCH", flush=True)
+os._exit(0 if int(flag.item()) == 1 else 1)
+"""
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_two_processes_two_gpus(tmp_path):
+    script = tmp_path / "child.py"
+    script.write_text(_CHILD)
+    env = dict(os.environ, REPO=str(REPO), NCCL_NVLS_ENABLE="0")
+    r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2",
+                        "--master-addr", "127.0.0.1", "--master-port", "29533", str(script)],
+                       env=env, capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0 and r.stdout.count("PEER_OK") == 2, (r.stdout[-2000:], r.stderr[-3000:])
