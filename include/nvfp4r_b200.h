@@ -403,6 +403,13 @@ NVFP4R_API int nvfp4r_qk_norm_rope_kv(const void* qkv, const void* q_weight, con
                                       const int32_t* position, void* kcache, void* vcache,
                                       void* q_out, int Hq, int Hkv, int D, int Tmax, float theta,
                                       float eps, void* stream);
+/* nvfp4r_attn_decode_rope = nvfp4r_qk_norm_rope_kv + nvfp4r_attn_decode in one launch: `qkv`
+ * is the raw fused row [(Hq + 2 Hkv) * D]; the token's position is *seq_len - 1; the new K/V row
+ * is appended to the caches by the launch itself. Same workspace rule as nvfp4r_attn_decode. */
+NVFP4R_API int nvfp4r_attn_decode_rope(const void* qkv, const void* q_weight, const void* k_weight,
+                                       void* kcache, void* vcache, const int32_t* seq_len, void* out,
+                                       int Hq, int Hkv, int D, int Tmax, float theta, float eps,
+                                       void* workspace, size_t workspace_bytes, void* stream);
 NVFP4R_API size_t nvfp4r_attn_decode_workspace_bytes(int Hq, int Tmax);
 NVFP4R_API int nvfp4r_attn_decode(const void* q, const void* kcache, const void* vcache,
                                   const int32_t* seq_len, void* out, int Hq, int Hkv, int D,

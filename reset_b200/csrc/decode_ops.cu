@@ -71,6 +71,31 @@ add_rmsnorm_kernel(const __nv_bfloat16* __restrict__ x, __nv_bfloat16* __restric
     pdl_launch_dependents();
 }
 
+// RMSNorm(head) * w followed by the rotary embedding (rotate-half pairs d, d + D/2) of one
+// 128-wide head by one warp: lane holds dims lane, lane+32 (first half), lane+64, lane+96.
+__device__ __forceinline__ void head_norm_rope(const __nv_bfloat16* __restrict__ src,
+                                               const __nv_bfloat16* __restrict__ w, int pos, float theta,
+                                               float eps, int lane, float o[4]) {
+    constexpr int D = 128;
+    float v[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) v[j] = __bfloat162float(src[lane + 32 * j]);
+    const float ss = v[0] * v[0] + v[1] * v[1] + v[2] * v[2] + v[3] * v[3];
+    const float inv = rsqrtf(warp_sum_f(ss) / static_cast<float>(D) + eps);
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+        v[j] = __bfloat162float(__float2bfloat16_rn(v[j] * inv * __bfloat162float(w[lane + 32 * j])));
+#pragma unroll
+    for (int j = 0; j < 2; ++j) {
+        const int d = lane + 32 * j;                           // 0..63
+        const float freq = powf(theta, -static_cast<float>(2 * d) / static_cast<float>(D));
+        float sn, cs;
+        sincosf(static_cast<float>(pos) * freq, &sn, &cs);
+        o[j] = v[j] * cs - v[j + 2] * sn;
+        o[j + 2] = v[j + 2] * cs + v[j] * sn;
+    }
+}
+
 // One warp per head of the fused qkv row: q and k heads get RMSNorm(head) * w and the
 // rotary embedding (rotate-half pairs d, d + D/2); k and v are written to the cache at
 // `*position`; q goes to q_out. D == 128.
@@ -98,22 +123,8 @@ qk_norm_rope_kv_kernel(const __nv_bfloat16* __restrict__ qkv, const __nv_bfloat1
         return;
     }
     const bool is_q = head < Hq;
-    const __nv_bfloat16* w = is_q ? q_w : k_w;
-    float ss = v[0] * v[0] + v[1] * v[1] + v[2] * v[2] + v[3] * v[3];
-    const float inv = rsqrtf(warp_sum_f(ss) / static_cast<float>(D) + eps);
-#pragma unroll
-    for (int j = 0; j < 4; ++j)
-        v[j] = __bfloat162float(__float2bfloat16_rn(v[j] * inv * __bfloat162float(w[lane + 32 * j])));
     float o[4];
-#pragma unroll
-    for (int j = 0; j < 2; ++j) {
-        const int d = lane + 32 * j;                           // 0..63
-        const float freq = powf(theta, -static_cast<float>(2 * d) / static_cast<float>(D));
-        float s, c;
-        sincosf(static_cast<float>(pos) * freq, &s, &c);
-        o[j] = v[j] * c - v[j + 2] * s;
-        o[j + 2] = v[j + 2] * c + v[j] * s;
-    }
+    head_norm_rope(src, is_q ? q_w : k_w, pos, theta, eps, lane, o);
     __nv_bfloat16* dst = is_q ? q_out + static_cast<int64_t>(head) * D
                               : kcache + (static_cast<int64_t>(head - Hq) * Tmax + pos) * D;
 #pragma unroll
@@ -121,30 +132,61 @@ qk_norm_rope_kv_kernel(const __nv_bfloat16* __restrict__ qkv, const __nv_bfloat1
     pdl_launch_dependents();
 }
 
-// GQA decode attention in ONE launch, split over the context. CTA (kv head, split): the
-// chunk of K and V is staged in shared memory once and shared by the `group` query heads of
-// that kv head (one warp each); the partial (max, sum, acc[128]) per (q head, split) goes to
-// scratch, and the last CTA of a kv head to arrive (atomic ticket, nothing waits) merges the
-// partials of its heads and writes the output.
+// GQA decode attention in ONE launch, split over the context. CTA (kv head, split) stages its
+// chunk of K and V in shared memory once for the `group` (<= 8) query heads of that kv head and
+// runs both products on the tensor cores (mma.sync m16n8k16, bf16 in, fp32 accumulate; the
+// heads are the M rows of the tile, padded to 16):
+//   warp w: S[heads, 16 positions] = Q K^T over its 16 positions of the chunk -> chunk-wide
+//   max through shared memory -> P = exp(S - max) as bf16 in shared memory -> warp w:
+//   O[heads, 16 dims] = P V over ALL positions of the chunk for its 16 output dims.
+// The partial (max, sum, O[128]) per (q head, split) goes to scratch, and the last CTA of a kv
+// head to arrive (atomic ticket, nothing waits) merges the partials of its heads.
 // The cache rows of earlier tokens do not depend on the kernel that precedes this one, so they
 // are fetched BEFORE griddepcontrol.wait; only the newest row (*seq_len - 1, written by
 // qk_norm_rope_kv) and q are read after it. *seq_len itself must therefore be stable since
 // before the preceding launch (it is step input, not a product of the layer).
-constexpr int kAttnChunk = 64;                                 // positions per CTA
+constexpr int kAttnChunk = 128;                                // positions per CTA
 constexpr int kAttnD = 128;
-constexpr int kAttnPitch = kAttnD * 2 + 16;                    // bytes per staged row (bank skew)
+constexpr int kAttnPitch = kAttnD * 2 + 16;                    // bytes per staged row (bank skew, 16-byte aligned)
 constexpr int kAttnRec = kAttnD + 4;                           // floats per partial record
 constexpr int kAttnLoads = kAttnChunk * (kAttnD / 8) / 256;    // 16-byte units per thread per tensor
+constexpr size_t kAttnSmem = (2 * kAttnChunk + 32) * kAttnPitch;   // K, V, Q (16 rows), P (16 rows)
 
+__device__ __forceinline__ void ldsm_x4(uint32_t r[4], uint32_t addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void ldsm_x4_trans(uint32_t r[4], uint32_t addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void mma_bf16_16816(float c[4], const uint32_t a[4], uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+// kFusedRope: `q` is the raw fused qkv row [(Hq + 2 Hkv) * 128]; the CTA applies the q/k head
+// norms and the rotary embedding itself (what qk_norm_rope_kv does as a separate launch) and the
+// CTA whose chunk holds the newest position appends the new K/V row to the caches.
+struct AttnRope {
+    const __nv_bfloat16* q_w;
+    const __nv_bfloat16* k_w;
+    float theta, eps;
+};
+
+template <bool kFusedRope>
 __global__ void __launch_bounds__(256)
-attn_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ kcache,
-                   const __nv_bfloat16* __restrict__ vcache, const int* __restrict__ seq_len,
+attn_decode_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __restrict__ kcache,
+                   __nv_bfloat16* __restrict__ vcache, const int* __restrict__ seq_len,
                    float* __restrict__ scratch, unsigned* __restrict__ tickets,
-                   __nv_bfloat16* __restrict__ out, int Hq, int Hkv, int Tmax, float scale) {
-    __shared__ __align__(16) uint8_t ks[kAttnChunk * kAttnPitch];
-    __shared__ __align__(16) uint8_t vs[kAttnChunk * kAttnPitch];
-    __shared__ __align__(16) float qs[8 * kAttnD];             // [group][128]
-    __shared__ float ps[8 * kAttnChunk];                       // [group][chunk]
+                   __nv_bfloat16* __restrict__ out, int Hq, int Hkv, int Tmax, float scale, AttnRope rope) {
+    extern __shared__ __align__(16) uint8_t sm[];
+    uint8_t* ks = sm;
+    uint8_t* vs = ks + kAttnChunk * kAttnPitch;
+    uint8_t* qs = vs + kAttnChunk * kAttnPitch;                // bf16 [16][pitch], rows >= group unused
+    uint8_t* pb = qs + 16 * kAttnPitch;                        // bf16 [16][pitch]: P over the chunk
+    __shared__ float smax[8][8], ssum[8][8];                   // [warp][head]
     __shared__ int s_last;
     pdl_launch_dependents();
     const int kvh = blockIdx.x, split = blockIdx.y, n_splits = gridDim.y;
@@ -153,8 +195,7 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
     const int p0 = split * kAttnChunk;
     const int np = min(kAttnChunk, len - p0);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int qh = kvh * group + warp;
-    float* my = scratch + (static_cast<int64_t>(qh) * n_splits + split) * kAttnRec;
+    const int qh = kvh * group + warp;                         // the head this warp merges at the end
 
     // stage the chunk: all loads of a thread are issued before the first store
     {
@@ -167,13 +208,16 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
                 const int64_t g = (static_cast<int64_t>(kvh) * Tmax + p0 + r) * kAttnD + u * 8;
                 kk[j] = ldg_stream_16(kcache + g);
                 vv[j] = ldg_stream_16(vcache + g);
+            } else {
+                kk[j] = make_uint4(0, 0, 0, 0);                // rows past the end: finite values (P is 0 there)
+                vv[j] = kk[j];
             }
         }
 #pragma unroll
         for (int j = 0; j < kAttnLoads; ++j) {
             const int i = threadIdx.x + j * 256;
             const int r = i / (kAttnD / 8), u = i % (kAttnD / 8);
-            if (r < np && p0 + r != len - 1) {
+            if (p0 + r != len - 1) {
                 *reinterpret_cast<uint4*>(ks + r * kAttnPitch + u * 16) = kk[j];
                 *reinterpret_cast<uint4*>(vs + r * kAttnPitch + u * 16) = vv[j];
             }
@@ -182,72 +226,133 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
     pdl_wait_prior();
     if (np > 0) {
         const int r = len - 1 - p0;                            // the newest row, if it is in this chunk
-        if (r >= 0 && r < np && threadIdx.x < 2 * (kAttnD / 8)) {
-            const int u = threadIdx.x & (kAttnD / 8 - 1);
-            const int64_t g = (static_cast<int64_t>(kvh) * Tmax + len - 1) * kAttnD + u * 8;
-            if (threadIdx.x < kAttnD / 8)
-                *reinterpret_cast<uint4*>(ks + r * kAttnPitch + u * 16) = *reinterpret_cast<const uint4*>(kcache + g);
-            else
-                *reinterpret_cast<uint4*>(vs + r * kAttnPitch + u * 16) = *reinterpret_cast<const uint4*>(vcache + g);
+        if (!kFusedRope) {
+            if (r >= 0 && r < np && threadIdx.x < 2 * (kAttnD / 8)) {
+                const int u = threadIdx.x & (kAttnD / 8 - 1);
+                const int64_t g = (static_cast<int64_t>(kvh) * Tmax + len - 1) * kAttnD + u * 8;
+                if (threadIdx.x < kAttnD / 8)
+                    *reinterpret_cast<uint4*>(ks + r * kAttnPitch + u * 16) = *reinterpret_cast<const uint4*>(kcache + g);
+                else
+                    *reinterpret_cast<uint4*>(vs + r * kAttnPitch + u * 16) = *reinterpret_cast<const uint4*>(vcache + g);
+            }
+            // q heads of this kv head: 16 rows x 16 units of 16 bytes, rows >= group zero
+            const int r16 = threadIdx.x >> 4, u = threadIdx.x & 15;
+            uint4 v4 = make_uint4(0, 0, 0, 0);
+            if (r16 < group)
+                v4 = *reinterpret_cast<const uint4*>(q + (static_cast<int64_t>(kvh) * group + r16) * kAttnD + u * 8);
+            *reinterpret_cast<uint4*>(qs + r16 * kAttnPitch + u * 16) = v4;
+        } else {
+            // the row position is len - 1 (the token being decoded)
+            if (warp < group) {
+                float o[4];
+                head_norm_rope(q + static_cast<int64_t>(qh) * kAttnD, rope.q_w, len - 1, rope.theta, rope.eps, lane, o);
+                __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(qs + warp * kAttnPitch);
+#pragma unroll
+                for (int j = 0; j < 4; ++j) dst[lane + 32 * j] = __float2bfloat16_rn(o[j]);
+            }
+            if (r >= 0 && r < np) {
+                // new K row (warp 0) and V row (warp 1): into shared memory and into the caches
+                const int64_t g = (static_cast<int64_t>(kvh) * Tmax + len - 1) * kAttnD;
+                if (warp == 0) {
+                    float o[4];
+                    head_norm_rope(q + static_cast<int64_t>(Hq + kvh) * kAttnD, rope.k_w, len - 1, rope.theta, rope.eps, lane, o);
+                    __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(ks + r * kAttnPitch);
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        const __nv_bfloat16 b = __float2bfloat16_rn(o[j]);
+                        dst[lane + 32 * j] = b;
+                        kcache[g + lane + 32 * j] = b;
+                    }
+                } else if (warp == 1) {
+                    const __nv_bfloat16* src = q + static_cast<int64_t>(Hq + Hkv + kvh) * kAttnD;
+                    __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(vs + r * kAttnPitch);
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        const __nv_bfloat16 b = src[lane + 32 * j];
+                        dst[lane + 32 * j] = b;
+                        vcache[g + lane + 32 * j] = b;
+                    }
+                }
+            }
         }
-        if (warp < group)
-            for (int d = lane; d < kAttnD; d += 32)
-                qs[warp * kAttnD + d] = __bfloat162float(q[static_cast<int64_t>(qh) * kAttnD + d]) * scale;
     }
     __syncthreads();
-    if (warp < group) {
-        if (np <= 0) {
-            if (lane == 0) { my[0] = -INFINITY; my[1] = 0.0f; }
-        } else {
-            // scores: lane handles positions lane, lane+32
-            float sc[kAttnChunk / 32];
-            float mx = -INFINITY;
+    if (np > 0) {
+        const uint32_t ks_a = smem_u32(ks), vs_a = smem_u32(vs), qs_a = smem_u32(qs), pb_a = smem_u32(pb);
+        const int h = lane >> 2;                               // head row of this thread's c0/c1
+        // ---- S = Q K^T for this warp's 16 positions -------------------------------------------
+        float sc[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
 #pragma unroll
-            for (int j = 0; j < kAttnChunk / 32; ++j) {
-                const int r = lane + 32 * j;
-                float acc = -INFINITY;
-                if (r < np) {
-                    acc = 0.0f;
-                    const uint8_t* row = ks + r * kAttnPitch;
-#pragma unroll 4
-                    for (int u = 0; u < kAttnD / 8; ++u) {
-                        const uint4 kv = *reinterpret_cast<const uint4*>(row + u * 16);
-                        const float4 qa = *reinterpret_cast<const float4*>(qs + warp * kAttnD + u * 8);
-                        const float4 qb = *reinterpret_cast<const float4*>(qs + warp * kAttnD + u * 8 + 4);
-                        const uint32_t w[4] = {kv.x, kv.y, kv.z, kv.w};
-                        acc += __uint_as_float(w[0] << 16) * qa.x + __uint_as_float(w[0] & 0xFFFF0000u) * qa.y;
-                        acc += __uint_as_float(w[1] << 16) * qa.z + __uint_as_float(w[1] & 0xFFFF0000u) * qa.w;
-                        acc += __uint_as_float(w[2] << 16) * qb.x + __uint_as_float(w[2] & 0xFFFF0000u) * qb.y;
-                        acc += __uint_as_float(w[3] << 16) * qb.z + __uint_as_float(w[3] & 0xFFFF0000u) * qb.w;
-                    }
-                    mx = fmaxf(mx, acc);
-                }
-                sc[j] = acc;
-            }
-            mx = warp_max_f(mx);
-            float sum = 0.0f;
+        for (int kt = 0; kt < kAttnD / 16; kt += 2) {
+            uint32_t a0[4], a1[4];
+            ldsm_x4(a0, qs_a + (lane & 15) * kAttnPitch + kt * 32 + (lane >> 4) * 16);
+            ldsm_x4(a1, qs_a + (lane & 15) * kAttnPitch + (kt + 1) * 32 + (lane >> 4) * 16);
 #pragma unroll
-            for (int j = 0; j < kAttnChunk / 32; ++j) {
-                const float e = (lane + 32 * j < np) ? __expf(sc[j] - mx) : 0.0f;
-                ps[warp * kAttnChunk + lane + 32 * j] = e;
-                sum += e;
+            for (int nt = 0; nt < 2; ++nt) {
+                uint32_t b[4];                                 // {k 0-7, k 8-15} of kt, then of kt + 1
+                ldsm_x4(b, ks_a + (16 * warp + 8 * nt + (lane & 7)) * kAttnPitch + kt * 32 + (lane >> 3) * 16);
+                mma_bf16_16816(sc[nt], a0, b[0], b[1]);
+                mma_bf16_16816(sc[nt], a1, b[2], b[3]);
             }
-            sum = warp_sum_f(sum);
-            __syncwarp();
-            // weighted values: lane handles dims 4*lane .. 4*lane+3
-            float o[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-#pragma unroll 4
-            for (int r = 0; r < np; ++r) {
-                const float pr = ps[warp * kAttnChunk + r];
-                const uint2 vv = *reinterpret_cast<const uint2*>(vs + r * kAttnPitch + lane * 8);
-                o[0] += pr * __uint_as_float(vv.x << 16);
-                o[1] += pr * __uint_as_float(vv.x & 0xFFFF0000u);
-                o[2] += pr * __uint_as_float(vv.y << 16);
-                o[3] += pr * __uint_as_float(vv.y & 0xFFFF0000u);
-            }
-            if (lane == 0) { my[0] = mx; my[1] = sum; }
-            __stcg(reinterpret_cast<float4*>(my + 4 + lane * 4), make_float4(o[0], o[1], o[2], o[3]));
         }
+        float mx = -INFINITY;
+#pragma unroll
+        for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+                const int pos = 16 * warp + 8 * nt + (lane & 3) * 2 + e;
+                sc[nt][e] = (pos < np) ? sc[nt][e] * scale : -INFINITY;
+                mx = fmaxf(mx, sc[nt][e]);
+            }
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+        if ((lane & 3) == 0) smax[warp][h] = mx;
+        __syncthreads();
+        float m = smax[0][h];
+#pragma unroll
+        for (int w = 1; w < 8; ++w) m = fmaxf(m, smax[w][h]);
+        // ---- P = exp(S - max) as bf16, and this warp's share of the sums ------------------------
+        float sum = 0.0f;
+#pragma unroll
+        for (int nt = 0; nt < 2; ++nt) {
+            const float e0 = __expf(sc[nt][0] - m), e1 = __expf(sc[nt][1] - m);     // exp(-inf) = 0
+            const uint32_t pk = pack_bf16x2(e0, e1);
+            // the sums use the rounded values, like the product below
+            sum += __uint_as_float(pk << 16) + __uint_as_float(pk & 0xFFFF0000u);
+            *reinterpret_cast<uint32_t*>(pb + h * kAttnPitch + (16 * warp + 8 * nt + (lane & 3) * 2) * 2) = pk;
+        }
+        sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+        sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+        if ((lane & 3) == 0) ssum[warp][h] = sum;
+        __syncthreads();
+        // ---- O[heads, 16 dims of this warp] = P V over the whole chunk -----------------------------
+        float o[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+#pragma unroll
+        for (int kt = 0; kt < kAttnChunk / 16; ++kt) {
+            uint32_t a[4], b[4];
+            ldsm_x4(a, pb_a + (lane & 15) * kAttnPitch + kt * 32 + (lane >> 4) * 16);
+            // V rows are positions (k), columns are dims (n): transposed 8x8 loads give the col-major fragment
+            ldsm_x4_trans(b, vs_a + (16 * kt + (lane & 7) + ((lane >> 3) & 1) * 8) * kAttnPitch +
+                                 (16 * warp + (lane >> 4) * 8) * 2);
+            mma_bf16_16816(o[0], a, b[0], b[1]);
+            mma_bf16_16816(o[1], a, b[2], b[3]);
+        }
+        if (h < group) {
+            float* rec = scratch + (static_cast<int64_t>(kvh * group + h) * n_splits + split) * kAttnRec;
+#pragma unroll
+            for (int nt = 0; nt < 2; ++nt)
+                __stcg(reinterpret_cast<float2*>(rec + 4 + 16 * warp + 8 * nt + (lane & 3) * 2),
+                       make_float2(o[nt][0], o[nt][1]));
+            if (warp == 0 && (lane & 3) == 0) {
+                float tot = 0.0f;
+#pragma unroll
+                for (int w = 0; w < 8; ++w) tot += ssum[w][h];
+                __stcg(reinterpret_cast<float2*>(rec), make_float2(m, tot));
+            }
+        }
+    } else if (warp < group && lane == 0) {
+        float* rec = scratch + (static_cast<int64_t>(qh) * n_splits + split) * kAttnRec;
+        __stcg(reinterpret_cast<float2*>(rec), make_float2(-INFINITY, 0.0f));
     }
     // ticket: the barrier orders every warp's partial stores before thread 0's fence + atomic
     __syncthreads();
@@ -450,9 +555,9 @@ size_t nvfp4r_attn_decode_workspace_bytes(int Hq, int Tmax) {
     return static_cast<size_t>(Hq) * splits * kAttnRec * sizeof(float) + static_cast<size_t>(Hq) * sizeof(unsigned);
 }
 
-int nvfp4r_attn_decode(const void* q, const void* kcache, const void* vcache, const int32_t* seq_len,
-                       void* out, int Hq, int Hkv, int D, int Tmax, void* workspace,
-                       size_t workspace_bytes, void* stream) {
+static int attn_launch(bool fused, const void* q, void* kcache, void* vcache, const int32_t* seq_len, void* out,
+                       int Hq, int Hkv, int D, int Tmax, void* workspace, size_t workspace_bytes, AttnRope rope,
+                       void* stream) {
     if (!q || !kcache || !vcache || !seq_len || !out || !workspace) return NVFP4R_ERR_INVALID_ARGUMENT;
     if (D != 128 || Hkv <= 0 || Hq % Hkv != 0 || Hq / Hkv > 8) return NVFP4R_ERR_UNSUPPORTED_SHAPE;
     if (workspace_bytes < nvfp4r_attn_decode_workspace_bytes(Hq, Tmax)) return NVFP4R_ERR_INVALID_ARGUMENT;
@@ -460,10 +565,35 @@ int nvfp4r_attn_decode(const void* q, const void* kcache, const void* vcache, co
     if (splits > 65535) return NVFP4R_ERR_UNSUPPORTED_SHAPE;
     float* records = static_cast<float*>(workspace);
     unsigned* tickets = reinterpret_cast<unsigned*>(records + static_cast<size_t>(Hq) * splits * kAttnRec);
-    return done(launch_pdl(attn_decode_kernel, dim3(Hkv, splits), dim3(256), 0, st(stream),
-                           static_cast<const __nv_bfloat16*>(q), static_cast<const __nv_bfloat16*>(kcache),
-                           static_cast<const __nv_bfloat16*>(vcache), seq_len, records, tickets,
-                           static_cast<__nv_bfloat16*>(out), Hq, Hkv, Tmax, rsqrtf(static_cast<float>(D))));
+    auto kern = fused ? attn_decode_kernel<true> : attn_decode_kernel<false>;
+    static bool attr_done[2][64] = {};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) return NVFP4R_ERR_CUDA;
+    if (dev >= 0 && dev < 64 && !attr_done[fused ? 1 : 0][dev]) {
+        if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 static_cast<int>(kAttnSmem)) != cudaSuccess) return NVFP4R_ERR_CUDA;
+        attr_done[fused ? 1 : 0][dev] = true;
+    }
+    return done(launch_pdl(kern, dim3(Hkv, splits), dim3(256), kAttnSmem, st(stream),
+                           static_cast<const __nv_bfloat16*>(q), static_cast<__nv_bfloat16*>(kcache),
+                           static_cast<__nv_bfloat16*>(vcache), seq_len, records, tickets,
+                           static_cast<__nv_bfloat16*>(out), Hq, Hkv, Tmax, rsqrtf(static_cast<float>(D)), rope));
+}
+
+int nvfp4r_attn_decode(const void* q, const void* kcache, const void* vcache, const int32_t* seq_len,
+                       void* out, int Hq, int Hkv, int D, int Tmax, void* workspace,
+                       size_t workspace_bytes, void* stream) {
+    return attn_launch(false, q, const_cast<void*>(kcache), const_cast<void*>(vcache), seq_len, out, Hq, Hkv, D,
+                       Tmax, workspace, workspace_bytes, AttnRope{nullptr, nullptr, 0.0f, 0.0f}, stream);
+}
+
+int nvfp4r_attn_decode_rope(const void* qkv, const void* q_weight, const void* k_weight, void* kcache,
+                            void* vcache, const int32_t* seq_len, void* out, int Hq, int Hkv, int D, int Tmax,
+                            float theta, float eps, void* workspace, size_t workspace_bytes, void* stream) {
+    if (!q_weight || !k_weight) return NVFP4R_ERR_INVALID_ARGUMENT;
+    return attn_launch(true, qkv, kcache, vcache, seq_len, out, Hq, Hkv, D, Tmax, workspace, workspace_bytes,
+                       AttnRope{static_cast<const __nv_bfloat16*>(q_weight),
+                                static_cast<const __nv_bfloat16*>(k_weight), theta, eps}, stream);
 }
 
 int nvfp4r_silu_mul(const void* gate_up, void* out, int M, int I, void* stream) {

@@ -11,8 +11,9 @@
 //   3. reset_scale_kernel    : divides the slice by the temperature in place;
 //      rows whose temperature is exactly 1 are left untouched (x/1 == x).
 //
-// Kernels 2 and 3 are launched with programmatic stream serialization so their
-// launch latency overlaps the tail of the kernel before them.
+// All three are launched with programmatic stream serialization and release their
+// dependents at once, so launch latency overlaps the kernel before; each reads what the
+// previous kernel wrote only after griddepcontrol.wait.
 #include "kernels.h"
 #include "nvfp4_ptx.cuh"
 #include "reset_kernels.h"
@@ -63,6 +64,7 @@ __device__ __forceinline__ bool row_active(const ResetLaunch& p, int row, int* s
 // ---- kernel 1 ---------------------------------------------------------------
 __global__ void __launch_bounds__(kThreads)
 reset_partials_kernel(const ResetLaunch p) {
+    pdl_launch_dependents();
     pdl_wait_prior();
     const int row = blockIdx.y, slice = blockIdx.x;
     int slot;
@@ -128,7 +130,6 @@ reset_partials_kernel(const ResetLaunch p) {
         rs->parg[slice] = barg;
         if (slice == 0) rs->ticket = 0u;
     }
-    pdl_launch_dependents();
 }
 
 // ---- the per-request state machine (one thread) --------------------------------
@@ -202,20 +203,24 @@ reset_entropy_kernel(const ResetLaunch p) {
     __shared__ double s_part[kThreads / 32];
     __shared__ bool s_last;
 
+    pdl_launch_dependents();
     pdl_wait_prior();
-    // Row max and denominator from the slice partials (same order in every CTA).
-    float rmax = -INFINITY;
-    int rarg = 0x7fffffff;
-    for (int s = 0; s < p.n_slices; ++s) {
-        const float m = rs->pmax[s];
-        const int a = rs->parg[s];
-        if (m > rmax || (m == rmax && a < rarg)) { rmax = m; rarg = a; }
+    // Row max and denominator from the slice partials: lane s owns slice s (at most 32
+    // slices), the reductions are fixed shuffle trees, so every warp of every CTA of the row
+    // computes the same bits.
+    const int lane_m = threadIdx.x % 32;
+    float rmax = (lane_m < p.n_slices) ? rs->pmax[lane_m] : -INFINITY;
+    int rarg = (lane_m < p.n_slices) ? rs->parg[lane_m] : 0x7fffffff;
+    const float my_max = rmax;
+    const float my_sum = (lane_m < p.n_slices) ? rs->psum[lane_m] : 0.0f;
+#pragma unroll
+    for (int s = 16; s > 0; s >>= 1) {
+        const float om = __shfl_xor_sync(0xffffffffu, rmax, s);
+        const int oa = __shfl_xor_sync(0xffffffffu, rarg, s);
+        if (om > rmax || (om == rmax && oa < rarg)) { rmax = om; rarg = oa; }
     }
-    double denom_d = 0.0;
-    for (int s = 0; s < p.n_slices; ++s) {
-        const float ps = rs->psum[s];
-        if (ps > 0.0f) denom_d += static_cast<double>(ps) * exp(static_cast<double>(rs->pmax[s]) - rmax);
-    }
+    double denom_d = (my_sum > 0.0f) ? static_cast<double>(my_sum) * exp(static_cast<double>(my_max) - rmax) : 0.0;
+    denom_d = warp_sum(denom_d);
     const float denom = static_cast<float>(denom_d);
 
     double part = 0.0;
@@ -257,7 +262,6 @@ reset_entropy_kernel(const ResetLaunch p) {
         if (p.entropy_out != nullptr) p.entropy_out[row] = ent_f;
         if (p.needs_state) reset_decide(p, row, slot, static_cast<double>(ent_f), rarg, rs);
     }
-    pdl_launch_dependents();
 }
 
 // ---- kernel 3 ---------------------------------------------------------------
@@ -265,6 +269,7 @@ __global__ void __launch_bounds__(kThreads)
 reset_scale_kernel(const ResetLaunch p) {
     const int row = blockIdx.y, slice = blockIdx.x;
     int slot;
+    pdl_launch_dependents();
     if (!row_active(p, row, &slot)) return;
     pdl_wait_prior();
     const RowScratch* rs = p.scratch + row;

@@ -166,6 +166,15 @@ class DecodeStep:
     def _attention(self, layer, qkv):
         c = self.cfg
         lib = L.lib()
+        if self.fused:
+            # head norms + rotary + cache append + attention in one launch
+            L.check(lib.nvfp4r_attn_decode_rope(qkv.data_ptr(), layer["qn"].data_ptr(), layer["kn"].data_ptr(),
+                                                layer["k"].data_ptr(), layer["v"].data_ptr(),
+                                                self.seq_len.data_ptr(), self.attn.data_ptr(), self.hq, self.hkv,
+                                                c.head_dim, c.context, c.rope_theta, c.eps,
+                                                self.attn_ws.data_ptr(), self.attn_ws.numel() * 4, self._stream()),
+                    "attn_decode_rope")
+            return
         L.check(lib.nvfp4r_qk_norm_rope_kv(qkv.data_ptr(), layer["qn"].data_ptr(), layer["kn"].data_ptr(),
                                            self.position.data_ptr(), layer["k"].data_ptr(),
                                            layer["v"].data_ptr(), self.q.data_ptr(), self.hq, self.hkv,
@@ -186,7 +195,8 @@ class DecodeStep:
     def step(self) -> None:
         """One token: embedding row -> all layers -> logits -> arg-max into ``self.token``.
         With ``fused`` the two RMSNorms and the SiLU*up of a layer run inside the prologue of
-        the linear that consumes them (7 launches per layer instead of 10)."""
+        the linear that consumes them and the head norms / rotary embedding / cache append inside
+        the attention launch (5 launches per layer instead of 9)."""
         c = self.cfg
         lib = L.lib()
         cur = 0
@@ -262,4 +272,4 @@ class DecodeStep:
         return lin + kv + self.vocab_local * c.hidden * 2
 
     def kernels_per_step(self) -> int:
-        return self.cfg.layers * (7 if self.fused else 10) + 5
+        return self.cfg.layers * (5 if self.fused else 9) + 5

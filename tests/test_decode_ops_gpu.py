@@ -102,6 +102,40 @@ def test_qk_norm_rope_kv_and_attention(lib):
         assert torch.equal(out, out2)
 
 
+@pytest.mark.parametrize("pos", [0, 127, 128, 300, 511])
+def test_attention_with_fused_rope_equals_two_launches(lib, pos):
+    """nvfp4r_attn_decode_rope (head norms + rotary + cache append + attention in one launch)
+    against nvfp4r_qk_norm_rope_kv followed by nvfp4r_attn_decode: same caches bit for bit, same
+    attention output bit for bit (the same arithmetic runs in both)."""
+    Hq, Hkv, D, T = 16, 2, 128, 512
+    g = torch.Generator(device="cuda").manual_seed(10 + pos)
+    qkv = torch.randn(1, (Hq + 2 * Hkv) * D, device="cuda", generator=g).to(torch.bfloat16)
+    qw = (1 + 0.1 * torch.randn(D, device="cuda", generator=g)).to(torch.bfloat16)
+    kw = (1 + 0.1 * torch.randn(D, device="cuda", generator=g)).to(torch.bfloat16)
+    kc = (torch.randn(Hkv, T, D, device="cuda", generator=g) * 0.5).to(torch.bfloat16)
+    vc = (torch.randn(Hkv, T, D, device="cuda", generator=g) * 0.5).to(torch.bfloat16)
+    kc2, vc2 = kc.clone(), vc.clone()
+    position = torch.tensor([pos], dtype=torch.int32, device="cuda")
+    seq_len = torch.tensor([pos + 1], dtype=torch.int32, device="cuda")
+    n = lib.lib().nvfp4r_attn_decode_workspace_bytes(Hq, T)
+    ws = torch.zeros(n // 4 + 1, dtype=torch.float32, device="cuda")
+    q = torch.empty(1, Hq * D, dtype=torch.bfloat16, device="cuda")
+    out_a = torch.empty(1, Hq * D, dtype=torch.bfloat16, device="cuda")
+    out_b = torch.empty_like(out_a)
+    lib.check(lib.lib().nvfp4r_qk_norm_rope_kv(qkv.data_ptr(), qw.data_ptr(), kw.data_ptr(), position.data_ptr(),
+                                               kc.data_ptr(), vc.data_ptr(), q.data_ptr(), Hq, Hkv, D, T, 1e6,
+                                               1e-6, _s()), "qk")
+    lib.check(lib.lib().nvfp4r_attn_decode(q.data_ptr(), kc.data_ptr(), vc.data_ptr(), seq_len.data_ptr(),
+                                           out_a.data_ptr(), Hq, Hkv, D, T, ws.data_ptr(), ws.numel() * 4, _s()),
+              "attn")
+    lib.check(lib.lib().nvfp4r_attn_decode_rope(qkv.data_ptr(), qw.data_ptr(), kw.data_ptr(), kc2.data_ptr(),
+                                                vc2.data_ptr(), seq_len.data_ptr(), out_b.data_ptr(), Hq, Hkv, D,
+                                                T, 1e6, 1e-6, ws.data_ptr(), ws.numel() * 4, _s()), "attn_rope")
+    torch.cuda.synchronize()
+    assert torch.equal(kc, kc2) and torch.equal(vc, vc2)
+    assert torch.equal(out_a, out_b)
+
+
 def test_silu_mul_lm_head_argmax(lib):
     g = torch.Generator(device="cuda").manual_seed(2)
     I = 3072

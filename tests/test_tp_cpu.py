@@ -74,3 +74,16 @@ def test_shard_shapes_of_the_named_models():
     with pytest.raises(ValueError):
         tp.shard_shape(128, 100, "row", 4)
     assert tp.needs_all_reduce("row", 2) and not tp.needs_all_reduce("column", 8) and not tp.needs_all_reduce("row", 1)
+
+
+def test_peer_allreduce_single_rank_is_a_no_op():
+    """Without a process group the peer all-reduce has one rank: nothing is allocated, the
+    tensor comes back untouched (no CUDA call is made, so this runs without a GPU)."""
+    import torch
+    from reset_b200.comm import PeerAllReduce
+
+    ar = PeerAllReduce("cpu", 1000)
+    assert ar.world == 1 and ar.comm is None
+    t = torch.arange(8, dtype=torch.float32).to(torch.bfloat16)
+    assert ar.all_reduce_(t) is t
+    ar.close()
