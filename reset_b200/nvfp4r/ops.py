@@ -77,12 +77,35 @@ def use_gemv(M: int, N: int, K: int, gemv_max_m: int) -> bool:
     return limit is not None and N * K * 9 // 16 <= limit
 
 
+_OUT_WORKSPACE: dict = {}          # device -> zeroed split-K workspace of the out= path
+
+
+def _out_workspace(device, nbytes: int) -> torch.Tensor:
+    ws = _OUT_WORKSPACE.get(device)
+    if ws is None or ws.numel() * 8 < nbytes:
+        # grown outside any stream capture: callers warm a shape up eagerly before capturing it
+        ws = torch.zeros((max(nbytes, 1 << 20) + 7) // 8, dtype=torch.int64, device=device)
+        _OUT_WORKSPACE[device] = ws
+    return ws
+
+
 def linear_auto(x, global_scale_inv, weight, weight_scale_flat, packed, N: int, alpha: float,
-                out_dtype: torch.dtype = torch.bfloat16, rcp_mode: int = 1) -> torch.Tensor:
+                out_dtype: torch.dtype = torch.bfloat16, rcp_mode: int = 1,
+                out: Optional[torch.Tensor] = None) -> torch.Tensor:
     """One decode linear through whichever kernel the measured crossover picks. ``packed``
-    may be None (shape outside the tensor-core kernel's N % 128 / K % 256)."""
+    may be None (shape outside the tensor-core kernel's N % 128 / K % 256). With ``out`` (a
+    contiguous ``[M, N]`` tensor) the result is written there and nothing is allocated: the
+    out-variant convention of the reference's raw ops (kernels/csrc/bindings.cpp:27-84)."""
     from . import _config
     M, K = x.shape
-    if packed is None or (weight is not None and use_gemv(M, N, K, _config.GEMV_MAX_M)):
-        return linear(x, global_scale_inv, weight, weight_scale_flat, alpha, out_dtype, rcp_mode)
-    return linear_packed(x, global_scale_inv, packed, N, alpha, out_dtype, rcp_mode)
+    gemv = packed is None or (weight is not None and use_gemv(M, N, K, _config.GEMV_MAX_M))
+    if out is None:
+        if gemv:
+            return linear(x, global_scale_inv, weight, weight_scale_flat, alpha, out_dtype, rcp_mode)
+        return linear_packed(x, global_scale_inv, packed, N, alpha, out_dtype, rcp_mode)
+    from .. import _lib as L
+    from .. import capi
+    if gemv:
+        return capi.linear(x, global_scale_inv, weight, weight_scale_flat, alpha, out=out, rcp_mode=rcp_mode)
+    ws = _out_workspace(x.device, L.lib().nvfp4r_linear_packed_workspace_bytes(M, N, K))
+    return capi.linear_packed(x, global_scale_inv, packed, N, alpha, ws, rcp_mode=rcp_mode, out=out)

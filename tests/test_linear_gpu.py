@@ -89,3 +89,21 @@ def test_linear_rejects_m_above_limit(capi):
     gs = torch.tensor([1.0], dtype=torch.float32, device="cuda")
     with pytest.raises(_lib.Nvfp4rError):
         capi.linear(xb, gs, cuda(w), cuda(ws), 1.0)
+
+
+@pytest.mark.parametrize("N,K,M", [(4096, 1024, 1), (6144, 4096, 2), (1024, 4096, 8)])
+def test_linear_auto_out_variant(N, K, M):
+    """`linear_auto(..., out=buf)` writes the same bits into a caller-owned buffer as the
+    allocating call returns, on both sides of the crossover."""
+    from reset_b200 import nvfp4r
+    w, ws = onv.random_nvfp4((N,), K, seed=31)
+    wd, wsd = cuda(w), cuda(ws)
+    packed = nvfp4r.pack_weight(wd, wsd)
+    x = make_activation(M, K, seed=32).cuda()
+    gs = torch.tensor([50.0], dtype=torch.float32, device="cuda")
+    want = nvfp4r.linear_auto(x, gs, wd, wsd, packed, N, 0.75, torch.bfloat16)
+    buf = torch.full((M + 1, N), 7.0, dtype=torch.bfloat16, device="cuda")
+    got = nvfp4r.linear_auto(x, gs, wd, wsd, packed, N, 0.75, torch.bfloat16, out=buf[:M])
+    torch.cuda.synchronize()
+    assert got.data_ptr() == buf.data_ptr()
+    assert torch.equal(buf[:M], want) and bool((buf[M] == 7.0).all())
