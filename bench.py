@@ -180,13 +180,11 @@ def run_ours(args, rank, world, local_rank):
     def one_linear(name, n, k, style, copies, M, x):
         w, s, packed = copies[counters[name] % WEIGHT_COPIES]
         counters[name] += 1
-        out = nvfp4r.linear_auto(x, gs, w, s, packed, n, 1.0, torch.bfloat16)
+        fused_reduce = peer if (world > 1 and style == "row") else None
+        out = nvfp4r.linear_auto(x, gs, w, s, packed, n, 1.0, torch.bfloat16, reduce=fused_reduce)
         path_used[(name, M)] = "gemv" if (packed is None or nvfp4r.ops.use_gemv(M, n, k, gemv_max_m)) else "tcgen05"
-        if world > 1 and style == "row":
-            if peer is not None:
-                peer.all_reduce_(out)
-            else:
-                dist.all_reduce(out)
+        if world > 1 and style == "row" and peer is None:
+            dist.all_reduce(out)
         return out
 
     def step_resident():
@@ -221,12 +219,10 @@ def run_ours(args, rank, world, local_rank):
                 out = dev_out[oo:oo + M * n].view(M, n)
                 w, s, packed = copies[counters[name] % WEIGHT_COPIES]
                 counters[name] += 1
-                nvfp4r.linear_auto(x, gs, w, s, packed, n, 1.0, torch.bfloat16, out=out)
-                if world > 1 and style == "row":
-                    if peer is not None:
-                        peer.all_reduce_(out)
-                    else:
-                        dist.all_reduce(out)
+                fused_reduce = peer if (world > 1 and style == "row") else None
+                nvfp4r.linear_auto(x, gs, w, s, packed, n, 1.0, torch.bfloat16, out=out, reduce=fused_reduce)
+                if world > 1 and style == "row" and peer is None:
+                    dist.all_reduce(out)
         pin_out.copy_(dev_out, non_blocking=True)
 
     def capture_phases(fn):
@@ -368,7 +364,7 @@ def run_ours(args, rank, world, local_rank):
                    "launch": "CUDA-graph replay, one graph per step",
                    "parallelism": f"tp{world}",
                    "allreduce": "none" if world == 1 else
-                                ("one-shot kernel over NVLink peer memory" if peer is not None else "NCCL")},
+                                ("push in the linear epilogue + one-shot gather kernel over NVLink peer memory" if peer is not None else "NCCL")},
         "e2e": {"value": round(gbs_e2e, 1), "unit": "GB/s",
                 "h2d_bytes_per_step": h2d_bytes, "d2h_bytes_per_step": d2h_bytes},
         "gpu_launches": timed_launches,

@@ -195,10 +195,12 @@ NVFP4R_API int nvfp4r_linear_packed(const void* x, int64_t x_row_stride, int M, 
  *       residual_in + delta is also written to residual_out (must not alias residual_in);
  *       delta may be NULL; `x` is ignored; K is the hidden size.
  *   NVFP4R_PROLOGUE_SILU_MUL     input[m,k] = silu(x[m,k]) * x[m,K+k], x = [M, 2K] (gate|up).
+ *   NVFP4R_PROLOGUE_NONE         plain bf16 input (useful with push_to).
  * `pro` is a HOST pointer, read during the call. */
 typedef enum nvfp4r_prologue_kind {
     NVFP4R_PROLOGUE_NONE = 0, NVFP4R_PROLOGUE_ADD_RMSNORM = 1, NVFP4R_PROLOGUE_SILU_MUL = 2
 } nvfp4r_prologue_kind;
+struct nvfp4r_peer_comm;            /* defined with the peer all-reduce below */
 typedef struct nvfp4r_prologue {
     int kind;
     float eps;
@@ -206,6 +208,12 @@ typedef struct nvfp4r_prologue {
     const void* residual_in;
     void* residual_out;
     const void* norm_weight;
+    /* Epilogue option for row-parallel linears under tensor parallelism, NULL = off: instead of
+     * writing `out`, every finished 128-row tile of the bf16 result is stored straight into the
+     * receive memory of every rank (the PUSH half of nvfp4r_peer_allreduce_bf16, overlapped with
+     * the remaining tiles); a following nvfp4r_peer_allreduce_bf16(..., NVFP4R_PEER_GATHER)
+     * on `out` completes the sum. out_dtype must be bf16 and M*N <= push_to->max_elems. */
+    const struct nvfp4r_peer_comm* push_to;
 } nvfp4r_prologue;
 NVFP4R_API int nvfp4r_linear_packed_ex(const nvfp4r_prologue* pro, const void* x, int64_t x_row_stride,
                                        int M, int K, const float* global_scale_inv, const void* packed,

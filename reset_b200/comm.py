@@ -70,6 +70,17 @@ class PeerAllReduce:
         L.check(st, "nvfp4r_peer_allreduce_bf16")
         return t
 
+    def gather_(self, t: torch.Tensor) -> torch.Tensor:
+        """Second half only: the contributions were pushed by the epilogue of the linear that
+        produced ``t`` (``nvfp4r_linear_packed_ex`` with ``push_to``); sums them into ``t``."""
+        if self.world == 1:
+            return t
+        with torch.cuda.device(t.device):
+            st = L.lib().nvfp4r_peer_allreduce_bf16(C.byref(self.comm), t.data_ptr(), t.data_ptr(), t.numel(),
+                                                   L.PEER_GATHER, torch.cuda.current_stream().cuda_stream)
+        L.check(st, "nvfp4r_peer_allreduce_bf16")
+        return t
+
     def close(self) -> None:
         """Unmap the peers and free the receive memory (after a barrier of the caller's)."""
         lib = L.lib()

@@ -270,11 +270,22 @@ int nvfp4r_linear_packed_ex(const nvfp4r_prologue* pro, const void* x, int64_t x
                             int out_dtype, int rcp_mode, void* workspace, size_t workspace_bytes,
                             void* stream) {
     if (!pro) return fail(NVFP4R_ERR_INVALID_ARGUMENT, "linear_packed_ex: null prologue");
-    if (pro->kind == NVFP4R_PROLOGUE_NONE)
+    if (pro->kind == NVFP4R_PROLOGUE_NONE && pro->push_to == nullptr)
         return nvfp4r_linear_packed(x, x_row_stride, M, K, gs, packed, N, alpha, out, out_dtype, rcp_mode,
                                     workspace, workspace_bytes, stream);
-    if (pro->kind != NVFP4R_PROLOGUE_ADD_RMSNORM && pro->kind != NVFP4R_PROLOGUE_SILU_MUL)
+    if (pro->kind != NVFP4R_PROLOGUE_NONE && pro->kind != NVFP4R_PROLOGUE_ADD_RMSNORM &&
+        pro->kind != NVFP4R_PROLOGUE_SILU_MUL)
         return fail(NVFP4R_ERR_INVALID_ARGUMENT, "linear_packed_ex: bad prologue kind");
+    if (pro->push_to != nullptr) {
+        const nvfp4r_peer_comm* c = pro->push_to;
+        if (c->world < 1 || c->world > NVFP4R_PEER_MAX_WORLD || c->rank < 0 || c->rank >= c->world)
+            return fail(NVFP4R_ERR_INVALID_ARGUMENT, "linear_packed_ex: bad peer communicator");
+        if (out_dtype != NVFP4R_BF16 || (N & 1) ||
+            static_cast<size_t>(M) * static_cast<size_t>(N) > c->max_elems)
+            return fail(NVFP4R_ERR_UNSUPPORTED_SHAPE, "linear_packed_ex: push needs bf16 output of at most max_elems elements");
+        for (int r = 0; r < c->world; ++r)
+            if (!c->base[r]) return fail(NVFP4R_ERR_INVALID_ARGUMENT, "linear_packed_ex: peer base missing");
+    }
     if (!gs || !packed || !out) return fail(NVFP4R_ERR_INVALID_ARGUMENT, "linear_packed_ex: null pointer");
     if (rcp_mode != NVFP4R_RCP_EXACT && rcp_mode != NVFP4R_RCP_APPROX)
         return fail(NVFP4R_ERR_INVALID_ARGUMENT, "linear_packed_ex: bad rcp_mode");
@@ -301,11 +312,16 @@ int nvfp4r_linear_packed_ex(const nvfp4r_prologue* pro, const void* x, int64_t x
         g.delta = pro->delta; g.residual_in = pro->residual_in; g.residual_out = pro->residual_out;
         g.norm_w = pro->norm_weight; g.eps = pro->eps;
         g.xb = pro->residual_in; g.xb_stride = K;
+    } else if (pro->kind == NVFP4R_PROLOGUE_NONE) {
+        if (!x || !aligned(x, 16) || (x_row_stride % 8) || x_row_stride < static_cast<int64_t>(K))
+            return fail(NVFP4R_ERR_INVALID_ARGUMENT, "linear_packed_ex: x must be bf16 [M, K], 16-byte aligned rows");
+        g.xb = x; g.xb_stride = x_row_stride;
     } else {
         if (!x || !aligned(x, 16) || (x_row_stride % 8) || x_row_stride < 2 * static_cast<int64_t>(K))
             return fail(NVFP4R_ERR_INVALID_ARGUMENT, "linear_packed_ex: SiLU prologue needs x = [M, 2K] gate|up, 16-byte aligned");
         g.xb = x; g.xb_stride = x_row_stride;
     }
+    g.push = (pro->push_to != nullptr && pro->push_to->world > 1) ? pro->push_to : nullptr;
     const char* why = nullptr;
     cudaError_t e = nvfp4r::launch_linear_packed(g, as_stream(stream), &why);
     if (why != nullptr) return fail(NVFP4R_ERR_UNSUPPORTED_SHAPE, why);

@@ -1,6 +1,8 @@
 // Internal launch interface between the C ABI (api.cu) and the kernel files.
 #pragma once
 
+#include "../../include/nvfp4r_b200.h"
+
 #include <cuda_runtime.h>
 #include <stdint.h>
 
@@ -96,6 +98,8 @@ struct PackedLinearArgs {
     void* residual_out;
     const void* norm_w;
     float eps;
+    // epilogue: push the bf16 result into the peers' receive memory instead of writing `out`
+    const nvfp4r_peer_comm* push;
 };
 size_t packed_weight_bytes(int N, int K);
 size_t packed_workspace_bytes(int M, int N, int K);

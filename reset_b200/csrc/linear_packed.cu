@@ -33,6 +33,7 @@
 // Grid: persistent CTAs, two per SM. CTA c works on K part c % S of tiles
 // c / S, c / S + G/S, ... Roles: warp 0 = bulk-copy producer, warp 1 = MMA issuer,
 // warps 2-5 = epilogue (one TMEM lane quadrant each).
+#include "../../include/nvfp4r_b200.h"
 #include "kernels.h"
 #include "quant_core.cuh"
 #include "tcgen05_ptx.cuh"
@@ -76,6 +77,13 @@ struct PackedParams {
     void* residual_out;            // kind 1: bf16 [M, K], receives residual_in + delta
     const void* norm_w;            // kind 1: bf16 [K]
     float eps;
+    // fused first half of the tensor-parallel sum exchange (row-parallel linears): instead of
+    // writing `out`, the CTA that finishes a tile stores its bf16 results, two per 64-bit slot
+    // {1 : bf16x2}, into the receive memory of every rank (layout and protocol of
+    // peer_allreduce.cu); the gather half of nvfp4r_peer_allreduce_bf16 completes the sum.
+    int push_world, push_rank;
+    unsigned long long push_max_pairs;
+    unsigned char* push_base[NVFP4R_PEER_MAX_WORLD];
 };
 
 __device__ int g_packed_status = 0;
@@ -523,14 +531,39 @@ linear_packed_kernel(const __grid_constant__ PackedParams p) {
                                                  : slots_gather<4, 4>(tile_slots, S, p.M, mf, cnt, v);
                         if (!ok) wf.failed = true;
                     }
+                    if (p.push_world > 1) {
+                        // adjacent weight rows sit in adjacent lanes: the even lane sends the pair
+                        const unsigned parity = *reinterpret_cast<volatile unsigned*>(p.push_base[p.push_rank]) & 1u;
 #pragma unroll
-                    for (int j = 0; j < 4; ++j) {
-                        if (j < cnt) {
-                            const int64_t idx = (p.m0 + mf + j) * p.ldc + n;
-                            const float o = v[j] * p.alpha;
-                            if (p.out_dtype == 0) static_cast<__nv_bfloat16*>(p.out)[idx] = __float2bfloat16_rn(o);
-                            else if (p.out_dtype == 1) static_cast<__half*>(p.out)[idx] = __float2half_rn(o);
-                            else static_cast<float*>(p.out)[idx] = o;
+                        for (int j = 0; j < 4; ++j) {
+                            if (j < cnt) {
+                                const float o = v[j] * p.alpha;
+                                const float o2 = __shfl_down_sync(0xffffffffu, o, 1);
+                                if ((lane & 1) == 0) {
+                                    const unsigned long long w = (1ull << 32) | pack2_bf16(o, o2);
+                                    const unsigned long long i =
+                                        (static_cast<unsigned long long>(p.m0 + mf + j) * p.N + static_cast<unsigned long long>(n)) >> 1;
+#pragma unroll 1
+                                    for (int d = 0; d < p.push_world; ++d) {
+                                        const int dst = (p.push_rank + d) % p.push_world;
+                                        unsigned long long* slot =
+                                            reinterpret_cast<unsigned long long*>(p.push_base[dst] + 256) +
+                                            (static_cast<unsigned long long>(parity) * p.push_world + p.push_rank) * p.push_max_pairs + i;
+                                        asm volatile("st.relaxed.sys.global.u64 [%0], %1;" :: "l"(slot), "l"(w) : "memory");
+                                    }
+                                }
+                            }
+                        }
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) {
+                            if (j < cnt) {
+                                const int64_t idx = (p.m0 + mf + j) * p.ldc + n;
+                                const float o = v[j] * p.alpha;
+                                if (p.out_dtype == 0) static_cast<__nv_bfloat16*>(p.out)[idx] = __float2bfloat16_rn(o);
+                                else if (p.out_dtype == 1) static_cast<__half*>(p.out)[idx] = __float2half_rn(o);
+                                else static_cast<float*>(p.out)[idx] = o;
+                            }
                         }
                     }
                 }
@@ -649,6 +682,13 @@ cudaError_t launch_linear_packed(const PackedLinearArgs& g, cudaStream_t stream,
         p.norm_w = g.norm_w;
         p.eps = g.eps;
         p.slots = static_cast<unsigned long long*>(g.workspace);
+        p.push_world = 0;
+        if (g.push != nullptr && g.push->world > 1) {
+            p.push_world = g.push->world;
+            p.push_rank = g.push->rank;
+            p.push_max_pairs = (g.push->max_elems + 1) / 2;
+            for (int r = 0; r < g.push->world; ++r) p.push_base[r] = static_cast<unsigned char*>(g.push->base[r]);
+        }
 
         void (*kern)(PackedParams) = plan.bn == 16 ? linear_packed_kernel<16> : linear_packed_kernel<32>;
         static bool attr_done[2][64] = {};

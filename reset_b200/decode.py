@@ -65,7 +65,9 @@ class _Linear:
         if rms > 0 and rms == rms:
             self.alpha = 1.0 / rms
 
-    def plain(self, x: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    def plain(self, x: torch.Tensor, out: torch.Tensor, push=None) -> torch.Tensor:
+        if push is not None and not self.use_gemv:
+            return capi.linear_packed_push(x, self.gs_inv, self.packed, self.N, self.alpha, self.ws.buf, push, out)
         if self.use_gemv:
             return capi.linear(x, self.gs_inv, self.w, self.s, self.alpha, out=out, rcp_mode=L.RCP_APPROX)
         return capi.linear_packed(x, self.gs_inv, self.packed, self.N, self.alpha, self.ws.buf,
@@ -75,9 +77,9 @@ class _Linear:
         return capi.linear_packed_rmsnorm(delta, res_in, res_out, norm_w, eps, self.gs_inv, self.packed,
                                           self.N, self.alpha, self.ws.buf, rcp_mode=L.RCP_APPROX, out=out)
 
-    def after_silu_mul(self, gate_up, out):
+    def after_silu_mul(self, gate_up, out, push=None):
         return capi.linear_packed_silu(gate_up, self.gs_inv, self.packed, self.N, self.alpha, self.ws.buf,
-                                       rcp_mode=L.RCP_APPROX, out=out)
+                                       rcp_mode=L.RCP_APPROX, out=out, push=push)
 
     def weight_bytes(self) -> int:
         return self.N * self.K * 9 // 16
@@ -185,11 +187,18 @@ class DecodeStep:
                                        c.head_dim, c.context, self.attn_ws.data_ptr(),
                                        self.attn_ws.numel() * 4, self._stream()), "attn_decode")
 
-    def _all_reduce(self, t):
+    def _all_reduce(self, t, pushed: bool = False):
         if self.peer is not None:
-            self.peer.all_reduce_(t)
+            if pushed:
+                self.peer.gather_(t)          # the linear's epilogue already pushed the contributions
+            else:
+                self.peer.all_reduce_(t)
         elif self.world > 1:
             torch.distributed.all_reduce(t, group=self.pg)
+
+    def _push(self, lin):
+        """The communicator to push into from this linear's epilogue, or None."""
+        return self.peer.comm if (self.peer is not None and not lin.use_gemv) else None
 
     # -- the step ---------------------------------------------------------------------
     def step(self) -> None:
@@ -210,20 +219,23 @@ class DecodeStep:
                 self._add_rmsnorm(x, self.res[cur], layer["ln1"])
                 layer["qkv"].plain(self.normed, self.qkv_out)
             self._attention(layer, self.qkv_out)
-            layer["o"].plain(self.attn, self.o_out)
-            self._all_reduce(self.o_out)
+            push = self._push(layer["o"])
+            layer["o"].plain(self.attn, self.o_out, push=push)
+            self._all_reduce(self.o_out, pushed=push is not None)
             if self.fused:
                 layer["gate_up"].after_rmsnorm(self.o_out, self.res[cur], self.res[1 - cur], layer["ln2"], c.eps,
                                                self.gu_out)
                 cur = 1 - cur
-                layer["down"].after_silu_mul(self.gu_out, self.down_out)
+                push = self._push(layer["down"])
+                layer["down"].after_silu_mul(self.gu_out, self.down_out, push=push)
             else:
+                push = None
                 self._add_rmsnorm(self.o_out, self.res[cur], layer["ln2"])
                 layer["gate_up"].plain(self.normed, self.gu_out)
                 L.check(lib.nvfp4r_silu_mul(self.gu_out.data_ptr(), self.act.data_ptr(), 1, self.act.shape[1],
                                             self._stream()), "silu_mul")
                 layer["down"].plain(self.act, self.down_out)
-            self._all_reduce(self.down_out)
+            self._all_reduce(self.down_out, pushed=push is not None)
             x = self.down_out
         self._add_rmsnorm(x, self.res[cur], self.final_ln)
         L.check(lib.nvfp4r_lm_head(self.normed.data_ptr(), self.lm_head.data_ptr(), self.logits_local.data_ptr(),

@@ -91,14 +91,28 @@ def _out_workspace(device, nbytes: int) -> torch.Tensor:
 
 def linear_auto(x, global_scale_inv, weight, weight_scale_flat, packed, N: int, alpha: float,
                 out_dtype: torch.dtype = torch.bfloat16, rcp_mode: int = 1,
-                out: Optional[torch.Tensor] = None) -> torch.Tensor:
+                out: Optional[torch.Tensor] = None, reduce=None) -> torch.Tensor:
     """One decode linear through whichever kernel the measured crossover picks. ``packed``
     may be None (shape outside the tensor-core kernel's N % 128 / K % 256). With ``out`` (a
     contiguous ``[M, N]`` tensor) the result is written there and nothing is allocated: the
-    out-variant convention of the reference's raw ops (kernels/csrc/bindings.cpp:27-84)."""
+    out-variant convention of the reference's raw ops (kernels/csrc/bindings.cpp:27-84).
+    ``reduce`` (a ``reset_b200.comm.PeerAllReduce``) makes this a row-parallel linear of a
+    tensor-parallel layer: the result is summed over the ranks, with the first half of the
+    exchange running in the tensor-core kernel's epilogue where that kernel is chosen."""
     from . import _config
     M, K = x.shape
     gemv = packed is None or (weight is not None and use_gemv(M, N, K, _config.GEMV_MAX_M))
+    if reduce is not None and reduce.world > 1:
+        from .. import _lib as L
+        from .. import capi
+        if out is None:
+            out = torch.empty((M, N), dtype=torch.bfloat16, device=x.device)
+        if gemv:
+            capi.linear(x, global_scale_inv, weight, weight_scale_flat, alpha, out=out, rcp_mode=rcp_mode)
+            return reduce.all_reduce_(out)
+        ws = _out_workspace(x.device, L.lib().nvfp4r_linear_packed_workspace_bytes(M, N, K))
+        capi.linear_packed_push(x, global_scale_inv, packed, N, alpha, ws, reduce.comm, out, rcp_mode=rcp_mode)
+        return reduce.gather_(out)
     if out is None:
         if gemv:
             return linear(x, global_scale_inv, weight, weight_scale_flat, alpha, out_dtype, rcp_mode)

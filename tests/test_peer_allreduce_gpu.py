@@ -125,3 +125,61 @@ def test_two_processes_two_gpus(tmp_path):
                         "--master-addr", "127.0.0.1", "--master-port", "29533", str(script)],
                        env=env, capture_output=True, text=True, timeout=300)
     assert r.returncode == 0 and r.stdout.count("PEER_OK") == 2, (r.stdout[-2000:], r.stderr[-3000:])
+
+
+@pytest.mark.parametrize("M", [1, 3, 8])
+def test_linear_push_epilogue_emulated_ranks(M):
+    """Row-parallel linear with the PUSH half of the all-reduce fused into its epilogue
+    (`nvfp4r_linear_packed_ex`, `push_to`), two ranks emulated on one GPU: each rank's linear
+    over its K shard pushes into both receive buffers, then each rank's GATHER half runs. The
+    result equals the rank-ordered sum of the two unfused bf16 linear outputs bit for bit."""
+    import numpy as np
+    from oracle import nvfp4 as onv
+    from reset_b200 import _lib as L
+    from reset_b200 import capi
+    lib = L.lib()
+    world, N, K = 2, 1024, 4096
+    max_elems = 8 * N
+    nbytes = lib.nvfp4r_peer_buffer_bytes(world, max_elems)
+    ptrs = []
+    for _ in range(world):
+        p, h = C.c_void_p(), C.create_string_buffer(64)
+        L.check(lib.nvfp4r_peer_alloc(nbytes, C.byref(p), h), "alloc")
+        ptrs.append(p)
+    try:
+        comms = []
+        for r in range(world):
+            c = L.PeerComm()
+            c.world, c.rank, c.max_elems = world, r, max_elems
+            for k in range(world):
+                c.base[k] = ptrs[k].value
+            comms.append(c)
+        g = torch.Generator(device="cuda").manual_seed(40 + M)
+        gs = torch.tensor([60.0], dtype=torch.float32, device="cuda")
+        stream = torch.cuda.current_stream().cuda_stream
+        for call in range(3):                                            # parity flips between calls
+            x = torch.randn(M, K, device="cuda", generator=g).to(torch.bfloat16)
+            shards, parts = [], []
+            for r in range(world):
+                w, ws = onv.random_nvfp4((N,), K // world, seed=50 + 10 * call + r)
+                packed = capi.pack_weight(torch.from_numpy(w).cuda(), torch.from_numpy(ws).cuda())
+                xs = x[:, r * (K // world):(r + 1) * (K // world)]
+                wk = capi.packed_workspace(M, N, K // world, "cuda")
+                shards.append((packed, xs, wk))
+                parts.append(capi.linear_packed(xs, gs, packed, N, 0.5, wk, rcp_mode=L.RCP_APPROX))
+            outs = [torch.zeros(M, N, dtype=torch.bfloat16, device="cuda") for _ in range(world)]
+            for r in range(world):
+                packed, xs, wk = shards[r]
+                capi.linear_packed_push(xs, gs, packed, N, 0.5, wk, comms[r], outs[r])
+            for r in range(world):
+                L.check(lib.nvfp4r_peer_allreduce_bf16(C.byref(comms[r]), outs[r].data_ptr(), outs[r].data_ptr(),
+                                                       M * N, L.PEER_GATHER, stream), "gather")
+            torch.cuda.synchronize()
+            want = _expected(parts)
+            for r in range(world):
+                assert torch.equal(outs[r], want), (call, r)
+        L.check(lib.nvfp4r_check_device_status(), "device status")
+    finally:
+        torch.cuda.synchronize()
+        for p in ptrs:
+            lib.nvfp4r_peer_free(p)
