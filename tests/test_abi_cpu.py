@@ -86,3 +86,37 @@ def test_ops_are_registered_with_the_reference_schemas():
     assert str(gemv) == ("nvfp4r::gemv(Tensor weight, Tensor weight_scale, Tensor x, Tensor x_scale, "
                          "Tensor(a!) out, float alpha=1.) -> ()")
     assert str(gemm) == "nvfp4r::gemm(Tensor A, Tensor B, Tensor SFA, Tensor SFB, Tensor(a!) C, float alpha=1.) -> ()"
+
+
+def test_newline_id_scan_and_bitmap():
+    import torch
+    """`get_newline_token_ids` (reference reset/reset/logits_processor.py:39-59) on a stand-in
+    tokenizer, and the id bitmap the kernels read."""
+    from reset_b200.reset import logits_processor as lp
+
+    class Tok:
+        vocab_size = 70
+        table = {3: "\n", 5: "\n\n", 9: "a\n\nb", 40: " \n", 63: "\n"}
+
+        def decode(self, ids, skip_special_tokens=False):
+            if ids[0] == 7:
+                raise ValueError("undecodable id")
+            return self.table.get(ids[0], "x")
+
+    nl, dnl = lp.get_newline_token_ids(Tok())
+    assert nl == [3, 63] and dnl == [5, 9]
+    bm = lp._bitmap([3, 63, 31, 64, 999, -1], 70, "cpu")
+    assert bm.shape == (3,) and bm.dtype == torch.int32
+    words = [int(w) & 0xFFFFFFFF for w in bm.tolist()]
+    assert words == [(1 << 3) | (1 << 31), 1 << 31, 1 << 0]
+    assert lp._bitmap([], 70, "cpu") is None
+
+
+def test_scale_by_temperature_matches_oracle_on_cpu():
+    import torch
+    from oracle import reset_policy as orp
+    from reset_b200.reset.logits_processor import scale_by_temperature
+
+    x = orp.synthetic_logits(2, 100, 3)
+    for t in (1.0, 0.1, 0.0, 1e-7):
+        assert torch.equal(scale_by_temperature(x[0], t), orp.apply_temperature(x[0], t))

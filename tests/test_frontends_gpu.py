@@ -1,0 +1,143 @@
+"""The reference-facing front ends on the GPU: `ReSETRequest` / `ReSETBatchProcessor`
+(reset/reset/logits_processor.py:62-155 of the reference) against the CPU oracle policy, and
+the vLLM adapter entry points `prime_nvfp4r_caches` / `apply_nvfp4r_linear`
+(kernels/python/nvfp4r/vllm_integration.py:359-396,448-496) on a stand-in layer object."""
+
+from __future__ import annotations
+
+from collections import namedtuple
+from types import SimpleNamespace
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import nvfp4 as onv
+from oracle import reset_policy as orp
+from helpers import cuda, make_activation, rel_l2
+
+pytestmark = pytest.mark.gpu
+TIE_BAND = 1e-4
+BatchUpdate = namedtuple("BatchUpdate", "removed added moved")
+
+
+def _near_tie(d, tau0):
+    thr = d.h_step if d.high_step else tau0
+    return abs(d.entropy - thr) < TIE_BAND or abs(d.h_step - d.h_bar) < TIE_BAND
+
+
+def test_reset_request_matches_oracle():
+    from reset_b200.reset import ReSETRequest
+    V, steps, nl, dnl = 4096, 90, 11, 13
+    ids = orp.synthetic_token_stream(steps, dnl, V, seed=5, gap_lo=10, gap_hi=25)
+    ids[30:32] = nl                                     # two single newlines in a row: a boundary too
+    req = ReSETRequest(1.0, 0.3, 6.0, 8, [nl], [dnl])
+    pol = orp.ResetPolicy(1.0, 0.3, 6.0, 8, frozenset([nl]), frozenset([dnl]))
+    temps = set()
+    for t in range(steps):
+        logits = orp.synthetic_logits(1, V, 1000 + t, sigma=2.0)[0]
+        got = req(ids[:t].tolist(), logits.cuda())
+        want, d = pol(ids[:t].tolist(), logits)
+        g = req.last_decision()
+        assert bool(g["boundary"]) == d.boundary
+        assert abs(g["entropy"] - d.entropy) <= 1e-4
+        if g["temp"] == d.temp:
+            assert torch.equal(got.cpu(), want)
+        else:
+            assert _near_tie(d, 6.0)
+        temps.add(g["temp"])
+    assert temps == {1.0, 0.3}                          # both regimes were exercised
+
+
+def test_batch_processor_matches_per_request_oracle():
+    """Three batch rows (one not opted in), a removal and a move in mid-stream, through the
+    vLLM v1 LogitsProcessor interface."""
+    from reset_b200.reset import ReSETBatchProcessor
+    V, dnl = 4096, 17
+    ea = {"reset": True, "t_high": 1.0, "t_low": 0.5, "tau_0": 6.0, "window": 4, "reset_nl_ids": [],
+          "reset_dnl_ids": [dnl]}
+    proc = ReSETBatchProcessor(device="cuda", max_num_reqs=4, vocab_size=V)
+    assert proc.is_argmax_invariant() is False
+    outs = {0: [], 1: [], 2: []}                        # live output-id lists, as vLLM hands them over
+    pols = {0: orp.ResetPolicy(1.0, 0.5, 6.0, 4, frozenset(), frozenset([dnl])),
+            2: orp.ResetPolicy(1.0, 0.5, 6.0, 4, frozenset(), frozenset([dnl]))}
+    proc.update_state(BatchUpdate(removed=[], moved=[], added=[
+        (0, SimpleNamespace(extra_args=dict(ea)), [1, 2], outs[0]),
+        (1, SimpleNamespace(extra_args=None), [3], outs[1]),
+        (2, SimpleNamespace(extra_args=dict(ea)), [4], outs[2])]))
+    rng = np.random.default_rng(3)
+    rows = {0: 0, 1: 1, 2: 2}                           # request -> batch row
+
+    def step(t, batch):
+        logits = orp.synthetic_logits(batch, V, 2000 + t, sigma=2.0)
+        dev = logits.cuda()
+        ret = proc.apply(dev)
+        assert ret.data_ptr() == dev.data_ptr()          # in place, like vLLM expects
+        res = dev.cpu()
+        for rq, row in rows.items():
+            if rq in pols:
+                want, d = pols[rq](list(outs[rq]), logits[row])
+                if not _near_tie(d, 6.0):
+                    assert torch.equal(res[row], want), (t, rq)
+            else:
+                assert torch.equal(res[row], logits[row])          # not opted in: untouched
+        for rq in rows:
+            outs[rq].append(dnl if rng.random() < 0.15 else int(rng.integers(20, V)))
+
+    for t in range(12):
+        step(t, 3)
+        proc.update_state(None)
+    # request 0 finishes; request 2 moves from row 2 to row 0 (vLLM condenses the batch)
+    del rows[0], pols[0]
+    rows[2] = 0
+    proc.update_state(BatchUpdate(removed=[0], added=[], moved=[(2, 0, SimpleNamespace(name="UNIDIRECTIONAL"))]))
+    for t in range(12, 24):
+        step(t, 2)
+        proc.update_state(None)
+
+
+def _fake_layer(N, K, seed, alpha=0.37, gs_inv=55.0, swizzled=True):
+    from reset_b200 import capi
+    w, ws = onv.random_nvfp4((N,), K, seed=seed)
+    layer = torch.nn.Module()
+    layer.weight = torch.nn.Parameter(cuda(w), requires_grad=False)
+    flat = cuda(ws)
+    scale = capi.swizzle_blockscale(flat) if swizzled else flat
+    layer.weight_scale = torch.nn.Parameter(scale.view(torch.float8_e4m3fn), requires_grad=False)
+    layer._nvfp4r_weight_scale_is_flat = not swizzled
+    layer.input_global_scale_inv = torch.tensor([gs_inv], dtype=torch.float32, device="cuda")
+    layer.alpha = torch.tensor(alpha, dtype=torch.float32, device="cuda")
+    layer.input_size_per_partition, layer.output_size_per_partition = K, N
+    layer.weights_padding_cols = 0
+    return layer, w, ws
+
+
+@pytest.mark.parametrize("N,K,swizzled", [(4096, 1024, True), (6144, 4096, True), (1000, 320, False)])
+def test_vllm_adapter_on_a_stand_in_layer(N, K, swizzled):
+    from reset_b200.nvfp4r import vllm_integration as vi
+    layer, w, ws = _fake_layer(N, K, seed=N % 97, swizzled=swizzled)
+    vi.prime_nvfp4r_caches(layer)
+    vi.prime_nvfp4r_caches(layer)                       # idempotent
+    assert layer._nvfp4r_caches_primed and abs(layer._nvfp4r_alpha_host - 0.37) < 1e-7
+    assert tuple(layer._nvfp4r_weight_scale_flat_3d.shape) == (1, N, K // 16)
+    assert np.array_equal(layer._nvfp4r_weight_scale_flat_3d[0].cpu().numpy(), ws)
+    assert (layer._nvfp4r_weight_packed is not None) == (N % 128 == 0 and K % 256 == 0)
+    bias = torch.randn(N, device="cuda").to(torch.bfloat16)
+    for M in (1, 2, 5, 40):
+        x = make_activation(M, K, seed=M).cuda()
+        y = vi.apply_nvfp4r_linear(layer, x.view(1, M, K), bias if M == 5 else None)
+        assert tuple(y.shape) == (1, M, N) and y.dtype == torch.bfloat16
+        xc, xsf = onv.quantize_nvfp4(x.float().cpu().numpy(), 55.0)
+        exact = onv.linear_f64(w, ws, xc, xsf, alpha=0.37)
+        if M == 5:
+            exact = exact + bias.float().cpu().numpy()
+        assert rel_l2(y[0].float().cpu().numpy(), exact) <= 6e-3        # bf16 output rounding
+
+
+def test_vllm_adapter_rejects_padded_weights():
+    from reset_b200.nvfp4r import vllm_integration as vi
+    layer, _, _ = _fake_layer(256, 512, seed=1)
+    vi.prime_nvfp4r_caches(layer)
+    layer.weights_padding_cols = 64
+    with pytest.raises(RuntimeError):
+        vi.apply_nvfp4r_linear(layer, torch.zeros(1, 512, dtype=torch.bfloat16, device="cuda"))
