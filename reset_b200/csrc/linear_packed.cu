@@ -145,9 +145,10 @@ __device__ __forceinline__ void tmem_ld4(uint32_t taddr, float v[4]) {
 }
 
 // ---- split-K hand-over through self-validating 8-byte slots ------------------------------
-// A K part that is not part 0 publishes every partial value as ONE 64-bit store
-// {flag = 1 : fp32 bits}; the CTA of part 0 polls the slots, adds the values in part order
-// and writes zeros back, so the scratch is all-zero again when the kernel ends. A 64-bit
+// Token m of a tile is finished by the CTA of K part m % S. The other parts publish their
+// partial value for it as ONE 64-bit store {flag = 1 : fp32 bits}; the finishing CTA polls
+// those slots, adds all S values in part order and writes zeros back, so the scratch is
+// all-zero again when the kernel ends. A 64-bit
 // scalar access is single-copy atomic, so a slot is either still zero or complete: no
 // fence, no ticket, one store latency plus one load latency on the critical path. All CTAs
 // of the grid are resident at once (the grid never exceeds two CTAs per SM), so the part
@@ -163,45 +164,43 @@ __device__ __forceinline__ unsigned long long slot_load(const unsigned long long
 }
 constexpr uint32_t kSlotPollLimit = 4000000u;      // polls per group before giving up (~ a second)
 
-// Adds to v[0..cnt) the values of parts 1..S-1 for tokens m_first .. m_first+cnt-1 of this
-// thread's weight row, in part order; GP parts x TJ tokens are polled together (all loads in
-// flight at once: one round trip per group). `base` points at the slot of (part 1, token 0,
-// this row); M is the launch's token count; cnt <= TJ.
-template <int GP, int TJ>
-__device__ __forceinline__ bool slots_gather(unsigned long long* base, int S, int M, int m_first, int cnt,
-                                             float* v) {
-    const int64_t part_stride = static_cast<int64_t>(M) * kTileRows;
+// Sum of one token's partial values over the parts 0..S-1 in ascending part order for this
+// thread's weight row: `own` stands at position `part`, the others come from the slots
+// (`tok` points at the slot of (token, part 0, this row); parts are kTileRows slots apart).
+// Eight parts are polled together (all loads in flight at once: one round trip per group).
+// Gathering two tokens per call was measured slower (more registers and code for the same
+// number of round trips on the shapes of the bench).
+__device__ __forceinline__ bool token_gather(unsigned long long* tok, int S, int part, float own, float* result) {
+    float acc = 0.0f;
 #pragma unroll 1
-    for (int s0 = 1; s0 < S; s0 += GP) {
-        unsigned long long w[GP][TJ];
-        unsigned long long* ps = base + (static_cast<int64_t>(s0 - 1) * M + m_first) * kTileRows;
+    for (int s0 = 0; s0 < S; s0 += 8) {
+        unsigned long long w[8];
 #pragma unroll
-        for (int g = 0; g < GP; ++g)
-#pragma unroll
-            for (int j = 0; j < TJ; ++j)
-                if (s0 + g < S && j < cnt) w[g][j] = slot_load(ps + g * part_stride + j * kTileRows);
+        for (int g = 0; g < 8; ++g)
+            if (s0 + g < S && s0 + g != part) w[g] = slot_load(tok + (s0 + g) * kTileRows);
         for (uint32_t it = 0;; ++it) {
             bool all = true;
 #pragma unroll
-            for (int g = 0; g < GP; ++g)
-#pragma unroll
-                for (int j = 0; j < TJ; ++j)
-                    if (s0 + g < S && j < cnt && (w[g][j] >> 32) != 1ull) {
-                        w[g][j] = slot_load(ps + g * part_stride + j * kTileRows);
-                        all = false;
-                    }
+            for (int g = 0; g < 8; ++g)
+                if (s0 + g < S && s0 + g != part && (w[g] >> 32) != 1ull) {
+                    w[g] = slot_load(tok + (s0 + g) * kTileRows);
+                    all = false;
+                }
             if (all) break;
             if (it > kSlotPollLimit) return false;
         }
 #pragma unroll
-        for (int g = 0; g < GP; ++g)
-#pragma unroll
-            for (int j = 0; j < TJ; ++j)
-                if (s0 + g < S && j < cnt) {
-                    v[j] += __uint_as_float(static_cast<uint32_t>(w[g][j]));
-                    ps[g * part_stride + j * kTileRows] = 0ull;
+        for (int g = 0; g < 8; ++g)
+            if (s0 + g < S) {
+                if (s0 + g == part) {
+                    acc += own;
+                } else {
+                    acc += __uint_as_float(static_cast<uint32_t>(w[g]));
+                    tok[(s0 + g) * kTileRows] = 0ull;
                 }
+            }
     }
+    *result = acc;
     return true;
 }
 
@@ -512,60 +511,59 @@ linear_packed_kernel(const __grid_constant__ PackedParams p) {
             tc_fence_after();
             const uint32_t taddr = tmem + (static_cast<uint32_t>(q * 32) << 16) + buf * BN;
             const int64_t n = static_cast<int64_t>(tile) * kTileRows + row_in_tile;
+            // Token m is finished by the CTA of part m % S: the hand-over work of a tile is spread
+            // over its S CTAs instead of falling on one of them.
             unsigned long long* tile_slots =
-                p.slots + static_cast<int64_t>(tile) * (S - 1) * p.M * kTileRows + row_in_tile;
+                p.slots + static_cast<int64_t>(tile) * p.M * S * kTileRows + row_in_tile;
+            // pass 1: publish this part's values for the tokens that other parts finish (nothing
+            // waits here, so no part holds up another)
+            if (S > 1) {
+                int owner = 0;                                     // part that finishes token mf + j
 #pragma unroll 1
-            for (int mf = 0; mf < p.M; mf += 4) {
-                const int cnt = min(4, p.M - mf);
-                float v[4];
-                tmem_ld4(taddr + mf, v);
+                for (int mf = 0; mf < p.M; mf += 4) {
+                    const int cnt = min(4, p.M - mf);
+                    float v[4];
+                    tmem_ld4(taddr + mf, v);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        if (j < cnt && owner != part)
+                            slot_store(tile_slots + (static_cast<int64_t>(mf + j) * S + part) * kTileRows, v[j]);
+                        owner = (owner + 1 == S) ? 0 : owner + 1;
+                    }
+                }
+            }
+            // pass 2: finish this part's own tokens part, part + S, ...
+#pragma unroll 1
+            for (int m = part; m < p.M; m += S) {
+                float val;
+                asm volatile("tcgen05.ld.sync.aligned.32x32b.x1.b32 {%0}, [%1];" : "=f"(val) : "r"(taddr + m) : "memory");
                 tmem_ld_wait();
-                if (part != 0) {
-                    unsigned long long* dst = tile_slots + (static_cast<int64_t>(part - 1) * p.M + mf) * kTileRows;
-#pragma unroll
-                    for (int j = 0; j < 4; ++j)
-                        if (j < cnt) slot_store(dst + j * kTileRows, v[j]);
-                } else {
-                    if (S > 1) {
-                        const bool ok = cnt == 1 ? slots_gather<8, 1>(tile_slots, S, p.M, mf, cnt, v)
-                                                 : slots_gather<4, 4>(tile_slots, S, p.M, mf, cnt, v);
-                        if (!ok) wf.failed = true;
-                    }
-                    if (p.push_world > 1) {
-                        // adjacent weight rows sit in adjacent lanes: the even lane sends the pair
-                        const unsigned parity = *reinterpret_cast<volatile unsigned*>(p.push_base[p.push_rank]) & 1u;
-#pragma unroll
-                        for (int j = 0; j < 4; ++j) {
-                            if (j < cnt) {
-                                const float o = v[j] * p.alpha;
-                                const float o2 = __shfl_down_sync(0xffffffffu, o, 1);
-                                if ((lane & 1) == 0) {
-                                    const unsigned long long w = (1ull << 32) | pack2_bf16(o, o2);
-                                    const unsigned long long i =
-                                        (static_cast<unsigned long long>(p.m0 + mf + j) * p.N + static_cast<unsigned long long>(n)) >> 1;
+                if (S > 1 && !token_gather(tile_slots + static_cast<int64_t>(m) * S * kTileRows, S, part, val, &val))
+                    wf.failed = true;
+                const float o = val * p.alpha;
+                if (p.push_world > 1) {
+                    // adjacent weight rows sit in adjacent lanes: the even lane sends the pair
+                    const unsigned parity = *reinterpret_cast<volatile unsigned*>(p.push_base[p.push_rank]) & 1u;
+                    const float o2 = __shfl_down_sync(0xffffffffu, o, 1);
+                    if ((lane & 1) == 0) {
+                        const unsigned long long w = (1ull << 32) | pack2_bf16(o, o2);
+                        const unsigned long long i =
+                            (static_cast<unsigned long long>(p.m0 + m) * p.N + static_cast<unsigned long long>(n)) >> 1;
 #pragma unroll 1
-                                    for (int d = 0; d < p.push_world; ++d) {
-                                        const int dst = (p.push_rank + d) % p.push_world;
-                                        unsigned long long* slot =
-                                            reinterpret_cast<unsigned long long*>(p.push_base[dst] + 256) +
-                                            (static_cast<unsigned long long>(parity) * p.push_world + p.push_rank) * p.push_max_pairs + i;
-                                        asm volatile("st.relaxed.sys.global.u64 [%0], %1;" :: "l"(slot), "l"(w) : "memory");
-                                    }
-                                }
-                            }
-                        }
-                    } else {
-#pragma unroll
-                        for (int j = 0; j < 4; ++j) {
-                            if (j < cnt) {
-                                const int64_t idx = (p.m0 + mf + j) * p.ldc + n;
-                                const float o = v[j] * p.alpha;
-                                if (p.out_dtype == 0) static_cast<__nv_bfloat16*>(p.out)[idx] = __float2bfloat16_rn(o);
-                                else if (p.out_dtype == 1) static_cast<__half*>(p.out)[idx] = __float2half_rn(o);
-                                else static_cast<float*>(p.out)[idx] = o;
-                            }
+                        for (int d = 0; d < p.push_world; ++d) {
+                            const int dst = (p.push_rank + d) % p.push_world;
+                            unsigned long long* slot =
+                                reinterpret_cast<unsigned long long*>(p.push_base[dst] + 256) +
+                                (static_cast<unsigned long long>(parity) * p.push_world + p.push_rank) * p.push_max_pairs + i;
+                            asm volatile("st.relaxed.sys.global.u64 [%0], %1;" :: "l"(slot), "l"(w) : "memory");
                         }
                     }
+                } else {
+                    const int64_t idx = (p.m0 + m) * p.ldc + n;
+                    if (p.out_dtype == 0) static_cast<__nv_bfloat16*>(p.out)[idx] = __float2bfloat16_rn(o);
+                    else if (p.out_dtype == 1) static_cast<__half*>(p.out)[idx] = __float2half_rn(o);
+                    else static_cast<float*>(p.out)[idx] = o;
                 }
             }
             tc_fence_before();
@@ -634,7 +632,7 @@ size_t packed_workspace_bytes(int M, int N, int K) {
     if (!plan_packed(M < 32 ? M : 32, N, K, &plan)) return 16;
     const size_t tiles = N / kTileRows;
     const size_t m = M < 32 ? M : 32;
-    const size_t slots = plan.splits > 1 ? tiles * (plan.splits - 1) * m * kTileRows * sizeof(unsigned long long) : 0;
+    const size_t slots = plan.splits > 1 ? tiles * plan.splits * m * kTileRows * sizeof(unsigned long long) : 0;
     return slots + 256;
 }
 
