@@ -14,4 +14,6 @@ FALLBACK_BACKEND = os.environ.get("NVFP4R_FALLBACK_BACKEND", "none").lower()
 # B200 (L2-cold weights, CUDA-graph replay): the GEMV's shorter fixed latency wins only
 # for the smallest batches on weights of at most this many bytes; everything else goes
 # to the tensor cores. Index = M.
-GEMV_MAX_WEIGHT_BYTES = {1: 11_000_000, 2: 6_500_000, 3: 4_800_000, 4: 2_500_000}
+GEMV_MAX_WEIGHT_BYTES = {1: 11_000_000, 2: 5_000_000, 3: 2_500_000, 4: 2_500_000}
+# ... and, above one token, only for short rows (the GEMV's time grows with M * K per row)
+GEMV_MAX_K_MULTI_TOKEN = 2048

@@ -74,7 +74,9 @@ def use_gemv(M: int, N: int, K: int, gemv_max_m: int) -> bool:
     if M > gemv_max_m:
         return False
     limit = _config.GEMV_MAX_WEIGHT_BYTES.get(M)
-    return limit is not None and N * K * 9 // 16 <= limit
+    if limit is None or N * K * 9 // 16 > limit:
+        return False
+    return M == 1 or K <= _config.GEMV_MAX_K_MULTI_TOKEN
 
 
 _OUT_WORKSPACE: dict = {}          # device -> zeroed split-K workspace of the out= path

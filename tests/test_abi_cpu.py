@@ -73,6 +73,7 @@ def test_crossover_rule():
     from reset_b200.nvfp4r.ops import use_gemv
     assert use_gemv(1, 4096, 4096, 4) and use_gemv(2, 4096, 2048, 4) and use_gemv(4, 4096, 1024, 4)
     assert not use_gemv(2, 4096, 4096, 4) and not use_gemv(1, 6144, 4096, 4)
+    assert not use_gemv(2, 1280, 5120, 4)                     # long rows go to the tensor cores above one token
     assert not use_gemv(1, 24576, 4096, 4) and not use_gemv(4, 4096, 4096, 4)
     assert not use_gemv(3, 4096, 1024, 2)                     # above gemv_max_m
     assert not use_gemv(1, 4096, 4096, 0)                     # gemv_max_m = 0 disables the GEMV
