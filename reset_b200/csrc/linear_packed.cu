@@ -516,8 +516,8 @@ linear_packed_kernel(const __grid_constant__ PackedParams p) {
             unsigned long long* tile_slots =
                 p.slots + static_cast<int64_t>(tile) * p.M * S * kTileRows + row_in_tile;
             // pass 1: publish this part's values for the tokens that other parts finish (nothing
-            // waits here, so no part holds up another)
-            if (S > 1) {
+            // waits here, so no part holds up another); with a single token part 0 has none
+            if (S > 1 && (p.M > 1 || part != 0)) {
                 int owner = 0;                                     // part that finishes token mf + j
 #pragma unroll 1
                 for (int mf = 0; mf < p.M; mf += 4) {
