@@ -381,6 +381,10 @@ NVFP4R_API int nvfp4r_peer_close(void* peer_ptr);
 NVFP4R_API int nvfp4r_peer_free(void* ptr);
 NVFP4R_API int nvfp4r_peer_allreduce_bf16(const nvfp4r_peer_comm* comm, const void* in, void* out,
                                           size_t count, int mode, void* stream);
+/* Polls a gather makes per group of slots before it gives up on a peer (0 = default, a second
+ * or two). Failure detection: the launch then finishes, the result is undefined and
+ * nvfp4r_check_device_status returns NVFP4R_ERR_DEVICE_TIMEOUT. */
+NVFP4R_API int nvfp4r_set_peer_poll_limit(unsigned polls);
 
 /* Reads and clears the device-side time-out flag of the current device
  * (synchronises the device; diagnostics only). Returns 0, or

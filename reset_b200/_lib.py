@@ -101,6 +101,7 @@ PROTOTYPES = {
     "nvfp4r_peer_close": (_i, [_vp]),
     "nvfp4r_peer_free": (_i, [_vp]),
     "nvfp4r_peer_allreduce_bf16": (_i, [C.POINTER(PeerComm), _vp, _vp, _sz, _i, _vp]),
+    "nvfp4r_set_peer_poll_limit": (_i, [C.c_uint]),
     "nvfp4r_check_device_status": (_i, []),
 }
 

@@ -30,7 +30,8 @@ namespace {
 
 constexpr int kMaxWorld = NVFP4R_PEER_MAX_WORLD;
 constexpr size_t kHeaderBytes = 256;                 // [0] call counter, [1] finished-CTA counter
-constexpr uint32_t kPeerPollLimit = 20000000u;       // ~ seconds; a dead peer ends the wait, not the GPU
+constexpr uint32_t kPeerPollLimit = 4000000u;        // default: a second or two; a dead peer ends the wait, not the GPU
+uint32_t g_peer_poll_limit = kPeerPollLimit;         // host copy, passed with every launch
 
 __device__ int g_peer_status = 0;
 
@@ -42,6 +43,7 @@ struct PeerParams {
     uint32_t* out;
     unsigned long long pairs;
     int mode;                                        // bit 0: push, bit 1: gather
+    uint32_t poll_limit;
 };
 
 __device__ __forceinline__ void peer_store(unsigned long long* p, unsigned long long v) {
@@ -91,7 +93,7 @@ peer_allreduce_kernel(const PeerParams p) {
                         all = false;
                     }
                 if (all) break;
-                if (it > kPeerPollLimit) { ok = false; break; }
+                if (it > p.poll_limit) { ok = false; break; }
             }
             float lo = 0.0f, hi = 0.0f;
 #pragma unroll
@@ -176,6 +178,11 @@ int nvfp4r_peer_free(void* ptr) {
     return cudaFree(ptr) == cudaSuccess ? NVFP4R_OK : NVFP4R_ERR_CUDA;
 }
 
+int nvfp4r_set_peer_poll_limit(unsigned polls) {
+    g_peer_poll_limit = polls == 0 ? kPeerPollLimit : polls;
+    return NVFP4R_OK;
+}
+
 int nvfp4r_peer_allreduce_bf16(const nvfp4r_peer_comm* comm, const void* in, void* out, size_t count,
                                int mode, void* stream) {
     if (!comm || !in || !out || count == 0 || (count & 1)) return NVFP4R_ERR_INVALID_ARGUMENT;
@@ -197,6 +204,7 @@ int nvfp4r_peer_allreduce_bf16(const nvfp4r_peer_comm* comm, const void* in, voi
     p.out = static_cast<uint32_t*>(out);
     p.pairs = pairs;
     p.mode = mode;
+    p.poll_limit = g_peer_poll_limit;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(static_cast<unsigned>((pairs + 255) / 256));
     cfg.blockDim = dim3(256);

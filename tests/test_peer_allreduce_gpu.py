@@ -183,3 +183,40 @@ def test_linear_push_epilogue_emulated_ranks(M):
         torch.cuda.synchronize()
         for p in ptrs:
             lib.nvfp4r_peer_free(p)
+
+
+def test_missing_peer_is_reported_not_waited_for_forever():
+    """Failure detection: a gather whose peer never pushed gives up after its poll limit (set
+    short here), the launch finishes, and the host reads a time-out status; the device stays
+    usable."""
+    from reset_b200 import _lib as L
+    lib = L.lib()
+    world, max_elems = 2, 1024
+    nbytes = lib.nvfp4r_peer_buffer_bytes(world, max_elems)
+    ptrs = []
+    for _ in range(world):
+        p, h = C.c_void_p(), C.create_string_buffer(64)
+        L.check(lib.nvfp4r_peer_alloc(nbytes, C.byref(p), h), "alloc")
+        ptrs.append(p)
+    try:
+        c = L.PeerComm()
+        c.world, c.rank, c.max_elems = world, 0, max_elems
+        for k in range(world):
+            c.base[k] = ptrs[k].value
+        x = torch.ones(512, dtype=torch.bfloat16, device="cuda")
+        stream = torch.cuda.current_stream().cuda_stream
+        L.check(lib.nvfp4r_check_device_status(), "clean before")
+        L.check(lib.nvfp4r_set_peer_poll_limit(100000), "limit")       # a few tens of milliseconds
+        # rank 0 pushes and gathers, "rank 1" never shows up
+        L.check(lib.nvfp4r_peer_allreduce_bf16(C.byref(c), x.data_ptr(), x.data_ptr(), 512, L.PEER_ALLREDUCE, stream),
+                "launch")
+        torch.cuda.synchronize()
+        assert lib.nvfp4r_check_device_status() == -5                  # NVFP4R_ERR_DEVICE_TIMEOUT, and cleared
+        L.check(lib.nvfp4r_check_device_status(), "cleared")
+        y = torch.arange(8, device="cuda").float().sum()                # the context is alive
+        assert float(y) == 28.0
+    finally:
+        lib.nvfp4r_set_peer_poll_limit(0)
+        torch.cuda.synchronize()
+        for p in ptrs:
+            lib.nvfp4r_peer_free(p)
