@@ -220,7 +220,9 @@ NVFP4R_API int nvfp4r_linear_packed_ex(const nvfp4r_prologue* pro, const void* x
                                        int N, float alpha, void* out, int out_dtype, int rcp_mode,
                                        void* workspace, size_t workspace_bytes, void* stream);
 
-/* Debug/tuning: force the K split of the packed linear (0 = automatic). */
+/* Debug/tuning of the packed linear: bits 0-7 force the K split (0 = automatic), bit 8 records
+ * an in-kernel time line of eight CTAs (bits 12-23: the first of them), bit 9 runs one CTA per
+ * SM instead of two. */
 NVFP4R_API int nvfp4r_set_packed_tuning(int splits);
 
 /* Debug/tuning: force the K split and ring depth of the tensor-core kernel (0 = automatic). */

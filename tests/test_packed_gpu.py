@@ -55,7 +55,10 @@ def test_pack_weight_layout(capi):
 
 
 @pytest.mark.parametrize("N,K", [(128, 256), (256, 768), (4096, 4096), (6144, 4096), (1280, 5120),
-                                 (4096, 12288), (512, 25600), (24576, 4096), (896, 5120)])
+                                 (4096, 12288), (512, 25600), (24576, 4096), (896, 5120),
+                                 # tensor-parallel shards of the bench's Qwen3-8B set (TP 4 / 8)
+                                 (768, 4096), (4096, 512), (3072, 4096), (4096, 1536), (4096, 1024),
+                                 (6144, 4096), (4096, 3072)])
 @pytest.mark.parametrize("M", [1, 8])
 def test_linear_packed_matches_oracle(capi, N, K, M):
     w, ws = onv.random_nvfp4((N,), K, seed=N % 89 + M)
