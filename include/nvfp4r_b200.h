@@ -417,6 +417,12 @@ NVFP4R_API int nvfp4r_qk_norm_rope_kv(const void* qkv, const void* q_weight, con
                                       const int32_t* position, void* kcache, void* vcache,
                                       void* q_out, int Hq, int Hkv, int D, int Tmax, float theta,
                                       float eps, void* stream);
+/* Optional table for the rotary embedding of nvfp4r_qk_norm_rope_kv / nvfp4r_attn_decode_rope:
+ * `cos_sin` = device array of float pairs [rows][64] = (cos, sin)(pos * theta^(-2d/128)), built
+ * once by the caller for its theta (vLLM keeps the same kind of cos_sin_cache). While set, and
+ * rows >= Tmax of the call, the kernels read it instead of evaluating powf/sincosf. Process-wide
+ * (one device per process); NULL clears it. */
+NVFP4R_API int nvfp4r_set_rope_table(const float* cos_sin, int rows);
 /* nvfp4r_attn_decode_rope = nvfp4r_qk_norm_rope_kv + nvfp4r_attn_decode in one launch: `qkv`
  * is the raw fused row [(Hq + 2 Hkv) * D]; the token's position is *seq_len - 1; the new K/V row
  * is appended to the caches by the launch itself. Same workspace rule as nvfp4r_attn_decode. */

@@ -92,6 +92,7 @@ PROTOTYPES = {
     "nvfp4r_attn_decode_workspace_bytes": (_sz, [_i, _i]),
     "nvfp4r_attn_decode": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp, _sz, _vp]),
     "nvfp4r_attn_decode_rope": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _f, _f, _vp, _sz, _vp]),
+    "nvfp4r_set_rope_table": (_i, [_vp, _i]),
     "nvfp4r_silu_mul": (_i, [_vp, _vp, _i, _i, _vp]),
     "nvfp4r_lm_head": (_i, [_vp, _vp, _vp, _i, _i, _vp]),
     "nvfp4r_argmax": (_i, [_vp, _i64, _i, _i, _vp, _vp]),

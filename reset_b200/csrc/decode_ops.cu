@@ -73,9 +73,13 @@ add_rmsnorm_kernel(const __nv_bfloat16* __restrict__ x, __nv_bfloat16* __restric
 
 // RMSNorm(head) * w followed by the rotary embedding (rotate-half pairs d, d + D/2) of one
 // 128-wide head by one warp: lane holds dims lane, lane+32 (first half), lane+64, lane+96.
+// `table` (optional): cos/sin of pos * theta^(-2d/D) as float2 [Tmax][D/2], prepared once by the
+// host; without it the angles are computed here (powf + sincosf: a few hundred instructions
+// that run once per launch).
 __device__ __forceinline__ void head_norm_rope(const __nv_bfloat16* __restrict__ src,
                                                const __nv_bfloat16* __restrict__ w, int pos, float theta,
-                                               float eps, int lane, float o[4]) {
+                                               float eps, int lane, float o[4],
+                                               const float2* __restrict__ table = nullptr) {
     constexpr int D = 128;
     float v[4];
 #pragma unroll
@@ -88,9 +92,15 @@ __device__ __forceinline__ void head_norm_rope(const __nv_bfloat16* __restrict__
 #pragma unroll
     for (int j = 0; j < 2; ++j) {
         const int d = lane + 32 * j;                           // 0..63
-        const float freq = powf(theta, -static_cast<float>(2 * d) / static_cast<float>(D));
         float sn, cs;
-        sincosf(static_cast<float>(pos) * freq, &sn, &cs);
+        if (table != nullptr) {
+            const float2 t = __ldg(table + static_cast<int64_t>(pos) * (D / 2) + d);
+            cs = t.x;
+            sn = t.y;
+        } else {
+            const float freq = powf(theta, -static_cast<float>(2 * d) / static_cast<float>(D));
+            sincosf(static_cast<float>(pos) * freq, &sn, &cs);
+        }
         o[j] = v[j] * cs - v[j + 2] * sn;
         o[j + 2] = v[j + 2] * cs + v[j] * sn;
     }
@@ -104,7 +114,7 @@ qk_norm_rope_kv_kernel(const __nv_bfloat16* __restrict__ qkv, const __nv_bfloat1
                        const __nv_bfloat16* __restrict__ k_w, const int* __restrict__ position,
                        __nv_bfloat16* __restrict__ kcache, __nv_bfloat16* __restrict__ vcache,
                        __nv_bfloat16* __restrict__ q_out, int Hq, int Hkv, int Tmax, float theta,
-                       float eps) {
+                       float eps, const float2* __restrict__ table) {
     constexpr int D = 128;
     pdl_wait_prior();
     const int head = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
@@ -124,7 +134,7 @@ qk_norm_rope_kv_kernel(const __nv_bfloat16* __restrict__ qkv, const __nv_bfloat1
     }
     const bool is_q = head < Hq;
     float o[4];
-    head_norm_rope(src, is_q ? q_w : k_w, pos, theta, eps, lane, o);
+    head_norm_rope(src, is_q ? q_w : k_w, pos, theta, eps, lane, o, table);
     __nv_bfloat16* dst = is_q ? q_out + static_cast<int64_t>(head) * D
                               : kcache + (static_cast<int64_t>(head - Hq) * Tmax + pos) * D;
 #pragma unroll
@@ -173,6 +183,7 @@ struct AttnRope {
     const __nv_bfloat16* q_w;
     const __nv_bfloat16* k_w;
     float theta, eps;
+    const float2* table;
 };
 
 template <bool kFusedRope>
@@ -245,7 +256,7 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __restric
             // the row position is len - 1 (the token being decoded)
             if (warp < group) {
                 float o[4];
-                head_norm_rope(q + static_cast<int64_t>(qh) * kAttnD, rope.q_w, len - 1, rope.theta, rope.eps, lane, o);
+                head_norm_rope(q + static_cast<int64_t>(qh) * kAttnD, rope.q_w, len - 1, rope.theta, rope.eps, lane, o, rope.table);
                 __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(qs + warp * kAttnPitch);
 #pragma unroll
                 for (int j = 0; j < 4; ++j) dst[lane + 32 * j] = __float2bfloat16_rn(o[j]);
@@ -255,7 +266,7 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __restric
                 const int64_t g = (static_cast<int64_t>(kvh) * Tmax + len - 1) * kAttnD;
                 if (warp == 0) {
                     float o[4];
-                    head_norm_rope(q + static_cast<int64_t>(Hq + kvh) * kAttnD, rope.k_w, len - 1, rope.theta, rope.eps, lane, o);
+                    head_norm_rope(q + static_cast<int64_t>(Hq + kvh) * kAttnD, rope.k_w, len - 1, rope.theta, rope.eps, lane, o, rope.table);
                     __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(ks + r * kAttnPitch);
 #pragma unroll
                     for (int j = 0; j < 4; ++j) {
@@ -524,6 +535,11 @@ inline int done(cudaError_t e) { return e == cudaSuccess ? NVFP4R_OK : NVFP4R_ER
 
 using namespace nvfp4r;
 
+// Optional rotary table of the current process (one device per process): set by
+// nvfp4r_set_rope_table, read by the two rotary entry points.
+static const float2* g_rope_table = nullptr;
+static int g_rope_table_rows = 0;
+
 extern "C" {
 
 int nvfp4r_add_rmsnorm(const void* x, void* residual, const void* weight, void* out, int M, int H,
@@ -546,7 +562,15 @@ int nvfp4r_qk_norm_rope_kv(const void* qkv, const void* q_weight, const void* k_
                            static_cast<const __nv_bfloat16*>(qkv), static_cast<const __nv_bfloat16*>(q_weight),
                            static_cast<const __nv_bfloat16*>(k_weight), position,
                            static_cast<__nv_bfloat16*>(kcache), static_cast<__nv_bfloat16*>(vcache),
-                           static_cast<__nv_bfloat16*>(q_out), Hq, Hkv, Tmax, theta, eps));
+                           static_cast<__nv_bfloat16*>(q_out), Hq, Hkv, Tmax, theta, eps,
+                           (g_rope_table != nullptr && g_rope_table_rows >= Tmax) ? g_rope_table : nullptr));
+}
+
+int nvfp4r_set_rope_table(const float* cos_sin, int rows) {
+    if (cos_sin != nullptr && rows <= 0) return NVFP4R_ERR_INVALID_ARGUMENT;
+    g_rope_table = reinterpret_cast<const float2*>(cos_sin);
+    g_rope_table_rows = cos_sin ? rows : 0;
+    return NVFP4R_OK;
 }
 
 size_t nvfp4r_attn_decode_workspace_bytes(int Hq, int Tmax) {
@@ -584,7 +608,7 @@ int nvfp4r_attn_decode(const void* q, const void* kcache, const void* vcache, co
                        void* out, int Hq, int Hkv, int D, int Tmax, void* workspace,
                        size_t workspace_bytes, void* stream) {
     return attn_launch(false, q, const_cast<void*>(kcache), const_cast<void*>(vcache), seq_len, out, Hq, Hkv, D,
-                       Tmax, workspace, workspace_bytes, AttnRope{nullptr, nullptr, 0.0f, 0.0f}, stream);
+                       Tmax, workspace, workspace_bytes, AttnRope{nullptr, nullptr, 0.0f, 0.0f, nullptr}, stream);
 }
 
 int nvfp4r_attn_decode_rope(const void* qkv, const void* q_weight, const void* k_weight, void* kcache,
@@ -593,7 +617,9 @@ int nvfp4r_attn_decode_rope(const void* qkv, const void* q_weight, const void* k
     if (!q_weight || !k_weight) return NVFP4R_ERR_INVALID_ARGUMENT;
     return attn_launch(true, qkv, kcache, vcache, seq_len, out, Hq, Hkv, D, Tmax, workspace, workspace_bytes,
                        AttnRope{static_cast<const __nv_bfloat16*>(q_weight),
-                                static_cast<const __nv_bfloat16*>(k_weight), theta, eps}, stream);
+                                static_cast<const __nv_bfloat16*>(k_weight), theta, eps,
+                                (g_rope_table != nullptr && g_rope_table_rows >= Tmax) ? g_rope_table : nullptr},
+                       stream);
 }
 
 int nvfp4r_silu_mul(const void* gate_up, void* out, int M, int I, void* stream) {

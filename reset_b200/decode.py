@@ -149,6 +149,12 @@ class DecodeStep:
         n = L.lib().nvfp4r_attn_decode_workspace_bytes(self.hq, cfg.context)
         self.attn_ws = torch.zeros((n + 3) // 4, dtype=torch.float32, device=self.device)
         self.graph = None
+        # rotary table (cos, sin)(pos * theta^(-2d/D)) for every position of the context
+        half = D // 2
+        freq = cfg.rope_theta ** (-torch.arange(0, half, device=self.device, dtype=torch.float32) * 2 / D)
+        ang = torch.arange(cfg.context, device=self.device, dtype=torch.float32)[:, None] * freq[None, :]
+        self.rope_table = torch.stack([torch.cos(ang), torch.sin(ang)], dim=-1).contiguous()
+        L.check(L.lib().nvfp4r_set_rope_table(self.rope_table.data_ptr(), cfg.context), "set_rope_table")
         # the sum exchange after o_proj / down_proj: one-shot kernel over peer memory, or NCCL
         self.peer = None
         if world > 1 and peer_allreduce:

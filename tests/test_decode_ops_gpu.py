@@ -54,6 +54,7 @@ def _rope_ref(v, pos, theta):
 
 
 def test_qk_norm_rope_kv_and_attention(lib):
+    lib.check(lib.lib().nvfp4r_set_rope_table(None, 0), "no table: angles computed in the kernel")
     Hq, Hkv, D, T = 16, 2, 128, 512
     pos = 300
     g = torch.Generator(device="cuda").manual_seed(1)
@@ -102,12 +103,20 @@ def test_qk_norm_rope_kv_and_attention(lib):
         assert torch.equal(out, out2)
 
 
+@pytest.mark.parametrize("with_table", [False, True])
 @pytest.mark.parametrize("pos", [0, 127, 128, 300, 511])
-def test_attention_with_fused_rope_equals_two_launches(lib, pos):
+def test_attention_with_fused_rope_equals_two_launches(lib, pos, with_table):
     """nvfp4r_attn_decode_rope (head norms + rotary + cache append + attention in one launch)
     against nvfp4r_qk_norm_rope_kv followed by nvfp4r_attn_decode: same caches bit for bit, same
     attention output bit for bit (the same arithmetic runs in both)."""
     Hq, Hkv, D, T = 16, 2, 128, 512
+    table = None
+    if with_table:                                      # (cos, sin) pairs per position and frequency
+        freq = 1e6 ** (-torch.arange(0, D // 2, device="cuda", dtype=torch.float32) * 2 / D)
+        ang = torch.arange(T, device="cuda", dtype=torch.float32)[:, None] * freq[None, :]
+        table = torch.stack([torch.cos(ang), torch.sin(ang)], dim=-1).contiguous()
+    lib.check(lib.lib().nvfp4r_set_rope_table(None if table is None else table.data_ptr(), T if with_table else 0),
+              "rope table")
     g = torch.Generator(device="cuda").manual_seed(10 + pos)
     qkv = torch.randn(1, (Hq + 2 * Hkv) * D, device="cuda", generator=g).to(torch.bfloat16)
     qw = (1 + 0.1 * torch.randn(D, device="cuda", generator=g)).to(torch.bfloat16)
@@ -132,8 +141,12 @@ def test_attention_with_fused_rope_equals_two_launches(lib, pos):
                                                 vc2.data_ptr(), seq_len.data_ptr(), out_b.data_ptr(), Hq, Hkv, D,
                                                 T, 1e6, 1e-6, ws.data_ptr(), ws.numel() * 4, _s()), "attn_rope")
     torch.cuda.synchronize()
+    lib.check(lib.lib().nvfp4r_set_rope_table(None, 0), "clear")
     assert torch.equal(kc, kc2) and torch.equal(vc, vc2)
     assert torch.equal(out_a, out_b)
+    heads = qkv.float().view(Hq + 2 * Hkv, D)
+    qn = (heads[:Hq] * torch.rsqrt(heads[:Hq].pow(2).mean(-1, keepdim=True) + 1e-6) * qw.float()).to(torch.bfloat16).float()
+    assert torch.allclose(q.float().view(Hq, D), _rope_ref(qn, pos, 1e6), rtol=2e-2, atol=2e-2)
 
 
 def test_silu_mul_lm_head_argmax(lib):
