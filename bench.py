@@ -46,7 +46,7 @@ FALLBACK_HBM_GBS = 6650.0
 # dram__bytes_read.sum + dram__bytes_write.sum per launch, averaged over the launches of a
 # step, from the ncu launch list summarised in profiles/bench_step_launch_list.md
 # (algorithmic bytes per launch: 27.1 MB)
-NCU_TRAFFIC_BYTES_PER_LAUNCH = 25.2e6
+NCU_TRAFFIC_BYTES_PER_LAUNCH = 27.4e6
 
 
 def linear_bytes(N: int, K: int, M: int) -> int:
