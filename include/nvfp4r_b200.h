@@ -297,8 +297,14 @@ NVFP4R_API size_t nvfp4r_reset_workspace_bytes(int B);
  *   params      one record on the HOST, copied by value into the launch
  *   decisions   [B] or NULL
  *   workspace   >= nvfp4r_reset_workspace_bytes(B) bytes of device scratch, 8-byte
- *               aligned, contents irrelevant on entry; calls that share a
- *               workspace must be ordered on the stream
+ *               aligned, ALL ZERO before its first use (it holds a step counter per
+ *               row that the calls advance); calls that share a workspace must be
+ *               ordered on the stream
+ * The step is ONE launch when the logits rows are 16-byte aligned, V % 4 == 0 and the
+ * grid fits the device at once (slices of at most 5120 elements, a few hundred CTAs):
+ * every CTA keeps its slice of the row in registers between the load and the final store,
+ * and the CTAs of a row exchange their partial results through epoch-tagged 64-bit
+ * slots. Otherwise three stream-ordered launches compute the same values.
  */
 NVFP4R_API int nvfp4r_reset_step(float* logits, int64_t row_stride, int B, int V,
                                  nvfp4r_reset_state* states, const int32_t* state_slots,

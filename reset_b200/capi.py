@@ -251,7 +251,7 @@ def swizzle_blockscale(flat: torch.Tensor) -> torch.Tensor:
 
 def reset_workspace(B: int, device) -> torch.Tensor:
     n = L.lib().nvfp4r_reset_workspace_bytes(B)
-    return torch.empty((n + 7) // 8, dtype=torch.int64, device=device)
+    return torch.zeros((n + 7) // 8, dtype=torch.int64, device=device)       # zeroed: it holds step counters
 
 
 def entropy(logits: torch.Tensor, workspace: torch.Tensor | None = None) -> torch.Tensor:

@@ -358,7 +358,7 @@ int nvfp4r_swizzle_blockscale(const void* flat, void* swizzled, int rows, int K,
 }
 
 size_t nvfp4r_reset_workspace_bytes(int B) {
-    return B > 0 ? static_cast<size_t>(B) * sizeof(nvfp4r::RowScratch) : 0;
+    return B > 0 ? static_cast<size_t>(B) * (sizeof(nvfp4r::RowScratch) + sizeof(nvfp4r::RowSlots)) : 0;
 }
 
 int nvfp4r_reset_step(float* logits, int64_t row_stride, int B, int V, nvfp4r_reset_state* states,
@@ -382,6 +382,7 @@ int nvfp4r_reset_step(float* logits, int64_t row_stride, int B, int V, nvfp4r_re
     p.B = B;
     p.V = V;
     p.scratch = static_cast<nvfp4r::RowScratch*>(workspace);
+    p.slots = reinterpret_cast<nvfp4r::RowSlots*>(static_cast<nvfp4r::RowScratch*>(workspace) + B);
     p.states = states;
     p.state_slots = state_slots;
     p.last_ids = last_ids;
@@ -446,6 +447,7 @@ int nvfp4r_entropy(const float* logits, int64_t row_stride, int B, int V, float*
     p.B = B;
     p.V = V;
     p.scratch = static_cast<nvfp4r::RowScratch*>(workspace);
+    p.slots = reinterpret_cast<nvfp4r::RowSlots*>(static_cast<nvfp4r::RowScratch*>(workspace) + B);
     p.entropy_out = entropy;
     p.needs_state = 0;
     cudaError_t e = nvfp4r::launch_reset(p, false, as_stream(stream));
@@ -467,8 +469,10 @@ int nvfp4r_check_device_status(void) {
     int flag3 = 0;
     if (e == cudaSuccess) e = nvfp4r::read_and_clear_tc_status(&flag2);
     if (e == cudaSuccess) e = nvfp4r::read_and_clear_packed_status(&flag3);
-    int flag4 = 0;
+    int flag4 = 0, flag5 = 0;
     if (e == cudaSuccess) e = nvfp4r::read_and_clear_peer_status(&flag4);
+    if (e == cudaSuccess) e = nvfp4r::read_and_clear_reset_status(&flag5);
+    flag4 |= flag5;
     if (e != cudaSuccess) return cuda_fail(e, "device status");
     flag |= flag2 | flag3 | flag4;
     return flag ? fail(NVFP4R_ERR_DEVICE_TIMEOUT, "a bounded device-side wait gave up") : NVFP4R_OK;

@@ -115,6 +115,7 @@ cudaError_t read_packed_trace(unsigned long long* out16);
 cudaError_t read_and_clear_device_status(int* flag);
 
 cudaError_t read_and_clear_peer_status(int* flag);
+cudaError_t read_and_clear_reset_status(int* flag);
 
 int device_sm_count();
 

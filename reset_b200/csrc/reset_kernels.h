@@ -21,12 +21,28 @@ struct RowScratch {
     int argmax;                     // row argmax
 };
 
+// Hand-over slots of the single-launch step (reset_fused_kernel): 64-bit words {epoch:32 |
+// payload:32}; a word counts only while its epoch equals the row's current one, so nothing is
+// ever cleared. All-zero memory is a valid initial state (epoch 0, first step uses 1).
+struct RowSlots {
+    unsigned long long pmax[kResetMaxSlices];    // slice max (float bits)
+    unsigned long long psum[kResetMaxSlices];    // slice sum of exp(x - slice max)
+    unsigned long long parg[kResetMaxSlices];    // slice argmax
+    unsigned long long ent_hi[kResetMaxSlices];  // slice sum of p*log(max(p,1e-10)), double, high word
+    unsigned long long ent_lo[kResetMaxSlices];  //                                    low word
+    unsigned long long temp;                     // chosen temperature (float bits)
+    unsigned long long mode;                     // 0: divide, 1: leave untouched (T == 1), 2: one-hot at argmax
+    unsigned epoch;                              // step counter of the row, advanced by its deciding CTA
+    unsigned pad;
+};
+
 struct ResetLaunch {
     const float* logits;
     int64_t row_stride;
     int B, V;
     int n_slices, slice_len;
     RowScratch* scratch;
+    RowSlots* slots;       // single-launch path; nullptr = three-launch path only
     nvfp4r_reset_state* states;
     const int32_t* state_slots;
     const int32_t* last_ids;

@@ -38,7 +38,7 @@ def test_host_side_sizes_without_a_gpu():
     lib = _lib.lib()
     assert lib.nvfp4r_packed_weight_bytes(4096, 4096) == 4096 * 4096 * 9 // 16
     assert lib.nvfp4r_packed_weight_bytes(100, 4096) == 0
-    assert lib.nvfp4r_reset_workspace_bytes(8) == 8 * 656
+    assert lib.nvfp4r_reset_workspace_bytes(8) == 8 * (656 + 1304)
     assert lib.nvfp4r_attn_decode_workspace_bytes(64, 2048) == 64 * 16 * 132 * 4 + 64 * 4
     assert lib.nvfp4r_peer_buffer_bytes(2, 5120) == 256 + 2 * 2 * 2560 * 8
     assert lib.nvfp4r_peer_buffer_bytes(9, 5120) == 0
