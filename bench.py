@@ -382,7 +382,7 @@ def run_ours(args, rank, world, local_rank):
 
 
 def run_decode(args, rank, world, device):
-    """Qwen3-32B batch-1 decode step (BASELINE config 3): random-init NVFP4 weights, bf16 KV
+    """Qwen3-32B batch-1 decode step: random-init NVFP4 weights, bf16 KV
     cache at context 2048, one CUDA graph per token, tensor-parallel over `world` ranks with
     an NCCL all-reduce after o_proj and down_proj."""
     import torch.distributed as dist
@@ -470,7 +470,7 @@ SWEEP_SHAPES = {
 
 
 def run_sweep(args):
-    """M sweep 1..16 over one model's four linear shapes (BASELINE config 4): the fused
+    """M sweep 1..16 over one model's four linear shapes: the fused
     quantize + CUDA-core GEMV, the fused quantize + tcgen05 packed linear, and, when the
     installed vLLM's operators load, its `scaled_fp4_quant` + `cutlass_scaled_fp4_mm` pair.
     Every launch reads a weight copy that has left L2 (copies total > 1 GB)."""
@@ -541,7 +541,7 @@ def run_sweep(args):
 
 
 def run_reset_loop(args):
-    """ReSET decode loop (BASELINE config 2): vocab 151936, batch 1..8, a delimiter every 40-120
+    """ReSET decode loop: vocab 151936, batch 1..8, a delimiter every 40-120
     tokens, t_high 1.0 / t_low 0.1 / tau_0 0.5505 / w 32. GPU: one fused step per token for the
     whole batch (three launches), CUDA-graph replay over a pool of distinct logits buffers larger
     than L2, restored before every replay because the step divides in place. CPU: the oracle's

@@ -129,7 +129,7 @@ def test_gemv_large_scales_do_not_overflow(capi, path):
 
 
 def test_gemv_config0_quantized_weights(capi, path):
-    """BASELINE config 0: M=1, K=N=4096, bf16 N(0,0.02) weights and N(0,1) activations
+    """The 4096 x 4096 single-token case: M=1, K=N=4096, bf16 N(0,0.02) weights and N(0,1) activations
     with outlier channels, both quantized; result vs fp32 dequant-matmul."""
     N = K = 4096
     wc, wsf, gs_w = make_weight(N, K, seed=0)

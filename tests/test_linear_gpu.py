@@ -27,7 +27,7 @@ QWEN3_8B = {"qkv_proj": (6144, 4096), "o_proj": (4096, 4096),
 @pytest.mark.parametrize("name", list(QWEN3_8B))
 @pytest.mark.parametrize("M", [1, 2, 4, 8])
 def test_linear_qwen3_8b_shapes(capi, name, M):
-    """BASELINE config 1: the Qwen3-8B decode linears incl. activation quantization.
+    """The Qwen3-8B decode linears incl. activation quantization.
     Row count is cut to 512 rows of the full N for the oracle's sake; the full-N
     case is covered by the property test below."""
     N, K = QWEN3_8B[name]

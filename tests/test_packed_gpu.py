@@ -109,7 +109,7 @@ def test_linear_packed_every_split_agrees(capi, splits):
 
 
 def test_linear_packed_equals_cuda_core_linear_config1(capi):
-    """BASELINE config 1 shapes at full size: tensor-core path vs CUDA-core path on the
+    """The Qwen3-8B linear set at full size: tensor-core path vs CUDA-core path on the
     same quantized weights (bf16 N(0,0.02)) and activations (N(0,1) + outliers)."""
     for name, (N, K) in {"qkv": (6144, 4096), "down": (4096, 12288)}.items():
         wc, wsf, gs_w = make_weight(N, K, seed=7)

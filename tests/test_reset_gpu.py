@@ -122,7 +122,7 @@ def _decode_loop(capi, B, V, steps, seed, t_high, t_low, tau0, window, sigma=3.0
 
 
 def test_reset_decode_loop_full_vocab(capi):
-    """BASELINE config 2 at reduced length: vocab 151936, batch 4, delimiter every
+    """The decode-loop case at reduced length: vocab 151936, batch 4, delimiter every
     40-120 tokens, t_low 0.1, tau0 0.5505, 160 steps."""
     ties, mism, err = _decode_loop(capi, 4, 151936, 160, seed=1, t_high=1.0, t_low=0.1,
                                    tau0=0.5505, window=32)
