@@ -445,6 +445,21 @@ NVFP4R_API int nvfp4r_lm_head(const void* x, const void* weight, float* logits, 
                               void* stream);
 NVFP4R_API int nvfp4r_argmax(const float* logits, int64_t row_stride, int B, int V, int32_t* out,
                              void* stream);
+/* One token id per row drawn from softmax(logits[b, :]) by the Gumbel-max rule
+ * (arg-max of logits + Gumbel noise), entirely on the device. In the reference's deployment
+ * this is vLLM's sampler running at temperature 1.0 on the logits the ReSET processor has
+ * already scaled (reset/README.md:87-88); here it lets a whole decode step, processor and
+ * sampling included, stay in one CUDA graph with no host round trip.
+ *   seed      any value; together with the row index and the row's draw counter it keys a
+ *             counter-based generator, so results are reproducible
+ *   draws     [B] uint64 on the device, zeroed by the caller at request start; advanced by
+ *             one per call (a replayed graph therefore keeps drawing fresh numbers)
+ *   last_ids  [B,2] int32 on the device or NULL: shifted left with the drawn id appended,
+ *             which is the `last_ids` input of nvfp4r_reset_step for the next step
+ * Rows holding one 0 and -inf elsewhere (what ReSET writes for temperatures <= 1e-6) return
+ * the position of the 0. B <= 256. */
+NVFP4R_API int nvfp4r_sample(const float* logits, int64_t row_stride, int B, int V, uint64_t seed,
+                             uint64_t* draws, int32_t* last_ids, int32_t* out, void* stream);
 
 #ifdef __cplusplus
 }

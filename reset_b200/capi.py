@@ -290,6 +290,30 @@ def reset_step(logits: torch.Tensor, states: torch.Tensor, params: L.ResetParams
     L.check(st, "nvfp4r_reset_step")
 
 
+def sample(logits: torch.Tensor, draws: torch.Tensor, *, seed: int = 0,
+           last_ids: torch.Tensor | None = None, out: torch.Tensor | None = None) -> torch.Tensor:
+    """One id per row drawn from softmax(logits) on the device (Gumbel-max). ``draws`` is an
+    int64 [B] counter tensor (zero at request start, advanced by the call); ``last_ids``
+    (int32 [B,2], optional) gets the new id shifted in. Returns int32 [B]."""
+    _need_cuda(logits, draws, last_ids, out)
+    if logits.dtype != torch.float32 or logits.dim() != 2 or logits.stride(1) != 1:
+        raise ValueError("sample: logits must be fp32 [B,V] with unit inner stride")
+    B, V = logits.shape
+    if draws.dtype != torch.int64 or draws.numel() < B:
+        raise ValueError("sample: draws must be int64 [B]")
+    if last_ids is not None and (last_ids.dtype != torch.int32 or last_ids.numel() < 2 * B
+                                 or not last_ids.is_contiguous()):
+        raise ValueError("sample: last_ids must be contiguous int32 [B,2]")
+    if out is None:
+        out = torch.empty(B, dtype=torch.int32, device=logits.device)
+    with torch.cuda.device(logits.device):
+        st = L.lib().nvfp4r_sample(logits.data_ptr(), logits.stride(0), B, V, int(seed) & (2 ** 64 - 1),
+                                   draws.data_ptr(), None if last_ids is None else last_ids.data_ptr(),
+                                   out.data_ptr(), _stream())
+    L.check(st, "nvfp4r_sample")
+    return out
+
+
 def linear_packed_push(x: torch.Tensor, global_scale_inv: torch.Tensor, packed: torch.Tensor, N: int,
                        alpha: float, workspace: torch.Tensor, push, out: torch.Tensor,
                        rcp_mode: int = L.RCP_APPROX) -> torch.Tensor:

@@ -479,8 +479,28 @@ __device__ __forceinline__ void argmax_block_reduce(float& best, int& arg, float
             if (smax[w] > best || (smax[w] == best && sarg[w] < arg)) { best = smax[w]; arg = sarg[w]; }
 }
 
+// Standard Gumbel noise -log(-log(u)) for element i of a row, from a counter-based generator:
+// the 64-bit finalizer of splitmix64 over (key + i * odd constant), top 23 bits -> u in (0, 1).
+// `key` already mixes the seed, the row and the row's draw counter, so every draw of every row
+// uses its own stream and a replayed CUDA graph keeps drawing fresh numbers.
+__device__ __forceinline__ unsigned long long mix64(unsigned long long z) {
+    z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ull;
+    z = (z ^ (z >> 27)) * 0x94D049BB133111EBull;
+    return z ^ (z >> 31);
+}
+__device__ __forceinline__ float gumbel_noise(unsigned long long key, int i) {
+    const unsigned long long r = mix64(key + static_cast<unsigned long long>(i) * 0x9E3779B97F4A7C15ull);
+    // 23 bits: (x + 0.5) / 2^23 is exact in fp32 and stays strictly inside (0, 1)
+    const float u = (static_cast<float>(static_cast<unsigned>(r >> 41)) + 0.5f) * (1.0f / 8388608.0f);
+    return -logf(-logf(u));
+}
+
+// kGumbel: the slice's maximum of logits[i] + Gumbel noise (sampling from softmax(logits) by
+// the Gumbel-max rule) instead of the plain maximum.
+template <bool kGumbel>
 __global__ void __launch_bounds__(256)
-argmax_partial_kernel(const float* __restrict__ logits, int64_t row_stride, int V) {
+argmax_partial_kernel(const float* __restrict__ logits, int64_t row_stride, int V, unsigned long long seed,
+                      const unsigned long long* __restrict__ draws) {
     __shared__ float smax[8];
     __shared__ int sarg[8];
     pdl_wait_prior();
@@ -489,8 +509,12 @@ argmax_partial_kernel(const float* __restrict__ logits, int64_t row_stride, int 
     const int lo = blockIdx.x * per, hi = min(V, lo + per);
     float best = -INFINITY;
     int arg = 0x7fffffff;
+    unsigned long long key = 0;
+    if (kGumbel)
+        key = mix64(seed ^ mix64((static_cast<unsigned long long>(blockIdx.y) << 40) + draws[blockIdx.y]));
     for (int i = lo + threadIdx.x; i < hi; i += blockDim.x) {
-        const float v = row[i];
+        float v = row[i];
+        if (kGumbel) v += gumbel_noise(key, i);
         if (v > best) { best = v; arg = i; }
     }
     argmax_block_reduce(best, arg, smax, sarg);
@@ -501,15 +525,26 @@ argmax_partial_kernel(const float* __restrict__ logits, int64_t row_stride, int 
     pdl_launch_dependents();
 }
 
+// draws / last_ids (sampling only, may be null): the row's draw counter advances by one and
+// the row's pair of most recent ids is shifted with the new id appended.
 __global__ void __launch_bounds__(64)
-argmax_final_kernel(int* __restrict__ out) {
+argmax_final_kernel(int* __restrict__ out, unsigned long long* __restrict__ draws, int* __restrict__ last_ids) {
     __shared__ float smax[2];
     __shared__ int sarg[2];
     pdl_wait_prior();
     float best = g_argmax_val[blockIdx.x * kArgmaxParts + threadIdx.x];
     int arg = g_argmax_idx[blockIdx.x * kArgmaxParts + threadIdx.x];
     argmax_block_reduce(best, arg, smax, sarg);
-    if (threadIdx.x == 0) out[blockIdx.x] = arg;
+    if (threadIdx.x == 0) {
+        // a row without any finite candidate (all -inf or NaN) yields id 0, never the sentinel
+        if (arg == 0x7fffffff) arg = 0;
+        out[blockIdx.x] = arg;
+        if (draws != nullptr) draws[blockIdx.x] += 1ull;
+        if (last_ids != nullptr) {
+            last_ids[2 * blockIdx.x] = last_ids[2 * blockIdx.x + 1];
+            last_ids[2 * blockIdx.x + 1] = arg;
+        }
+    }
 }
 
 template <typename Kern, typename... Args>
@@ -642,10 +677,23 @@ int nvfp4r_lm_head(const void* x, const void* weight, float* logits, int V, int 
 int nvfp4r_argmax(const float* logits, int64_t row_stride, int B, int V, int32_t* out, void* stream) {
     if (!logits || !out || B <= 0 || V <= 0) return NVFP4R_ERR_INVALID_ARGUMENT;
     if (B > kArgmaxMaxRows) return NVFP4R_ERR_UNSUPPORTED_SHAPE;
-    cudaError_t e = launch_pdl(argmax_partial_kernel, dim3(kArgmaxParts, B), dim3(256), 0, st(stream), logits,
-                               row_stride, V);
+    cudaError_t e = launch_pdl(argmax_partial_kernel<false>, dim3(kArgmaxParts, B), dim3(256), 0, st(stream), logits,
+                               row_stride, V, 0ull, static_cast<const unsigned long long*>(nullptr));
     if (e != cudaSuccess) return NVFP4R_ERR_CUDA;
-    return done(launch_pdl(argmax_final_kernel, dim3(B), dim3(kArgmaxParts), 0, st(stream), out));
+    return done(launch_pdl(argmax_final_kernel, dim3(B), dim3(kArgmaxParts), 0, st(stream), out,
+                           static_cast<unsigned long long*>(nullptr), static_cast<int*>(nullptr)));
+}
+
+int nvfp4r_sample(const float* logits, int64_t row_stride, int B, int V, uint64_t seed, uint64_t* draws,
+                  int32_t* last_ids, int32_t* out, void* stream) {
+    if (!logits || !out || !draws || B <= 0 || V <= 0) return NVFP4R_ERR_INVALID_ARGUMENT;
+    if (B > kArgmaxMaxRows) return NVFP4R_ERR_UNSUPPORTED_SHAPE;
+    cudaError_t e = launch_pdl(argmax_partial_kernel<true>, dim3(kArgmaxParts, B), dim3(256), 0, st(stream), logits,
+                               row_stride, V, static_cast<unsigned long long>(seed),
+                               reinterpret_cast<const unsigned long long*>(draws));
+    if (e != cudaSuccess) return NVFP4R_ERR_CUDA;
+    return done(launch_pdl(argmax_final_kernel, dim3(B), dim3(kArgmaxParts), 0, st(stream), out,
+                           reinterpret_cast<unsigned long long*>(draws), last_ids));
 }
 
 }  // extern "C"

@@ -56,6 +56,24 @@ class _Linear:
         if self.packed is not None:
             workspace.reserve(L.lib().nvfp4r_linear_packed_workspace_bytes(1, N, K))
 
+    @classmethod
+    def from_checkpoint(cls, lin, device, workspace: "Workspace") -> "_Linear":
+        """A shard read from a ModelOpt NVFP4 checkpoint (``nvfp4r.checkpoint.Nvfp4Linear``):
+        codes, flat block scales, ``1 / input_global_scale`` for the quantizer and
+        ``alpha = input_global_scale * weight_global_scale`` for the output."""
+        self = cls.__new__(cls)
+        self.N, self.K, self.ws = lin.N, lin.K, workspace
+        w = lin.weight.to(device).contiguous()
+        s = lin.weight_scale.to(device).contiguous()
+        self.packed = capi.pack_weight(w, s) if (self.N % 128 == 0 and self.K % 256 == 0) else None
+        self.use_gemv = self.packed is None or nvops.use_gemv(1, self.N, self.K, 2)
+        self.w, self.s = (w, s) if self.use_gemv else (None, None)
+        self.gs_inv = torch.tensor([lin.input_global_scale_inv], dtype=torch.float32, device=device)
+        self.alpha = lin.alpha
+        if self.packed is not None:
+            workspace.reserve(L.lib().nvfp4r_linear_packed_workspace_bytes(1, self.N, self.K))
+        return self
+
     def calibrate(self, x: torch.Tensor) -> None:
         """Pick alpha so that the output has unit RMS on a sample input (keeps the random
         model's activations finite; done once, outside any timed region)."""
@@ -131,6 +149,8 @@ class DecodeStep:
         self.position = torch.tensor([cfg.context - 1], dtype=torch.int32, device=self.device)
         self.seq_len = torch.tensor([cfg.context], dtype=torch.int32, device=self.device)
         self.token = torch.zeros(1, dtype=torch.int32, device=self.device)
+        self.feed_tokens = False          # random model: the embedding table is a 1024-row stand-in
+        self.reset = None                 # set by enable_reset(): ReSET processor + sampling instead of arg-max
         self.ws.allocate()
         self.res = [torch.zeros(1, H, **bf), torch.zeros(1, H, **bf)]     # ping-pong residual stream
         self.residual = self.res[0]
@@ -161,6 +181,40 @@ class DecodeStep:
             from .comm import PeerAllReduce
             self.peer = PeerAllReduce(self.device, H, group=process_group)
         self._calibrate()
+
+    def load_checkpoint(self, reader, embed_rows: int = 0) -> None:
+        """Replace the random weights by those of a ModelOpt NVFP4 Qwen3 checkpoint
+        (``nvfp4r.checkpoint.CheckpointReader``), sliced for this rank. Call before
+        :meth:`capture`. ``embed_rows`` limits how many embedding rows are kept on the device
+        (0 = all). The lm_head stays bf16, as ModelOpt leaves it (tied to the embedding when the
+        checkpoint has no ``lm_head.weight``)."""
+        from .nvfp4r import checkpoint as ck
+        c = self.cfg
+        bf = dict(dtype=torch.bfloat16, device=self.device)
+        for i, layer in enumerate(self.layers):
+            got = ck.qwen3_layer(reader, i, self.rank, self.world, head_dim=c.head_dim)
+            shapes = {"qkv": ((self.hq + 2 * self.hkv) * c.head_dim, c.hidden), "o": (c.hidden, self.hq * c.head_dim),
+                      "gate_up": (2 * c.intermediate // self.world, c.hidden),
+                      "down": (c.hidden, c.intermediate // self.world)}
+            for name, (n, k) in shapes.items():
+                lin = got[name]
+                if (lin.N, lin.K) != (n, k):
+                    raise ValueError(f"layer {i} {name}: checkpoint shard is {lin.N}x{lin.K}, model wants {n}x{k}")
+                layer[name] = _Linear.from_checkpoint(lin, self.device, self.ws)
+            for key in ("ln1", "ln2", "qn", "kn"):
+                if key in got:
+                    layer[key] = got[key].to(**bf).contiguous()
+        self.final_ln = reader.tensor("model.norm.weight").to(**bf).contiguous()
+        embed = reader.tensor("model.embed_tokens.weight")
+        head = reader.tensor("lm_head.weight") if reader.has("lm_head.weight") else embed
+        lo = self.rank * self.vocab_local
+        self.lm_head = head[lo:lo + self.vocab_local].to(**bf).contiguous()
+        self.embed = (embed[:embed_rows] if embed_rows else embed).to(**bf).contiguous()
+        self.feed_tokens = self.embed.shape[0] >= c.vocab
+        self.ws.allocate()
+        probe = self.layers[0]
+        self.fused = self.fused and all(probe[n].packed is not None for n in ("qkv", "gate_up", "down"))
+        self.graph = None
 
     # -- thin wrappers over the C ABI ------------------------------------------------
     def _stream(self) -> int:
@@ -215,7 +269,10 @@ class DecodeStep:
         c = self.cfg
         lib = L.lib()
         cur = 0
-        self.res[0].copy_(self.embed[:1])
+        if self.feed_tokens:
+            torch.index_select(self.embed, 0, self.token, out=self.res[0])   # the previous step's token
+        else:
+            self.res[0].copy_(self.embed[:1])
         x = None                                            # output of the previous row-parallel linear
         for layer in self.layers:
             if self.fused:
@@ -251,6 +308,14 @@ class DecodeStep:
             full = self.logits
         else:
             full = self.logits_local
+        if self.reset is not None:
+            # ReSET temperature on the full-vocabulary logits, then one draw from their softmax:
+            # processor and sampler stay on the device, nothing returns to the host per token
+            d = self.reset
+            capi.reset_step(full, d.states, d.params, last_ids=self.last_ids, nl_bitmap=d.nl_bitmap,
+                            dnl_bitmap=d.dnl_bitmap, decisions=d.decisions, workspace=d.workspace)
+            capi.sample(full, self.draws, seed=self.sample_seed, last_ids=self.last_ids, out=self.token)
+            return
         L.check(lib.nvfp4r_argmax(full.data_ptr(), full.stride(0), 1, c.vocab, self.token.data_ptr(),
                                   self._stream()), "argmax")
 
@@ -280,6 +345,28 @@ class DecodeStep:
     def replay(self) -> None:
         self.graph.replay()
 
+    def enable_reset(self, t_high: float = 1.0, t_low: float = 0.1, tau0: float = 0.5505, window: int = 32,
+                     nl_ids=(), dnl_ids=(), seed: int = 0) -> None:
+        """End every step with the ReSET processor (reset/reset/logits_processor.py:62-134) and a
+        draw from the softmax of the scaled logits instead of the arg-max. Every rank holds the
+        full logits after the gather and runs the same processor with the same seed, so all
+        ranks draw the same token. Call before :meth:`capture`; call again to start a new
+        request (state, counters and recent ids are cleared)."""
+        from .reset.logits_processor import _DeviceReset
+        self.reset = _DeviceReset(1, self.cfg.vocab, self.device, t_high, t_low, tau0, window, nl_ids, dnl_ids)
+        self.last_ids = torch.full((1, 2), -1, dtype=torch.int32, device=self.device)
+        self.draws = torch.zeros(1, dtype=torch.int64, device=self.device)
+        self.sample_seed = int(seed)
+        self.graph = None
+
+    def set_position(self, pos: int) -> None:
+        """The next step writes the cache row ``pos`` and attends to rows 0..pos (device-side
+        state, so a captured graph follows it)."""
+        if not 0 <= pos < self.cfg.context:
+            raise ValueError(f"position {pos} outside the context of {self.cfg.context}")
+        self.position.fill_(pos)
+        self.seq_len.fill_(pos + 1)
+
     # -- accounting -------------------------------------------------------------------
     def bytes_per_step(self) -> int:
         """Algorithmic HBM bytes one rank moves per token: NVFP4 linears, bf16 KV cache of the
@@ -290,4 +377,4 @@ class DecodeStep:
         return lin + kv + self.vocab_local * c.hidden * 2
 
     def kernels_per_step(self) -> int:
-        return self.cfg.layers * (5 if self.fused else 9) + 5
+        return self.cfg.layers * (5 if self.fused else 9) + 5 + (1 if self.reset is not None else 0)

@@ -4,7 +4,10 @@ step: CUDA-graph replay equals eager execution bit for bit."""
 
 from __future__ import annotations
 
+import ctypes
 import math
+
+import numpy as np
 
 import pytest
 import torch
@@ -197,3 +200,112 @@ def test_decode_step_graph_equals_eager():
     torch.cuda.synchronize()
     a, b = eager_logits.float(), u.logits_local.float()
     assert (a - b).norm() / b.norm() < 5e-2
+
+
+# ---------------------------------------------------------------------------------------
+# Device-side sampling (Gumbel-max) and the decode step with the ReSET processor in its graph
+# ---------------------------------------------------------------------------------------
+
+_M64 = (1 << 64) - 1
+
+
+def _mix64(z):
+    z = ((z ^ (z >> 30)) * 0xBF58476D1CE4E5B9) & _M64
+    z = ((z ^ (z >> 27)) * 0x94D049BB133111EB) & _M64
+    return z ^ (z >> 31)
+
+
+def _gumbel_token(logits_row, seed, row, draw):
+    """CPU restatement of the generator of nvfp4r_sample for one row (Python integers)."""
+    key = _mix64((seed ^ _mix64(((row << 40) + draw) & _M64)) & _M64)
+    best, arg = -np.inf, 0
+    for i, v in enumerate(logits_row):
+        r = _mix64((key + i * 0x9E3779B97F4A7C15) & _M64)
+        u = np.float32((np.float32(r >> 41) + np.float32(0.5)) * np.float32(1.0 / 8388608.0))
+        g = -np.log(-np.log(u, dtype=np.float32), dtype=np.float32)
+        s = np.float32(v) + g
+        if s > best:
+            best, arg = s, i
+    return arg
+
+
+def test_sample_follows_the_restated_generator_and_is_reproducible():
+    from reset_b200 import capi
+    B, V = 6, 700
+    g = torch.Generator().manual_seed(3)
+    logits = (torch.randn(B, V, generator=g) * 3).cuda()
+    draws = torch.tensor([0, 1, 2, 3, 40, 1 << 33], dtype=torch.int64, device="cuda")
+    start = draws.clone()
+    last = torch.full((B, 2), -1, dtype=torch.int32, device="cuda")
+    ids = capi.sample(logits, draws, seed=1234, last_ids=last)
+    torch.cuda.synchronize()
+    expect = [_gumbel_token(logits[b].cpu().numpy(), 1234, b, int(start[b])) for b in range(B)]
+    assert ids.tolist() == expect
+    assert torch.equal(draws, start + 1)
+    assert last[:, 0].tolist() == [-1] * B and last[:, 1].tolist() == expect
+    again = capi.sample(logits, start.clone(), seed=1234)
+    other = capi.sample(logits, start.clone(), seed=1235)
+    assert again.tolist() == expect and other.tolist() != expect
+    ids2 = capi.sample(logits, draws, seed=1234, last_ids=last)       # next draw of the same request
+    assert last[:, 0].tolist() == expect and last[:, 1].tolist() == ids2.tolist()
+    # what ReSET writes for a temperature of (almost) zero: 0 at one id, -inf elsewhere
+    row = torch.full((1, V), float("-inf"), device="cuda")
+    row[0, 321] = 0.0
+    assert capi.sample(row, torch.zeros(1, dtype=torch.int64, device="cuda"), seed=9).tolist() == [321]
+
+
+def test_sample_frequencies_match_softmax():
+    from reset_b200 import capi
+    B, V, calls = 256, 50, 60
+    g = torch.Generator().manual_seed(8)
+    row = torch.randn(V, generator=g) * 1.5
+    logits = row.repeat(B, 1).contiguous().cuda()
+    draws = torch.zeros(B, dtype=torch.int64, device="cuda")
+    counts = torch.zeros(V, dtype=torch.int64)
+    for _ in range(calls):
+        counts += torch.bincount(capi.sample(logits, draws, seed=77).cpu().long(), minlength=V)
+    n = B * calls
+    p = torch.softmax(row.double(), dim=0)
+    sigma = torch.sqrt(p * (1 - p) / n)
+    z = (counts.double() / n - p).abs() / sigma
+    assert float(z.max()) < 5.0, (float(z.max()), int(z.argmax()))
+    chi2 = float((((counts.double() - n * p) ** 2) / (n * p)).sum())
+    assert chi2 < 2.2 * (V - 1)                          # mean V-1, sd sqrt(2(V-1)) ~ 9.9
+
+
+def test_decode_step_with_reset_processor_and_sampling_in_the_graph():
+    from reset_b200 import _lib
+    from reset_b200.decode import DecodeConfig, DecodeStep
+    cfg = DecodeConfig("tiny", layers=2, hidden=1024, q_heads=8, kv_heads=2, head_dim=128,
+                       intermediate=2048, vocab=4096, context=256)
+    plain = DecodeStep(cfg, "cuda", seed=5)
+    plain.step()
+    torch.cuda.synchronize()
+    raw = plain.logits_local.clone()
+    m = DecodeStep(cfg, "cuda", seed=5)
+    m.enable_reset(t_high=1.0, t_low=0.1, tau0=0.5505, window=32, dnl_ids=[7], seed=42)
+    m.step()
+    torch.cuda.synchronize()
+    dec = _lib.ResetDecision.from_buffer_copy(m.reset.decisions.cpu().numpy().tobytes()[:ctypes.sizeof(_lib.ResetDecision)])
+    assert dec.temp in (0.1, 1.0) and dec.boundary == 0
+    # same model, same input: the processor divided the raw logits by the temperature it chose
+    want = raw / np.float32(dec.temp) if dec.temp != 1.0 else raw
+    assert torch.allclose(m.logits_local, want, rtol=3e-7, atol=0)
+    p = torch.softmax(raw.double()[0], dim=0)
+    ent = float(-(p * torch.log(p.clamp_min(1e-10))).sum())
+    assert abs(dec.entropy - ent) <= 1e-4 * max(1.0, ent)
+    first = int(m.token.item())
+    assert 0 <= first < cfg.vocab and m.draws.tolist() == [1] and m.last_ids.tolist() == [[-1, first]]
+    # graph replays keep drawing: counters advance, the recent ids follow the tokens
+    m.capture()
+    torch.cuda.synchronize()
+    base = int(m.draws.item())
+    toks = []
+    for _ in range(4):
+        m.replay()
+        torch.cuda.synchronize()
+        toks.append(int(m.token.item()))
+    assert int(m.draws.item()) == base + 4
+    assert m.last_ids.tolist() == [[toks[-2], toks[-1]]]
+    assert all(0 <= t < cfg.vocab for t in toks)
+    assert _lib.lib().nvfp4r_check_device_status() == 0
