@@ -109,6 +109,13 @@ NVFP4R_API int nvfp4r_gemv(const void* weight, const void* weight_scale,
  * same rcp_mode; they stay on chip. weight [N,K/2] and weight_scale [N,K/16]
  * (flat) contiguous; x bf16 with row stride `x_row_stride` elements; out [M,N]
  * contiguous.
+ * Like the weight, `global_scale_inv` is a constant of the layer (the reference passes the
+ * parameter `layer.input_global_scale_inv`): this entry point and the packed ones below
+ * launch with programmatic stream serialization and read it, as they read the weight, while
+ * the preceding kernel of the stream may still be running. It must therefore hold its
+ * value before that kernel is launched. The same holds for `norm_weight` of the RMSNorm
+ * prologue of nvfp4r_linear_packed_ex. Only `x` (and `delta` / `residual_in` of that
+ * prologue) may be produced by the preceding kernel.
  * ------------------------------------------------------------------------- */
 #define NVFP4R_LINEAR_MAX_M 16
 NVFP4R_API int nvfp4r_linear(const void* x, int64_t x_row_stride, int M, int K,

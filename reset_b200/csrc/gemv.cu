@@ -154,12 +154,14 @@ gemv_stream_kernel(const __grid_constant__ StreamParams p) {
                        my_bars + 8 * t, policy);
         }
     }
+    // The global scale is a constant of the layer (not written by the preceding kernel): its
+    // trip to L2 happens here, not after the wait.
+    const float gs = (p.a.xb != nullptr) ? __ldg(p.a.gs) : 1.0f;
     pdl_launch_dependents();
 
     // Activations come from the preceding kernel.
     pdl_wait_prior();
     if (p.a.xb != nullptr) {
-        const float gs = __ldg(p.a.gs);
         const int blocks_per_tok = K / kBlockElems;
         const __nv_bfloat16* xb = static_cast<const __nv_bfloat16*>(p.a.xb);
         const QuantScales qe = make_quant_scales<kRcpExact>(gs);

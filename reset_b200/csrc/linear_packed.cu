@@ -282,12 +282,30 @@ linear_packed_kernel(const __grid_constant__ PackedParams p) {
 #pragma unroll 1
         while (issued < total && issued < kStages) issue_next();
     }
+    // The layer's global scale is a constant of the layer, not a product of the previous kernel:
+    // it is fetched here, under the ring set-up, instead of costing a trip to L2 after the wait.
+    const float gs = __ldg(p.gs);
     if (warp == 1) tmem_alloc(smem_u32(&s_tmem), kTmemCols);
     if (warp == 0) TRACE(1);
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem = s_tmem;
+    const bool exact = (p.rcp_mode == kRcpExact);
+    const QuantScales q = exact ? make_quant_scales<kRcpExact>(gs) : make_quant_scales<kRcpApprox>(gs);
+    // RMSNorm prologue: the norm weight is a constant of the layer too; the 16 weights of this
+    // thread's first block are fetched before the wait (the other operands of that block come
+    // out of L1 after the mean-square pass, so the norm weight was the prologue's second trip
+    // to L2).
+    uint4 nw_first0 = make_uint4(0, 0, 0, 0), nw_first1 = nw_first0;
+    if (p.pro_kind == 1 && my_tiles > 0 && tid < p.M * nkb * (kBlockK / 16)) {
+        const int blocks = nkb * (kBlockK / 16);
+        const int blk = tid % blocks;
+        const uint4* src = reinterpret_cast<const uint4*>(
+            static_cast<const __nv_bfloat16*>(p.norm_w) + static_cast<int64_t>(kb0 * (kBlockK / 16) + blk) * 16);
+        nw_first0 = __ldg(src);
+        nw_first1 = __ldg(src + 1);
+    }
     pdl_launch_dependents();
     pdl_wait_prior();
     if (warp == 0) TRACE(2);
@@ -297,9 +315,6 @@ linear_packed_kernel(const __grid_constant__ PackedParams p) {
         const int blk0 = kb0 * (kBlockK / 16);
         const int blocks = nkb * (kBlockK / 16);
         const int n_items = p.M * blocks;
-        const bool exact = (p.rcp_mode == kRcpExact);
-        const float gs = __ldg(p.gs);
-        const QuantScales q = exact ? make_quant_scales<kRcpExact>(gs) : make_quant_scales<kRcpApprox>(gs);
         const __nv_bfloat16* xb = static_cast<const __nv_bfloat16*>(p.xb);
         const __nv_bfloat16* rin = static_cast<const __nv_bfloat16*>(p.residual_in);
         const __nv_bfloat16* dl = static_cast<const __nv_bfloat16*>(p.delta);
@@ -392,8 +407,11 @@ linear_packed_kernel(const __grid_constant__ PackedParams p) {
                 const int64_t off = static_cast<int64_t>(p.m0 + m) * p.K + koff;
                 const uint4 r0 = __ldg(reinterpret_cast<const uint4*>(rin + off));
                 const uint4 r1 = __ldg(reinterpret_cast<const uint4*>(rin + off) + 1);
-                const uint4 w0 = __ldg(reinterpret_cast<const uint4*>(nw + koff));
-                const uint4 w1 = __ldg(reinterpret_cast<const uint4*>(nw + koff) + 1);
+                uint4 w0 = nw_first0, w1 = nw_first1;
+                if (i != tid) {
+                    w0 = __ldg(reinterpret_cast<const uint4*>(nw + koff));
+                    w1 = __ldg(reinterpret_cast<const uint4*>(nw + koff) + 1);
+                }
                 float r[16], t[16];
                 unpack8(r0, r); unpack8(r1, r + 8);
                 if (dl != nullptr) {
