@@ -457,7 +457,7 @@ int nvfp4r_entropy(const float* logits, int64_t row_stride, int B, int V, float*
 int nvfp4r_set_gemv_tuning(int ctas_per_sm, int use_pdl, int force_generic) {
     nvfp4r::GemvTuning& t = nvfp4r::gemv_tuning();
     if (ctas_per_sm > 8) return fail(NVFP4R_ERR_INVALID_ARGUMENT, "tuning: ctas_per_sm > 8");
-    if (ctas_per_sm > 0) t.ctas_per_sm = ctas_per_sm;
+    if (ctas_per_sm >= 0) t.ctas_per_sm = ctas_per_sm;      // 0 = automatic
     if (use_pdl >= 0) t.use_pdl = use_pdl ? 1 : 0;
     if (force_generic >= 0) t.force_generic = force_generic ? 1 : 0;
     return NVFP4R_OK;

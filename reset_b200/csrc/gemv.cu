@@ -378,7 +378,7 @@ cudaError_t read_and_clear_device_status(int* flag) {
 }
 
 GemvTuning& gemv_tuning() {
-    static GemvTuning t = {1, 1, 0};
+    static GemvTuning t = {0, 1, 0};
     return t;
 }
 
@@ -418,7 +418,11 @@ cudaError_t launch_gemv_stream(const GemvArgs& a, cudaStream_t stream) {
     p.n_chunks = (a.K / 2 + kChunkBytes - 1) / kChunkBytes;
     p.x_token_bytes = a.K / 2 + a.K / 16;
     const GemvTuning& tune = gemv_tuning();
-    int ctas_per_sm = tune.ctas_per_sm > 0 ? tune.ctas_per_sm : 1;
+    // Automatic choice (measured, M = 1: 24576x4096 17.4 -> 12.8 us, 6144x4096 5.8 -> 5.1 us with
+    // three CTAs per SM; 4096x4096 3.6 -> 4.7 us and 5120x25600 34 -> 41 us, hence the bounds:
+    // every CTA quantizes the whole activation row, which is what long rows pay for).
+    const bool wide = a.M == 1 && p.n_groups >= 1536 && a.K <= 8192;
+    int ctas_per_sm = tune.ctas_per_sm > 0 ? tune.ctas_per_sm : (wide ? 3 : 1);
     if (a.M > 1 && ctas_per_sm > 2) ctas_per_sm = 2;     // register budget of the M > 1 variants
     const bool two_slots = ctas_per_sm >= 3;
     const size_t smem = ring_bytes(two_slots ? 2 : 3) + static_cast<size_t>(a.M) * p.x_token_bytes;

@@ -74,6 +74,9 @@ def use_gemv(M: int, N: int, K: int, gemv_max_m: int) -> bool:
     if M > gemv_max_m:
         return False
     limit = _config.GEMV_MAX_WEIGHT_BYTES.get(M)
+    if (M == 1 and N >= _config.GEMV_WIDE_MIN_N and K <= _config.GEMV_WIDE_MAX_K
+            and N * K * 9 // 16 <= _config.GEMV_WIDE_MAX_WEIGHT_BYTES):
+        return True
     if limit is None or N * K * 9 // 16 > limit:
         return False
     return M == 1 or K <= _config.GEMV_MAX_K_MULTI_TOKEN

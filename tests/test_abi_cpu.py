@@ -72,7 +72,10 @@ def test_enable_disable_configure_status(monkeypatch):
 def test_crossover_rule():
     from reset_b200.nvfp4r.ops import use_gemv
     assert use_gemv(1, 4096, 4096, 4) and use_gemv(2, 4096, 2048, 4) and use_gemv(4, 4096, 1024, 4)
-    assert not use_gemv(2, 4096, 4096, 4) and not use_gemv(1, 6144, 4096, 4)
+    assert not use_gemv(2, 4096, 4096, 4) and not use_gemv(1, 5120, 5120, 4)
+    # wide single-token launches (three GEMV CTAs per SM) stay on the GEMV up to 19 MB
+    assert use_gemv(1, 6144, 4096, 4) and use_gemv(1, 8192, 4096, 4)
+    assert not use_gemv(1, 12288, 4096, 4) and not use_gemv(1, 7168, 5120, 4) and not use_gemv(2, 6144, 4096, 4)
     assert not use_gemv(2, 1280, 5120, 4)                     # long rows go to the tensor cores above one token
     assert not use_gemv(1, 24576, 4096, 4) and not use_gemv(4, 4096, 4096, 4)
     assert not use_gemv(3, 4096, 1024, 2)                     # above gemv_max_m
