@@ -21,23 +21,40 @@ __all__ = ["gemv", "gemm", "quant", "linear", "linear_packed", "linear_auto", "p
 __version__ = "0.1.0"
 
 
+_REGISTERED = False      # the kernel class sits in vLLM's own NVFP4 kernel registry
+
+
 def enable(backend: str = "nvfp4r") -> None:
-    """Route vLLM's NVFP4 linear layers through these kernels; same effect as
-    ``VLLM_NVFP4_GEMM_BACKEND=nvfp4r``. Call before constructing the engine
-    (reference: __init__.py:30-36). With a vLLM that has the NVFP4 kernel
-    registry, the kernel class is registered under that name as well."""
-    os.environ["VLLM_NVFP4_GEMM_BACKEND"] = str(backend)
+    """Route vLLM's NVFP4 linear layers through these kernels. Call before constructing the
+    engine (reference: __init__.py:30-36, which sets ``VLLM_NVFP4_GEMM_BACKEND``).
+
+    With a vLLM that has the NVFP4 kernel registry (0.22), the kernel class is put first in
+    its automatic selection and the environment variable is NOT set: that vLLM checks the
+    variable against its own list of names and raises on ``nvfp4r``. Without the registry
+    (the reference's patched vLLM) the environment variable is the contract, as in the
+    reference."""
+    global _REGISTERED
+    _REGISTERED = False
     if backend == "nvfp4r":
         try:
             from . import vllm_integration as _vi
-            _vi.register_with_vllm()
+            _REGISTERED = bool(_vi.register_with_vllm())
         except ImportError:
-            pass  # vLLM absent: the environment variable alone is the contract
+            _REGISTERED = False  # vLLM absent: the environment variable alone is the contract
+    if _REGISTERED:
+        os.environ.pop("VLLM_NVFP4_GEMM_BACKEND", None)
+    else:
+        os.environ["VLLM_NVFP4_GEMM_BACKEND"] = str(backend)
 
 
 def disable() -> None:
     """Back to vLLM's stock NVFP4 path (reference: __init__.py:39-41)."""
+    global _REGISTERED
     os.environ.pop("VLLM_NVFP4_GEMM_BACKEND", None)
+    if _REGISTERED:
+        from . import vllm_integration as _vi
+        _vi.unregister_from_vllm()
+    _REGISTERED = False
 
 
 def configure(*, gemv_max_m: int | None = None, enable_gemm: bool | None = None,
@@ -63,7 +80,7 @@ def configure(*, gemv_max_m: int | None = None, enable_gemm: bool | None = None,
 def status() -> dict:
     """Active configuration (reference: __init__.py:72-82)."""
     return {
-        "active": os.environ.get("VLLM_NVFP4_GEMM_BACKEND") == "nvfp4r",
+        "active": _REGISTERED or os.environ.get("VLLM_NVFP4_GEMM_BACKEND") == "nvfp4r",
         "gemv_max_m": _config.GEMV_MAX_M,
         "enable_gemm": _config.ENABLE_GEMM_PATH,
         "gemm_pad_max_m": _config.GEMM_PAD_MAX_M,

@@ -114,22 +114,50 @@ def apply_nvfp4r_linear(layer: torch.nn.Module, x: torch.Tensor,
     return out.view(*output_shape)
 
 
+_KERNEL_CLASS = None
+
+
 def register_with_vllm() -> bool:
-    """Make ``VLLM_NVFP4_GEMM_BACKEND=nvfp4r`` resolve to :class:`Nvfp4rLinearKernel` in a
-    vLLM that has the NVFP4 linear-kernel registry. Returns False when this vLLM has no
-    such registry (the reference's patched-vLLM route then applies: the patched
-    ``apply_nvfp4_linear`` calls :func:`apply_nvfp4r_linear`)."""
+    """Put :class:`Nvfp4rLinearKernel` into the NVFP4 linear-kernel registry of a vLLM that
+    has one (``vllm/model_executor/kernels/linear``, vLLM 0.22): FIRST in the list its
+    automatic selection walks for CUDA (``_POSSIBLE_NVFP4_KERNELS``), and under the name
+    ``nvfp4r`` in ``_NVFP4_BACKEND_TO_KERNEL``. That vLLM validates
+    ``VLLM_NVFP4_GEMM_BACKEND`` against its own fixed list of names and rejects ``nvfp4r``,
+    so the environment variable of the reference (kernels/python/nvfp4r/__init__.py:30-36)
+    cannot select the kernel there; being first in the automatic selection does. Returns
+    False when this vLLM has no such registry (the reference's patched-vLLM route then
+    applies: the patched ``apply_nvfp4_linear`` calls :func:`apply_nvfp4r_linear`)."""
+    global _KERNEL_CLASS
     try:
         import vllm.model_executor.kernels.linear as vk
         from vllm.model_executor.kernels.linear.nvfp4.base import NvFp4LinearKernel
     except ImportError:
         return False
     table = getattr(vk, "_NVFP4_BACKEND_TO_KERNEL", None)
-    if table is None:
+    possible = getattr(vk, "_POSSIBLE_NVFP4_KERNELS", None)
+    if table is None or possible is None:
         return False
-    if "nvfp4r" not in table:
-        table["nvfp4r"] = _make_kernel_class(NvFp4LinearKernel)
+    if _KERNEL_CLASS is None:
+        _KERNEL_CLASS = _make_kernel_class(NvFp4LinearKernel)
+    table["nvfp4r"] = _KERNEL_CLASS
+    for platform, kernels in possible.items():
+        if getattr(platform, "name", "") == "CUDA" and _KERNEL_CLASS not in kernels:
+            kernels.insert(0, _KERNEL_CLASS)
     return True
+
+
+def unregister_from_vllm() -> None:
+    """Undo :func:`register_with_vllm` (``nvfp4r.disable()``)."""
+    try:
+        import vllm.model_executor.kernels.linear as vk
+    except ImportError:
+        return
+    table = getattr(vk, "_NVFP4_BACKEND_TO_KERNEL", None)
+    if table is not None:
+        table.pop("nvfp4r", None)
+    for kernels in (getattr(vk, "_POSSIBLE_NVFP4_KERNELS", None) or {}).values():
+        while _KERNEL_CLASS is not None and _KERNEL_CLASS in kernels:
+            kernels.remove(_KERNEL_CLASS)
 
 
 def _make_kernel_class(base):

@@ -7,6 +7,8 @@ from __future__ import annotations
 import ctypes
 import os
 import re
+
+import pytest
 from pathlib import Path
 
 REPO = Path(__file__).resolve().parent.parent
@@ -124,3 +126,37 @@ def test_scale_by_temperature_matches_oracle_on_cpu():
     x = orp.synthetic_logits(2, 100, 3)
     for t in (1.0, 0.1, 0.0, 1e-7):
         assert torch.equal(scale_by_temperature(x[0], t), orp.apply_temperature(x[0], t))
+
+
+def test_enable_registers_first_in_the_installed_vllm_registry(monkeypatch):
+    """With a vLLM that has the NVFP4 linear-kernel registry, ``enable()`` puts the kernel class
+    first in the automatic CUDA selection and leaves ``VLLM_NVFP4_GEMM_BACKEND`` unset (that
+    vLLM rejects names outside its own list); ``disable()`` takes it out again."""
+    vk = pytest.importorskip("vllm.model_executor.kernels.linear")
+    if not hasattr(vk, "_POSSIBLE_NVFP4_KERNELS"):
+        pytest.skip("this vLLM has no NVFP4 kernel registry")
+    from vllm.model_executor.kernels.linear.nvfp4.base import NvFp4LinearKernel
+    monkeypatch.delenv("VLLM_NVFP4_GEMM_BACKEND", raising=False)
+    from reset_b200 import nvfp4r
+    cuda_lists = [v for k, v in vk._POSSIBLE_NVFP4_KERNELS.items() if getattr(k, "name", "") == "CUDA"]
+    assert cuda_lists
+    before = [list(v) for v in cuda_lists]
+    try:
+        nvfp4r.enable()
+        assert nvfp4r.status()["active"] is True
+        assert "VLLM_NVFP4_GEMM_BACKEND" not in os.environ
+        cls = vk._NVFP4_BACKEND_TO_KERNEL["nvfp4r"]
+        assert issubclass(cls, NvFp4LinearKernel) and cls.__name__ == "Nvfp4rLinearKernel"
+        assert all(v[0] is cls and v.count(cls) == 1 for v in cuda_lists)
+        nvfp4r.enable()                                     # idempotent
+        assert all(v.count(cls) == 1 for v in cuda_lists)
+        ok, why = cls.is_supported()
+        import torch
+        if not torch.cuda.is_available():
+            assert ok is False and "CUDA" in why           # no silent CPU path
+        assert cls.can_implement(None) == (True, None)
+    finally:
+        nvfp4r.disable()
+    assert nvfp4r.status()["active"] is False
+    assert "nvfp4r" not in vk._NVFP4_BACKEND_TO_KERNEL
+    assert [list(v) for v in cuda_lists] == before

@@ -148,3 +148,58 @@ def test_vllm_adapter_rejects_padded_weights():
     layer.weights_padding_cols = 64
     with pytest.raises(RuntimeError):
         vi.apply_nvfp4r_linear(layer, torch.zeros(1, 512, dtype=torch.bfloat16, device="cuda"))
+
+
+def _modelopt_style_layer(N, K, seed, alpha=0.4, gs_inv=48.0):
+    """The attributes vLLM's ModelOpt NVFP4 linear method leaves on a layer before it calls
+    ``kernel.process_weights_after_loading`` (flat e4m3 block scales)."""
+    w, ws = onv.random_nvfp4((N,), K, seed=seed)
+    layer = torch.nn.Module()
+    layer.weight = torch.nn.Parameter(cuda(w), requires_grad=False)
+    layer.weight_scale = torch.nn.Parameter(cuda(ws).view(torch.float8_e4m3fn), requires_grad=False)
+    layer.input_global_scale_inv = torch.nn.Parameter(torch.tensor(gs_inv, dtype=torch.float32, device="cuda"),
+                                                      requires_grad=False)
+    layer.alpha = torch.nn.Parameter(torch.tensor(alpha, dtype=torch.float32, device="cuda"), requires_grad=False)
+    layer.input_size_per_partition, layer.output_size_per_partition = K, N
+    return layer, w, ws
+
+
+@pytest.mark.parametrize("N,K", [(4096, 1024), (6144, 4096)])
+def test_kernel_class_selected_by_the_installed_vllm_and_agrees_with_its_cutlass_kernel(N, K, monkeypatch):
+    """`nvfp4r.enable()` makes the installed vLLM's own selection routine return this
+    library's kernel class; on the same layer it agrees with vLLM's CUTLASS kernel class
+    (the comparison the reference makes in kernels/tests/test_vllm_integration.py:61-95,
+    there against a patched vLLM) and with the oracle."""
+    vk = pytest.importorskip("vllm.model_executor.kernels.linear")
+    if not hasattr(vk, "_POSSIBLE_NVFP4_KERNELS"):
+        pytest.skip("this vLLM has no NVFP4 kernel registry")
+    from vllm.model_executor.kernels.linear.nvfp4.base import NvFp4LinearLayerConfig
+    from vllm.model_executor.kernels.linear.nvfp4.cutlass import CutlassNvFp4LinearKernel
+    from reset_b200 import _lib, capi, nvfp4r
+    monkeypatch.delenv("VLLM_NVFP4_GEMM_BACKEND", raising=False)
+    nvfp4r.enable()
+    try:
+        kernel = vk.init_nvfp4_linear_kernel()
+        assert type(kernel).__name__ == "Nvfp4rLinearKernel"
+    finally:
+        nvfp4r.disable()
+    ours, w, ws = _modelopt_style_layer(N, K, seed=21)
+    kernel.process_weights_after_loading(ours)
+    assert ours._nvfp4r_caches_primed and ours.weights_padding_cols == 0
+    stock = None
+    if CutlassNvFp4LinearKernel.is_supported()[0]:
+        stock_layer, _, _ = _modelopt_style_layer(N, K, seed=21)
+        stock = CutlassNvFp4LinearKernel(NvFp4LinearLayerConfig())
+        stock.process_weights_after_loading(stock_layer)
+    for M in (1, 2, 8, 32):
+        x = make_activation(M, K, seed=100 + M).cuda()
+        y = kernel.apply_weights(ours, x.view(1, M, K))
+        assert tuple(y.shape) == (1, M, N) and y.dtype == torch.bfloat16
+        codes, scales = capi.quant(x, ours.input_global_scale_inv.reshape(1), rcp_mode=_lib.RCP_APPROX)
+        exact = onv.linear_f64(w, ws, codes.cpu().numpy(), scales.cpu().numpy(), alpha=0.4)
+        assert rel_l2(y[0].float().cpu().numpy(), exact) <= 6e-3            # bf16 output rounding
+        if stock is not None:
+            z = stock.apply_weights(stock_layer, x.view(1, M, K))
+            # same codes and scales on both sides (the quantizers are bit-identical in this mode),
+            # fp32 accumulation in different orders, one bf16 rounding each
+            assert rel_l2(y.float().cpu().numpy(), z.float().cpu().numpy()) <= 8e-3
