@@ -226,6 +226,26 @@ class ReSETBatchProcessor:
         return logits
 
 
+_BATCH_CLASS = None
+
+
+def make_batch_processor_class():
+    """:class:`ReSETBatchProcessor` as vLLM wants it: ``LLM(logits_processors=[cls])`` only
+    accepts subclasses of ``vllm.v1.sample.logits_processor.LogitsProcessor``. The subclass is
+    built on first use (importing vLLM takes seconds and the kernels do not need it) and has the
+    same name and constructor; without vLLM the plain class is returned."""
+    global _BATCH_CLASS
+    if _BATCH_CLASS is None:
+        try:
+            from vllm.v1.sample.logits_processor import LogitsProcessor
+        except ImportError:
+            _BATCH_CLASS = ReSETBatchProcessor
+        else:
+            _BATCH_CLASS = type("ReSETBatchProcessor", (ReSETBatchProcessor, LogitsProcessor),
+                                {"__doc__": ReSETBatchProcessor.__doc__, "__module__": __name__})
+    return _BATCH_CLASS
+
+
 def make_adapter_class():
     """The reference's ``ReSETAdapter`` (:137-155): a vLLM ``AdapterLogitsProcessor``
     producing one :class:`ReSETRequest` per opted-in request."""

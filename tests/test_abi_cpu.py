@@ -160,3 +160,16 @@ def test_enable_registers_first_in_the_installed_vllm_registry(monkeypatch):
     assert nvfp4r.status()["active"] is False
     assert "nvfp4r" not in vk._NVFP4_BACKEND_TO_KERNEL
     assert [list(v) for v in cuda_lists] == before
+
+
+def test_batch_processor_is_a_vllm_logits_processor():
+    """``LLM(logits_processors=[ReSETBatchProcessor])`` (and the ``module:Class`` string form)
+    go through vLLM's loader, which only accepts subclasses of its ``LogitsProcessor``."""
+    lp = pytest.importorskip("vllm.v1.sample.logits_processor")
+    from reset_b200 import reset
+    cls = reset.ReSETBatchProcessor
+    assert cls is reset.ReSETBatchProcessor and cls.__name__ == "ReSETBatchProcessor"
+    assert issubclass(cls, lp.LogitsProcessor) and not getattr(cls, "__abstractmethods__", None)
+    assert lp._load_logitsprocs_by_fqcns([cls]) == [cls]
+    assert lp._load_logitsprocs_by_fqcns(["reset_b200.reset:ReSETBatchProcessor"]) == [cls]
+    assert issubclass(reset.ReSETAdapter, lp.LogitsProcessor)

@@ -18,7 +18,16 @@ from helpers import cuda, make_activation, rel_l2
 
 pytestmark = pytest.mark.gpu
 TIE_BAND = 1e-4
-BatchUpdate = namedtuple("BatchUpdate", "removed added moved")
+try:      # vLLM's own batch-update record and move enum when vLLM is installed, stand-ins otherwise
+    from vllm.v1.sample.logits_processor import BatchUpdate as _VllmBatchUpdate, MoveDirectionality
+
+    def BatchUpdate(removed, added, moved):
+        return _VllmBatchUpdate(batch_size=len(added), removed=removed, added=added, moved=moved)
+
+    UNIDIRECTIONAL = MoveDirectionality.UNIDIRECTIONAL
+except ImportError:
+    BatchUpdate = namedtuple("BatchUpdate", "removed added moved")
+    UNIDIRECTIONAL = SimpleNamespace(name="UNIDIRECTIONAL")
 
 
 def _near_tie(d, tau0):
@@ -90,7 +99,7 @@ def test_batch_processor_matches_per_request_oracle():
     # request 0 finishes; request 2 moves from row 2 to row 0 (vLLM condenses the batch)
     del rows[0], pols[0]
     rows[2] = 0
-    proc.update_state(BatchUpdate(removed=[0], added=[], moved=[(2, 0, SimpleNamespace(name="UNIDIRECTIONAL"))]))
+    proc.update_state(BatchUpdate(removed=[0], added=[], moved=[(2, 0, UNIDIRECTIONAL)]))
     for t in range(12, 24):
         step(t, 2)
         proc.update_state(None)
