@@ -309,3 +309,35 @@ def test_decode_step_with_reset_processor_and_sampling_in_the_graph():
     assert m.last_ids.tolist() == [[toks[-2], toks[-1]]]
     assert all(0 <= t < cfg.vocab for t in toks)
     assert _lib.lib().nvfp4r_check_device_status() == 0
+
+
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_decode_step_runs_with_every_tensor_parallel_shard_shape(world, monkeypatch):
+    """Rank 0's shard of a Qwen3-32B-shaped step at TP = 2 / 4 / 8 on one GPU (the collectives
+    are replaced by their single-rank effect): every per-rank linear shape goes through the
+    kernel the crossover picks for it (at TP = 8 the down projection has K = 3200, which only
+    the plain-load GEMV takes, so the step falls back to separate norm / activation launches),
+    eager and graph replay agree bit for bit, and no kernel reports a failed wait."""
+    import dataclasses
+    from reset_b200 import _lib
+    from reset_b200.decode import QWEN3_32B, DecodeStep
+    import torch.distributed as dist
+
+    monkeypatch.setattr(dist, "all_reduce", lambda t, group=None: None)
+    monkeypatch.setattr(dist, "all_gather_into_tensor",
+                        lambda out, inp, group=None: out[:inp.numel()].copy_(inp))
+    cfg = dataclasses.replace(QWEN3_32B, layers=2, context=256)
+    m = DecodeStep(cfg, "cuda", rank=0, world=world, seed=11, peer_allreduce=False)
+    inter = cfg.intermediate // world
+    assert m.fused == (inter % 256 == 0)
+    assert m.layers[0]["down"].K == inter and m.layers[0]["o"].K == cfg.q_heads // world * cfg.head_dim
+    m.step()
+    torch.cuda.synchronize()
+    eager = m.logits_local.clone()
+    assert torch.isfinite(eager).all() and float(eager.abs().max()) > 0
+    m.capture()
+    m.logits_local.zero_()
+    m.replay()
+    torch.cuda.synchronize()
+    assert torch.equal(m.logits_local, eager)
+    assert _lib.lib().nvfp4r_check_device_status() == 0
