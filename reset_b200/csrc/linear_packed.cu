@@ -315,6 +315,10 @@ linear_packed_kernel(const __grid_constant__ PackedParams p) {
         const int blk0 = kb0 * (kBlockK / 16);
         const int blocks = nkb * (kBlockK / 16);
         const int n_items = p.M * blocks;
+        // i / blocks as a multiply and a shift: exact for blocks = 16 .. 128 in steps of 16 and
+        // i < 4608 (M <= 32 tokens of at most 128 blocks); a real division costs ~20 instructions
+        // and the loop below needs two per block
+        const uint32_t inv_blocks = ((1u << 20) + static_cast<uint32_t>(blocks) - 1u) / static_cast<uint32_t>(blocks);
         const __nv_bfloat16* xb = static_cast<const __nv_bfloat16*>(p.xb);
         const __nv_bfloat16* rin = static_cast<const __nv_bfloat16*>(p.residual_in);
         const __nv_bfloat16* dl = static_cast<const __nv_bfloat16*>(p.delta);
@@ -365,7 +369,7 @@ linear_packed_kernel(const __grid_constant__ PackedParams p) {
         // block while the current one is quantized.
         uint4 nlo = make_uint4(0, 0, 0, 0), nhi = nlo;
         auto src0 = [&](int i) {
-            const int m = i / blocks, blk = i - m * blocks;
+            const int m = static_cast<int>((static_cast<uint32_t>(i) * inv_blocks) >> 20), blk = i - m * blocks;
             return reinterpret_cast<const uint4*>(xb + (p.m0 + m) * p.xb_stride + static_cast<int64_t>(blk0 + blk) * 16);
         };
         if (kind == 0 && tid < n_items) {
@@ -375,7 +379,7 @@ linear_packed_kernel(const __grid_constant__ PackedParams p) {
         }
 #pragma unroll 1
         for (int i = tid; i < n_items; i += kThreadsP) {
-            const int m = i / blocks, blk = i - m * blocks;
+            const int m = static_cast<int>((static_cast<uint32_t>(i) * inv_blocks) >> 20), blk = i - m * blocks;
             uint4 lo, hi;
             if (kind == 0) {
                 lo = nlo;

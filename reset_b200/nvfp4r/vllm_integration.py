@@ -19,8 +19,8 @@ Differences from the reference, all inside the dispatch:
   kernels cannot take raises.
 
 For a vLLM with the NVFP4 kernel registry (``model_executor/kernels/linear/nvfp4``),
-:class:`Nvfp4rLinearKernel` plugs in under ``VLLM_NVFP4_GEMM_BACKEND=nvfp4r`` through
-:func:`register_with_vllm`; no vLLM file is patched.
+:func:`register_with_vllm` puts :class:`Nvfp4rLinearKernel` first in that vLLM's own kernel
+selection; no vLLM file is patched.
 """
 
 from __future__ import annotations
