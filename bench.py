@@ -120,7 +120,7 @@ def build_weights(rank: int, tp: int, device, nvfp4r):
             s = torch.randint(1, 0x38, (n, k // 16), dtype=torch.uint8, device=device, generator=g)
             # weight preparation (once per layer, not timed): the packed block format of the
             # tensor-core path next to the flat format of the CUDA-core GEMV
-            packed = nvfp4r.pack_weight(w, s) if (n % 128 == 0 and k % 256 == 0) else None
+            packed = nvfp4r.pack_weight(w, s) if (n % 128 == 0 and k % 128 == 0) else None
             copies.append((w, s, packed))
         shards.append((name, n, k, style, copies))
     return shards
@@ -427,6 +427,25 @@ def run_decode(args, rank, world, device):
            "frac_of_hbm_roofline": round((bytes_rank / (ms_tok * 1e-3) / 1e9) / peak, 4),
            "launch": "one CUDA graph per token", "kernels_per_token": model.kernels_per_step(),
            "allreduce": "none" if world == 1 else ("peer one-shot" if model.peer is not None else "NCCL")}
+    if world == 1:
+        # the same token with the ReSET processor and a draw from the scaled logits inside the
+        # graph instead of the arg-max (the reference's deployment: processor + vLLM sampler;
+        # its README puts the processor at ~1.5 % of a decode step)
+        model.enable_reset(t_high=1.0, t_low=0.1, tau0=0.5505, window=32, dnl_ids=[198], seed=1)
+        model.capture()
+        for _ in range(3):
+            model.replay()
+        torch.cuda.synchronize()
+        e0.record()
+        for _ in range(steps):
+            model.replay()
+        e1.record()
+        torch.cuda.synchronize()
+        ms_reset = e0.elapsed_time(e1) / steps
+        out["with_reset_processor"] = {"tok_s": round(1e3 / ms_reset, 1), "ms_per_token": round(ms_reset, 4),
+                                       "added_us_per_token": round((ms_reset - ms_tok) * 1e3, 1),
+                                       "added_pct": round(100.0 * (ms_reset - ms_tok) / ms_tok, 2),
+                                       "kernels_per_token": model.kernels_per_step()}
     del model
     torch.cuda.empty_cache()
     return out

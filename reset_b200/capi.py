@@ -145,13 +145,14 @@ def gemm(A, B, SFA, SFB, C: torch.Tensor, alpha: float, workspace: torch.Tensor,
 
 
 def pack_weight(weight: torch.Tensor, weight_scale_flat: torch.Tensor) -> torch.Tensor:
-    """[N,K/2] codes + flat [N,K/16] scales -> packed block format (uint8, N*K*9/16 bytes)."""
+    """[N,K/2] codes + flat [N,K/16] scales -> packed block format (uint8, N*K*9/16 bytes for K % 256 == 0;
+    K % 256 == 128 is padded with half a block of zeros)."""
     _need_cuda(weight, weight_scale_flat)
     w, ws = _u8(weight).contiguous(), _u8(weight_scale_flat).contiguous()
     N, K = w.shape[0], w.shape[1] * 2
     n = L.lib().nvfp4r_packed_weight_bytes(N, K)
     if n == 0:
-        raise ValueError("pack_weight: needs N % 128 == 0 and K % 256 == 0")
+        raise ValueError("pack_weight: needs N % 128 == 0 and K % 128 == 0")
     packed = torch.empty(n, dtype=torch.uint8, device=w.device)
     with torch.cuda.device(w.device):
         st = L.lib().nvfp4r_pack_weight(w.data_ptr(), ws.data_ptr(), packed.data_ptr(), N, K, _stream())

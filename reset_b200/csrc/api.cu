@@ -219,7 +219,7 @@ NVFP4R_API int nvfp4r_debug_read_trace(unsigned long long* out16) {
     return nvfp4r::read_packed_trace(out16) == cudaSuccess ? 0 : -4;
 }
 size_t nvfp4r_packed_weight_bytes(int N, int K) {
-    if (N <= 0 || K <= 0 || N % 128 || K % 256) return 0;
+    if (N <= 0 || K <= 0 || N % 128 || K % 128) return 0;
     return nvfp4r::packed_weight_bytes(N, K);
 }
 
@@ -231,8 +231,8 @@ int nvfp4r_pack_weight(const void* weight, const void* weight_scale_flat, void* 
                        void* stream) {
     if (!weight || !weight_scale_flat || !packed) return fail(NVFP4R_ERR_INVALID_ARGUMENT, "pack_weight: null pointer");
     if (N <= 0 || K <= 0) return fail(NVFP4R_ERR_INVALID_ARGUMENT, "pack_weight: bad sizes");
-    if (N % 128 != 0 || K % 256 != 0)
-        return fail(NVFP4R_ERR_UNSUPPORTED_SHAPE, "pack_weight: N % 128 == 0 and K % 256 == 0 required");
+    if (N % 128 != 0 || K % 128 != 0)
+        return fail(NVFP4R_ERR_UNSUPPORTED_SHAPE, "pack_weight: N % 128 == 0 and K % 128 == 0 required");
     if (!aligned(weight, 16) || !aligned(weight_scale_flat, 4) || !aligned(packed, 16))
         return fail(NVFP4R_ERR_ALIGNMENT, "pack_weight: weight 16-byte, scales 4-byte, packed 16-byte aligned");
     cudaError_t e = nvfp4r::launch_pack_weight(weight, weight_scale_flat, packed, N, K, as_stream(stream));
@@ -248,8 +248,8 @@ int nvfp4r_linear_packed(const void* x, int64_t x_row_stride, int M, int K, cons
     if (M < 0 || N < 0 || K <= 0) return fail(NVFP4R_ERR_INVALID_ARGUMENT, "linear_packed: bad sizes");
     if (out_dtype < NVFP4R_BF16 || out_dtype > NVFP4R_F32)
         return fail(NVFP4R_ERR_INVALID_ARGUMENT, "linear_packed: bad out_dtype");
-    if (N % 128 != 0 || K % 256 != 0)
-        return fail(NVFP4R_ERR_UNSUPPORTED_SHAPE, "linear_packed: N % 128 == 0 and K % 256 == 0 required");
+    if (N % 128 != 0 || K % 128 != 0)
+        return fail(NVFP4R_ERR_UNSUPPORTED_SHAPE, "linear_packed: N % 128 == 0 and K % 128 == 0 required");
     if (M == 0 || N == 0) return NVFP4R_OK;
     if (!workspace || workspace_bytes < nvfp4r_linear_packed_workspace_bytes(M, N, K) || !aligned(workspace, 16))
         return fail(NVFP4R_ERR_INVALID_ARGUMENT, "linear_packed: workspace missing, too small or misaligned");
@@ -292,8 +292,10 @@ int nvfp4r_linear_packed_ex(const nvfp4r_prologue* pro, const void* x, int64_t x
     if (M < 0 || N < 0 || K <= 0) return fail(NVFP4R_ERR_INVALID_ARGUMENT, "linear_packed_ex: bad sizes");
     if (out_dtype < NVFP4R_BF16 || out_dtype > NVFP4R_F32)
         return fail(NVFP4R_ERR_INVALID_ARGUMENT, "linear_packed_ex: bad out_dtype");
-    if (N % 128 != 0 || K % 256 != 0)
-        return fail(NVFP4R_ERR_UNSUPPORTED_SHAPE, "linear_packed_ex: N % 128 == 0 and K % 256 == 0 required");
+    if (N % 128 != 0 || K % 128 != 0)
+        return fail(NVFP4R_ERR_UNSUPPORTED_SHAPE, "linear_packed_ex: N % 128 == 0 and K % 128 == 0 required");
+    if (pro->kind == NVFP4R_PROLOGUE_ADD_RMSNORM && K % 256 != 0)
+        return fail(NVFP4R_ERR_UNSUPPORTED_SHAPE, "linear_packed_ex: the RMSNorm prologue needs K % 256 == 0");
     if (M == 0 || N == 0) return NVFP4R_OK;
     if (!workspace || workspace_bytes < nvfp4r_linear_packed_workspace_bytes(M, N, K) || !aligned(workspace, 16))
         return fail(NVFP4R_ERR_INVALID_ARGUMENT, "linear_packed_ex: workspace missing, too small or misaligned");

@@ -9,6 +9,9 @@
 //                   XOR row%8), 8-row groups 1024 B apart
 //   [16384, 18432)  the block's 128 x 16 scales as four 512-byte chunks (one per 64
 //                   K-elements) in the 32x4x4 order that tcgen05.cp 32x128b.warpx4 copies
+// K may end in the middle of a block (K % 128 == 0, e.g. the 3200-wide row-parallel shard of
+// Qwen3-32B at TP = 8): the last block is then half zeros (codes and scales), and the linear
+// quantizes zeros for the activation blocks past K, so the padding adds nothing to the sums.
 // Consecutive K blocks of a tile are contiguous, so a pipeline stage of 1 or 2 blocks is
 // ONE 1-D bulk copy of 18 or 36 KB: perfectly sequential DRAM reads, one TMA instruction
 // and one mbarrier transaction per 36 KB, no tensor map.
@@ -109,13 +112,17 @@ pack_weight_kernel(const uint8_t* __restrict__ w, const uint8_t* __restrict__ sf
                    uint8_t* __restrict__ packed, int N, int K) {
     const int kb = blockIdx.x, tile = blockIdx.y;
     const int row = threadIdx.x >> 3, unit = threadIdx.x & 7;
-    uint8_t* dst = packed + (static_cast<int64_t>(tile) * (K / kBlockK) + kb) * kBlockBytes;
+    const int kblocks = (K + kBlockK - 1) / kBlockK;           // the last block may be half padding
+    uint8_t* dst = packed + (static_cast<int64_t>(tile) * kblocks + kb) * kBlockBytes;
     const int64_t n = static_cast<int64_t>(tile) * kTileRows + row;
-    const uint4 v = *reinterpret_cast<const uint4*>(w + n * (K / 2) + kb * 128 + unit * 16);
+    uint4 v = make_uint4(0, 0, 0, 0);
+    if (kb * 128 + unit * 16 < K / 2) v = *reinterpret_cast<const uint4*>(w + n * (K / 2) + kb * 128 + unit * 16);
     *reinterpret_cast<uint4*>(dst + swz128(row, unit * 16)) = v;
     // scales: 16 per row in this block = 4 chunks x 4; threads with unit < 4 move 4 bytes
     if (unit < 4) {
-        const uint32_t s4 = *reinterpret_cast<const uint32_t*>(sf_flat + n * (K / 16) + kb * 16 + unit * 4);
+        uint32_t s4 = 0;
+        if (kb * 16 + unit * 4 < K / 16)
+            s4 = *reinterpret_cast<const uint32_t*>(sf_flat + n * (K / 16) + kb * 16 + unit * 4);
         *reinterpret_cast<uint32_t*>(dst + kCodesBytes + unit * 512 + (row % 32) * 16 + (row / 32) * 4) = s4;
     }
 }
@@ -301,10 +308,12 @@ linear_packed_kernel(const __grid_constant__ PackedParams p) {
     if (p.pro_kind == 1 && my_tiles > 0 && tid < p.M * nkb * (kBlockK / 16)) {
         const int blocks = nkb * (kBlockK / 16);
         const int blk = tid % blocks;
-        const uint4* src = reinterpret_cast<const uint4*>(
-            static_cast<const __nv_bfloat16*>(p.norm_w) + static_cast<int64_t>(kb0 * (kBlockK / 16) + blk) * 16);
-        nw_first0 = __ldg(src);
-        nw_first1 = __ldg(src + 1);
+        if (kb0 * (kBlockK / 16) + blk < p.K / 16) {
+            const uint4* src = reinterpret_cast<const uint4*>(
+                static_cast<const __nv_bfloat16*>(p.norm_w) + static_cast<int64_t>(kb0 * (kBlockK / 16) + blk) * 16);
+            nw_first0 = __ldg(src);
+            nw_first1 = __ldg(src + 1);
+        }
     }
     pdl_launch_dependents();
     pdl_wait_prior();
@@ -315,6 +324,9 @@ linear_packed_kernel(const __grid_constant__ PackedParams p) {
         const int blk0 = kb0 * (kBlockK / 16);
         const int blocks = nkb * (kBlockK / 16);
         const int n_items = p.M * blocks;
+        // blocks of this part that lie inside K; the ones past it (K % 256 == 128, last part only)
+        // are quantized from zeros, which gives zero codes and a zero scale
+        const int real = min(blocks, p.K / 16 - blk0);
         // i / blocks as a multiply and a shift: exact for blocks = 16 .. 128 in steps of 16 and
         // i < 4608 (M <= 32 tokens of at most 128 blocks); a real division costs ~20 instructions
         // and the loop below needs two per block
@@ -372,7 +384,11 @@ linear_packed_kernel(const __grid_constant__ PackedParams p) {
             const int m = static_cast<int>((static_cast<uint32_t>(i) * inv_blocks) >> 20), blk = i - m * blocks;
             return reinterpret_cast<const uint4*>(xb + (p.m0 + m) * p.xb_stride + static_cast<int64_t>(blk0 + blk) * 16);
         };
-        if (kind == 0 && tid < n_items) {
+        auto inside = [&](int i) {
+            const int m = static_cast<int>((static_cast<uint32_t>(i) * inv_blocks) >> 20);
+            return i - m * blocks < real;
+        };
+        if (kind == 0 && tid < n_items && inside(tid)) {
             const uint4* s0 = src0(tid);
             nlo = __ldg(s0);
             nhi = __ldg(s0 + 1);
@@ -384,7 +400,9 @@ linear_packed_kernel(const __grid_constant__ PackedParams p) {
             if (kind == 0) {
                 lo = nlo;
                 hi = nhi;
-                if (i + kThreadsP < n_items) {
+                nlo = make_uint4(0, 0, 0, 0);
+                nhi = nlo;
+                if (i + kThreadsP < n_items && inside(i + kThreadsP)) {
                     const uint4* s0 = src0(i + kThreadsP);
                     nlo = __ldg(s0);
                     nhi = __ldg(s0 + 1);
@@ -392,10 +410,13 @@ linear_packed_kernel(const __grid_constant__ PackedParams p) {
             } else if (kind == 2) {
                 // activation = bf16(silu(gate) * up), gate_up row = [gate (K) | up (K)]
                 const __nv_bfloat16* row = xb + (p.m0 + m) * p.xb_stride + static_cast<int64_t>(blk0 + blk) * 16;
-                const uint4 g0 = __ldg(reinterpret_cast<const uint4*>(row));
-                const uint4 g1 = __ldg(reinterpret_cast<const uint4*>(row) + 1);
-                const uint4 u0 = __ldg(reinterpret_cast<const uint4*>(row + p.K));
-                const uint4 u1 = __ldg(reinterpret_cast<const uint4*>(row + p.K) + 1);
+                uint4 g0 = make_uint4(0, 0, 0, 0), g1 = g0, u0 = g0, u1 = g0;
+                if (blk < real) {
+                    g0 = __ldg(reinterpret_cast<const uint4*>(row));
+                    g1 = __ldg(reinterpret_cast<const uint4*>(row) + 1);
+                    u0 = __ldg(reinterpret_cast<const uint4*>(row + p.K));
+                    u1 = __ldg(reinterpret_cast<const uint4*>(row + p.K) + 1);
+                }
                 float g[16], u[16];
                 unpack8(g0, g); unpack8(g1, g + 8); unpack8(u0, u); unpack8(u1, u + 8);
 #pragma unroll
@@ -614,7 +635,7 @@ bool plan_packed(int M, int N, int K, PackedPlan* plan) {
     const int bn = M <= 16 ? 16 : 32;
     const int per_sm = (bn == 16 && g_packed_ctas_per_sm == 2) ? 2 : 1;
     const int G = device_sm_count() * per_sm;
-    const int tiles = N / kTileRows, kblocks = K / kBlockK;
+    const int tiles = N / kTileRows, kblocks = (K + kBlockK - 1) / kBlockK;
     const int min_s = (kblocks + kMaxPartBlocks - 1) / kMaxPartBlocks;
     if (min_s > G) return false;
     // Estimated time of a split count, fitted to sweeps on B200: the CTAs make
@@ -645,11 +666,11 @@ bool plan_packed(int M, int N, int K, PackedPlan* plan) {
 }  // namespace
 
 size_t packed_weight_bytes(int N, int K) {
-    return static_cast<size_t>(N / kTileRows) * (K / kBlockK) * kBlockBytes;
+    return static_cast<size_t>(N / kTileRows) * ((K + kBlockK - 1) / kBlockK) * kBlockBytes;
 }
 
 size_t packed_workspace_bytes(int M, int N, int K) {
-    if (M <= 0 || N <= 0 || K <= 0 || N % kTileRows || K % kBlockK) return 16;
+    if (M <= 0 || N <= 0 || K <= 0 || N % kTileRows || K % (kBlockK / 2)) return 16;
     PackedPlan plan;
     if (!plan_packed(M < 32 ? M : 32, N, K, &plan)) return 16;
     const size_t tiles = N / kTileRows;
@@ -660,7 +681,7 @@ size_t packed_workspace_bytes(int M, int N, int K) {
 
 cudaError_t launch_pack_weight(const void* w, const void* sf_flat, void* packed, int N, int K,
                                cudaStream_t stream) {
-    const dim3 grid(static_cast<unsigned>(K / kBlockK), static_cast<unsigned>(N / kTileRows));
+    const dim3 grid(static_cast<unsigned>((K + kBlockK - 1) / kBlockK), static_cast<unsigned>(N / kTileRows));
     pack_weight_kernel<<<grid, 1024, 0, stream>>>(static_cast<const uint8_t*>(w),
                                                   static_cast<const uint8_t*>(sf_flat),
                                                   static_cast<uint8_t*>(packed), N, K);
@@ -670,7 +691,8 @@ cudaError_t launch_pack_weight(const void* w, const void* sf_flat, void* packed,
 cudaError_t launch_linear_packed(const PackedLinearArgs& g, cudaStream_t stream, const char** why) {
     *why = nullptr;
     if (g.N % kTileRows != 0) { *why = "packed linear: N must be a multiple of 128"; return cudaSuccess; }
-    if (g.K % kBlockK != 0) { *why = "packed linear: K must be a multiple of 256"; return cudaSuccess; }
+    if (g.K % (kBlockK / 2) != 0) { *why = "packed linear: K must be a multiple of 128"; return cudaSuccess; }
+    if (g.pro_kind == 1 && g.K % kBlockK != 0) { *why = "packed linear: the RMSNorm prologue needs K % 256 == 0"; return cudaSuccess; }
     for (int m0 = 0; m0 < g.M; m0 += 32) {
         const int m = g.M - m0 < 32 ? g.M - m0 : 32;
         PackedPlan plan;
@@ -691,7 +713,7 @@ cudaError_t launch_linear_packed(const PackedLinearArgs& g, cudaStream_t stream,
         p.alpha = g.alpha;
         p.tiles = g.N / kTileRows;
         p.splits = plan.splits;
-        p.kblocks = g.K / kBlockK;
+        p.kblocks = (g.K + kBlockK - 1) / kBlockK;
         p.ctas_per_part = plan.grid / plan.splits;
         p.kb_q = p.kblocks / plan.splits;
         p.kb_r = p.kblocks % plan.splits;

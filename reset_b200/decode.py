@@ -48,7 +48,7 @@ class _Linear:
         self.N, self.K, self.ws = N, K, workspace
         w = torch.randint(0, 256, (N, K // 2), dtype=torch.uint8, device=device, generator=gen)
         s = torch.randint(0x20, 0x38, (N, K // 16), dtype=torch.uint8, device=device, generator=gen)
-        self.packed = capi.pack_weight(w, s) if (N % 128 == 0 and K % 256 == 0) else None
+        self.packed = capi.pack_weight(w, s) if (N % 128 == 0 and K % 128 == 0) else None
         self.use_gemv = self.packed is None or nvops.use_gemv(1, N, K, 2)
         self.w, self.s = (w, s) if self.use_gemv else (None, None)
         self.gs_inv = torch.tensor([64.0], dtype=torch.float32, device=device)
@@ -65,7 +65,7 @@ class _Linear:
         self.N, self.K, self.ws = lin.N, lin.K, workspace
         w = lin.weight.to(device).contiguous()
         s = lin.weight_scale.to(device).contiguous()
-        self.packed = capi.pack_weight(w, s) if (self.N % 128 == 0 and self.K % 256 == 0) else None
+        self.packed = capi.pack_weight(w, s) if (self.N % 128 == 0 and self.K % 128 == 0) else None
         self.use_gemv = self.packed is None or nvops.use_gemv(1, self.N, self.K, 2)
         self.w, self.s = (w, s) if self.use_gemv else (None, None)
         self.gs_inv = torch.tensor([lin.input_global_scale_inv], dtype=torch.float32, device=device)

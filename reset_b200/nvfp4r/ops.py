@@ -73,6 +73,8 @@ def use_gemv(M: int, N: int, K: int, gemv_max_m: int) -> bool:
     from . import _config
     if M > gemv_max_m:
         return False
+    if K % 256:
+        return False     # the streaming GEMV wants K % 256 == 0; its plain-load fallback is slow
     limit = _config.GEMV_MAX_WEIGHT_BYTES.get(M)
     if (M == 1 and N >= _config.GEMV_WIDE_MIN_N and K <= _config.GEMV_WIDE_MAX_K
             and N * K * 9 // 16 <= _config.GEMV_WIDE_MAX_WEIGHT_BYTES):
@@ -98,7 +100,7 @@ def linear_auto(x, global_scale_inv, weight, weight_scale_flat, packed, N: int, 
                 out_dtype: torch.dtype = torch.bfloat16, rcp_mode: int = 1,
                 out: Optional[torch.Tensor] = None, reduce=None) -> torch.Tensor:
     """One decode linear through whichever kernel the measured crossover picks. ``packed``
-    may be None (shape outside the tensor-core kernel's N % 128 / K % 256). With ``out`` (a
+    may be None (shape outside the tensor-core kernel's N % 128 / K % 128). With ``out`` (a
     contiguous ``[M, N]`` tensor) the result is written there and nothing is allocated: the
     out-variant convention of the reference's raw ops (kernels/csrc/bindings.cpp:27-84).
     ``reduce`` (a ``reset_b200.comm.PeerAllReduce``) makes this a row-parallel linear of a

@@ -46,7 +46,7 @@ def prime_nvfp4r_caches(layer: torch.nn.Module) -> None:
     ``_nvfp4r_alpha_host``            Python float of ``layer.alpha``
     ``_nvfp4r_weight_scale_flat_3d``  ``[1, N, K/16]`` uint8 flat block scales
     ``_nvfp4r_weight_packed``         the weight in the packed block format of the
-                                      tensor-core path (None when N % 128 or K % 256)
+                                      tensor-core path (None when N % 128 or K % 128)
 
     ``layer.weight_scale`` may be swizzled (the reference's case, vLLM's CUTLASS
     format) or still flat ``[N, K/16]``; ``layer._nvfp4r_weight_scale_is_flat`` says
@@ -69,7 +69,7 @@ def prime_nvfp4r_caches(layer: torch.nn.Module) -> None:
         flat = ws_u8.contiguous() if is_flat else _unswizzle_blockscale(ws_u8, N, K)
         layer._nvfp4r_weight_scale_flat_3d = flat.reshape(1, N, K // 16).contiguous()
         layer._nvfp4r_weight_packed = None
-        if N % 128 == 0 and K % 256 == 0 and getattr(layer, "weights_padding_cols", 0) == 0:
+        if N % 128 == 0 and K % 128 == 0 and getattr(layer, "weights_padding_cols", 0) == 0:
             layer._nvfp4r_weight_packed = capi.pack_weight(
                 layer.weight.data.view(torch.uint8), layer._nvfp4r_weight_scale_flat_3d[0])
     layer._nvfp4r_caches_primed = True

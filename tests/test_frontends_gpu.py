@@ -131,7 +131,7 @@ def test_vllm_adapter_on_a_stand_in_layer(N, K, swizzled):
     assert layer._nvfp4r_caches_primed and abs(layer._nvfp4r_alpha_host - 0.37) < 1e-7
     assert tuple(layer._nvfp4r_weight_scale_flat_3d.shape) == (1, N, K // 16)
     assert np.array_equal(layer._nvfp4r_weight_scale_flat_3d[0].cpu().numpy(), ws)
-    assert (layer._nvfp4r_weight_packed is not None) == (N % 128 == 0 and K % 256 == 0)
+    assert (layer._nvfp4r_weight_packed is not None) == (N % 128 == 0 and K % 128 == 0)
     bias = torch.randn(N, device="cuda").to(torch.bfloat16)
     for M in (1, 2, 5, 40):
         x = make_activation(M, K, seed=M).cuda()

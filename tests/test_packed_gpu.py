@@ -58,7 +58,10 @@ def test_pack_weight_layout(capi):
                                  (4096, 12288), (512, 25600), (24576, 4096), (896, 5120),
                                  # tensor-parallel shards of the bench's Qwen3-8B set (TP 4 / 8)
                                  (768, 4096), (4096, 512), (3072, 4096), (4096, 1536), (4096, 1024),
-                                 (6144, 4096), (4096, 3072)])
+                                 (6144, 4096), (4096, 3072),
+                                 # rows that end in the middle of a 256-element block: the row-parallel
+                                 # shards of Qwen3-32B (TP 8: 3200) and Qwen3-14B (TP 8: 640, 2176)
+                                 (128, 128), (256, 384), (5120, 3200), (5120, 640), (5120, 2176)])
 @pytest.mark.parametrize("M", [1, 8])
 def test_linear_packed_matches_oracle(capi, N, K, M):
     w, ws = onv.random_nvfp4((N,), K, seed=N % 89 + M)
@@ -213,9 +216,9 @@ def test_fused_add_rmsnorm_prologue(capi, M, with_delta):
 
 
 @pytest.mark.parametrize("M", [1, 4])
-def test_fused_silu_mul_prologue(capi, M):
+@pytest.mark.parametrize("N,K", [(1024, 3072), (5120, 3200)])          # 3200: ends inside a block
+def test_fused_silu_mul_prologue(capi, M, N, K):
     from reset_b200 import _lib
-    N, K = 1024, 3072
     w, ws = onv.random_nvfp4((N,), K, seed=23)
     packed = capi.pack_weight(cuda(w), cuda(ws))
     g = torch.Generator(device="cuda").manual_seed(24)
