@@ -171,9 +171,15 @@ NVFP4R_API int nvfp4r_linear_tc(const void* x, int64_t x_row_stride, int M, int 
  * contiguous bytes: 16 KB of codes in the tensor core's shared-memory image (K-major,
  * 128-byte swizzle) followed by 2 KB of block scales in tcgen05.cp order. The linear then
  * streams the weight with one 36 KB bulk copy per pipeline stage.
- *   nvfp4r_packed_weight_bytes(N, K)   = N*K/2 + N*K/16 (0 if the shape is unsupported)
+ *   nvfp4r_packed_weight_bytes(N, K)   = N*K/2 + N*K/16 with K rounded up to a multiple of 256
+ *                                      (0 if the shape is unsupported)
  *   nvfp4r_pack_weight                 weight [N,K/2] + flat scales [N,K/16] -> packed
- *                                      (packed 16-byte aligned; N % 128 == 0, K % 256 == 0)
+ *                                      (packed 16-byte aligned; N % 128 == 0, K % 128 == 0; with
+ *                                      K % 256 == 128 the last block is half zeros and the linear
+ *                                      quantizes zeros for it: tensor-parallel shards such as the
+ *                                      3200-wide down projection of Qwen3-32B at TP 8. The
+ *                                      RMSNorm prologue of nvfp4r_linear_packed_ex still needs
+ *                                      K % 256 == 0.)
  *   nvfp4r_linear_packed               out[M,N] = alpha * quant(x)[M,K] . W^T, same
  *                                      arithmetic and rcp_mode meaning as nvfp4r_linear;
  *                                      workspace >= nvfp4r_linear_packed_workspace_bytes(M,..)
