@@ -286,6 +286,47 @@ def run_ours(args, rank, world, local_rank):
         return {"case": args.case, "us_eager": round(us, 2), "launches": args.steps,
                 "algorithmic_bytes": linear_bytes(n, k, cm)}
 
+    tp_check = None
+    if world > 1:
+        # Untimed correctness check of the real multi-GPU exchange: every row-parallel linear at
+        # every M through the path the timed region uses, against the rank-ordered fp32 sum of
+        # the ranks' own bf16 partial results (gathered with NCCL), rounded once to bf16.
+        worst = 0.0
+        for name, n, k, style, copies in shards:
+            if style != "row":
+                continue
+            for M in M_VALUES:
+                x = dev_x[(name, M)]
+                w, s, packed = copies[0]
+                got = nvfp4r.linear_auto(x, gs, w, s, packed, n, 1.0, torch.bfloat16,
+                                         reduce=peer) if peer is not None else None
+                part = nvfp4r.linear_auto(x, gs, w, s, packed, n, 1.0, torch.bfloat16).contiguous()
+                if got is None:
+                    got = part.clone()
+                    dist.all_reduce(got)
+                parts = [torch.empty_like(part) for _ in range(world)]
+                dist.all_gather(parts, part)
+                want32 = torch.zeros_like(part, dtype=torch.float32)
+                for r in range(world):
+                    want32 += parts[r].float()
+                want = want32.to(torch.bfloat16)
+                torch.cuda.synchronize()
+                if peer is not None and not torch.equal(got, want):
+                    worst = float("inf")           # the one-shot kernel promises exactly these bits
+                err = (got.float() - want32).abs().max().item()
+                scale = want32.abs().max().item() + 1e-30
+                worst = max(worst, err / scale)    # NCCL may round per hop: one bf16 ulp of the largest value
+        flag = torch.tensor([worst], dtype=torch.float64, device=device)
+        dist.all_reduce(flag, op=dist.ReduceOp.MAX)
+        tp_check = "ok" if float(flag.item()) <= 2.0 ** -7 else f"FAILED (max relative error {float(flag.item()):.3e})"
+        stage(rank, f"tp_check {tp_check}")
+        if tp_check != "ok":
+            if rank == 0:
+                _STDOUT.write(json.dumps({"tp_check": tp_check, "n_gpus": world}) + "\n")
+                _STDOUT.flush()
+            dist.barrier()
+            os._exit(3)
+
     sampler = ClockSampler(local_rank) if rank == 0 else None
     g_res = capture_phases(step_resident)
     stage(rank, "resident graphs captured")
@@ -376,6 +417,8 @@ def run_ours(args, rank, world, local_rank):
         "detail_us_gbs": detail,
         "decode": decode,
     }
+    if tp_check is not None:
+        line["tp_check"] = tp_check
     if world == 1:
         line["cpu_baseline"] = cpu_baseline(sample_repeats=2)
     return line

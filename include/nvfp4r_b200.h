@@ -283,7 +283,8 @@ typedef struct nvfp4r_reset_params {
     double t_low;    /* temperature for tokens below it                             */
     double tau0;     /* global threshold used while the step is not "uncertain"     */
     int32_t window;  /* w, 1..NVFP4R_RESET_MAX_WINDOW                               */
-    int32_t reserved;
+    int32_t id_set;  /* which newline-id set the request uses (per-request entry point
+                        only; the single-record entry points ignore it)              */
 } nvfp4r_reset_params;
 
 /* What a step decided, one record per row (optional output, for logging/tests). */
@@ -327,6 +328,26 @@ NVFP4R_API int nvfp4r_reset_step(float* logits, int64_t row_stride, int B, int V
                                  nvfp4r_reset_decision* decisions,
                                  void* workspace, size_t workspace_bytes, void* stream);
 
+/* The same step with each request's OWN hyper-parameters, as the reference builds one
+ * ReSETRequest per request from that request's SamplingParams.extra_args
+ * (reset/reset/logits_processor.py:144-155: t_high, t_low, tau_0, window, reset_nl_ids,
+ * reset_dnl_ids). Differences from nvfp4r_reset_step:
+ *   slot_params  records on the DEVICE, indexed by state slot like `states`; the host fills
+ *                a slot's record when the request is admitted (window must be in
+ *                1..NVFP4R_RESET_MAX_WINDOW; the kernel clamps it)
+ *   nl_bitmaps / dnl_bitmaps  n_id_sets consecutive bitmaps of ceil(V/32) words each;
+ *                a request uses set `slot_params[slot].id_set` (n_id_sets = 0: no ids)
+ * A workspace that saw NVFP4R_ERR_DEVICE_TIMEOUT (nvfp4r_check_device_status) holds a
+ * half-finished exchange: zero it before the next call. This holds for every entry point
+ * that takes a workspace. */
+NVFP4R_API int nvfp4r_reset_step_per_request(float* logits, int64_t row_stride, int B, int V,
+                                             nvfp4r_reset_state* states, const int32_t* state_slots,
+                                             const int32_t* last_ids,
+                                             const uint32_t* nl_bitmaps, const uint32_t* dnl_bitmaps,
+                                             int n_id_sets, const nvfp4r_reset_params* slot_params,
+                                             nvfp4r_reset_decision* decisions,
+                                             void* workspace, size_t workspace_bytes, void* stream);
+
 /* ReSET step without any caller-provided scratch. No counterpart in the reference (its
  * processor is PyTorch code and allocates freely); it exists for hosts that cannot
  * allocate device memory when they need the processor: a sampler plug-in inside an engine
@@ -369,6 +390,15 @@ NVFP4R_API int nvfp4r_entropy(const float* logits, int64_t row_stride, int B, in
  *   force_generic 1 = always use the plain-load fallback kernel (default 0)
  * ------------------------------------------------------------------------- */
 NVFP4R_API int nvfp4r_set_gemv_tuning(int ctas_per_sm, int use_pdl, int force_generic);
+
+/* Tuning of the register-resident GEMV that takes launches of one or two tokens (same
+ * standing as the call above: the reference's counterpart is its NVFP4R_GEMV_* environment,
+ * kernels/cuda/gemv/gemv_nvfp4.cu:870-948).
+ *   mode           0 = automatic (default), 1 = whenever the arguments allow it, -1 = never
+ *   rows_per_step  weight rows a lane multiplies per pipeline step: 0 = automatic, 2 or 4
+ *   warps_per_sm   resident warps the launch aims for: 0 = automatic (24), at most 32
+ */
+NVFP4R_API int nvfp4r_set_gemv_rows_tuning(int mode, int rows_per_step, int warps_per_sm);
 
 /* ------------------------------------------------------------------------- *
  * One-shot all-reduce (sum) of a small bf16 tensor over NVLink peer memory: the exchange

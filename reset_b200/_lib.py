@@ -31,7 +31,7 @@ class ResetState(C.Structure):
 
 class ResetParams(C.Structure):
     _fields_ = [("t_high", C.c_double), ("t_low", C.c_double), ("tau0", C.c_double),
-                ("window", C.c_int32), ("reserved", C.c_int32)]
+                ("window", C.c_int32), ("id_set", C.c_int32)]
 
 
 class ResetDecision(C.Structure):
@@ -83,10 +83,13 @@ PROTOTYPES = {
     "nvfp4r_reset_workspace_bytes": (_sz, [_i]),
     "nvfp4r_reset_step": (_i, [_vp, _i64, _i, _i, _vp, _vp, _vp, _vp, _vp,
                                C.POINTER(ResetParams), _vp, _vp, _sz, _vp]),
+    "nvfp4r_reset_step_per_request": (_i, [_vp, _i64, _i, _i, _vp, _vp, _vp, _vp, _vp, _i, _vp, _vp,
+                                           _vp, _sz, _vp]),
     "nvfp4r_reset_step_static": (_i, [_vp, _i64, _i, _i, _vp, _vp, _vp, _vp, _vp,
                                       C.POINTER(ResetParams), _vp, _vp]),
     "nvfp4r_entropy": (_i, [_vp, _i64, _i, _i, _vp, _vp, _sz, _vp]),
     "nvfp4r_set_gemv_tuning": (_i, [_i, _i, _i]),
+    "nvfp4r_set_gemv_rows_tuning": (_i, [_i, _i, _i]),
     "nvfp4r_add_rmsnorm": (_i, [_vp, _vp, _vp, _vp, _i, _i, _f, _vp]),
     "nvfp4r_qk_norm_rope_kv": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _f, _f, _vp]),
     "nvfp4r_attn_decode_workspace_bytes": (_sz, [_i, _i]),

@@ -291,6 +291,33 @@ def reset_step(logits: torch.Tensor, states: torch.Tensor, params: L.ResetParams
     L.check(st, "nvfp4r_reset_step")
 
 
+def reset_step_per_request(logits: torch.Tensor, states: torch.Tensor, slot_params: torch.Tensor, *,
+                           state_slots: torch.Tensor | None = None, last_ids: torch.Tensor | None = None,
+                           nl_bitmaps: torch.Tensor | None = None, dnl_bitmaps: torch.Tensor | None = None,
+                           n_id_sets: int = 0, decisions: torch.Tensor | None = None,
+                           workspace: torch.Tensor) -> None:
+    """One ReSET step in place with per-request hyper-parameters: ``slot_params`` is a uint8
+    device tensor of ``sizeof(nvfp4r_reset_params)`` bytes per state slot; ``nl_bitmaps`` /
+    ``dnl_bitmaps`` hold ``n_id_sets`` bitmaps of ceil(V/32) int32 words each (both given, or
+    neither)."""
+    _need_cuda(logits, states, slot_params, state_slots, last_ids, nl_bitmaps, dnl_bitmaps, decisions, workspace)
+    if logits.dtype != torch.float32 or logits.dim() != 2 or logits.stride(1) != 1:
+        raise ValueError("reset_step_per_request: logits must be fp32 [B,V] with unit inner stride")
+    B, V = logits.shape
+    words = (V + 31) // 32
+    if n_id_sets > 0:
+        for bm in (nl_bitmaps, dnl_bitmaps):
+            if bm is None or bm.numel() * bm.element_size() < n_id_sets * words * 4:
+                raise ValueError("reset_step_per_request: bitmaps must hold n_id_sets * ceil(V/32) words")
+    ptr = lambda t: t.data_ptr() if t is not None else None
+    with torch.cuda.device(logits.device):
+        st = L.lib().nvfp4r_reset_step_per_request(
+            logits.data_ptr(), logits.stride(0), B, V, states.data_ptr(), ptr(state_slots), ptr(last_ids),
+            ptr(nl_bitmaps), ptr(dnl_bitmaps), int(n_id_sets), slot_params.data_ptr(), ptr(decisions),
+            workspace.data_ptr(), workspace.numel() * workspace.element_size(), _stream())
+    L.check(st, "nvfp4r_reset_step_per_request")
+
+
 def sample(logits: torch.Tensor, draws: torch.Tensor, *, seed: int = 0,
            last_ids: torch.Tensor | None = None, out: torch.Tensor | None = None) -> torch.Tensor:
     """One id per row drawn from softmax(logits) on the device (Gumbel-max). ``draws`` is an

@@ -98,9 +98,7 @@ int nvfp4r_gemv(const void* weight, const void* weight_scale, const void* x, con
         a.xsf = static_cast<const uint8_t*>(x_scale) + l0 * xsf_stride_l;
         a.out = static_cast<uint8_t*>(out) + static_cast<size_t>(l0) * N * out_elt;
         a.M = m;
-        cudaError_t e = nvfp4r::gemv_stream_supported(a)
-                            ? nvfp4r::launch_gemv_stream(a, as_stream(stream))
-                            : nvfp4r::launch_gemv_generic(a, as_stream(stream));
+        cudaError_t e = nvfp4r::launch_gemv_auto(a, as_stream(stream));
         if (e != cudaSuccess) return cuda_fail(e, "gemv launch");
     }
     return NVFP4R_OK;
@@ -141,9 +139,7 @@ int nvfp4r_linear(const void* x, int64_t x_row_stride, int M, int K, const float
         a.M = M - m0 < 8 ? M - m0 : 8;
         a.xb = static_cast<const uint8_t*>(x) + static_cast<size_t>(m0) * x_row_stride * 2;
         a.out = static_cast<uint8_t*>(out) + static_cast<size_t>(m0) * N * out_elt;
-        cudaError_t e = nvfp4r::gemv_stream_supported(a)
-                            ? nvfp4r::launch_gemv_stream(a, as_stream(stream))
-                            : nvfp4r::launch_gemv_generic(a, as_stream(stream));
+        cudaError_t e = nvfp4r::launch_gemv_auto(a, as_stream(stream));
         if (e != cudaSuccess) return cuda_fail(e, "linear launch");
     }
     return NVFP4R_OK;
@@ -212,12 +208,15 @@ int nvfp4r_linear_tc(const void* x, int64_t x_row_stride, int M, int K, const fl
     return e == cudaSuccess ? NVFP4R_OK : cuda_fail(e, "linear_tc launch");
 }
 
-// Diagnostics, not part of the public header: the %globaltimer time line of CTA 0 of the
-// last four packed-linear launches (enabled by bit 8 of nvfp4r_set_packed_tuning).
+#ifdef NVFP4R_TRACE
+// Diagnostics of a -DNVFP4R_TRACE build only (not in the header, not in the default library):
+// the %globaltimer time line of eight CTAs of the last four packed-linear launches (enabled by
+// bit 8 of nvfp4r_set_packed_tuning).
 NVFP4R_API int nvfp4r_debug_read_trace(unsigned long long* out16) {
     cudaDeviceSynchronize();
     return nvfp4r::read_packed_trace(out16) == cudaSuccess ? 0 : -4;
 }
+#endif
 size_t nvfp4r_packed_weight_bytes(int N, int K) {
     if (N <= 0 || K <= 0 || N % 128 || K % 128) return 0;
     return nvfp4r::packed_weight_bytes(N, K);
@@ -391,11 +390,49 @@ int nvfp4r_reset_step(float* logits, int64_t row_stride, int B, int V, nvfp4r_re
     p.nl_bitmap = nl_bitmap;
     p.dnl_bitmap = dnl_bitmap;
     p.params = *params;
+    p.params.id_set = 0;
     p.decisions = decisions;
     p.entropy_out = nullptr;
     p.needs_state = 1;
     cudaError_t e = nvfp4r::launch_reset(p, true, as_stream(stream));
     return e == cudaSuccess ? NVFP4R_OK : cuda_fail(e, "reset_step launch");
+}
+
+int nvfp4r_reset_step_per_request(float* logits, int64_t row_stride, int B, int V,
+                                  nvfp4r_reset_state* states, const int32_t* state_slots,
+                                  const int32_t* last_ids, const uint32_t* nl_bitmaps,
+                                  const uint32_t* dnl_bitmaps, int n_id_sets,
+                                  const nvfp4r_reset_params* slot_params,
+                                  nvfp4r_reset_decision* decisions, void* workspace,
+                                  size_t workspace_bytes, void* stream) {
+    if (!logits || !states || !slot_params || !workspace)
+        return fail(NVFP4R_ERR_INVALID_ARGUMENT, "reset_step_per_request: null pointer");
+    if (B < 0 || V <= 0 || row_stride < V || n_id_sets < 0)
+        return fail(NVFP4R_ERR_INVALID_ARGUMENT, "reset_step_per_request: bad sizes");
+    if (workspace_bytes < nvfp4r_reset_workspace_bytes(B))
+        return fail(NVFP4R_ERR_INVALID_ARGUMENT, "reset_step_per_request: workspace too small");
+    if (!aligned(workspace, 8) || !aligned(logits, 4) || !aligned(states, 8) || !aligned(slot_params, 8))
+        return fail(NVFP4R_ERR_ALIGNMENT, "reset_step_per_request: workspace/states/params need 8-byte alignment");
+    if (B == 0) return NVFP4R_OK;
+    nvfp4r::ResetLaunch p = {};
+    p.logits = logits;
+    p.row_stride = row_stride;
+    p.B = B;
+    p.V = V;
+    p.scratch = static_cast<nvfp4r::RowScratch*>(workspace);
+    p.slots = reinterpret_cast<nvfp4r::RowSlots*>(static_cast<nvfp4r::RowScratch*>(workspace) + B);
+    p.states = states;
+    p.state_slots = state_slots;
+    p.last_ids = last_ids;
+    p.nl_bitmap = n_id_sets > 0 ? nl_bitmaps : nullptr;
+    p.dnl_bitmap = n_id_sets > 0 ? dnl_bitmaps : nullptr;
+    p.slot_params = slot_params;
+    p.bitmap_words = (V + 31) / 32;
+    p.decisions = decisions;
+    p.entropy_out = nullptr;
+    p.needs_state = 1;
+    cudaError_t e = nvfp4r::launch_reset(p, true, as_stream(stream));
+    return e == cudaSuccess ? NVFP4R_OK : cuda_fail(e, "reset_step_per_request launch");
 }
 
 int nvfp4r_reset_step_static(float* logits, int64_t row_stride, int B, int V,
@@ -427,6 +464,7 @@ int nvfp4r_reset_step_static(float* logits, int64_t row_stride, int B, int V,
     p.nl_bitmap = nl_bitmap;
     p.dnl_bitmap = dnl_bitmap;
     p.params = *params;
+    p.params.id_set = 0;
     p.decisions = decisions;
     p.entropy_out = nullptr;
     p.needs_state = 1;
@@ -462,6 +500,16 @@ int nvfp4r_set_gemv_tuning(int ctas_per_sm, int use_pdl, int force_generic) {
     if (ctas_per_sm >= 0) t.ctas_per_sm = ctas_per_sm;      // 0 = automatic
     if (use_pdl >= 0) t.use_pdl = use_pdl ? 1 : 0;
     if (force_generic >= 0) t.force_generic = force_generic ? 1 : 0;
+    return NVFP4R_OK;
+}
+
+int nvfp4r_set_gemv_rows_tuning(int mode, int rows_per_step, int warps_per_sm) {
+    if (mode < -1 || mode > 1) return fail(NVFP4R_ERR_INVALID_ARGUMENT, "rows tuning: mode is -1, 0 or 1");
+    if (rows_per_step != 0 && rows_per_step != 2 && rows_per_step != 4)
+        return fail(NVFP4R_ERR_INVALID_ARGUMENT, "rows tuning: rows_per_step is 0, 2 or 4");
+    if (warps_per_sm < 0 || warps_per_sm > 32)
+        return fail(NVFP4R_ERR_INVALID_ARGUMENT, "rows tuning: warps_per_sm 0..32");
+    nvfp4r::set_gemv_rows_tuning(mode, rows_per_step, warps_per_sm);
     return NVFP4R_OK;
 }
 

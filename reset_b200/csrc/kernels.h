@@ -44,6 +44,15 @@ bool gemv_stream_supported(const GemvArgs& a);
 cudaError_t launch_gemv_stream(const GemvArgs& a, cudaStream_t stream);
 cudaError_t launch_gemv_generic(const GemvArgs& a, cudaStream_t stream);
 
+// The register-resident kernel for one or two tokens (gemv_rows.cu).
+bool gemv_rows_supported(const GemvArgs& a);
+cudaError_t launch_gemv_rows(const GemvArgs& a, cudaStream_t stream);
+// mode: 0 automatic, 1 whenever supported, -1 never; rows per step 0 (automatic), 2 or 4;
+// warps per SM 0 (automatic) .. 32.
+void set_gemv_rows_tuning(int mode, int rows, int target_warps);
+// Picks the kernel for one launch of at most 8 tokens and launches it.
+cudaError_t launch_gemv_auto(const GemvArgs& a, cudaStream_t stream);
+
 // Tuning knobs of the streaming kernel (process-wide; 0 = built-in default).
 struct GemvTuning {
     int ctas_per_sm;   // grid = SMs * ctas_per_sm
@@ -108,7 +117,9 @@ cudaError_t launch_pack_weight(const void* w, const void* sf_flat, void* packed,
 cudaError_t launch_linear_packed(const PackedLinearArgs& g, cudaStream_t stream, const char** why);
 cudaError_t read_and_clear_packed_status(int* flag);
 void set_packed_tuning(int splits);
+#ifdef NVFP4R_TRACE
 cudaError_t read_packed_trace(unsigned long long* out16);
+#endif
 
 // Synchronises the device, returns the time-out flag set by bounded waits
 // inside the kernels and clears it.

@@ -90,9 +90,11 @@ struct PackedParams {
 };
 
 __device__ int g_packed_status = 0;
-// Optional time line (nanoseconds of %globaltimer) of eight consecutive CTAs, filled when
-// g_packed_trace != 0: CTAs base .. base+7 with base = g_packed_trace - 1 (a multiple of 8),
-// the last four launches each.
+// Optional time line (nanoseconds of %globaltimer) of eight consecutive CTAs, compiled in only
+// with -DNVFP4R_TRACE (the default build carries none of it): filled when g_packed_trace != 0,
+// CTAs base .. base+7 with base = g_packed_trace - 1 (a multiple of 8), the last four launches
+// each.
+#ifdef NVFP4R_TRACE
 __device__ int g_packed_trace = 0;
 __device__ unsigned long long g_packed_times[8 * 4 * 16];
 __device__ unsigned g_packed_launch[8] = {};
@@ -102,6 +104,9 @@ __device__ __forceinline__ unsigned long long gtime() {
     return t;
 }
 #define TRACE(slot) do { if (trace) g_packed_times[((blockIdx.x & 7) * 4 + (launch_id & 3)) * 16 + (slot)] = gtime(); } while (0)
+#else
+#define TRACE(slot) do { } while (0)
+#endif
 
 // ---- one-time re-layout ----------------------------------------------------------
 
@@ -223,9 +228,10 @@ linear_packed_kernel(const __grid_constant__ PackedParams p) {
     __shared__ __align__(8) uint64_t bars[2 * kStages + 4 + kMaxPartBlocks / kBlocksPerStage];
     __shared__ uint32_t s_tmem;
     __shared__ float s_red[32 * 8];                    // RMSNorm: per token, per warp sum of squares
-    __shared__ unsigned s_launch_id;
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+#ifdef NVFP4R_TRACE
+    __shared__ unsigned s_launch_id;
     const bool traced_cta = (g_packed_trace != 0) && (static_cast<int>(blockIdx.x) >> 3) == ((g_packed_trace - 1) >> 3);
     const bool trace = traced_cta && lane == 0;
     if (traced_cta) {
@@ -233,6 +239,7 @@ linear_packed_kernel(const __grid_constant__ PackedParams p) {
         __syncthreads();
     }
     const unsigned launch_id = traced_cta ? s_launch_id : 0u;
+#endif
     if (warp == 0) TRACE(0);
 
     const int S = p.splits;
@@ -766,14 +773,18 @@ cudaError_t launch_linear_packed(const PackedLinearArgs& g, cudaStream_t stream,
 void set_packed_tuning(int splits) {
     g_force_packed_splits = splits & 0xff;
     g_packed_ctas_per_sm = ((splits >> 9) & 1) ? 1 : 2;
+#ifdef NVFP4R_TRACE
     // bit 8: record the time line of eight CTAs; bits 12..23: the first of them
     const int trace = ((splits >> 8) & 1) ? 1 + ((splits >> 12) & 0xfff) : 0;
     cudaMemcpyToSymbol(g_packed_trace, &trace, sizeof(int));
+#endif
 }
 
+#ifdef NVFP4R_TRACE
 cudaError_t read_packed_trace(unsigned long long* out512) {
     return cudaMemcpyFromSymbol(out512, g_packed_times, 8 * 64 * sizeof(unsigned long long));
 }
+#endif
 
 cudaError_t read_and_clear_packed_status(int* flag) {
     cudaError_t e = cudaMemcpyFromSymbol(flag, g_packed_status, sizeof(int));

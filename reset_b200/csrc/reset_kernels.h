@@ -48,7 +48,10 @@ struct ResetLaunch {
     const int32_t* last_ids;
     const uint32_t* nl_bitmap;
     const uint32_t* dnl_bitmap;
-    nvfp4r_reset_params params;
+    nvfp4r_reset_params params;               // the one record of the by-value entry points
+    const nvfp4r_reset_params* slot_params;   // per-request records on the device, indexed by state
+                                              // slot (nullptr = `params` for every row)
+    int bitmap_words;                         // words between two id sets in nl_bitmap / dnl_bitmap
     nvfp4r_reset_decision* decisions;
     float* entropy_out;
     int needs_state;     // 0: entropy only

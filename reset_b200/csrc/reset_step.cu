@@ -135,12 +135,24 @@ reset_partials_kernel(const ResetLaunch p) {
 // ---- the per-request state machine (one thread) --------------------------------
 // Step boundary of a row: the last generated id contains a double newline, or the last two are
 // both single newlines (reference logits_processor.py:91-99).
-__device__ bool reset_boundary(const ResetLaunch& p, int row) {
+// The hyper-parameters of a row: the request's own record when the caller passed per-request
+// records (indexed by state slot), else the launch's single record.
+__device__ __forceinline__ nvfp4r_reset_params reset_params_of(const ResetLaunch& p, int slot) {
+    nvfp4r_reset_params prm = p.params;
+    if (p.slot_params != nullptr) {
+        prm = p.slot_params[slot];
+        prm.window = min(max(prm.window, 1), NVFP4R_RESET_MAX_WINDOW);
+    }
+    return prm;
+}
+
+__device__ bool reset_boundary(const ResetLaunch& p, int row, int id_set) {
     bool boundary = false;
     if (p.last_ids != nullptr) {
         const int prev = p.last_ids[2 * row], last = p.last_ids[2 * row + 1];
+        const int64_t set_off = static_cast<int64_t>(id_set) * p.bitmap_words;
         auto in_set = [&](const uint32_t* bm, int id) {
-            return bm != nullptr && id >= 0 && id < p.V && ((bm[id >> 5] >> (id & 31)) & 1u);
+            return bm != nullptr && id >= 0 && id < p.V && ((bm[set_off + (id >> 5)] >> (id & 31)) & 1u);
         };
         if (last >= 0) {
             if (in_set(p.dnl_bitmap, last)) boundary = true;
@@ -151,9 +163,9 @@ __device__ bool reset_boundary(const ResetLaunch& p, int row) {
 }
 
 // `st` may be the record in global memory or a copy of it in shared memory.
-__device__ void reset_decide_on(const ResetLaunch& p, int row, nvfp4r_reset_state* st, bool boundary, double ent,
-                                int argmax, RowScratch* rs) {
-    const int w = p.params.window;
+__device__ void reset_decide_on(const ResetLaunch& p, const nvfp4r_reset_params& prm, int row,
+                                nvfp4r_reset_state* st, bool boundary, double ent, int argmax, RowScratch* rs) {
+    const int w = prm.window;
     if (boundary) { st->step_count = 0; st->step_sum = 0.0; }
 
     double h_step;
@@ -172,8 +184,8 @@ __device__ void reset_decide_on(const ResetLaunch& p, int row, nvfp4r_reset_stat
     const double h_bar = st->total_count > 0
                              ? st->total_sum / static_cast<double>(st->total_count) : h_step;
     const bool high = h_step > h_bar;
-    const double thr = high ? h_step : p.params.tau0;
-    const double temp = (ent >= thr) ? p.params.t_high : p.params.t_low;
+    const double thr = high ? h_step : prm.tau0;
+    const double temp = (ent >= thr) ? prm.t_high : prm.t_low;
 
     // bookkeeping
     st->step_sum += ent;
@@ -199,7 +211,8 @@ __device__ void reset_decide_on(const ResetLaunch& p, int row, nvfp4r_reset_stat
 }
 
 __device__ void reset_decide(const ResetLaunch& p, int row, int slot, double ent, int argmax, RowScratch* rs) {
-    reset_decide_on(p, row, p.states + slot, reset_boundary(p, row), ent, argmax, rs);
+    const nvfp4r_reset_params prm = reset_params_of(p, slot);
+    reset_decide_on(p, prm, row, p.states + slot, reset_boundary(p, row, prm.id_set), ent, argmax, rs);
 }
 
 // ---- kernel 2 ---------------------------------------------------------------
@@ -207,14 +220,14 @@ __global__ void __launch_bounds__(kThreads)
 reset_entropy_kernel(const ResetLaunch p) {
     const int row = blockIdx.y, slice = blockIdx.x;
     int slot;
+    pdl_launch_dependents();
+    pdl_wait_prior();
     if (!row_active(p, row, &slot)) return;
     const SliceView sv = slice_of(p, row, slice);
     RowScratch* rs = p.scratch + row;
     __shared__ double s_part[kThreads / 32];
     __shared__ bool s_last;
 
-    pdl_launch_dependents();
-    pdl_wait_prior();
     // Row max and denominator from the slice partials: lane s owns slice s (at most 32
     // slices), the reductions are fixed shuffle trees, so every warp of every CTA of the row
     // computes the same bits.
@@ -280,8 +293,8 @@ reset_scale_kernel(const ResetLaunch p) {
     const int row = blockIdx.y, slice = blockIdx.x;
     int slot;
     pdl_launch_dependents();
-    if (!row_active(p, row, &slot)) return;
     pdl_wait_prior();
+    if (!row_active(p, row, &slot)) return;
     const RowScratch* rs = p.scratch + row;
     const double temp_d = rs->temp;
     if (temp_d == 1.0) return;
@@ -352,12 +365,15 @@ reset_fused_kernel(const ResetLaunch p, const int scale) {
     __shared__ int s_fail;
     __shared__ __align__(8) nvfp4r_reset_state s_state;        // slice 0 only: the request's record
     __shared__ int s_boundary;
+    __shared__ __align__(8) nvfp4r_reset_params s_prm;
     pdl_launch_dependents();
     const int row = blockIdx.y, slice = blockIdx.x;
     const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
     int slot;
-    if (!row_active(p, row, &slot)) return;
+    // The wait comes before anything is read and before any return: completion of this grid
+    // must imply completion of the kernel before it for whatever is launched next.
     pdl_wait_prior();
+    if (!row_active(p, row, &slot)) return;
     if (threadIdx.x == 0) s_fail = 0;
     RowSlots* sl = p.slots + row;
     const unsigned epoch = *reinterpret_cast<volatile unsigned*>(&sl->epoch) + 1u;
@@ -370,7 +386,10 @@ reset_fused_kernel(const ResetLaunch p, const int scale) {
         if (threadIdx.x < kStateWords)
             reinterpret_cast<unsigned long long*>(&s_state)[threadIdx.x] =
                 reinterpret_cast<const unsigned long long*>(p.states + slot)[threadIdx.x];
-        if (threadIdx.x == kThreads - 1) s_boundary = reset_boundary(p, row) ? 1 : 0;
+        if (threadIdx.x == kThreads - 1) {
+            s_prm = reset_params_of(p, slot);
+            s_boundary = reset_boundary(p, row, s_prm.id_set) ? 1 : 0;
+        }
     }
 
     // ---- load the slice once; slice max / argmax / sum exp --------------------------------
@@ -507,7 +526,7 @@ reset_fused_kernel(const ResetLaunch p, const int scale) {
                 uint32_t mode = 1u;
                 if (p.needs_state) {
                     RowScratch* rs = p.scratch + row;
-                    reset_decide_on(p, row, &s_state, s_boundary != 0, static_cast<double>(ent_f), rarg, rs);
+                    reset_decide_on(p, s_prm, row, &s_state, s_boundary != 0, static_cast<double>(ent_f), rarg, rs);
                     const double temp_d = rs->temp;
                     temp_f = static_cast<float>(temp_d);
                     mode = (temp_d == 1.0) ? 1u : (temp_d <= 1e-6 ? 2u : 0u);

@@ -12,6 +12,9 @@
 #include <torch/extension.h>
 #include <torch/library.h>
 
+#include <c10/cuda/CUDAGraphsC10Utils.h>
+
+#include <cstdlib>
 #include <mutex>
 #include <unordered_map>
 
@@ -72,18 +75,40 @@ void gemv_op(const at::Tensor& weight, const at::Tensor& weight_scale, const at:
     check_status(st, "gemv");
 }
 
-// Split-K scratch of the tensor-core GEMM: one zero-initialised buffer per device,
-// grown on demand and kept for the life of the process (the op's schema, which is the
-// reference's, has no workspace argument). The kernel leaves it zeroed.
-at::Tensor& gemm_workspace(const at::Device& dev, size_t bytes) {
+// Hidden scratch of the operators whose schema (the reference's) has no workspace argument:
+// ONE zero-initialised buffer per device and per kernel family, allocated at the first call on
+// that device with a fixed size and never replaced, so that a pointer recorded in a CUDA graph
+// stays valid for the life of the process. A call that needs more than the fixed size raises
+// (set NVFP4R_WORKSPACE_MB before the first call to change it); a first call inside a stream
+// capture raises too, because memory allocated there belongs to the capturing graph.
+// kind 0: tickets + fp32 split-K partials of `gemm` / `linear_tc` (the kernel leaves the
+// tickets zeroed); kind 1: the split-K slots of `linear_packed` (all zero between launches).
+// The two never share memory.
+size_t workspace_capacity() {
+    static const size_t cap = [] {
+        const char* env = std::getenv("NVFP4R_WORKSPACE_MB");
+        long mb = env ? std::atol(env) : 128;
+        if (mb < 1) mb = 1;
+        return static_cast<size_t>(mb) << 20;
+    }();
+    return cap;
+}
+
+at::Tensor& fixed_workspace(int kind, const at::Device& dev, size_t bytes, const char* who) {
     static std::mutex mu;
-    static std::unordered_map<int, at::Tensor> cache;
+    static std::unordered_map<int, at::Tensor> cache[2];
     std::lock_guard<std::mutex> lock(mu);
-    at::Tensor& t = cache[dev.index()];
-    if (!t.defined() || static_cast<size_t>(t.nbytes()) < bytes) {
-        const int64_t n = static_cast<int64_t>((bytes + 1023) / 1024 * 1024);
-        t = at::zeros({n}, at::TensorOptions().device(dev).dtype(at::kByte));
+    at::Tensor& t = cache[kind][dev.index()];
+    if (!t.defined()) {
+        TORCH_CHECK(c10::cuda::currentStreamCaptureStatusMayInitCtx() == c10::cuda::CaptureStatus::None, who,
+                    ": the first call on a device allocates the operator's scratch; make it before "
+                    "capturing a CUDA graph");
+        t = at::zeros({static_cast<int64_t>(workspace_capacity())},
+                      at::TensorOptions().device(dev).dtype(at::kByte));
     }
+    TORCH_CHECK(bytes <= static_cast<size_t>(t.nbytes()), who, ": this shape needs ", bytes,
+                " bytes of split-K scratch, the fixed buffer holds ", t.nbytes(),
+                "; set NVFP4R_WORKSPACE_MB before the first call");
     return t;
 }
 
@@ -106,9 +131,9 @@ void gemm_op(const at::Tensor& A, const at::Tensor& B, const at::Tensor& SFA, co
     const int64_t M = A.size(0), K2 = A.size(1), N = B.size(0);
     TORCH_CHECK(B.size(1) == K2 && C.size(0) == M && C.size(1) == N, "gemm: shape mismatch");
     const c10::cuda::OptionalCUDAGuard guard(A.device());
-    at::Tensor& ws = gemm_workspace(A.device(), nvfp4r_gemm_workspace_bytes(
-                                                    static_cast<int>(M), static_cast<int>(N),
-                                                    static_cast<int>(2 * K2)));
+    at::Tensor& ws = fixed_workspace(0, A.device(),
+                                     nvfp4r_gemm_workspace_bytes(static_cast<int>(M), static_cast<int>(N),
+                                                                 static_cast<int>(2 * K2)), "gemm");
     const int st = nvfp4r_gemm(A.data_ptr(), B.data_ptr(), SFA.data_ptr(), SFB.data_ptr(), C.data_ptr(),
                                static_cast<int>(M), static_cast<int>(N), static_cast<int>(2 * K2),
                                static_cast<float>(alpha), dtype_code(C.scalar_type(), "gemm"),
@@ -183,9 +208,9 @@ at::Tensor linear_tc_op(const at::Tensor& x, const at::Tensor& global_scale_inv,
     const c10::cuda::OptionalCUDAGuard guard(x.device());
     const auto dt = out_dtype_int == 0 ? at::kBFloat16 : out_dtype_int == 1 ? at::kHalf : at::kFloat;
     auto out = at::empty({M, N}, x.options().dtype(dt));
-    at::Tensor& ws = gemm_workspace(x.device(), nvfp4r_gemm_workspace_bytes(
-                                                    static_cast<int>(M), static_cast<int>(N),
-                                                    static_cast<int>(K)));
+    at::Tensor& ws = fixed_workspace(0, x.device(),
+                                     nvfp4r_gemm_workspace_bytes(static_cast<int>(M), static_cast<int>(N),
+                                                                 static_cast<int>(K)), "linear_tc");
     const int st = nvfp4r_linear_tc(x.data_ptr(), x.stride(0), static_cast<int>(M), static_cast<int>(K),
                                     global_scale_inv.data_ptr<float>(), weight.data_ptr(),
                                     weight_scale_swizzled.data_ptr(), static_cast<int>(N),
@@ -204,7 +229,7 @@ at::Tensor pack_weight_op(const at::Tensor& weight, const at::Tensor& weight_sca
     const int64_t N = weight.size(0), K = weight.size(1) * 2;
     TORCH_CHECK(weight_scale_flat.numel() == N * (K / 16), "pack_weight: weight_scale shape mismatch");
     const size_t bytes = nvfp4r_packed_weight_bytes(static_cast<int>(N), static_cast<int>(K));
-    TORCH_CHECK(bytes > 0, "pack_weight: needs N % 128 == 0 and K % 256 == 0");
+    TORCH_CHECK(bytes > 0, "pack_weight: needs N % 128 == 0 and K % 128 == 0");
     const c10::cuda::OptionalCUDAGuard guard(weight.device());
     auto packed = at::empty({static_cast<int64_t>(bytes)}, weight.options().dtype(at::kByte));
     check_status(nvfp4r_pack_weight(weight.data_ptr(), weight_scale_flat.data_ptr(), packed.data_ptr(),
@@ -229,9 +254,9 @@ at::Tensor linear_packed_op(const at::Tensor& x, const at::Tensor& global_scale_
     const c10::cuda::OptionalCUDAGuard guard(x.device());
     const auto dt = out_dtype_int == 0 ? at::kBFloat16 : out_dtype_int == 1 ? at::kHalf : at::kFloat;
     auto out = at::empty({M, N}, x.options().dtype(dt));
-    at::Tensor& ws = gemm_workspace(x.device(), nvfp4r_linear_packed_workspace_bytes(
-                                                    static_cast<int>(M), static_cast<int>(N),
-                                                    static_cast<int>(K)));
+    at::Tensor& ws = fixed_workspace(1, x.device(),
+                                     nvfp4r_linear_packed_workspace_bytes(static_cast<int>(M), static_cast<int>(N),
+                                                                          static_cast<int>(K)), "linear_packed");
     const int st = nvfp4r_linear_packed(x.data_ptr(), x.stride(0), static_cast<int>(M), static_cast<int>(K),
                                         global_scale_inv.data_ptr<float>(), packed.data_ptr(),
                                         static_cast<int>(N), static_cast<float>(alpha), out.data_ptr(),

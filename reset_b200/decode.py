@@ -312,8 +312,9 @@ class DecodeStep:
             # ReSET temperature on the full-vocabulary logits, then one draw from their softmax:
             # processor and sampler stay on the device, nothing returns to the host per token
             d = self.reset
-            capi.reset_step(full, d.states, d.params, last_ids=self.last_ids, nl_bitmap=d.nl_bitmap,
-                            dnl_bitmap=d.dnl_bitmap, decisions=d.decisions, workspace=d.workspace)
+            capi.reset_step_per_request(full, d.states, d.params_dev, last_ids=self.last_ids,
+                                        nl_bitmaps=d.nl_bitmaps, dnl_bitmaps=d.dnl_bitmaps,
+                                        n_id_sets=d.n_id_sets, decisions=d.decisions, workspace=d.workspace)
             capi.sample(full, self.draws, seed=self.sample_seed, last_ids=self.last_ids, out=self.token)
             return
         L.check(lib.nvfp4r_argmax(full.data_ptr(), full.stride(0), 1, c.vocab, self.token.data_ptr(),
@@ -353,7 +354,8 @@ class DecodeStep:
         ranks draw the same token. Call before :meth:`capture`; call again to start a new
         request (state, counters and recent ids are cleared)."""
         from .reset.logits_processor import _DeviceReset
-        self.reset = _DeviceReset(1, self.cfg.vocab, self.device, t_high, t_low, tau0, window, nl_ids, dnl_ids)
+        self.reset = _DeviceReset(1, self.cfg.vocab, self.device)
+        self.reset.set_slot(0, t_high, t_low, tau0, window, nl_ids, dnl_ids)
         self.last_ids = torch.full((1, 2), -1, dtype=torch.int32, device=self.device)
         self.draws = torch.zeros(1, dtype=torch.int64, device=self.device)
         self.sample_seed = int(seed)

@@ -8,7 +8,9 @@ import os
 GEMV_MAX_M = int(os.environ.get("NVFP4R_GEMV_MAX_M", "4"))
 GEMM_PAD_MAX_M = int(os.environ.get("NVFP4R_GEMM_PAD_MAX_M", "63"))
 ENABLE_GEMM_PATH = os.environ.get("NVFP4R_ENABLE_GEMM", "1") == "1"
-FALLBACK_BACKEND = os.environ.get("NVFP4R_FALLBACK_BACKEND", "none").lower()
+# Large-M (prefill) fallback of the adapter: "vllm-cutlass" = the installed vLLM's own NVFP4 GEMM
+# when importable (the reference's fallback branch), "none" = always this library's kernels.
+FALLBACK_BACKEND = os.environ.get("NVFP4R_FALLBACK_BACKEND", "vllm-cutlass").lower()
 
 # Measured crossover between the CUDA-core GEMV and the packed tensor-core linear on
 # B200 (L2-cold weights, CUDA-graph replay): the GEMV's shorter fixed latency wins only

@@ -85,14 +85,24 @@ def use_gemv(M: int, N: int, K: int, gemv_max_m: int) -> bool:
 
 
 _OUT_WORKSPACE: dict = {}          # device -> zeroed split-K workspace of the out= path
+_OUT_WORKSPACE_BYTES = int(__import__("os").environ.get("NVFP4R_WORKSPACE_MB", "128")) << 20
 
 
 def _out_workspace(device, nbytes: int) -> torch.Tensor:
+    """The split-K slots of ``linear_auto(..., out=)``: one buffer per device, allocated at the
+    first call with a fixed size (``NVFP4R_WORKSPACE_MB``, default 128) and never replaced, so a
+    pointer recorded in a CUDA graph stays valid. A larger request, or a first call inside a
+    stream capture, raises instead of re-allocating."""
     ws = _OUT_WORKSPACE.get(device)
-    if ws is None or ws.numel() * 8 < nbytes:
-        # grown outside any stream capture: callers warm a shape up eagerly before capturing it
-        ws = torch.zeros((max(nbytes, 1 << 20) + 7) // 8, dtype=torch.int64, device=device)
+    if ws is None:
+        if torch.cuda.is_current_stream_capturing():
+            raise RuntimeError("nvfp4r.linear_auto: the first call on a device allocates the split-K "
+                               "scratch; make it before capturing a CUDA graph")
+        ws = torch.zeros(_OUT_WORKSPACE_BYTES // 8, dtype=torch.int64, device=device)
         _OUT_WORKSPACE[device] = ws
+    if ws.numel() * 8 < nbytes:
+        raise RuntimeError(f"nvfp4r.linear_auto: this shape needs {nbytes} bytes of split-K scratch, the "
+                           f"fixed buffer holds {ws.numel() * 8}; set NVFP4R_WORKSPACE_MB before the first call")
     return ws
 
 

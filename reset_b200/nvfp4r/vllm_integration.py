@@ -15,8 +15,12 @@ Differences from the reference, all inside the dispatch:
   ``torch.ops.nvfp4r.linear_packed`` (quantize + tcgen05 block-scaled MMA over a weight
   re-laid out once per layer), for any M, written M-major: no padding to 64 rows, no
   transpose/contiguous copy.
-* There is no CUTLASS/FlashInfer fallback branch (reference :299-318): a shape the
-  kernels cannot take raises.
+* The dispatch is the operator ``torch.ops.vllm.nvfp4r_linear`` (reference :342-353) with a
+  fake implementation, so a compiled forward holds one node per linear and M is read at run
+  time.
+* The CUTLASS-class fallback (reference :299-318) is kept for M above ``gemm_pad_max_m``
+  only (prefill), through the installed vLLM's own ops; a shape the decode kernels cannot
+  take raises.
 
 For a vLLM with the NVFP4 kernel registry (``model_executor/kernels/linear/nvfp4``),
 :func:`register_with_vllm` puts :class:`Nvfp4rLinearKernel` first in that vLLM's own kernel
@@ -33,6 +37,7 @@ from .. import capi
 from . import _config
 
 _OUT_DTYPE_INT = {torch.bfloat16: 0, torch.float16: 1, torch.float32: 2}
+_OUT_DTYPES = {0: torch.bfloat16, 1: torch.float16, 2: torch.float32}
 
 
 def _unswizzle_blockscale(sw_u8: torch.Tensor, M: int, K: int) -> torch.Tensor:
@@ -75,14 +80,46 @@ def prime_nvfp4r_caches(layer: torch.nn.Module) -> None:
     layer._nvfp4r_caches_primed = True
 
 
-def nvfp4r_linear(x_2d: torch.Tensor, weight: torch.Tensor, weight_scale_flat_3d: torch.Tensor,
-                  weight_packed: Optional[torch.Tensor], input_global_scale_inv: torch.Tensor,
-                  alpha_host: float, output_size: int, gemv_max_m: int, out_dtype_int: int,
-                  enable_gemm: bool) -> torch.Tensor:
-    """All M-dependent branching of one linear (reference ``_nvfp4r_linear_impl``,
-    :165-318). Returns ``[M, output_size]`` in the requested dtype."""
+def _fallback_available() -> bool:
+    """True when a large-M library GEMM can be called (the reference's CUTLASS-class
+    fallback, :299-318): vLLM's own NVFP4 ops are importable and not switched off."""
+    if _config.FALLBACK_BACKEND == "none":
+        return False
+    try:
+        import vllm._custom_ops as vops
+    except ImportError:
+        return False
+    return hasattr(vops, "cutlass_scaled_fp4_mm") and hasattr(vops, "scaled_fp4_quant")
+
+
+def _nvfp4r_linear_impl(x_2d: torch.Tensor, weight: torch.Tensor, weight_scale_swizzled: torch.Tensor,
+                        weight_scale_flat_3d: torch.Tensor, input_global_scale_inv: torch.Tensor,
+                        alpha: torch.Tensor, alpha_host: float, output_size: int,
+                        weights_padding_cols: int, gemv_max_m: int, out_dtype_int: int,
+                        enable_gemm: bool, weight_packed: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """All M-dependent branching of one linear, inside ONE opaque operator (reference
+    ``_nvfp4r_linear_impl``, :165-318; the first twelve arguments are the reference's, in its
+    order; ``weight_packed`` is this build's re-laid-out weight). Dynamo sees a single
+    ``vllm::nvfp4r_linear`` node whatever M is, so the branch is taken at run time with the
+    concrete M of the call (per captured batch size under vLLM's piecewise CUDA graphs), not
+    frozen at trace time. Returns ``[M, output_size]``.
+
+    * decode sizes: ONE launch, quantizer fused - the CUDA-core GEMV below the measured
+      crossover, the tcgen05 kernel over the packed weight above it;
+    * M above ``gemm_pad_max_m`` (prefill): vLLM's own ``scaled_fp4_quant`` +
+      ``cutlass_scaled_fp4_mm`` when that vLLM is importable and ``fallback_backend`` is not
+      ``none`` (the reference's fallback branch), else this library's kernels in launches of
+      32 rows, each of which streams the weight once.
+    """
     from .ops import use_gemv
     M, K = x_2d.shape
+    if weights_padding_cols != 0:
+        raise RuntimeError("nvfp4r: K-padded weights are not supported")
+    if M > _config.GEMM_PAD_MAX_M and _fallback_available():
+        import vllm._custom_ops as vops
+        x_fp4, x_sf = vops.scaled_fp4_quant(x_2d, input_global_scale_inv, is_sf_swizzled_layout=True)
+        out_dtype = {0: torch.bfloat16, 1: torch.float16}.get(out_dtype_int, x_2d.dtype)
+        return vops.cutlass_scaled_fp4_mm(x_fp4, weight, x_sf, weight_scale_swizzled, alpha, out_dtype)
     tc_ok = enable_gemm and weight_packed is not None
     if tc_ok and not use_gemv(M, output_size, K, gemv_max_m):
         return torch.ops.nvfp4r.linear_packed(x_2d, input_global_scale_inv, weight_packed,
@@ -96,19 +133,59 @@ def nvfp4r_linear(x_2d: torch.Tensor, weight: torch.Tensor, weight_scale_flat_3d
     return torch.cat(parts, dim=0)
 
 
+def _nvfp4r_linear_fake(x_2d: torch.Tensor, weight: torch.Tensor, weight_scale_swizzled: torch.Tensor,
+                        weight_scale_flat_3d: torch.Tensor, input_global_scale_inv: torch.Tensor,
+                        alpha: torch.Tensor, alpha_host: float, output_size: int,
+                        weights_padding_cols: int, gemv_max_m: int, out_dtype_int: int,
+                        enable_gemm: bool, weight_packed: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Shape and dtype of the result for tracing (reference ``_nvfp4r_linear_fake``, :321-339)."""
+    return torch.empty((x_2d.shape[0], output_size), dtype=_OUT_DTYPES[out_dtype_int],
+                       device=x_2d.device)
+
+
+def _register_ops_once() -> None:
+    """Define ``torch.ops.vllm.nvfp4r_linear`` with its fake, once per process (reference
+    :342-353). vLLM's ``direct_register_custom_op`` when that vLLM is importable, else the
+    same registration through ``torch.library`` so the adapter works without vLLM."""
+    try:
+        if hasattr(torch.ops.vllm, "nvfp4r_linear"):
+            return
+    except (AttributeError, RuntimeError):
+        pass
+    try:
+        from vllm.utils.torch_utils import direct_register_custom_op
+    except ImportError:
+        direct_register_custom_op = None
+    if direct_register_custom_op is not None:
+        direct_register_custom_op(op_name="nvfp4r_linear", op_func=_nvfp4r_linear_impl,
+                                  mutates_args=[], fake_impl=_nvfp4r_linear_fake,
+                                  dispatch_key="CUDA")
+        return
+    global _VLLM_FRAGMENT
+    _VLLM_FRAGMENT = torch.library.Library("vllm", "FRAGMENT")
+    schema = torch.library.infer_schema(_nvfp4r_linear_impl, mutates_args=[])
+    _VLLM_FRAGMENT.define("nvfp4r_linear" + schema)
+    _VLLM_FRAGMENT.impl("nvfp4r_linear", _nvfp4r_linear_impl, "CUDA")
+    _VLLM_FRAGMENT._register_fake("nvfp4r_linear", _nvfp4r_linear_fake)
+
+
+_VLLM_FRAGMENT = None
+_register_ops_once()
+
+
 def apply_nvfp4r_linear(layer: torch.nn.Module, x: torch.Tensor,
                         bias: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """Hot path (reference :448-496). Reads only tensors and constant Python
-    attributes of ``layer``: no ``.item()``, no ``setattr``, no environment reads."""
+    """Hot path (reference :448-496): one ``vllm::nvfp4r_linear`` node per linear. Reads only
+    tensors and constant Python attributes of ``layer``: no ``.item()``, no ``setattr``, no
+    environment reads, no branch on M, so it traces under ``torch.compile(fullgraph=True)``."""
     output_size = layer.output_size_per_partition
-    if getattr(layer, "weights_padding_cols", 0) != 0:
-        raise RuntimeError("nvfp4r: K-padded weights are not supported (no fallback backend)")
     output_shape = (*x.shape[:-1], output_size)
     x_2d = x.reshape(-1, x.shape[-1])
-    out = nvfp4r_linear(x_2d, layer.weight, layer._nvfp4r_weight_scale_flat_3d,
-                        layer._nvfp4r_weight_packed, layer.input_global_scale_inv,
-                        layer._nvfp4r_alpha_host, output_size, _config.GEMV_MAX_M,
-                        _OUT_DTYPE_INT[x.dtype], _config.ENABLE_GEMM_PATH)
+    out = torch.ops.vllm.nvfp4r_linear(
+        x_2d, layer.weight, layer.weight_scale, layer._nvfp4r_weight_scale_flat_3d,
+        layer.input_global_scale_inv, layer.alpha, layer._nvfp4r_alpha_host, output_size,
+        getattr(layer, "weights_padding_cols", 0), _config.GEMV_MAX_M, _OUT_DTYPE_INT[x.dtype],
+        _config.ENABLE_GEMM_PATH, layer._nvfp4r_weight_packed)
     if bias is not None:
         out = out + bias
     return out.view(*output_shape)

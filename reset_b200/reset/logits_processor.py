@@ -4,7 +4,8 @@ Mirror of reset/reset/logits_processor.py of the reference. Per token with entro
 H_t: T_t = T_low if H_t < tau_t else T_high, with tau_t = tau_0 while the step
 entropy H_step is not above the running mean H_bar, and tau_t = H_step otherwise
 (reference :1-13). Here the entropy, the per-request bookkeeping, the decision and
-the temperature scaling run in three small stream-ordered kernels with the state
+the temperature scaling run in ONE kernel launch per step for the whole batch (three
+stream-ordered launches for shapes the single launch does not take) with the state
 resident on the GPU, so there is no device->host synchronisation per token
 (the reference calls ``.item()`` for every request and token, :36).
 
@@ -75,21 +76,79 @@ def _bitmap(ids: Iterable[int], vocab: int, device) -> Optional[torch.Tensor]:
     return torch.tensor(signed, dtype=torch.int32, device=device)
 
 
-class _DeviceReset:
-    """Device-side storage shared by the request- and batch-level front ends."""
+_PARAM_BYTES = C.sizeof(_lib.ResetParams)
+_MAX_ID_SETS = 8
 
-    def __init__(self, slots: int, vocab: int, device, t_high: float, t_low: float, tau0: float,
-                 window: int, nl_ids: Sequence[int], dnl_ids: Sequence[int]):
-        if not 1 <= int(window) <= _lib.RESET_MAX_WINDOW:
-            raise ValueError(f"window must be in 1..{_lib.RESET_MAX_WINDOW}")
+
+class _DeviceReset:
+    """Device-side storage shared by the request- and batch-level front ends: one state record,
+    one decision record and one hyper-parameter record per slot, and up to ``_MAX_ID_SETS``
+    distinct (newline ids, double-newline ids) bitmap pairs that the records refer to."""
+
+    def __init__(self, slots: int, vocab: int, device, pin: bool = False):
         self.device = torch.device(device)
         self.vocab = int(vocab)
-        self.params = _lib.ResetParams(float(t_high), float(t_low), float(tau0), int(window), 0)
+        self.slots = int(slots)
+        self.words = (self.vocab + 31) // 32
         self.states = torch.zeros(slots * _STATE_BYTES, dtype=torch.uint8, device=self.device)
         self.decisions = torch.zeros(slots * _DECISION_BYTES, dtype=torch.uint8, device=self.device)
         self.workspace = capi.reset_workspace(slots, self.device)
-        self.nl_bitmap = _bitmap(nl_ids, self.vocab, self.device)
-        self.dnl_bitmap = _bitmap(dnl_ids, self.vocab, self.device)
+        self.params_host = torch.zeros(slots * _PARAM_BYTES, dtype=torch.uint8, pin_memory=pin)
+        self.params_dev = torch.zeros(slots * _PARAM_BYTES, dtype=torch.uint8, device=self.device)
+        self.nl_bitmaps = torch.zeros(_MAX_ID_SETS * self.words, dtype=torch.int32, device=self.device)
+        self.dnl_bitmaps = torch.zeros(_MAX_ID_SETS * self.words, dtype=torch.int32, device=self.device)
+        self._id_sets: dict = {}
+        self.slot_record: dict[int, _lib.ResetParams] = {}
+
+    def _id_set(self, nl_ids, dnl_ids) -> int:
+        key = (frozenset(int(i) for i in nl_ids), frozenset(int(i) for i in dnl_ids))
+        idx = self._id_sets.get(key)
+        if idx is None:
+            idx = len(self._id_sets)
+            if idx >= _MAX_ID_SETS:
+                raise ValueError(f"more than {_MAX_ID_SETS} distinct newline-id sets in one processor")
+            for store, ids in ((self.nl_bitmaps, key[0]), (self.dnl_bitmaps, key[1])):
+                bm = _bitmap(ids, self.vocab, self.device)
+                if bm is not None:
+                    store[idx * self.words:(idx + 1) * self.words].copy_(bm)
+            self._id_sets[key] = idx
+        return idx
+
+    @property
+    def n_id_sets(self) -> int:
+        return len(self._id_sets)
+
+    def set_slot(self, slot: int, t_high: float, t_low: float, tau0: float, window: int,
+                 nl_ids: Sequence[int], dnl_ids: Sequence[int]) -> _lib.ResetParams:
+        """Start a request in ``slot``: zero its state and write ITS hyper-parameters
+        (reference: one ``ReSETRequest`` per request from its own ``extra_args``, :144-155)."""
+        if not 1 <= int(window) <= _lib.RESET_MAX_WINDOW:
+            raise ValueError(f"window must be in 1..{_lib.RESET_MAX_WINDOW}")
+        rec = _lib.ResetParams(float(t_high), float(t_low), float(tau0), int(window),
+                               self._id_set(nl_ids, dnl_ids))
+        lo, hi = slot * _PARAM_BYTES, (slot + 1) * _PARAM_BYTES
+        self.params_host[lo:hi] = torch.frombuffer(bytearray(bytes(rec)), dtype=torch.uint8)
+        self.params_dev[lo:hi].copy_(self.params_host[lo:hi], non_blocking=True)
+        self.slot_record[slot] = rec
+        self.clear_slot(slot)
+        return rec
+
+    def move_slot(self, a: int, b: int, swap: bool) -> None:
+        """Request in slot ``a`` moves to ``b`` (or the two trade places): state and parameters."""
+        for buf, n in ((self.states, _STATE_BYTES), (self.params_dev, _PARAM_BYTES),
+                       (self.params_host, _PARAM_BYTES)):
+            sa, sb = buf[a * n:(a + 1) * n], buf[b * n:(b + 1) * n]
+            if swap:
+                tmp = sb.clone()
+                sb.copy_(sa)
+                sa.copy_(tmp)
+            else:
+                sb.copy_(sa)
+        ra, rb = self.slot_record.pop(a, None), self.slot_record.pop(b, None)
+        if ra is not None:
+            self.slot_record[b] = ra
+        if swap and rb is not None:
+            self.slot_record[a] = rb
 
     def clear_slot(self, slot: int) -> None:
         self.states[slot * _STATE_BYTES:(slot + 1) * _STATE_BYTES].zero_()
@@ -110,8 +169,8 @@ class ReSETRequest:
 
     def __call__(self, output_ids, logits: torch.Tensor) -> torch.Tensor:
         if self._dev is None:
-            self._dev = _DeviceReset(1, logits.shape[-1], logits.device, self.t_high, self.t_low,
-                                     self.tau_raw, self.window, self.nl_ids, self.dnl_ids)
+            self._dev = _DeviceReset(1, logits.shape[-1], logits.device)
+            self._dev.set_slot(0, self.t_high, self.t_low, self.tau_raw, self.window, self.nl_ids, self.dnl_ids)
             self._last = torch.empty((1, 2), dtype=torch.int32, device=logits.device)
         n = len(output_ids)
         host = torch.tensor([[output_ids[-2] if n >= 2 else -1, output_ids[-1] if n >= 1 else -1]],
@@ -119,8 +178,9 @@ class ReSETRequest:
         self._last.copy_(host, non_blocking=True)
         out = logits.to(torch.float32, copy=True).unsqueeze(0)
         d = self._dev
-        capi.reset_step(out, d.states, d.params, last_ids=self._last, nl_bitmap=d.nl_bitmap,
-                        dnl_bitmap=d.dnl_bitmap, decisions=d.decisions, workspace=d.workspace)
+        capi.reset_step_per_request(out, d.states, d.params_dev, last_ids=self._last,
+                                    nl_bitmaps=d.nl_bitmaps, dnl_bitmaps=d.dnl_bitmaps, n_id_sets=d.n_id_sets,
+                                    decisions=d.decisions, workspace=d.workspace)
         return out[0].to(logits.dtype)
 
     def last_decision(self) -> dict:
@@ -137,8 +197,9 @@ class ReSETBatchProcessor:
     fused ReSET step for the whole batch. Requests opt in through
     ``SamplingParams.extra_args`` with the reference's keys (:144-155): ``reset``,
     ``t_high``, ``t_low``, ``tau_0``, ``window``, ``reset_nl_ids``, ``reset_dnl_ids``.
-    The temperatures, window and id sets of the first opted-in request apply to the
-    batch (they are per model and task in the reference, configs/hparams.json)."""
+    Every request keeps its OWN values, as in the reference: they are written into the
+    request's slot on the device when the request is admitted, and the kernel reads the
+    record of each row's slot."""
 
     def __init__(self, vllm_config=None, device="cuda", is_pin_memory: bool = False,
                  max_num_reqs: Optional[int] = None, vocab_size: Optional[int] = None):
@@ -159,12 +220,11 @@ class ReSETBatchProcessor:
     def is_argmax_invariant(self) -> bool:
         return False
 
-    def _ensure(self, ea: dict) -> None:
+    def _admit(self, idx: int, ea: dict) -> None:
         if self._dev is None:
-            self._dev = _DeviceReset(self.max_reqs, self.vocab, self.device, float(ea["t_high"]),
-                                     float(ea["t_low"]), float(ea.get("tau_0", 0.6349)),
-                                     int(ea.get("window", 32)), ea.get("reset_nl_ids", []),
-                                     ea.get("reset_dnl_ids", []))
+            self._dev = _DeviceReset(self.max_reqs, self.vocab, self.device, pin=self.pin)
+        self._dev.set_slot(idx, float(ea["t_high"]), float(ea["t_low"]), float(ea.get("tau_0", 0.6349)),
+                           int(ea.get("window", 32)), ea.get("reset_nl_ids", []), ea.get("reset_dnl_ids", []))
 
     def update_state(self, batch_update) -> None:
         if batch_update is not None:
@@ -174,10 +234,9 @@ class ReSETBatchProcessor:
             for idx, params, _prompt, out_ids in batch_update.added:
                 ea = getattr(params, "extra_args", None) or {}
                 if ea.get("reset"):
-                    self._ensure(ea)
+                    self._admit(idx, ea)
                     self._outputs[idx] = out_ids
                     self._slots_host[idx] = idx
-                    self._dev.clear_slot(idx)
                 else:
                     self._outputs.pop(idx, None)
                     self._slots_host[idx] = -1
@@ -193,16 +252,8 @@ class ReSETBatchProcessor:
             self._last_dev.copy_(self._last_host, non_blocking=True)
 
     def _move(self, a: int, b: int, swap: bool) -> None:
-        d = self._dev
-        if d is not None:
-            sa = d.states[a * _STATE_BYTES:(a + 1) * _STATE_BYTES]
-            sb = d.states[b * _STATE_BYTES:(b + 1) * _STATE_BYTES]
-            if swap:
-                tmp = sb.clone()
-                sb.copy_(sa)
-                sa.copy_(tmp)
-            else:
-                sb.copy_(sa)
+        if self._dev is not None:
+            self._dev.move_slot(a, b, swap)
         oa, ob = self._outputs.pop(a, None), self._outputs.pop(b, None)
         if oa is not None:
             self._outputs[b] = oa
@@ -218,9 +269,10 @@ class ReSETBatchProcessor:
         B = logits.shape[0]
         d = self._dev
         work = logits if logits.dtype == torch.float32 else logits.float()
-        capi.reset_step(work, d.states, d.params, state_slots=self._slots_dev[:B],
-                        last_ids=self._last_dev[:B], nl_bitmap=d.nl_bitmap, dnl_bitmap=d.dnl_bitmap,
-                        decisions=d.decisions, workspace=d.workspace)
+        capi.reset_step_per_request(work, d.states, d.params_dev, state_slots=self._slots_dev[:B],
+                                    last_ids=self._last_dev[:B], nl_bitmaps=d.nl_bitmaps,
+                                    dnl_bitmaps=d.dnl_bitmaps, n_id_sets=d.n_id_sets,
+                                    decisions=d.decisions, workspace=d.workspace)
         if work is not logits:
             logits.copy_(work)
         return logits

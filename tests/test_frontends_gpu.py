@@ -105,6 +105,49 @@ def test_batch_processor_matches_per_request_oracle():
         proc.update_state(None)
 
 
+def test_batch_processor_keeps_each_requests_own_parameters():
+    """Three requests with three different (t_high, t_low, tau_0, window) and two different
+    newline-id sets in one batch, each against its own oracle policy: the reference builds one
+    ReSETRequest per request from that request's extra_args
+    (reset/reset/logits_processor.py:144-155)."""
+    from reset_b200.reset import ReSETBatchProcessor
+    V = 4096
+    cfgs = {0: dict(t_high=1.0, t_low=0.5, tau_0=6.0, window=4, nl=[], dnl=[17]),
+            1: dict(t_high=0.9, t_low=0.2, tau_0=5.2, window=16, nl=[23], dnl=[29]),
+            2: dict(t_high=1.0, t_low=0.1, tau_0=6.6, window=32, nl=[], dnl=[17])}
+    proc = ReSETBatchProcessor(device="cuda", max_num_reqs=4, vocab_size=V)
+    outs = {r: [] for r in cfgs}
+    pols = {r: orp.ResetPolicy(c["t_high"], c["t_low"], c["tau_0"], c["window"], frozenset(c["nl"]),
+                               frozenset(c["dnl"])) for r, c in cfgs.items()}
+    proc.update_state(BatchUpdate(removed=[], moved=[], added=[
+        (r, SimpleNamespace(extra_args={"reset": True, "t_high": c["t_high"], "t_low": c["t_low"],
+                                        "tau_0": c["tau_0"], "window": c["window"],
+                                        "reset_nl_ids": c["nl"], "reset_dnl_ids": c["dnl"]}), [1], outs[r])
+        for r, c in cfgs.items()]))
+    rng = np.random.default_rng(11)
+    seen = {r: set() for r in cfgs}
+    checked = 0
+    for t in range(60):
+        logits = orp.synthetic_logits(3, V, 5000 + t, sigma=2.0)
+        dev = logits.cuda()
+        proc.apply(dev)
+        res = dev.cpu()
+        for r, c in cfgs.items():
+            want, d = pols[r](list(outs[r]), logits[r])
+            seen[r].add(d.temp)
+            if not _near_tie(d, c["tau_0"]):
+                assert torch.equal(res[r], want), (t, r)
+                checked += 1
+        for r, c in cfgs.items():
+            u = rng.random()
+            nxt = c["dnl"][0] if u < 0.1 else (c["nl"][0] if c["nl"] and u < 0.4 else int(rng.integers(40, V)))
+            outs[r].append(nxt)
+        proc.update_state(None)
+    assert checked >= 150
+    for r, c in cfgs.items():                            # every request used both of ITS temperatures
+        assert seen[r] == {c["t_high"], c["t_low"]}, (r, seen[r])
+
+
 def _fake_layer(N, K, seed, alpha=0.37, gs_inv=55.0, swizzled=True):
     from reset_b200 import capi
     w, ws = onv.random_nvfp4((N,), K, seed=seed)
@@ -212,3 +255,82 @@ def test_kernel_class_selected_by_the_installed_vllm_and_agrees_with_its_cutlass
             # same codes and scales on both sides (the quantizers are bit-identical in this mode),
             # fp32 accumulation in different orders, one bf16 rounding each
             assert rel_l2(y.float().cpu().numpy(), z.float().cpu().numpy()) <= 8e-3
+
+
+def test_dispatch_is_one_registered_operator_with_a_fake():
+    """`torch.ops.vllm.nvfp4r_linear` exists with the reference's argument list
+    (kernels/python/nvfp4r/vllm_integration.py:165-178,342-353) and traces on fake tensors."""
+    from torch._subclasses.fake_tensor import FakeTensorMode
+    from reset_b200.nvfp4r import vllm_integration as vi  # noqa: F401  (registers the op)
+    schema = str(torch.ops.vllm.nvfp4r_linear.default._schema)
+    for name in ("x_2d", "weight", "weight_scale_swizzled", "weight_scale_flat_3d", "input_global_scale_inv",
+                 "alpha", "alpha_host", "output_size", "weights_padding_cols", "gemv_max_m", "out_dtype_int",
+                 "enable_gemm"):
+        assert name in schema
+    layer, _, _ = _fake_layer(512, 1024, seed=2)
+    vi.prime_nvfp4r_caches(layer)
+    with FakeTensorMode(allow_non_fake_inputs=True):
+        x = torch.empty((7, 1024), dtype=torch.bfloat16, device="cuda")
+        y = vi.apply_nvfp4r_linear(layer, x)
+    assert tuple(y.shape) == (7, 512) and y.dtype == torch.bfloat16
+
+
+@pytest.mark.parametrize("N,K", [(4096, 1024), (6144, 4096)])
+def test_adapter_compiles_fullgraph_and_replays_in_a_cuda_graph(N, K):
+    """`apply_nvfp4r_linear` under torch.compile(fullgraph=True) is one opaque node whose M
+    branch is taken at run time: the same compiled function serves M = 1 and M = 8 (each on
+    its own side of the crossover) and equals the eager call bit for bit; the compiled call
+    then replays inside a CUDA graph."""
+    from reset_b200.nvfp4r import vllm_integration as vi
+    layer, w, ws = _fake_layer(N, K, seed=31)
+    vi.prime_nvfp4r_caches(layer)
+
+    def forward(x):
+        return vi.apply_nvfp4r_linear(layer, x)
+
+    compiled = torch.compile(forward, fullgraph=True, backend="aot_eager", dynamic=True)
+    xs = {M: make_activation(M, K, seed=40 + M).cuda() for M in (1, 8, 3)}
+    for M in (1, 8, 3):
+        eager = forward(xs[M])
+        got = compiled(xs[M])
+        torch.cuda.synchronize()
+        assert tuple(got.shape) == (M, N) and torch.equal(got, eager)
+    static_x = xs[8].clone()
+    s = torch.cuda.Stream()
+    with torch.cuda.stream(s):
+        compiled(static_x)
+        s.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=s):
+            static_y = compiled(static_x)
+    for seed in (50, 51):
+        fresh = make_activation(8, K, seed=seed).cuda()
+        static_x.copy_(fresh)
+        g.replay()
+        torch.cuda.synchronize()
+        assert torch.equal(static_y, forward(fresh))
+
+
+@pytest.mark.parametrize("fallback", ["vllm-cutlass", "none"])
+def test_adapter_prefill_sized_batch(fallback):
+    """M above gemm_pad_max_m: the installed vLLM's own NVFP4 GEMM when it is importable and
+    not switched off (the reference's fallback branch, vllm_integration.py:299-318), else this
+    library's kernels in launches of 32 rows. Both agree with the oracle."""
+    from reset_b200 import _lib, capi, nvfp4r
+    from reset_b200.nvfp4r import vllm_integration as vi
+    N, K, M = 1024, 2048, 100
+    layer, w, ws = _fake_layer(N, K, seed=61)
+    vi.prime_nvfp4r_caches(layer)
+    saved = nvfp4r.status()["fallback_backend"]
+    nvfp4r.configure(fallback_backend=fallback)
+    try:
+        if fallback != "none" and not vi._fallback_available():
+            pytest.skip("vLLM's NVFP4 ops are not importable here")
+        x = make_activation(M, K, seed=62).cuda()
+        y = vi.apply_nvfp4r_linear(layer, x)
+    finally:
+        nvfp4r.configure(fallback_backend=saved)
+    codes, scales = capi.quant(x, layer.input_global_scale_inv, rcp_mode=_lib.RCP_APPROX)
+    exact = onv.linear_f64(w, ws, codes.cpu().numpy(), scales.cpu().numpy(), alpha=0.37)
+    assert tuple(y.shape) == (M, N)
+    assert rel_l2(y.float().cpu().numpy(), exact) <= 8e-3               # bf16 output rounding

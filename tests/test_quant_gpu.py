@@ -137,3 +137,39 @@ def test_quant_approx_mode_vs_exact_and_vllm(capi):
     n_code = np.count_nonzero(onv.unpack_codes(vc) != onv.unpack_codes(ca))
     print(f"vs vLLM CUDA op: {n_sf} scale and {n_code} code mismatches of {M * K}")
     assert n_sf == 0 and n_code == 0
+
+
+@pytest.mark.parametrize("K", [4096, 12288, 5120, 8192, 17408, 25600, 3200, 640])
+@pytest.mark.parametrize("M", [1, 2, 4, 8])
+def test_quant_approx_mode_is_the_installed_vllm_op_on_every_decode_shape(capi, M, K):
+    """APPROX is the mode the adapter and the fused linears run in. Codes and scales against
+    the installed vLLM's CUDA ``scaled_fp4_quant`` (the op the reference calls,
+    kernels/python/nvfp4r/vllm_integration.py:213), bit for bit, for every K of the Qwen3-8B /
+    14B / 32B decode linears (and the TP-8 shards with K % 256 != 0) at M = 1, 2, 4, 8, in the
+    flat and in the swizzled scale layout."""
+    from reset_b200 import _lib
+    try:
+        import vllm._custom_ops as vops
+    except Exception as exc:
+        pytest.skip(f"vLLM is not importable here: {exc!r}")
+    x = make_activation(M, K, seed=1000 + M + K)
+    gs_inv = _gs_inv(x)
+    gs = torch.tensor([gs_inv], dtype=torch.float32, device="cuda")
+    ca, sa = _quant(capi, x, gs_inv, rcp_mode=_lib.RCP_APPROX)
+    try:
+        vc, vs = vops.scaled_fp4_quant(x.cuda(), gs, is_sf_swizzled_layout=False)
+        vcs, vss = vops.scaled_fp4_quant(x.cuda(), gs, is_sf_swizzled_layout=True)
+        torch.cuda.synchronize()
+    except Exception as exc:
+        pytest.skip(f"vLLM CUDA quantizer not usable here: {exc!r}")
+    vc = vc.view(torch.uint8).cpu().numpy()
+    vs = vs.view(torch.uint8).cpu().numpy().reshape(M, -1)[:, : K // 16]
+    assert np.array_equal(vs, sa), "scales differ from vLLM's"
+    assert np.array_equal(onv.unpack_codes(vc), onv.unpack_codes(ca)), "codes differ from vLLM's"
+    # swizzled layout: same codes; the scale bytes of the M real rows sit where vLLM puts them
+    cs, ss = capi.quant(x.cuda(), gs, swizzled=True, rcp_mode=_lib.RCP_APPROX)
+    torch.cuda.synchronize()
+    assert np.array_equal(cs.cpu().numpy(), vcs.view(torch.uint8).cpu().numpy())
+    ours_flat = capi.unswizzle_blockscale(ss, M, K).cpu().numpy()
+    vllm_flat = capi.unswizzle_blockscale(vss.view(torch.uint8).reshape(-1).contiguous(), M, K).cpu().numpy()
+    assert np.array_equal(ours_flat, sa) and np.array_equal(vllm_flat, sa)

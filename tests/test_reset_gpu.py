@@ -130,6 +130,78 @@ def test_reset_decode_loop_full_vocab(capi):
     assert mism <= ties
 
 
+def test_reset_decode_loop_as_the_benchmark_config_states_it(capi):
+    """The decode-loop configuration at full length: vocab 151936, 4096 steps, batch sizes 1, 2,
+    4 and 8 (each its own grid of the single-launch kernel), fp32 logits N(0, 3) with one token
+    per row at +12, a delimiter id every 40-120 tokens, t_high 1.0, t_low 0.1, tau0 0.5505,
+    window 32. Per step and row: (entropy, H_step, H_bar, temperature, boundary) against the
+    oracle policy and the scaled logits bit for bit. The batch of size b is rows 0..b-1 of the
+    step's logits, so one oracle evaluation per row serves all four batch sizes."""
+    from reset_b200 import _lib
+    V, steps, BMAX = 151936, 4096, 8
+    t_high, t_low, tau0, window = 1.0, 0.1, 0.5505, 32
+    sizes = (1, 2, 4, 8)
+    delim = V - 5
+    streams = [orp.synthetic_token_stream(steps, delim, V, 77 + 10 * b) for b in range(BMAX)]
+    pols = [orp.ResetPolicy(t_high, t_low, tau0, window, frozenset(), frozenset([delim])) for _ in range(BMAX)]
+    dnl_bm = _bitmap([delim], V)
+    params = _lib.ResetParams(t_high, t_low, tau0, window, 0)
+    dec_dtype = np.dtype([("entropy", "f8"), ("h_step", "f8"), ("h_bar", "f8"), ("temp", "f8"),
+                          ("boundary", "i4"), ("high", "i4")])
+    run = {B: dict(states=torch.zeros(B * C.sizeof(_lib.ResetState), dtype=torch.uint8, device="cuda"),
+                   dec=torch.zeros(B * C.sizeof(_lib.ResetDecision), dtype=torch.uint8, device="cuda"),
+                   ws=capi.reset_workspace(B, "cuda")) for B in sizes}
+    gen = torch.Generator(device="cuda").manual_seed(2024)
+    ties = mism = low_steps = boundaries = 0
+    max_ent_err = 0.0
+    last = np.full((BMAX, 2), -1, dtype=np.int32)
+    for t in range(steps):
+        dev_in = torch.randn(BMAX, V, generator=gen, device="cuda", dtype=torch.float32) * 3.0
+        peak = torch.randint(0, V, (BMAX,), generator=gen, device="cuda")
+        dev_in[torch.arange(BMAX, device="cuda"), peak] += 12.0
+        logits = dev_in.cpu()                               # the same bytes go to the oracle
+        for b in range(BMAX):
+            last[b, 1] = streams[b][t - 1] if t >= 1 else -1
+            last[b, 0] = streams[b][t - 2] if t >= 2 else -1
+        last_dev = torch.from_numpy(last).cuda()
+        outs = {}
+        for B in sizes:
+            r = run[B]
+            outs[B] = dev_in[:B].clone()
+            capi.reset_step(outs[B], r["states"], params, last_ids=last_dev[:B], dnl_bitmap=dnl_bm,
+                            decisions=r["dec"], workspace=r["ws"])
+        decs = {B: np.frombuffer(run[B]["dec"].cpu().numpy().tobytes(), dtype=dec_dtype) for B in sizes}
+        for b in range(BMAX):
+            d = pols[b].decide(pols[b].is_boundary(streams[b][max(0, t - 2):t].tolist()), orp.token_entropy(logits[b]))
+            thr = d.h_step if d.high_step else tau0
+            near_tie = abs(d.entropy - thr) < TIE_BAND or abs(d.h_step - d.h_bar) < TIE_BAND
+            ties += near_tie
+            low_steps += d.temp != 1.0
+            boundaries += d.boundary
+            want = None
+            for B in sizes:
+                if b >= B:
+                    continue
+                g = decs[B][b]
+                assert bool(g["boundary"]) == d.boundary, (t, B, b)
+                max_ent_err = max(max_ent_err, abs(g["entropy"] - d.entropy))
+                assert abs(g["entropy"] - d.entropy) <= 1e-4, (t, B, b)
+                assert abs(g["h_step"] - d.h_step) <= 1e-4 and abs(g["h_bar"] - d.h_bar) <= 1e-4, (t, B, b)
+                if g["temp"] != d.temp:
+                    assert near_tie, (t, B, b, g, d)
+                    mism += 1
+                elif d.temp == 1.0:
+                    assert torch.equal(outs[B][b], dev_in[b]), (t, B, b)    # x / 1: left untouched
+                else:
+                    if want is None:
+                        want = orp.apply_temperature(logits[b], d.temp)
+                    assert torch.equal(outs[B][b].cpu(), want), (t, B, b)
+    print(f"4096 steps: near-ties {ties}, mismatches inside the band {mism}, steps at t_low {low_steps}, "
+          f"boundaries {boundaries}, max |dH| vs the reference's fp32 value {max_ent_err:.2e}")
+    assert mism <= ties
+    assert boundaries >= BMAX * steps // 130
+
+
 def test_reset_decode_loop_small_vocab_both_regimes(capi):
     """tau0 near the entropy level so both temperatures occur; short window; the
     two-newline boundary rule is exercised."""
