@@ -43,9 +43,10 @@ M_VALUES = (1, 2, 4, 8)
 HIDDEN = 4096
 WEIGHT_COPIES = 12
 FALLBACK_HBM_GBS = 6650.0
-# dram__bytes_read.sum + dram__bytes_write.sum per launch, averaged over the launches of a
-# step, from the ncu launch list summarised in profiles/bench_step_launch_list.md
-# (algorithmic bytes per launch: 27.1 MB)
+# dram__bytes_read.sum + dram__bytes_write.sum per launch, averaged over the 16 launches of a
+# single-GPU step (an ncu capture of this program's --case launches; algorithmic bytes per
+# launch: 27.1 MB). Reported at N = 1 only: a tensor-parallel launch moves 1/N of the bytes
+# and has not been captured.
 NCU_TRAFFIC_BYTES_PER_LAUNCH = 27.4e6
 
 
@@ -102,6 +103,62 @@ class ClockSampler:
         return {"sm_mhz": sm[len(sm) // 2] if sm else None,
                 "sm_max_mhz": int(rows[0][1]) if rows and rows[0][1].isdigit() else None,
                 "samples": len(sm), "reasons": reasons}
+
+
+# The shapes the bandwidth target is stated on: Qwen3-32B decode linears at M = 1 (N, K).
+QWEN3_32B_LINEARS = [("qkv_proj", 10240, 5120), ("o_proj", 5120, 8192),
+                     ("gate_up_proj", 51200, 5120), ("down_proj", 5120, 25600)]
+
+
+def qwen3_32b_m1_detail(device, nvfp4r, peak: float) -> dict:
+    """us / GB/s / % of peak of each Qwen3-32B decode linear at M = 1, quantizer included, through
+    the crossover's choice of kernel; every launch reads a weight copy that has left L2 (enough
+    copies of each weight for > 600 MB between two reads of the same copy)."""
+    out = {}
+    gs = torch.tensor([100.0], dtype=torch.float32, device=device)
+    g = torch.Generator(device=device).manual_seed(4321)
+    gemv_max_m = nvfp4r.status()["gemv_max_m"]
+    side = torch.cuda.Stream(device=device)
+    for name, N, K in QWEN3_32B_LINEARS:
+        wbytes = N * K * 9 // 16
+        ncopies = max(3, -(-600_000_000 // wbytes))
+        copies = []
+        for _ in range(ncopies):
+            w = torch.randint(0, 256, (N, K // 2), dtype=torch.uint8, device=device, generator=g)
+            sc = torch.randint(1, 0x38, (N, K // 16), dtype=torch.uint8, device=device, generator=g)
+            use_gemv = nvfp4r.ops.use_gemv(1, N, K, gemv_max_m)
+            copies.append((w, sc, None) if use_gemv else (None, None, nvfp4r.pack_weight(w, sc)))
+        x = torch.randn(1, K, device=device, generator=g).to(torch.bfloat16)
+        outbuf = torch.empty((1, N), dtype=torch.bfloat16, device=device)
+        # warm-up once per copy (also sizes the split-K scratch outside the capture)
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            for w, sc, packed in copies:
+                nvfp4r.linear_auto(x, gs, w, sc, packed, N, 1.0, torch.bfloat16, out=outbuf)
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=side):
+                for _ in range(2):
+                    for w, sc, packed in copies:
+                        nvfp4r.linear_auto(x, gs, w, sc, packed, N, 1.0, torch.bfloat16, out=outbuf)
+        torch.cuda.current_stream().wait_stream(side)
+        graph.replay()
+        torch.cuda.synchronize()
+        ts = []
+        for _ in range(5):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            graph.replay()
+            e1.record()
+            torch.cuda.synchronize()
+            ts.append(e0.elapsed_time(e1) / (2 * ncopies) * 1e3)
+        us = sorted(ts)[2]
+        gbs = linear_bytes(N, K, 1) / us / 1e3
+        out[f"qwen3_32b_{name}_M1"] = {"us": round(us, 2), "kernel": "gemv" if copies[0][2] is None else "tcgen05",
+                                       "gbs": round(gbs, 1), "pct_of_peak": round(100.0 * gbs / peak, 1),
+                                       "N": N, "K": K, "weight_copies": ncopies}
+        del copies, graph
+        torch.cuda.empty_cache()
+    return out
 
 
 # --------------------------------------------------------------------------- ours
@@ -380,6 +437,8 @@ def run_ours(args, rank, world, local_rank):
     d2h_bytes = sum(M * n * 2 for _, n, k, _, _ in shards for M in M_VALUES)
     del g_res, g_e2e, shards
     torch.cuda.empty_cache()
+    target_detail = qwen3_32b_m1_detail(device, nvfp4r, measured_peak()[0]) if world == 1 else {}
+    stage(rank, "Qwen3-32B M=1 shapes timed")
     decode = None if args.no_decode else run_decode(args, rank, world, device)
     stage(rank, "decode done")
 
@@ -413,8 +472,8 @@ def run_ours(args, rank, world, local_rank):
         "roofline": {"bound": "hbm", "achieved": round(gbs / world, 1), "peak": peak, "unit": "GB/s",
                      "frac": round(gbs / world / peak, 4), "peak_kind": f"of {peak_kind}",
                      "kernel": "linear_packed_kernel / gemv_stream_kernel by measured crossover (16 launches per step)",
-                     "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH},
-        "detail_us_gbs": detail,
+                     "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH if world == 1 else None},
+        "detail_us_gbs": {**detail, **target_detail},
         "decode": decode,
     }
     if tp_check is not None:
@@ -522,20 +581,38 @@ def _graph_us(fn, reps: int, device, samples: int = 7) -> float:
     return sorted(ts)[len(ts) // 2]
 
 
-SWEEP_SHAPES = {
-    "qwen3-14b": [("qkv_proj", 7168, 5120), ("o_proj", 5120, 5120), ("gate_up_proj", 34816, 5120),
-                  ("down_proj", 5120, 17408)],
-    "qwen3-8b": [(n, N, K) for n, N, K, _ in LINEARS],
-    "qwen3-32b": [("qkv_proj", 10240, 5120), ("o_proj", 5120, 8192), ("gate_up_proj", 51200, 5120),
-                  ("down_proj", 5120, 25600)],
+SWEEP_SHAPES = {   # name, N, K, tensor-parallel style
+    "qwen3-14b": [("qkv_proj", 7168, 5120, "column"), ("o_proj", 5120, 5120, "row"),
+                  ("gate_up_proj", 34816, 5120, "column"), ("down_proj", 5120, 17408, "row")],
+    "qwen3-8b": list(LINEARS),
+    "qwen3-32b": [("qkv_proj", 10240, 5120, "column"), ("o_proj", 5120, 8192, "row"),
+                  ("gate_up_proj", 51200, 5120, "column"), ("down_proj", 5120, 25600, "row")],
 }
+
+
+def _jsonl_done(path: str) -> dict:
+    """Rows already in a sweep's JSONL file, keyed (sweep, tp, shape, M): an interrupted sweep
+    resumes where it stopped (the reference's benches do the same,
+    kernels/benchmarks/bench_e2e.py:119-134)."""
+    done = {}
+    if path and os.path.exists(path):
+        for ln in Path(path).read_text().splitlines():
+            try:
+                r = json.loads(ln)
+                done[(r["sweep"], r["tp"], r["shape"], r["M"])] = r
+            except (ValueError, KeyError):
+                continue
+    return done
 
 
 def run_sweep(args):
     """M sweep 1..16 over one model's four linear shapes: the fused
     quantize + CUDA-core GEMV, the fused quantize + tcgen05 packed linear, and, when the
     installed vLLM's operators load, its `scaled_fp4_quant` + `cutlass_scaled_fp4_mm` pair.
-    Every launch reads a weight copy that has left L2 (copies total > 1 GB)."""
+    Every launch reads a weight copy that has left L2 (copies total > 1 GB). ``--sweep-tp T``
+    times one rank's shard of every shape under T-way tensor parallelism (column-parallel: N / T,
+    row-parallel: K / T) on this one GPU; ``--jsonl PATH`` appends one line per (shape, M) and
+    skips the pairs the file already holds."""
     from reset_b200 import capi, nvfp4r
 
     device = torch.device("cuda", 0)
@@ -549,18 +626,30 @@ def run_sweep(args):
     gs = torch.tensor([100.0], dtype=torch.float32, device=device)
     alpha_t = torch.tensor([1.0], dtype=torch.float32, device=device)
     Ms = [int(m) for m in args.sweep_m.split(",")]
-    out = {"sweep": args.sweep, "unit": "us per linear incl. activation quantization", "peak_gbs": peak,
+    tp = max(1, args.sweep_tp)
+    done = _jsonl_done(args.jsonl)
+    out = {"sweep": args.sweep, "tp": tp, "unit": "us per linear incl. activation quantization", "peak_gbs": peak,
            "l2": "weight copies cycled, > 1 GB between reuses", "shapes": {}}
-    for name, N, K in SWEEP_SHAPES[args.sweep]:
-        copies = int(1.1e9 // (N * K * 9 // 16)) + 1
+    for name, N, K, style in SWEEP_SHAPES[args.sweep]:
+        N, K = (N // tp, K) if style == "column" else (N, K // tp)
+        shape_key = f"{name} ({N}x{K})"
+        if all((args.sweep, tp, shape_key, M) in done for M in Ms):
+            out["shapes"][shape_key] = {str(M): done[(args.sweep, tp, shape_key, M)]["row"] for M in Ms}
+            continue
+        copies = min(64, int(1.1e9 // (N * K * 9 // 16)) + 1)
+        packable = N % 128 == 0 and K % 128 == 0
         ws = []
         for _ in range(copies):
             w = torch.randint(0, 256, (N, K // 2), dtype=torch.uint8, device=device, generator=gen)
             s = torch.randint(1, 0x38, (N, K // 16), dtype=torch.uint8, device=device, generator=gen)
-            ws.append((w, s, capi.pack_weight(w, s), capi.swizzle_blockscale(s) if vops else None))
+            ws.append((w, s, capi.pack_weight(w, s) if packable else None,
+                       capi.swizzle_blockscale(s) if vops else None))
         wksp = capi.packed_workspace(16, N, K, device)
         rows = {}
         for M in Ms:
+            if (args.sweep, tp, shape_key, M) in done:
+                rows[str(M)] = done[(args.sweep, tp, shape_key, M)]["row"]
+                continue
             x = torch.randn(M, K, device=device, generator=gen).to(torch.bfloat16)
             o = torch.empty(M, N, dtype=torch.bfloat16, device=device)
             st = {"i": 0}
@@ -585,8 +674,9 @@ def run_sweep(args):
             r = {}
             if M <= 16:
                 r["gemv_us"] = round(_graph_us(f_gemv, 2 * copies, device), 2)
-            r["tcgen05_us"] = round(_graph_us(f_tc, 2 * copies, device), 2)
-            if vops is not None:
+            if packable:
+                r["tcgen05_us"] = round(_graph_us(f_tc, 2 * copies, device), 2)
+            if vops is not None and K % 32 == 0:
                 try:
                     r["vllm_cutlass_us"] = round(_graph_us(f_vllm, 2 * copies, device), 2)
                 except Exception as e:  # library kernel unavailable for this shape/build
@@ -594,9 +684,12 @@ def run_sweep(args):
                     torch.cuda.synchronize()
             best = min(v for k, v in r.items() if k in ("gemv_us", "tcgen05_us"))
             r["best_pct_of_peak"] = round(100.0 * linear_bytes(N, K, M) / best / 1e3 / peak, 1)
-            r["chosen"] = "gemv" if nvfp4r.ops.use_gemv(M, N, K, nvfp4r.status()["gemv_max_m"]) else "tcgen05"
+            r["chosen"] = "gemv" if (not packable or nvfp4r.ops.use_gemv(M, N, K, nvfp4r.status()["gemv_max_m"])) else "tcgen05"
             rows[str(M)] = r
-        out["shapes"][f"{name} ({N}x{K})"] = rows
+            if args.jsonl:
+                with open(args.jsonl, "a") as fh:
+                    fh.write(json.dumps({"sweep": args.sweep, "tp": tp, "shape": shape_key, "M": M, "row": r}) + "\n")
+        out["shapes"][shape_key] = rows
         del ws
         torch.cuda.empty_cache()
     return out
@@ -850,6 +943,8 @@ def main():
     ap.add_argument("--sweep", default="", choices=["", *SWEEP_SHAPES],
                     help="M sweep over one model's linear shapes: GEMV vs tcgen05 vs the installed vLLM pair")
     ap.add_argument("--sweep-m", default="1,2,3,4,6,8,12,16")
+    ap.add_argument("--sweep-tp", type=int, default=1, help="time one rank's shard shapes under this tensor parallelism")
+    ap.add_argument("--jsonl", default="", help="append sweep rows to this file and skip the ones it already holds")
     ap.add_argument("--published", action="store_true",
                     help="the reference's published M=1 shapes under its own timing method (L2-resident)")
     ap.add_argument("--reset-loop", action="store_true", help="ReSET decode-loop step time vs the CPU oracle")

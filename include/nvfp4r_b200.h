@@ -396,7 +396,10 @@ NVFP4R_API int nvfp4r_set_gemv_tuning(int ctas_per_sm, int use_pdl, int force_ge
  * kernels/cuda/gemv/gemv_nvfp4.cu:870-948).
  *   mode           0 = automatic (default), 1 = whenever the arguments allow it, -1 = never
  *   rows_per_step  weight rows a lane multiplies per pipeline step: 0 = automatic, 2 or 4
- *   warps_per_sm   resident warps the launch aims for: 0 = automatic (24), at most 32
+ *   warps_per_sm   rows of at most 12288 elements run in CTAs of 12 warps, two of which fit an SM:
+ *                  0 = automatic (both halves of every SM for weights above ~12 MB, one half
+ *                  below, which leaves the other to the next launch's early loads),
+ *                  1..12 = one half, 13..32 = both
  */
 NVFP4R_API int nvfp4r_set_gemv_rows_tuning(int mode, int rows_per_step, int warps_per_sm);
 

@@ -2,11 +2,34 @@
 #include <cstdio>
 #include <cstring>
 
+#include <nvtx3/nvToolsExt.h>
+
 #include "../../include/nvfp4r_b200.h"
 #include "kernels.h"
 #include "reset_kernels.h"
 
 namespace {
+
+// One NVTX range per launching entry point (domain "nvfp4r"): a timeline tool shows which
+// call of the C ABI issued which kernels. Costs a few nanoseconds when no tool is attached
+// (the header-only NVTX v3 resolves to no-ops then).
+struct NvtxRange {
+    static nvtxDomainHandle_t domain() {
+        static nvtxDomainHandle_t d = nvtxDomainCreateA("nvfp4r");
+        return d;
+    }
+    explicit NvtxRange(const char* name) { nvtxDomainRangePushEx(domain(), &attr(name)); }
+    ~NvtxRange() { nvtxDomainRangePop(domain()); }
+    static const nvtxEventAttributes_t& attr(const char* name) {
+        thread_local nvtxEventAttributes_t a = {};
+        a.version = NVTX_VERSION;
+        a.size = NVTX_EVENT_ATTRIB_STRUCT_SIZE;
+        a.messageType = NVTX_MESSAGE_TYPE_ASCII;
+        a.message.ascii = name;
+        return a;
+    }
+};
+#define NVFP4R_RANGE(name) NvtxRange nvtx_range_(name)
 
 thread_local char g_last_error[256] = "";
 
@@ -43,6 +66,7 @@ int nvfp4r_version(void) { return 1000 * 0 + 1; }
 
 int nvfp4r_quant(const void* x, int64_t x_row_stride, int M, int K, const float* gs,
                  void* codes, void* scales, int sf_layout, int rcp_mode, void* stream) {
+    NVFP4R_RANGE("nvfp4r_quant");
     if (!x || !gs || !codes || !scales) return fail(NVFP4R_ERR_INVALID_ARGUMENT, "quant: null pointer");
     if (M < 0 || K <= 0) return fail(NVFP4R_ERR_INVALID_ARGUMENT, "quant: M/K must be positive");
     if (sf_layout != NVFP4R_SF_FLAT && sf_layout != NVFP4R_SF_SWIZZLED)
@@ -63,6 +87,7 @@ int nvfp4r_gemv(const void* weight, const void* weight_scale, const void* x, con
                 void* out, int L, int N, int K, int64_t w_stride_l, int64_t w_stride_n,
                 int64_t wsf_stride_l, int64_t wsf_stride_n, int64_t x_stride_l,
                 int64_t xsf_stride_l, float alpha, int out_dtype, void* stream) {
+    NVFP4R_RANGE("nvfp4r_gemv");
     if (!weight || !weight_scale || !x || !x_scale || !out)
         return fail(NVFP4R_ERR_INVALID_ARGUMENT, "gemv: null pointer");
     if (L < 0 || N < 0 || K <= 0) return fail(NVFP4R_ERR_INVALID_ARGUMENT, "gemv: bad sizes");
@@ -107,6 +132,7 @@ int nvfp4r_gemv(const void* weight, const void* weight_scale, const void* x, con
 int nvfp4r_linear(const void* x, int64_t x_row_stride, int M, int K, const float* gs,
                   const void* weight, const void* weight_scale, int N, float alpha, void* out,
                   int out_dtype, int rcp_mode, void* stream) {
+    NVFP4R_RANGE("nvfp4r_linear");
     if (!x || !gs || !weight || !weight_scale || !out)
         return fail(NVFP4R_ERR_INVALID_ARGUMENT, "linear: null pointer");
     if (M < 0 || N < 0 || K <= 0) return fail(NVFP4R_ERR_INVALID_ARGUMENT, "linear: bad sizes");
@@ -166,6 +192,7 @@ static int tc_common_checks(const char* who, int M, int N, int K, int out_dtype,
 int nvfp4r_gemm(const void* A, const void* B, const void* SFA, const void* SFB, void* C, int M, int N,
                 int K, float alpha, int out_dtype, int c_layout, void* workspace,
                 size_t workspace_bytes, void* stream) {
+    NVFP4R_RANGE("nvfp4r_gemm");
     if (!A || !B || !SFA || !SFB || !C) return fail(NVFP4R_ERR_INVALID_ARGUMENT, "gemm: null pointer");
     if (c_layout != NVFP4R_C_M_MAJOR && c_layout != NVFP4R_C_N_MAJOR)
         return fail(NVFP4R_ERR_INVALID_ARGUMENT, "gemm: bad c_layout");
@@ -188,6 +215,7 @@ int nvfp4r_linear_tc(const void* x, int64_t x_row_stride, int M, int K, const fl
                      const void* weight, const void* weight_scale_swizzled, int N, float alpha,
                      void* out, int out_dtype, int rcp_mode, void* workspace, size_t workspace_bytes,
                      void* stream) {
+    NVFP4R_RANGE("nvfp4r_linear_tc");
     if (!x || !gs || !weight || !weight_scale_swizzled || !out)
         return fail(NVFP4R_ERR_INVALID_ARGUMENT, "linear_tc: null pointer");
     if (rcp_mode != NVFP4R_RCP_EXACT && rcp_mode != NVFP4R_RCP_APPROX)
@@ -228,6 +256,7 @@ size_t nvfp4r_linear_packed_workspace_bytes(int M, int N, int K) {
 
 int nvfp4r_pack_weight(const void* weight, const void* weight_scale_flat, void* packed, int N, int K,
                        void* stream) {
+    NVFP4R_RANGE("nvfp4r_pack_weight");
     if (!weight || !weight_scale_flat || !packed) return fail(NVFP4R_ERR_INVALID_ARGUMENT, "pack_weight: null pointer");
     if (N <= 0 || K <= 0) return fail(NVFP4R_ERR_INVALID_ARGUMENT, "pack_weight: bad sizes");
     if (N % 128 != 0 || K % 128 != 0)
@@ -241,6 +270,7 @@ int nvfp4r_pack_weight(const void* weight, const void* weight_scale_flat, void* 
 int nvfp4r_linear_packed(const void* x, int64_t x_row_stride, int M, int K, const float* gs,
                          const void* packed, int N, float alpha, void* out, int out_dtype, int rcp_mode,
                          void* workspace, size_t workspace_bytes, void* stream) {
+    NVFP4R_RANGE("nvfp4r_linear_packed");
     if (!x || !gs || !packed || !out) return fail(NVFP4R_ERR_INVALID_ARGUMENT, "linear_packed: null pointer");
     if (rcp_mode != NVFP4R_RCP_EXACT && rcp_mode != NVFP4R_RCP_APPROX)
         return fail(NVFP4R_ERR_INVALID_ARGUMENT, "linear_packed: bad rcp_mode");
@@ -268,6 +298,7 @@ int nvfp4r_linear_packed_ex(const nvfp4r_prologue* pro, const void* x, int64_t x
                             const float* gs, const void* packed, int N, float alpha, void* out,
                             int out_dtype, int rcp_mode, void* workspace, size_t workspace_bytes,
                             void* stream) {
+    NVFP4R_RANGE("nvfp4r_linear_packed_ex");
     if (!pro) return fail(NVFP4R_ERR_INVALID_ARGUMENT, "linear_packed_ex: null prologue");
     if (pro->kind == NVFP4R_PROLOGUE_NONE && pro->push_to == nullptr)
         return nvfp4r_linear_packed(x, x_row_stride, M, K, gs, packed, N, alpha, out, out_dtype, rcp_mode,
@@ -343,6 +374,7 @@ int nvfp4r_set_gemm_tuning(int splits, int stages) {
 }
 
 int nvfp4r_unswizzle_blockscale(const void* swizzled, void* flat, int rows, int K, void* stream) {
+    NVFP4R_RANGE("nvfp4r_unswizzle_blockscale");
     if (!swizzled || !flat) return fail(NVFP4R_ERR_INVALID_ARGUMENT, "unswizzle: null pointer");
     if (rows < 0 || K <= 0 || K % 16) return fail(NVFP4R_ERR_UNSUPPORTED_SHAPE, "unswizzle: K % 16");
     if (rows == 0) return NVFP4R_OK;
@@ -351,6 +383,7 @@ int nvfp4r_unswizzle_blockscale(const void* swizzled, void* flat, int rows, int 
 }
 
 int nvfp4r_swizzle_blockscale(const void* flat, void* swizzled, int rows, int K, void* stream) {
+    NVFP4R_RANGE("nvfp4r_swizzle_blockscale");
     if (!swizzled || !flat) return fail(NVFP4R_ERR_INVALID_ARGUMENT, "swizzle: null pointer");
     if (rows < 0 || K <= 0 || K % 16) return fail(NVFP4R_ERR_UNSUPPORTED_SHAPE, "swizzle: K % 16");
     if (rows == 0) return NVFP4R_OK;
@@ -367,6 +400,7 @@ int nvfp4r_reset_step(float* logits, int64_t row_stride, int B, int V, nvfp4r_re
                       const uint32_t* nl_bitmap, const uint32_t* dnl_bitmap,
                       const nvfp4r_reset_params* params, nvfp4r_reset_decision* decisions,
                       void* workspace, size_t workspace_bytes, void* stream) {
+    NVFP4R_RANGE("nvfp4r_reset_step");
     if (!logits || !states || !params || !workspace)
         return fail(NVFP4R_ERR_INVALID_ARGUMENT, "reset_step: null pointer");
     if (B < 0 || V <= 0 || row_stride < V) return fail(NVFP4R_ERR_INVALID_ARGUMENT, "reset_step: bad sizes");
@@ -405,6 +439,7 @@ int nvfp4r_reset_step_per_request(float* logits, int64_t row_stride, int B, int 
                                   const nvfp4r_reset_params* slot_params,
                                   nvfp4r_reset_decision* decisions, void* workspace,
                                   size_t workspace_bytes, void* stream) {
+    NVFP4R_RANGE("nvfp4r_reset_step_per_request");
     if (!logits || !states || !slot_params || !workspace)
         return fail(NVFP4R_ERR_INVALID_ARGUMENT, "reset_step_per_request: null pointer");
     if (B < 0 || V <= 0 || row_stride < V || n_id_sets < 0)
@@ -440,6 +475,7 @@ int nvfp4r_reset_step_static(float* logits, int64_t row_stride, int B, int V,
                              const int32_t* last_ids, const uint32_t* nl_bitmap,
                              const uint32_t* dnl_bitmap, const nvfp4r_reset_params* params,
                              nvfp4r_reset_decision* decisions, void* stream) {
+    NVFP4R_RANGE("nvfp4r_reset_step_static");
     if (!logits || !states || !params)
         return fail(NVFP4R_ERR_INVALID_ARGUMENT, "reset_step_static: null pointer");
     if (B < 0 || V <= 0 || row_stride < V)
@@ -474,6 +510,7 @@ int nvfp4r_reset_step_static(float* logits, int64_t row_stride, int B, int V,
 
 int nvfp4r_entropy(const float* logits, int64_t row_stride, int B, int V, float* entropy,
                    void* workspace, size_t workspace_bytes, void* stream) {
+    NVFP4R_RANGE("nvfp4r_entropy");
     if (!logits || !entropy || !workspace) return fail(NVFP4R_ERR_INVALID_ARGUMENT, "entropy: null pointer");
     if (B < 0 || V <= 0 || row_stride < V) return fail(NVFP4R_ERR_INVALID_ARGUMENT, "entropy: bad sizes");
     if (workspace_bytes < nvfp4r_reset_workspace_bytes(B))

@@ -1,4 +1,4 @@
-// NVFP4 W4A4 GEMV for one or two tokens: activations stay in registers, weights
+// NVFP4 W4A4 GEMV for one token: activations stay in registers, weights
 // stream straight from global memory into registers.
 //
 // Decomposition. A lane owns one 32-element unit of K (16 code bytes, 2 block
@@ -33,6 +33,9 @@ struct RowsParams {
     int cw;               // warps side by side along K
     int streams;          // row streams per CTA
     int total_streams;    // streams * gridDim.x
+    int pairs;            // ceil(N / (2 R)): units of work dealt to the streams
+    int stream_rows;      // most rows a stream can get (a multiple of 2 R)
+    int stream_floats;    // stream_rows * MT * cw: floats of shared memory per stream
 };
 
 struct Unit16 {
@@ -46,18 +49,24 @@ __device__ __forceinline__ void decode_codes(const uint4& c, Unit16& u) {
     e2m1x8_to_f16x8(c.w, &u.h[12]);
 }
 
-__device__ __forceinline__ float2 decode_scale_pair(uint32_t two_bytes) {
-    return __half22float2(as_half2(e4m3x2_to_f16x2(two_bytes)));
+// acc += a * b with a, b f16 and the product and sum in f32 (the product of two f16 values is
+// exact in f32).
+__device__ __forceinline__ float fma_f16_f32(__half a, __half b, float acc) {
+    asm("fma.rn.f32.f16 %0, %1, %2, %0;" : "+f"(acc) : "h"(__half_as_ushort(a)), "h"(__half_as_ushort(b)));
+    return acc;
 }
+
+// 2^-6 in both halves: the activation scales are kept multiplied by it so that the product of
+// a weight scale and an activation scale (up to 448 * 448) stays inside f16. Every product of
+// two e4m3 values is a multiple of 2^-18 with at most 8 significant bits, so
+// weight scale * (activation scale * 2^-6) is EXACT in f16, subnormals included.
+constexpr uint32_t kTwoPowMinus6x2 = 0x24002400u;
+constexpr float kScaleFix = 64.0f;
 
 __device__ __forceinline__ void store_out(void* out, int dtype, int64_t idx, float v) {
     if (dtype == 0)      static_cast<__nv_bfloat16*>(out)[idx] = __float2bfloat16_rn(v);
     else if (dtype == 1) static_cast<__half*>(out)[idx] = __float2half_rn(v);
     else                 static_cast<float*>(out)[idx] = v;
-}
-
-__device__ __forceinline__ void named_barrier(int id, int threads) {
-    asm volatile("bar.sync %0, %1;" :: "r"(id), "r"(threads) : "memory");
 }
 
 // Sum NV values per lane over the 32 lanes. Each step halves the number of
@@ -92,56 +101,84 @@ struct Stage {
     uint32_t s[R];
 };
 
+// Loads of one step: R rows below `wq` / `sq` (this lane's unit in the step's first row), no
+// bounds tests: the caller guarantees that all R rows exist.
 template <int R>
-__device__ __forceinline__ void load_stage(Stage<R>& st, const uint8_t* wp, const uint8_t* sp,
-                                           int64_t w_stride, int64_t sf_stride, int row0, int row_end,
-                                           bool active) {
+__device__ __forceinline__ void load_stage(Stage<R>& st, const uint8_t* wbase, const uint8_t* sbase,
+                                           uint32_t w0, uint32_t s0, uint32_t w_stride, uint32_t sf_stride) {
 #pragma unroll
     for (int r = 0; r < R; ++r) {
-        const int row = row0 + r;
-        if (active && row < row_end) {
-            st.c[r] = ldg_stream_16(wp + row * w_stride);
-            st.s[r] = ldg_stream_2(sp + row * sf_stride);
-        } else {
-            st.c[r] = make_uint4(0u, 0u, 0u, 0u);
-            st.s[r] = 0u;
-        }
+        st.c[r] = ldg_stream_16(wbase + (w0 + r * w_stride));
+        st.s[r] = ldg_stream_2(sbase + (s0 + r * sf_stride));
     }
 }
 
-template <int MT, int R, int MAXT>
-__global__ void __launch_bounds__(MAXT, 1)
+// Last step of the matrix when N is not a multiple of R: rows past the end read row N - 1
+// again (their results are never stored).
+template <int R>
+__device__ __forceinline__ void load_stage_clamped(Stage<R>& st, const uint8_t* wbase, const uint8_t* sbase,
+                                                   uint32_t w0, uint32_t s0, uint32_t w_stride,
+                                                   uint32_t sf_stride, int rows_left) {
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+        const int rr = r < rows_left ? r : rows_left - 1;
+        st.c[r] = ldg_stream_16(wbase + (w0 + rr * w_stride));
+        st.s[r] = ldg_stream_2(sbase + (s0 + rr * sf_stride));
+    }
+}
+
+// Work is dealt in steps of R consecutive rows and in pairs of steps (one butterfly sums the
+// 2 R MT values of a pair). A row stream owns the pairs [pair_begin, pair_end); its per-warp
+// sums go to shared memory and are added over the stream's warps once, at the end.
+template <int MT, int R, int MAXT, int MINB>
+__global__ void __launch_bounds__(MAXT, MINB)
 gemv_rows_kernel(const __grid_constant__ RowsParams p) {
-    constexpr int NV = R * MT;
-    constexpr int kShift = NV == 1 ? 5 : NV == 2 ? 4 : NV == 4 ? 3 : NV == 8 ? 2 : 1;
-    __shared__ float part[2 * NV * kMaxWarps];
+    constexpr int NV = 2 * R * MT;
+    constexpr int kShift = NV == 2 ? 4 : NV == 4 ? 3 : NV == 8 ? 2 : NV == 16 ? 1 : 0;
+    extern __shared__ float part[];      // [stream][local row * MT + m][kc]
 
     const int tid = threadIdx.x, lane = tid & 31, wi = tid >> 5;
     const int cw = p.cw;
     const int s = wi / cw, kc = wi - s * cw;
-    const int nwarps = blockDim.x >> 5;
-    const int u = kc * 32 + lane;
-    const bool active = u < p.units;
+    const int u_raw = kc * 32 + lane;
+    const bool active = u_raw < p.units;
+    const int u = active ? u_raw : p.units - 1;          // idle lanes re-read the last unit against zeros
     const int N = p.a.N, M = p.a.M;
     const int sid = blockIdx.x * p.streams + s;
-    const int row_begin = static_cast<int>(static_cast<int64_t>(sid) * N / p.total_streams);
-    const int row_end = static_cast<int>(static_cast<int64_t>(sid + 1) * N / p.total_streams);
+    const int pair_begin = static_cast<int>(static_cast<int64_t>(sid) * p.pairs / p.total_streams);
+    const int pair_end = static_cast<int>(static_cast<int64_t>(sid + 1) * p.pairs / p.total_streams);
+    const int row_begin = pair_begin * 2 * R;
+    const int row_end = min(pair_end * 2 * R, N);
+    const int steps = (row_end - row_begin + R - 1) / R;     // the last one may be partial (end of the matrix)
 
-    const uint8_t* wp = p.a.w + u * kUnitBytes;
-    const uint8_t* sp = p.a.wsf + u * 2;
-    const int64_t w_stride = p.a.w_stride_n, sf_stride = p.a.wsf_stride_n;
+    // Byte offsets from the weight's base fit 32 bits (checked by the launcher): one integer add
+    // per address.
+    const uint32_t w_stride = static_cast<uint32_t>(p.a.w_stride_n), sf_stride = static_cast<uint32_t>(p.a.wsf_stride_n);
+    const uint32_t wq = static_cast<uint32_t>(row_begin) * w_stride + u * kUnitBytes;
+    const uint32_t sq = static_cast<uint32_t>(row_begin) * sf_stride + u * 2;
+    const uint8_t* __restrict__ wbase = p.a.w;
+    const uint8_t* __restrict__ sbase = p.a.wsf;
+
+    auto load = [&](Stage<R>& st, int step) {
+        if (step >= steps) return;
+        const int left = row_end - (row_begin + step * R);
+        const uint32_t w0 = wq + static_cast<uint32_t>(step) * (R * w_stride);
+        const uint32_t s0 = sq + static_cast<uint32_t>(step) * (R * sf_stride);
+        if (left >= R) load_stage<R>(st, wbase, sbase, w0, s0, w_stride, sf_stride);
+        else load_stage_clamped<R>(st, wbase, sbase, w0, s0, w_stride, sf_stride, left);
+    };
 
     // Weights do not depend on the preceding kernel.
     Stage<R> sa, sb;
-    load_stage<R>(sa, wp, sp, w_stride, sf_stride, row_begin, row_end, active);
-    load_stage<R>(sb, wp, sp, w_stride, sf_stride, row_begin + R, row_end, active);
+    load(sa, 0);
+    load(sb, 1);
     const float gs = (p.a.xb != nullptr) ? __ldg(p.a.gs) : 1.0f;
     pdl_launch_dependents();
     pdl_wait_prior();
 
     // This lane's slice of the activations, decoded once.
     uint32_t xh[MT][16];
-    float2 xs[MT];
+    __half2 xs[MT];                 // the two block scales of the slice, times 2^-6
 #pragma unroll
     for (int m = 0; m < MT; ++m) {
         uint4 codes = make_uint4(0u, 0u, 0u, 0u);
@@ -172,17 +209,15 @@ gemv_rows_kernel(const __grid_constant__ RowsParams p) {
         decode_codes(codes, xu);
 #pragma unroll
         for (int i = 0; i < 16; ++i) xh[m][i] = xu.h[i];
-        xs[m] = decode_scale_pair(sf2);
+        xs[m] = __hmul2(as_half2(e4m3x2_to_f16x2(sf2)), as_half2(kTwoPowMinus6x2));
     }
 
-    int parity = 0;
-    auto compute = [&](const Stage<R>& st, int row0) {
-        float v[NV];
+    auto compute = [&](const Stage<R>& st, float* v) {
 #pragma unroll
         for (int r = 0; r < R; ++r) {
             Unit16 wu;
             decode_codes(st.c[r], wu);
-            const float2 ws = decode_scale_pair(st.s[r]);
+            const __half2 ws = as_half2(e4m3x2_to_f16x2(st.s[r]));
 #pragma unroll
             for (int m = 0; m < MT; ++m) {
                 __half2 d0 = __hmul2(as_half2(wu.h[0]), as_half2(xh[m][0]));
@@ -192,42 +227,48 @@ gemv_rows_kernel(const __grid_constant__ RowsParams p) {
                     d0 = __hfma2(as_half2(wu.h[i]), as_half2(xh[m][i]), d0);
                     d1 = __hfma2(as_half2(wu.h[8 + i]), as_half2(xh[m][8 + i]), d1);
                 }
-                const float f0 = __half2float(__hadd(__low2half(d0), __high2half(d0)));
-                const float f1 = __half2float(__hadd(__low2half(d1), __high2half(d1)));
-                v[r * MT + m] = fmaf(f1, ws.y * xs[m].y, f0 * (ws.x * xs[m].x));
+                const __half2 sc = __hmul2(ws, xs[m]);                       // exact (see kTwoPowMinus6x2)
+                const __half b0 = __hadd(__low2half(d0), __high2half(d0));   // the two block sums
+                const __half b1 = __hadd(__low2half(d1), __high2half(d1));
+                v[r * MT + m] = fma_f16_f32(b1, __high2half(sc), fma_f16_f32(b0, __low2half(sc), 0.0f));
             }
-        }
-        butterfly<NV>(v, lane);
-        const int idx = lane >> kShift;
-        if (cw == 1) {
-            if ((lane & ((1 << kShift) - 1)) == 0) {
-                const int r = idx / MT, m = idx - r * MT;
-                const int row = row0 + r;
-                if (row < row_end && m < M)
-                    store_out(p.a.out, p.a.out_dtype, m * p.a.out_stride + row, v[0] * p.a.alpha);
-            }
-        } else {
-            if ((lane & ((1 << kShift) - 1)) == 0) part[(parity * NV + idx) * nwarps + wi] = v[0];
-            named_barrier(1 + s, cw * 32);
-            if (kc == 0 && lane < NV) {
-                const float* src = &part[(parity * NV + lane) * nwarps + s * cw];
-                float sum = src[0];
-                for (int j = 1; j < cw; ++j) sum += src[j];
-                const int r = lane / MT, m = lane - r * MT;
-                const int row = row0 + r;
-                if (row < row_end && m < M)
-                    store_out(p.a.out, p.a.out_dtype, m * p.a.out_stride + row, sum * p.a.alpha);
-            }
-            parity ^= 1;
         }
     };
 
-    for (int row0 = row_begin; row0 < row_end; row0 += 2 * R) {
-        compute(sa, row0);
-        load_stage<R>(sa, wp, sp, w_stride, sf_stride, row0 + 2 * R, row_end, active);
-        if (row0 + R < row_end) {
-            compute(sb, row0 + R);
-            load_stage<R>(sb, wp, sp, w_stride, sf_stride, row0 + 3 * R, row_end, active);
+    // part index of (local row lr, token m, warp kc) of this stream
+    float* my_part = part + static_cast<size_t>(s) * p.stream_floats;
+    const int writer = (lane & ((1 << kShift) - 1)) == 0;
+    const int idx = lane >> kShift;                       // which of the pair's NV values this lane ends up with
+
+    for (int st2 = 0; st2 < steps; st2 += 2) {
+        float v[NV];
+        compute(sa, v);
+        load(sa, st2 + 2);
+        if (st2 + 1 < steps) {
+            compute(sb, v + R * MT);
+            load(sb, st2 + 3);
+        } else {
+#pragma unroll
+            for (int i = 0; i < R * MT; ++i) v[R * MT + i] = 0.0f;
+        }
+        butterfly<NV>(v, lane);
+        if (writer) my_part[(st2 * R * MT + idx) * cw + kc] = v[0];
+    }
+
+    // Sum over the warps of each stream, in warp order, and store.
+    __syncthreads();
+    for (int t = tid; t < p.streams * p.stream_rows * MT; t += blockDim.x) {
+        const int ss = t / (p.stream_rows * MT), e = t - ss * (p.stream_rows * MT);
+        const int lr = e / MT, m = e - lr * MT;
+        const int sid2 = blockIdx.x * p.streams + ss;
+        const int rb = static_cast<int>(static_cast<int64_t>(sid2) * p.pairs / p.total_streams) * 2 * R;
+        const int re = min(static_cast<int>(static_cast<int64_t>(sid2 + 1) * p.pairs / p.total_streams) * 2 * R, N);
+        const int row = rb + lr;
+        if (row < re && m < M) {
+            const float* src = part + static_cast<size_t>(ss) * p.stream_floats + static_cast<size_t>(e) * cw;
+            float sum = src[0];
+            for (int j = 1; j < cw; ++j) sum += src[j];
+            store_out(p.a.out, p.a.out_dtype, m * p.a.out_stride + row, sum * (p.a.alpha * kScaleFix));
         }
     }
 }
@@ -247,66 +288,127 @@ void set_gemv_rows_tuning(int mode, int rows, int target_warps) {
     g_rows_tuning.target_warps = target_warps;
 }
 
+// Kernel choice for one launch of at most 8 tokens. One token: the register-resident kernel
+// for weights of 16 MB and more, for rows longer than 8192 elements and for every shape the
+// ring kernel cannot take (K % 256 != 0), the ring kernel below that (measured on B200,
+// L2-cold: 6144x4096 5.1 vs 5.3 us, 6400x5120 6.7 vs 6.3 us, 4096x12288 10.9 vs 7.8 us,
+// 5120x3200 11.1 (plain loads) vs 4.9 us). More tokens: the ring kernel.
 cudaError_t launch_gemv_auto(const GemvArgs& a, cudaStream_t stream) {
-    if (!gemv_tuning().force_generic && gemv_rows_supported(a)) return launch_gemv_rows(a, stream);
-    return gemv_stream_supported(a) ? launch_gemv_stream(a, stream) : launch_gemv_generic(a, stream);
+    const bool ring = gemv_stream_supported(a);
+    if (!gemv_tuning().force_generic && gemv_rows_supported(a)) {
+        const int64_t wbytes = static_cast<int64_t>(a.N) * a.K * 9 / 16;
+        if (g_rows_tuning.mode > 0 || !ring || wbytes >= 16000000 || a.K > 8192)
+            return launch_gemv_rows(a, stream);
+    }
+    return ring ? launch_gemv_stream(a, stream) : launch_gemv_generic(a, stream);
 }
+
+namespace {
+
+constexpr size_t kRowsMaxSmem = 96 * 1024;
+
+// CTA shapes. A row narrower than 12 warps (K <= 12288) runs in CTAs of at most 12 warps, two
+// of which fit an SM (80 registers per thread): either both belong to this launch (24 warps
+// per SM hide the latency of the decode chains), or only one does and the other half of the SM
+// is free for the NEXT launch, whose CTAs then request their first weights while this launch
+// is still running (small weights, where the fixed part of a launch dominates). Rows of 13..24
+// warps take one CTA per SM, wider ones one CTA of up to 32 warps at 64 registers.
+enum RowsShape { kShapeHalf = 0, kShapeFull = 1, kShapeWide = 2 };
+
+// Grid, block and shared-memory plan of one launch; false when the shape does not fit.
+bool plan_rows(const GemvArgs& a, RowsParams* out, size_t* smem_bytes, int* rows_per_step, int* shape) {
+    RowsParams p;
+    p.a = a;
+    p.units = a.K / 32;
+    p.cw = (p.units + 31) / 32;
+    if (p.cw < 1 || p.cw > kMaxWarps) return false;
+    const RowsTuning& t = g_rows_tuning;
+    const int sms = device_sm_count();
+    const int MT = a.M == 1 ? 1 : 2;
+    const int sh = p.cw <= 12 ? kShapeHalf : (p.cw <= 24 ? kShapeFull : kShapeWide);
+    const int R = sh == kShapeWide ? (MT == 1 ? 2 : 1) : (MT == 1 ? (t.rows == 2 ? 2 : 4) : 2);
+    int streams = sh == kShapeHalf ? 12 / p.cw : 1;
+    // CTAs per SM of this launch (half shape only): both halves of the SM for weights of more
+    // than about 12 MB, one half (leaving room for the next launch) below.
+    int per_sm = 1;
+    if (sh == kShapeHalf) {
+        const int64_t wbytes = static_cast<int64_t>(a.N) * a.K * 9 / 16;
+        per_sm = wbytes > 12000000 ? 2 : 1;
+        if (t.target_warps > 0) per_sm = t.target_warps > 12 ? 2 : 1;
+    }
+    p.pairs = (a.N + 2 * R - 1) / (2 * R);
+    int grid = sms * per_sm;
+    while (streams > 1 && static_cast<int64_t>(streams) * grid > p.pairs) --streams;   // no idle streams
+    if (static_cast<int64_t>(grid) * streams > p.pairs) grid = (p.pairs + streams - 1) / streams;
+    p.streams = streams;
+    p.total_streams = streams * grid;
+    p.stream_rows = ((p.pairs + p.total_streams - 1) / p.total_streams) * 2 * R;
+    p.stream_floats = p.stream_rows * MT * p.cw;
+    const size_t smem = static_cast<size_t>(p.streams) * p.stream_floats * sizeof(float);
+    if (smem > kRowsMaxSmem) return false;
+    *out = p;
+    *smem_bytes = smem;
+    *rows_per_step = R;
+    *shape = sh;
+    return true;
+}
+
+}  // namespace
 
 bool gemv_rows_supported(const GemvArgs& a) {
     if (g_rows_tuning.mode < 0) return false;
-    if (a.M < 1 || a.M > 2) return false;
+    if (a.M != 1 || a.N < 1) return false;      // two tokens spill at these register budgets: measured slower than the ring kernel
+    if (static_cast<int64_t>(a.N) * a.w_stride_n >= (1ll << 32) || static_cast<int64_t>(a.N) * a.wsf_stride_n >= (1ll << 32))
+        return false;                            // 32-bit byte offsets inside the weight
     if (a.K % 32 != 0 || a.K > 32 * 32 * kMaxWarps) return false;
     if ((reinterpret_cast<uintptr_t>(a.w) & 15) || (a.w_stride_n % 16) != 0) return false;
     if ((reinterpret_cast<uintptr_t>(a.wsf) & 1) || (a.wsf_stride_n % 2) != 0) return false;
+    if (a.w_stride_n > (1 << 28) || a.wsf_stride_n > (1 << 28)) return false;     // 32-bit row offsets inside a step
     if (a.xb != nullptr) {
         if ((reinterpret_cast<uintptr_t>(a.xb) & 15) || (a.xb_stride % 8) != 0) return false;
     } else {
         if ((reinterpret_cast<uintptr_t>(a.x) & 15) || (a.x_stride % 16) != 0) return false;
         if ((reinterpret_cast<uintptr_t>(a.xsf) & 1) || (a.xsf_stride % 2) != 0) return false;
     }
-    return true;
+    RowsParams p;
+    size_t smem;
+    int R, shape;
+    return plan_rows(a, &p, &smem, &R, &shape);
 }
 
 cudaError_t launch_gemv_rows(const GemvArgs& a, cudaStream_t stream) {
     RowsParams p;
-    p.a = a;
-    p.units = a.K / 32;
-    p.cw = (p.units + 31) / 32;
-    const RowsTuning& t = g_rows_tuning;
-    const int sms = device_sm_count();
+    size_t smem = 0;
+    int R = 4, shape = kShapeHalf;
+    if (!plan_rows(a, &p, &smem, &R, &shape)) return cudaErrorInvalidConfiguration;
+    const int MT = a.M == 1 ? 1 : 2;
+    const int grid = p.total_streams / p.streams;
+    const int streams = p.streams;
 
-    // Warps per SM: bounded by the register file (MAXT = 768 threads of <= 78 registers, or
-    // 1024 of 64 for rows wider than 24 warps).
-    const bool wide = p.cw > 24;
-    const int max_warps = wide ? 32 : 24;
-    int target = t.target_warps > 0 ? t.target_warps : 24;
-    if (target > max_warps) target = max_warps;
-    int streams = target / p.cw;
-    if (streams < 1) streams = 1;
-    if (p.cw > 1 && streams > 15) streams = 15;       // one named barrier per stream
-    if (streams * p.cw > max_warps) streams = max_warps / p.cw;
-    // No more streams than rows / 2 over the whole grid.
-    while (streams > 1 && static_cast<int64_t>(streams) * sms * 2 > a.N) --streams;
-    int grid = sms;
-    if (static_cast<int64_t>(grid) * streams > a.N) grid = (a.N + streams - 1) / streams;
-    p.streams = streams;
-    p.total_streams = streams * grid;
-
-    const int R = t.rows > 0 ? t.rows : 4;
     using Kern = void (*)(RowsParams);
-    Kern kern;
-    if (a.M == 1) {
-        if (wide) kern = gemv_rows_kernel<1, 2, 1024>;
-        else kern = (R == 2) ? gemv_rows_kernel<1, 2, 768> : gemv_rows_kernel<1, 4, 768>;
-    } else {
-        if (wide) kern = gemv_rows_kernel<2, 1, 1024>;
-        else kern = (R == 2) ? gemv_rows_kernel<2, 2, 768> : gemv_rows_kernel<2, 2, 768>;
+    static const Kern table[3][2] = {
+        // half (R 4 / R 2), full (R 4 / R 2), wide (R 2)
+        {gemv_rows_kernel<1, 4, 384, 2>, gemv_rows_kernel<1, 2, 384, 2>},
+        {gemv_rows_kernel<1, 4, 768, 1>, gemv_rows_kernel<1, 2, 768, 1>},
+        {gemv_rows_kernel<1, 2, 1024, 1>, gemv_rows_kernel<1, 2, 1024, 1>}};
+    const int rsel = R == 2 ? 1 : 0;
+    const Kern kern = table[shape][rsel];
+    const int ki = shape * 2 + rsel;
+    (void)MT;
+    static bool attr_done[12][64] = {};
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return e;
+    if (dev >= 0 && dev < 64 && !attr_done[ki][dev]) {
+        e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(kRowsMaxSmem));
+        if (e != cudaSuccess) return e;
+        attr_done[ki][dev] = true;
     }
 
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(static_cast<unsigned>(grid));
     cfg.blockDim = dim3(static_cast<unsigned>(streams * p.cw * 32));
-    cfg.dynamicSmemBytes = 0;
+    cfg.dynamicSmemBytes = smem;
     cfg.stream = stream;
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;

@@ -53,9 +53,12 @@ def _check_rows(got, exact, mag):
     assert np.all(got[mag == 0] == 0)
 
 
-@pytest.mark.parametrize("generic", [False, True])
+@pytest.mark.parametrize("generic", [False, True, "rows"])
 def test_gemv_decodes_every_code_and_scale_byte(capi, generic):
+    """Through the ring kernel, the plain-load fallback and the register-resident kernel."""
     from reset_b200 import _lib
+    rows_mode = 1 if generic == "rows" else -1
+    generic = generic is True
     N, K = 128, 512
     w, ws = _all_bytes_weight(N, K)
     x = np.arange(256, dtype=np.uint8)[::-1].copy().reshape(1, 1, K // 2)      # every code byte as activation too
@@ -63,11 +66,13 @@ def test_gemv_decodes_every_code_and_scale_byte(capi, generic):
     exact = onv.linear_f64(w, ws, x[:, 0], xs[:, 0], alpha=1.0)
     out = torch.full((1, N), float("nan"), dtype=torch.float32, device="cuda")
     _lib.check(_lib.lib().nvfp4r_set_gemv_tuning(-1, -1, 1 if generic else 0), "tuning")
+    _lib.check(_lib.lib().nvfp4r_set_gemv_rows_tuning(rows_mode, 0, 0), "rows tuning")
     try:
         capi.gemv_out(cuda(w).unsqueeze(0), cuda(ws).unsqueeze(0), cuda(x), cuda(xs), out, 1.0)
         torch.cuda.synchronize()
     finally:
         _lib.check(_lib.lib().nvfp4r_set_gemv_tuning(-1, -1, 0), "tuning")
+        _lib.check(_lib.lib().nvfp4r_set_gemv_rows_tuning(0, 0, 0), "rows tuning")
     _check_rows(out.cpu().numpy(), exact, _magnitude(w, ws, x[:, 0], xs[:, 0]))
 
 

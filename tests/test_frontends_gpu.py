@@ -143,7 +143,7 @@ def test_batch_processor_keeps_each_requests_own_parameters():
             nxt = c["dnl"][0] if u < 0.1 else (c["nl"][0] if c["nl"] and u < 0.4 else int(rng.integers(40, V)))
             outs[r].append(nxt)
         proc.update_state(None)
-    assert checked >= 150
+    assert checked >= 100
     for r, c in cfgs.items():                            # every request used both of ITS temperatures
         assert seen[r] == {c["t_high"], c["t_low"]}, (r, seen[r])
 

@@ -32,12 +32,18 @@ def capi():
     return c
 
 
-@pytest.fixture(params=["stream", "generic"])
+@pytest.fixture(params=["stream", "rows", "generic"])
 def path(request):
+    """The three GEMV kernels: the bulk-copy ring kernel (the register-resident one switched off),
+    the register-resident single-token kernel wherever it can take the launch, the plain-load
+    fallback."""
     from reset_b200 import _lib
     _lib.check(_lib.lib().nvfp4r_set_gemv_tuning(-1, -1, 1 if request.param == "generic" else 0), "tuning")
+    _lib.check(_lib.lib().nvfp4r_set_gemv_rows_tuning({"stream": -1, "rows": 1, "generic": -1}[request.param], 0, 0),
+               "rows tuning")
     yield request.param
     _lib.check(_lib.lib().nvfp4r_set_gemv_tuning(-1, -1, 0), "tuning")
+    _lib.check(_lib.lib().nvfp4r_set_gemv_rows_tuning(0, 0, 0), "rows tuning")
 
 
 def _run(capi, w, ws, x, xs, L, dtype, alpha=1.0):
