@@ -211,7 +211,13 @@ def run_ours(args, rank, world, local_rank):
     import torch.distributed as dist
 
     from reset_b200 import nvfp4r  # registers torch.ops.nvfp4r.* (raises if not built)
+    from reset_b200.nvfp4r import _config as nv_config
 
+    if args.no_fused_gather:
+        nv_config.FUSED_GATHER = False
+    if args.packed_tuning:
+        from reset_b200 import _lib
+        _lib.check(_lib.lib().nvfp4r_set_packed_tuning(args.packed_tuning), "packed tuning")
     device = torch.device("cuda", local_rank)
     torch.cuda.set_device(device)
     tp = world
@@ -464,7 +470,10 @@ def run_ours(args, rank, world, local_rank):
                    "launch": "CUDA-graph replay, one graph per step",
                    "parallelism": f"tp{world}",
                    "allreduce": "none" if world == 1 else
-                                ("push in the linear epilogue + one-shot gather kernel over NVLink peer memory" if peer is not None else "NCCL")},
+                                (("push + sum inside the row-parallel linear's own launch over NVLink peer memory"
+                                  if nv_config.FUSED_GATHER else
+                                  "push in the linear epilogue + one-shot gather kernel over NVLink peer memory")
+                                 if peer is not None else "NCCL")},
         "e2e": {"value": round(gbs_e2e, 1), "unit": "GB/s",
                 "h2d_bytes_per_step": h2d_bytes, "d2h_bytes_per_step": d2h_bytes},
         "gpu_launches": timed_launches,
@@ -496,7 +505,14 @@ def run_decode(args, rank, world, device):
     cfg = QWEN3_32B
     if args.decode_layers:                     # fewer layers of the same geometry: profiler captures
         cfg = dataclasses.replace(cfg, layers=args.decode_layers, name=f"{cfg.name} ({args.decode_layers} layers)")
-    model = DecodeStep(cfg, device, rank=rank, world=world, seed=11, peer_allreduce=(args.allreduce == "peer"))
+    shard_of = args.decode_shard_of
+    if shard_of > 1 and world == 1:
+        # rank 0's shard of a `shard_of`-way tensor-parallel model on this one GPU, exchanges
+        # left out: what the launches of one rank cost before any communication
+        model = DecodeStep(cfg, device, rank=0, world=shard_of, seed=11, skip_exchange=True)
+    else:
+        model = DecodeStep(cfg, device, rank=rank, world=world, seed=11, peer_allreduce=(args.allreduce == "peer"),
+                           fused_gather=not args.no_fused_gather)
     if args.decode_eager:
         for _ in range(args.decode_steps):
             model.step()
@@ -951,6 +967,12 @@ def main():
     ap.add_argument("--reset-steps", type=int, default=256)
     ap.add_argument("--allreduce", default="peer", choices=["peer", "nccl"],
                     help="sum exchange after row-parallel linears at N > 1: this library's one-shot kernel or NCCL")
+    ap.add_argument("--packed-tuning", type=int, default=0,
+                    help="value for nvfp4r_set_packed_tuning (experiments: 512 = one CTA per SM)")
+    ap.add_argument("--decode-shard-of", type=int, default=0,
+                    help="single GPU: time rank 0's shard of this tensor-parallel degree without the exchanges")
+    ap.add_argument("--no-fused-gather", action="store_true",
+                    help="tensor-parallel runs: gather in a second launch instead of inside the linear's own")
     ap.add_argument("--watchdog", type=int, default=1200,
                     help="seconds after which every rank dumps its Python stacks to stderr and exits")
     args = ap.parse_args()

@@ -227,6 +227,14 @@ typedef struct nvfp4r_prologue {
      * the remaining tiles); a following nvfp4r_peer_allreduce_bf16(..., NVFP4R_PEER_GATHER)
      * on `out` completes the sum. out_dtype must be bf16 and M*N <= push_to->max_elems. */
     const struct nvfp4r_peer_comm* push_to;
+    /* With push_to: non-zero = finish the all-reduce inside this launch. The thread that pushed a
+     * pair of results then waits for the other ranks' contributions to that pair in this rank's
+     * own receive memory, adds them in rank order in fp32, rounds once, writes `out` and zeroes
+     * the slots; no gather call follows. Every rank must run the same call at about the same
+     * time: a CTA spins (bounded, nvfp4r_set_peer_poll_limit) until its peers have pushed, so
+     * this mode needs one GPU per rank - ranks emulated as successive launches on one GPU must
+     * use push + a separate gather. M <= 32. */
+    int push_gather;
 } nvfp4r_prologue;
 NVFP4R_API int nvfp4r_linear_packed_ex(const nvfp4r_prologue* pro, const void* x, int64_t x_row_stride,
                                        int M, int K, const float* global_scale_inv, const void* packed,

@@ -42,7 +42,7 @@ class ResetDecision(C.Structure):
 class Prologue(C.Structure):
     _fields_ = [("kind", C.c_int), ("eps", C.c_float), ("delta", C.c_void_p),
                 ("residual_in", C.c_void_p), ("residual_out", C.c_void_p), ("norm_weight", C.c_void_p),
-                ("push_to", C.c_void_p)]
+                ("push_to", C.c_void_p), ("push_gather", C.c_int)]
 
 
 PROLOGUE_NONE, PROLOGUE_ADD_RMSNORM, PROLOGUE_SILU_MUL = 0, 1, 2

@@ -208,16 +208,18 @@ def linear_packed_rmsnorm(delta, residual_in: torch.Tensor, residual_out: torch.
 
 def linear_packed_silu(gate_up: torch.Tensor, global_scale_inv: torch.Tensor, packed: torch.Tensor, N: int,
                        alpha: float, workspace: torch.Tensor, out_dtype: torch.dtype = torch.bfloat16,
-                       rcp_mode: int = L.RCP_APPROX, out: torch.Tensor | None = None, push=None) -> torch.Tensor:
+                       rcp_mode: int = L.RCP_APPROX, out: torch.Tensor | None = None, push=None,
+                       gather: bool = False) -> torch.Tensor:
     """out = linear(silu(gate) * up) with gate_up = [M, 2K] bf16, one launch. With ``push`` (a
-    ``_lib.PeerComm``) the result goes into the peers' receive memory instead of ``out``."""
+    ``_lib.PeerComm``) the result goes into the peers' receive memory instead of ``out``; with
+    ``gather`` as well, the launch also completes the sum over the ranks into ``out``."""
     _need_cuda(gate_up, global_scale_inv, packed, workspace)
     M, K2 = gate_up.shape
     K = K2 // 2
     if out is None:
         out = torch.empty((M, N), dtype=out_dtype, device=gate_up.device)
     pro = L.Prologue(L.PROLOGUE_SILU_MUL, 0.0, None, None, None, None,
-                     None if push is None else C.addressof(push))
+                     None if push is None else C.addressof(push), 1 if (gather and push is not None) else 0)
     with torch.cuda.device(gate_up.device):
         st = L.lib().nvfp4r_linear_packed_ex(C.byref(pro), gate_up.data_ptr(), gate_up.stride(0), M, K,
                                              global_scale_inv.data_ptr(), packed.data_ptr(), N, float(alpha),
@@ -344,13 +346,14 @@ def sample(logits: torch.Tensor, draws: torch.Tensor, *, seed: int = 0,
 
 def linear_packed_push(x: torch.Tensor, global_scale_inv: torch.Tensor, packed: torch.Tensor, N: int,
                        alpha: float, workspace: torch.Tensor, push, out: torch.Tensor,
-                       rcp_mode: int = L.RCP_APPROX) -> torch.Tensor:
+                       rcp_mode: int = L.RCP_APPROX, gather: bool = False) -> torch.Tensor:
     """Row-parallel linear whose bf16 result is pushed into the peers' receive memory tile by
-    tile (``push``: a ``_lib.PeerComm``); ``out`` is only written by the gather half of the
-    all-reduce that must follow."""
+    tile (``push``: a ``_lib.PeerComm``). With ``gather`` the same launch also completes the
+    sum into ``out`` (one GPU per rank required); without it ``out`` is only written by the
+    gather half of the all-reduce that must follow."""
     _need_cuda(x, global_scale_inv, packed, workspace, out)
     M, K = x.shape
-    pro = L.Prologue(L.PROLOGUE_NONE, 0.0, None, None, None, None, C.addressof(push))
+    pro = L.Prologue(L.PROLOGUE_NONE, 0.0, None, None, None, None, C.addressof(push), 1 if gather else 0)
     with torch.cuda.device(x.device):
         st = L.lib().nvfp4r_linear_packed_ex(C.byref(pro), x.data_ptr(), x.stride(0), M, K,
                                              global_scale_inv.data_ptr(), packed.data_ptr(), N, float(alpha),

@@ -354,6 +354,9 @@ int nvfp4r_linear_packed_ex(const nvfp4r_prologue* pro, const void* x, int64_t x
         g.xb = x; g.xb_stride = x_row_stride;
     }
     g.push = (pro->push_to != nullptr && pro->push_to->world > 1) ? pro->push_to : nullptr;
+    g.push_gather = g.push != nullptr && pro->push_gather != 0;
+    if (g.push_gather && M > 32)
+        return fail(NVFP4R_ERR_UNSUPPORTED_SHAPE, "linear_packed_ex: push_gather takes at most 32 rows (one launch)");
     const char* why = nullptr;
     cudaError_t e = nvfp4r::launch_linear_packed(g, as_stream(stream), &why);
     if (why != nullptr) return fail(NVFP4R_ERR_UNSUPPORTED_SHAPE, why);

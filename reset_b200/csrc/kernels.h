@@ -109,6 +109,7 @@ struct PackedLinearArgs {
     float eps;
     // epilogue: push the bf16 result into the peers' receive memory instead of writing `out`
     const nvfp4r_peer_comm* push;
+    bool push_gather;            // finish the all-reduce inside the launch (see nvfp4r_prologue)
 };
 size_t packed_weight_bytes(int N, int K);
 size_t packed_workspace_bytes(int M, int N, int K);
@@ -126,6 +127,7 @@ cudaError_t read_packed_trace(unsigned long long* out16);
 cudaError_t read_and_clear_device_status(int* flag);
 
 cudaError_t read_and_clear_peer_status(int* flag);
+uint32_t peer_poll_limit();      // polls a wait for a peer GPU may take (nvfp4r_set_peer_poll_limit)
 cudaError_t read_and_clear_reset_status(int* flag);
 
 int device_sm_count();

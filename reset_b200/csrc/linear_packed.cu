@@ -87,6 +87,12 @@ struct PackedParams {
     int push_world, push_rank;
     unsigned long long push_max_pairs;
     unsigned char* push_base[NVFP4R_PEER_MAX_WORLD];
+    // push_gather != 0: the thread that pushed a pair also completes it: it polls the W
+    // contributions to that pair in this rank's own receive memory, adds them in rank order in
+    // fp32, rounds once, writes `out` and zeroes the slots, and the last CTA of the grid advances
+    // the call counter - the whole all-reduce inside this launch, no gather kernel after it.
+    int push_gather;
+    uint32_t push_poll_limit;
 };
 
 __device__ int g_packed_status = 0;
@@ -168,6 +174,12 @@ __device__ __forceinline__ void tmem_ld4(uint32_t taddr, float v[4]) {
 __device__ __forceinline__ void slot_store(unsigned long long* p, float v) {
     const unsigned long long w = (1ull << 32) | static_cast<unsigned long long>(__float_as_uint(v));
     asm volatile("st.relaxed.gpu.global.u64 [%0], %1;" :: "l"(p), "l"(w) : "memory");
+}
+// Poll of a slot that a peer GPU writes (system scope).
+__device__ __forceinline__ unsigned long long peer_poll(const unsigned long long* p) {
+    unsigned long long w;
+    asm volatile("ld.relaxed.sys.global.u64 %0, [%1];" : "=l"(w) : "l"(p) : "memory");
+    return w;
 }
 __device__ __forceinline__ unsigned long long slot_load(const unsigned long long* p) {
     unsigned long long w;
@@ -551,6 +563,10 @@ linear_packed_kernel(const __grid_constant__ PackedParams p) {
             }
         }
         __syncwarp();
+        // Which half of the peers' receive memory this call uses: the call counter in this rank's
+        // own header, final before this kernel started (its writer is an earlier kernel).
+        const unsigned push_parity =
+            p.push_world > 1 ? (*reinterpret_cast<volatile unsigned*>(p.push_base[p.push_rank]) & 1u) : 0u;
 #pragma unroll 1
         for (int ti = 0; ti < my_tiles; ++ti) {
             const int buf = ti & 1;
@@ -594,7 +610,6 @@ linear_packed_kernel(const __grid_constant__ PackedParams p) {
                 const float o = val * p.alpha;
                 if (p.push_world > 1) {
                     // adjacent weight rows sit in adjacent lanes: the even lane sends the pair
-                    const unsigned parity = *reinterpret_cast<volatile unsigned*>(p.push_base[p.push_rank]) & 1u;
                     const float o2 = __shfl_down_sync(0xffffffffu, o, 1);
                     if ((lane & 1) == 0) {
                         const unsigned long long w = (1ull << 32) | pack2_bf16(o, o2);
@@ -605,8 +620,38 @@ linear_packed_kernel(const __grid_constant__ PackedParams p) {
                             const int dst = (p.push_rank + d) % p.push_world;
                             unsigned long long* slot =
                                 reinterpret_cast<unsigned long long*>(p.push_base[dst] + 256) +
-                                (static_cast<unsigned long long>(parity) * p.push_world + p.push_rank) * p.push_max_pairs + i;
+                                (static_cast<unsigned long long>(push_parity) * p.push_world + p.push_rank) * p.push_max_pairs + i;
                             asm volatile("st.relaxed.sys.global.u64 [%0], %1;" :: "l"(slot), "l"(w) : "memory");
+                        }
+                        if (p.push_gather) {
+                            unsigned long long* mine =
+                                reinterpret_cast<unsigned long long*>(p.push_base[p.push_rank] + 256) +
+                                static_cast<unsigned long long>(push_parity) * p.push_world * p.push_max_pairs + i;
+                            unsigned long long v[NVFP4R_PEER_MAX_WORLD];
+#pragma unroll
+                            for (int r = 0; r < NVFP4R_PEER_MAX_WORLD; ++r)
+                                if (r < p.push_world) v[r] = peer_poll(mine + r * p.push_max_pairs);
+                            for (uint32_t it = 0;; ++it) {
+                                bool all = true;
+#pragma unroll
+                                for (int r = 0; r < NVFP4R_PEER_MAX_WORLD; ++r)
+                                    if (r < p.push_world && (v[r] >> 32) != 1ull) {
+                                        v[r] = peer_poll(mine + r * p.push_max_pairs);
+                                        all = false;
+                                    }
+                                if (all) break;
+                                if (it > p.push_poll_limit) { wf.failed = true; break; }
+                            }
+                            float lo = 0.0f, hi = 0.0f;
+#pragma unroll
+                            for (int r = 0; r < NVFP4R_PEER_MAX_WORLD; ++r)
+                                if (r < p.push_world) {
+                                    const uint32_t bits = static_cast<uint32_t>(v[r]);
+                                    lo += __uint_as_float(bits << 16);
+                                    hi += __uint_as_float(bits & 0xFFFF0000u);
+                                    mine[r * p.push_max_pairs] = 0ull;
+                                }
+                            static_cast<uint32_t*>(p.out)[i] = pack2_bf16(lo, hi);
                         }
                     }
                 } else {
@@ -629,6 +674,17 @@ linear_packed_kernel(const __grid_constant__ PackedParams p) {
     if (warp == 1) {
         tc_fence_after();
         tmem_dealloc(tmem, kTmemCols);
+    }
+    if (p.push_world > 1 && p.push_gather && tid == 0) {
+        // the last CTA of the grid to finish advances the call counter: nobody of this launch
+        // reads it any more (same rule as the stand-alone gather kernel)
+        unsigned* header = reinterpret_cast<unsigned*>(p.push_base[p.push_rank]);
+        __threadfence();
+        const unsigned t = atomicAdd(header + 1, 1u);
+        if (t == gridDim.x - 1) {
+            header[1] = 0u;
+            header[0] = header[0] + 1u;
+        }
     }
 }
 
@@ -737,6 +793,8 @@ cudaError_t launch_linear_packed(const PackedLinearArgs& g, cudaStream_t stream,
             p.push_rank = g.push->rank;
             p.push_max_pairs = (g.push->max_elems + 1) / 2;
             for (int r = 0; r < g.push->world; ++r) p.push_base[r] = static_cast<unsigned char*>(g.push->base[r]);
+            p.push_gather = g.push_gather ? 1 : 0;
+            p.push_poll_limit = peer_poll_limit();
         }
 
         void (*kern)(PackedParams) = plan.bn == 16 ? linear_packed_kernel<16> : linear_packed_kernel<32>;

@@ -126,6 +126,8 @@ peer_allreduce_kernel(const PeerParams p) {
 
 }  // namespace
 
+uint32_t peer_poll_limit() { return g_peer_poll_limit; }
+
 cudaError_t read_and_clear_peer_status(int* flag) {
     cudaError_t e = cudaMemcpyFromSymbol(flag, g_peer_status, sizeof(int));
     if (e != cudaSuccess) return e;

@@ -83,9 +83,10 @@ class _Linear:
         if rms > 0 and rms == rms:
             self.alpha = 1.0 / rms
 
-    def plain(self, x: torch.Tensor, out: torch.Tensor, push=None) -> torch.Tensor:
+    def plain(self, x: torch.Tensor, out: torch.Tensor, push=None, gather: bool = False) -> torch.Tensor:
         if push is not None and not self.use_gemv:
-            return capi.linear_packed_push(x, self.gs_inv, self.packed, self.N, self.alpha, self.ws.buf, push, out)
+            return capi.linear_packed_push(x, self.gs_inv, self.packed, self.N, self.alpha, self.ws.buf, push, out,
+                                           gather=gather)
         if self.use_gemv:
             return capi.linear(x, self.gs_inv, self.w, self.s, self.alpha, out=out, rcp_mode=L.RCP_APPROX)
         return capi.linear_packed(x, self.gs_inv, self.packed, self.N, self.alpha, self.ws.buf,
@@ -95,9 +96,9 @@ class _Linear:
         return capi.linear_packed_rmsnorm(delta, res_in, res_out, norm_w, eps, self.gs_inv, self.packed,
                                           self.N, self.alpha, self.ws.buf, rcp_mode=L.RCP_APPROX, out=out)
 
-    def after_silu_mul(self, gate_up, out, push=None):
+    def after_silu_mul(self, gate_up, out, push=None, gather: bool = False):
         return capi.linear_packed_silu(gate_up, self.gs_inv, self.packed, self.N, self.alpha, self.ws.buf,
-                                       rcp_mode=L.RCP_APPROX, out=out, push=push)
+                                       rcp_mode=L.RCP_APPROX, out=out, push=push, gather=gather)
 
     def weight_bytes(self) -> int:
         return self.N * self.K * 9 // 16
@@ -119,7 +120,8 @@ class Workspace:
 
 class DecodeStep:
     def __init__(self, cfg: DecodeConfig, device, rank: int = 0, world: int = 1, seed: int = 0,
-                 process_group=None, fused: bool = True, peer_allreduce: bool = True):
+                 process_group=None, fused: bool = True, peer_allreduce: bool = True,
+                 fused_gather: bool = True, skip_exchange: bool = False):
         if cfg.q_heads % world or cfg.kv_heads % world or cfg.intermediate % world or cfg.vocab % world:
             raise ValueError("tensor-parallel degree must divide heads, intermediate and vocab")
         self.cfg, self.device, self.rank, self.world, self.pg = cfg, torch.device(device), rank, world, process_group
@@ -176,8 +178,16 @@ class DecodeStep:
         self.rope_table = torch.stack([torch.cos(ang), torch.sin(ang)], dim=-1).contiguous()
         L.check(L.lib().nvfp4r_set_rope_table(self.rope_table.data_ptr(), cfg.context), "set_rope_table")
         # the sum exchange after o_proj / down_proj: one-shot kernel over peer memory, or NCCL
+        # fused_gather: the row-parallel linear's own launch completes the all-reduce (push in the
+        # epilogue, then the pushing thread sums the ranks' contributions); off = push in the
+        # epilogue + one gather launch per exchange
+        self.fused_gather = bool(fused_gather)
+        # skip_exchange: one rank's shard of a tensor-parallel model on a single GPU with the sum
+        # exchanges and the logits gather left out (timing / profiling of the compute only; the
+        # values are those of the rank's partial sums)
+        self.skip_exchange = bool(skip_exchange)
         self.peer = None
-        if world > 1 and peer_allreduce:
+        if world > 1 and peer_allreduce and not skip_exchange:
             from .comm import PeerAllReduce
             self.peer = PeerAllReduce(self.device, H, group=process_group)
         self._calibrate()
@@ -248,7 +258,11 @@ class DecodeStep:
                                        self.attn_ws.numel() * 4, self._stream()), "attn_decode")
 
     def _all_reduce(self, t, pushed: bool = False):
+        if self.skip_exchange:
+            return
         if self.peer is not None:
+            if pushed and self.fused_gather:
+                return                        # the linear's launch pushed AND summed: nothing left to do
             if pushed:
                 self.peer.gather_(t)          # the linear's epilogue already pushed the contributions
             else:
@@ -283,14 +297,14 @@ class DecodeStep:
                 layer["qkv"].plain(self.normed, self.qkv_out)
             self._attention(layer, self.qkv_out)
             push = self._push(layer["o"])
-            layer["o"].plain(self.attn, self.o_out, push=push)
+            layer["o"].plain(self.attn, self.o_out, push=push, gather=self.fused_gather)
             self._all_reduce(self.o_out, pushed=push is not None)
             if self.fused:
                 layer["gate_up"].after_rmsnorm(self.o_out, self.res[cur], self.res[1 - cur], layer["ln2"], c.eps,
                                                self.gu_out)
                 cur = 1 - cur
                 push = self._push(layer["down"])
-                layer["down"].after_silu_mul(self.gu_out, self.down_out, push=push)
+                layer["down"].after_silu_mul(self.gu_out, self.down_out, push=push, gather=self.fused_gather)
             else:
                 push = None
                 self._add_rmsnorm(self.o_out, self.res[cur], layer["ln2"])
@@ -303,7 +317,7 @@ class DecodeStep:
         self._add_rmsnorm(x, self.res[cur], self.final_ln)
         L.check(lib.nvfp4r_lm_head(self.normed.data_ptr(), self.lm_head.data_ptr(), self.logits_local.data_ptr(),
                                    self.vocab_local, c.hidden, self._stream()), "lm_head")
-        if self.world > 1:
+        if self.world > 1 and not self.skip_exchange:
             torch.distributed.all_gather_into_tensor(self.logits.view(-1), self.logits_local.view(-1), group=self.pg)
             full = self.logits
         else:
@@ -317,7 +331,7 @@ class DecodeStep:
                                         n_id_sets=d.n_id_sets, decisions=d.decisions, workspace=d.workspace)
             capi.sample(full, self.draws, seed=self.sample_seed, last_ids=self.last_ids, out=self.token)
             return
-        L.check(lib.nvfp4r_argmax(full.data_ptr(), full.stride(0), 1, c.vocab, self.token.data_ptr(),
+        L.check(lib.nvfp4r_argmax(full.data_ptr(), full.stride(0), 1, full.shape[1], self.token.data_ptr(),
                                   self._stream()), "argmax")
 
     def _calibrate(self) -> None:
@@ -379,4 +393,18 @@ class DecodeStep:
         return lin + kv + self.vocab_local * c.hidden * 2
 
     def kernels_per_step(self) -> int:
-        return self.cfg.layers * (5 if self.fused else 9) + 5 + (1 if self.reset is not None else 0)
+        """Launches of this library per token on this rank (the logits all-gather of a
+        tensor-parallel run is NCCL's and not counted)."""
+        per_layer = 5 if self.fused else 9
+        if self.world > 1:
+            if self.peer is None:
+                per_layer += 0                                   # two NCCL all-reduces, not ours
+            else:
+                # o_proj / down_proj each: nothing extra when the linear's launch completes the
+                # all-reduce, one gather launch after a pushing linear, one all-reduce launch
+                # after a GEMV-sized linear
+                probe = self.layers[0]
+                for name in ("o", "down"):
+                    pushed = not probe[name].use_gemv and (self.fused or name == "o")
+                    per_layer += 0 if (pushed and self.fused_gather) else 1
+        return self.cfg.layers * per_layer + 5 + (1 if self.reset is not None else 0)

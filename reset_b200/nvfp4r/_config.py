@@ -12,17 +12,24 @@ ENABLE_GEMM_PATH = os.environ.get("NVFP4R_ENABLE_GEMM", "1") == "1"
 # when importable (the reference's fallback branch), "none" = always this library's kernels.
 FALLBACK_BACKEND = os.environ.get("NVFP4R_FALLBACK_BACKEND", "vllm-cutlass").lower()
 
-# Measured crossover between the CUDA-core GEMV and the packed tensor-core linear on
-# B200 (L2-cold weights, CUDA-graph replay): the GEMV's shorter fixed latency wins only
-# for the smallest batches on weights of at most this many bytes; everything else goes
-# to the tensor cores. Index = M.
-GEMV_MAX_WEIGHT_BYTES = {1: 11_000_000, 2: 5_000_000, 3: 2_500_000, 4: 2_500_000}
-# Single-token launches with at least GEMV_WIDE_MIN_N rows of at most GEMV_WIDE_MAX_K elements
-# run the GEMV with three CTAs per SM (24 warps instead of 8 hide its decode latency); there it
-# stays ahead of the tensor-core kernel up to GEMV_WIDE_MAX_WEIGHT_BYTES (6144x4096: 5.0 vs
-# 5.6 us, 8192x4096: 6.05 vs 6.35 us; 12288x4096: 7.7 vs 7.3 us, 7168x5120: 7.1 vs 6.6 us).
-GEMV_WIDE_MIN_N = 6144
-GEMV_WIDE_MAX_K = 4096
-GEMV_WIDE_MAX_WEIGHT_BYTES = 19_000_000
+# Measured crossover between the CUDA-core GEMV and the packed tensor-core linear on B200
+# (L2-cold weights, CUDA-graph replay; Qwen3-8B / 14B / 32B shapes and their tensor-parallel
+# shards at TP 2 / 4 / 8). The GEMV's shorter fixed latency wins for single tokens on weights up
+# to GEMV_MAX_WEIGHT_BYTES[1] (3584x5120 4.6 vs 5.1 us, 8704x5120 6.5 vs 6.9 us, 10240x5120 8.1
+# vs 8.6 us, 4096x12288 7.5 vs 8.0 us; level at 17408x5120 and above), and for two to four tokens
+# only on the smallest weights with short rows; everything else goes to the tensor cores (every
+# M >= 2 of the 14B sweep). Index = M.
+GEMV_MAX_WEIGHT_BYTES = {1: 30_000_000, 2: 5_000_000, 3: 2_500_000, 4: 2_500_000}
 # ... and, above one token, only for short rows (the GEMV's time grows with M * K per row)
 GEMV_MAX_K_MULTI_TOKEN = 2048
+# Rows shorter than this stay on the tensor cores at every M (5120x640: 3.6 vs 3.8 us).
+GEMV_MIN_K = 1024
+# The ring kernel deals groups of 4 rows to GEMV_RING_WARPS warps; with N between 4 and 5 times
+# that count a second round runs on under a quarter of the warps and the tensor cores win unless
+# the rows are short (5120x2560 4.4 vs 4.8 us, 5120x5120 5.4 vs 7.5 us; 5120x1280 3.9 vs 3.2 us).
+GEMV_RING_WARPS = 148 * 8
+GEMV_SHORT_ROW_K = 1280
+
+# Tensor-parallel row-parallel linears: complete the all-reduce inside the linear's own launch
+# (1) or push in the epilogue and gather in a second launch (0).
+FUSED_GATHER = os.environ.get("NVFP4R_FUSED_GATHER", "1") == "1"

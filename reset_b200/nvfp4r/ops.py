@@ -71,15 +71,16 @@ def linear_packed(x: torch.Tensor, global_scale_inv: torch.Tensor, packed: torch
 def use_gemv(M: int, N: int, K: int, gemv_max_m: int) -> bool:
     """The measured crossover: True when the CUDA-core GEMV is the faster path."""
     from . import _config
-    if M > gemv_max_m:
+    if M > gemv_max_m or M not in _config.GEMV_MAX_WEIGHT_BYTES:
         return False
-    if K % 256:
-        return False     # the streaming GEMV wants K % 256 == 0; its plain-load fallback is slow
-    limit = _config.GEMV_MAX_WEIGHT_BYTES.get(M)
-    if (M == 1 and N >= _config.GEMV_WIDE_MIN_N and K <= _config.GEMV_WIDE_MAX_K
-            and N * K * 9 // 16 <= _config.GEMV_WIDE_MAX_WEIGHT_BYTES):
-        return True
-    if limit is None or N * K * 9 // 16 > limit:
+    if K % 32 or K < _config.GEMV_MIN_K:
+        return False
+    if M > 1 and K % 256:
+        return False     # above one token the ring kernel is the GEMV, and it wants K % 256 == 0
+    ring = _config.GEMV_RING_WARPS
+    if 4 * ring < N <= 5 * ring and K > _config.GEMV_SHORT_ROW_K:
+        return False
+    if N * K * 9 // 16 > _config.GEMV_MAX_WEIGHT_BYTES[M]:
         return False
     return M == 1 or K <= _config.GEMV_MAX_K_MULTI_TOKEN
 
@@ -128,6 +129,10 @@ def linear_auto(x, global_scale_inv, weight, weight_scale_flat, packed, N: int, 
             capi.linear(x, global_scale_inv, weight, weight_scale_flat, alpha, out=out, rcp_mode=rcp_mode)
             return reduce.all_reduce_(out)
         ws = _out_workspace(x.device, L.lib().nvfp4r_linear_packed_workspace_bytes(M, N, K))
+        # push in the epilogue and, in the same launch, the sum over the ranks (one GPU per rank)
+        if M <= 32 and _config.FUSED_GATHER:
+            return capi.linear_packed_push(x, global_scale_inv, packed, N, alpha, ws, reduce.comm, out,
+                                           rcp_mode=rcp_mode, gather=True)
         capi.linear_packed_push(x, global_scale_inv, packed, N, alpha, ws, reduce.comm, out, rcp_mode=rcp_mode)
         return reduce.gather_(out)
     if out is None:

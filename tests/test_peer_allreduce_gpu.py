@@ -127,6 +127,91 @@ def test_two_processes_two_gpus(tmp_path):
     assert r.returncode == 0 and r.stdout.count("PEER_OK") == 2, (r.stdout[-2000:], r.stderr[-3000:])
 
 
+_CHILD_FUSED = r"""
+import os, sys
+sys.path.insert(0, os.environ["REPO"])
+import torch, torch.distributed as dist
+rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+dev = torch.device("cuda", rank); torch.cuda.set_device(dev)
+dist.init_process_group("nccl", device_id=dev)
+from reset_b200.comm import PeerAllReduce
+from reset_b200 import _lib as L, capi
+from reset_b200 import nvfp4r
+ar = PeerAllReduce(dev, 8 * 5120)
+ok = True
+gs = torch.tensor([60.0], device=dev)
+gen = torch.Generator(device=dev).manual_seed(7 + rank)
+# row-parallel shards of o_proj / down_proj at TP 2: every rank holds its own K slice
+for N, K, M in [(5120, 4096, 1), (5120, 12800, 1), (5120, 4096, 8), (4096, 2048, 3), (5120, 12800, 2)]:
+    w = torch.randint(0, 256, (N, K // 2), dtype=torch.uint8, device=dev, generator=gen)
+    s = torch.randint(1, 0x38, (N, K // 16), dtype=torch.uint8, device=dev, generator=gen)
+    packed = capi.pack_weight(w, s)
+    x = torch.randn(M, K, device=dev, generator=gen).to(torch.bfloat16)
+    wk = capi.packed_workspace(M, N, K, dev)
+    part = capi.linear_packed(x, gs, packed, N, 0.01, wk, rcp_mode=1)            # this rank's bf16 partial
+    parts = [torch.empty_like(part) for _ in range(world)]
+    dist.all_gather(parts, part)
+    acc = torch.zeros_like(part, dtype=torch.float32)
+    for p in parts: acc += p.float()
+    want = acc.to(torch.bfloat16)
+    for rep in range(3):                                                         # both halves of the double buffer
+        out = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device=dev)
+        capi.linear_packed_push(x, gs, packed, N, 0.01, wk, ar.comm, out, rcp_mode=1, gather=True)
+        torch.cuda.synchronize()
+        ok = ok and torch.equal(out, want)
+    ok = ok and int(wk.count_nonzero().item()) == 0
+    # interleaved with the two-launch form and the stand-alone all-reduce: one call counter serves all
+    out2 = torch.empty_like(out)
+    capi.linear_packed_push(x, gs, packed, N, 0.01, wk, ar.comm, out2, rcp_mode=1)
+    ar.gather_(out2)
+    mine = part.clone(); ar.all_reduce_(mine)
+    torch.cuda.synchronize()
+    ok = ok and torch.equal(out2, want) and torch.equal(mine, want)
+# through the public call, captured and replayed
+N, K, M = 5120, 4096, 1
+w = torch.randint(0, 256, (N, K // 2), dtype=torch.uint8, device=dev, generator=gen)
+s = torch.randint(1, 0x38, (N, K // 16), dtype=torch.uint8, device=dev, generator=gen)
+packed = capi.pack_weight(w, s)
+x = torch.randn(M, K, device=dev, generator=gen).to(torch.bfloat16)
+part = nvfp4r.linear_auto(x, gs, None, None, packed, N, 0.01)
+parts = [torch.empty_like(part) for _ in range(world)]
+dist.all_gather(parts, part)
+want = sum(p.float() for p in parts).to(torch.bfloat16)
+out = torch.zeros((M, N), dtype=torch.bfloat16, device=dev)
+nvfp4r.linear_auto(x, gs, None, None, packed, N, 0.01, out=out, reduce=ar)
+side = torch.cuda.Stream(); side.wait_stream(torch.cuda.current_stream())
+with torch.cuda.stream(side):
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g, stream=side):
+        for _ in range(3):
+            nvfp4r.linear_auto(x, gs, None, None, packed, N, 0.01, out=out, reduce=ar)
+torch.cuda.current_stream().wait_stream(side)
+for _ in range(4):
+    out.zero_(); g.replay(); torch.cuda.synchronize()
+    ok = ok and torch.equal(out, want)
+L.check(L.lib().nvfp4r_check_device_status(), "status")
+flag = torch.tensor([1 if ok else 0], device=dev); dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+dist.barrier(); torch.cuda.synchronize()
+print("FUSED_OK" if int(flag.item()) == 1 else "FUSED_MISMATCH", flush=True)
+os._exit(0 if int(flag.item()) == 1 else 1)
+"""
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_linear_completes_the_all_reduce_in_its_own_launch_two_gpus(tmp_path):
+    """Row-parallel linear with push AND sum in one launch (``push_gather``) on two GPUs: equal,
+    bit for bit, to the rank-ordered fp32 sum of the ranks' bf16 partial results, for both halves
+    of the double-buffered receive memory, mixed with the two-launch form and the stand-alone
+    all-reduce, and under CUDA-graph replay through ``nvfp4r.linear_auto(..., reduce=)``."""
+    script = tmp_path / "child_fused.py"
+    script.write_text(_CHILD_FUSED)
+    env = dict(os.environ, REPO=str(REPO), NCCL_NVLS_ENABLE="0")
+    r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2",
+                        "--master-addr", "127.0.0.1", "--master-port", "29534", str(script)],
+                       env=env, capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0 and r.stdout.count("FUSED_OK") == 2, (r.stdout[-2000:], r.stderr[-3000:])
+
+
 @pytest.mark.parametrize("M", [1, 3, 8])
 def test_linear_push_epilogue_emulated_ranks(M):
     """Row-parallel linear with the PUSH half of the all-reduce fused into its epilogue
