@@ -519,6 +519,23 @@ NVFP4R_API int nvfp4r_argmax(const float* logits, int64_t row_stride, int B, int
 NVFP4R_API int nvfp4r_sample(const float* logits, int64_t row_stride, int B, int V, uint64_t seed,
                              uint64_t* draws, int32_t* last_ids, int32_t* out, void* stream);
 
+/* The same draw restricted to the top-k and / or top-p (nucleus) set of every row, as vLLM's
+ * sampler applies them behind the processor: top-k first (the k largest logits; keys equal to the
+ * k-th are all kept), then top-p on the distribution renormalised over that set (the smallest set
+ * of largest probabilities whose mass reaches top_p). top_k <= 0 or >= V and top_p >= 1 switch the
+ * respective truncation off; with both off this is nvfp4r_sample. The sets are found by a radix
+ * descent over order-preserving keys of the logits (three levels of 2048-bin histograms of count
+ * and fixed-point probability mass, integer atomics: the result does not depend on the order of
+ * the additions), then the Gumbel-max draw skips everything below the threshold key.
+ *   workspace  >= nvfp4r_sample_workspace_bytes(B) bytes, 8-byte aligned, ALL ZERO before its first
+ *              use; every call leaves the histograms zeroed. Calls that share it must be ordered.
+ * No counterpart in the reference (vLLM owns the sampler there, reset/README.md:87-88). */
+NVFP4R_API size_t nvfp4r_sample_workspace_bytes(int B);
+NVFP4R_API int nvfp4r_sample_top_k_top_p(const float* logits, int64_t row_stride, int B, int V,
+                                         int top_k, float top_p, uint64_t seed, uint64_t* draws,
+                                         int32_t* last_ids, int32_t* out, void* workspace,
+                                         size_t workspace_bytes, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -100,6 +100,8 @@ PROTOTYPES = {
     "nvfp4r_lm_head": (_i, [_vp, _vp, _vp, _i, _i, _vp]),
     "nvfp4r_argmax": (_i, [_vp, _i64, _i, _i, _vp, _vp]),
     "nvfp4r_sample": (_i, [_vp, _i64, _i, _i, C.c_uint64, _vp, _vp, _vp, _vp]),
+    "nvfp4r_sample_workspace_bytes": (_sz, [_i]),
+    "nvfp4r_sample_top_k_top_p": (_i, [_vp, _i64, _i, _i, _i, C.c_float, C.c_uint64, _vp, _vp, _vp, _vp, _sz, _vp]),
     "nvfp4r_peer_buffer_bytes": (_sz, [_i, _sz]),
     "nvfp4r_peer_alloc": (_i, [_sz, C.POINTER(C.c_void_p), C.c_char_p]),
     "nvfp4r_peer_open": (_i, [C.c_char_p, C.POINTER(C.c_void_p)]),

@@ -321,11 +321,14 @@ def reset_step_per_request(logits: torch.Tensor, states: torch.Tensor, slot_para
 
 
 def sample(logits: torch.Tensor, draws: torch.Tensor, *, seed: int = 0,
-           last_ids: torch.Tensor | None = None, out: torch.Tensor | None = None) -> torch.Tensor:
+           last_ids: torch.Tensor | None = None, out: torch.Tensor | None = None,
+           top_k: int = 0, top_p: float = 1.0, workspace: torch.Tensor | None = None) -> torch.Tensor:
     """One id per row drawn from softmax(logits) on the device (Gumbel-max). ``draws`` is an
     int64 [B] counter tensor (zero at request start, advanced by the call); ``last_ids``
-    (int32 [B,2], optional) gets the new id shifted in. Returns int32 [B]."""
-    _need_cuda(logits, draws, last_ids, out)
+    (int32 [B,2], optional) gets the new id shifted in. Returns int32 [B]. ``top_k`` (> 0) and
+    ``top_p`` (< 1) restrict the draw to vLLM's top-k / nucleus set; they need ``workspace``
+    (:func:`sample_workspace`)."""
+    _need_cuda(logits, draws, last_ids, out, workspace)
     if logits.dtype != torch.float32 or logits.dim() != 2 or logits.stride(1) != 1:
         raise ValueError("sample: logits must be fp32 [B,V] with unit inner stride")
     B, V = logits.shape
@@ -336,12 +339,27 @@ def sample(logits: torch.Tensor, draws: torch.Tensor, *, seed: int = 0,
         raise ValueError("sample: last_ids must be contiguous int32 [B,2]")
     if out is None:
         out = torch.empty(B, dtype=torch.int32, device=logits.device)
+    truncated = (0 < int(top_k) < V) or float(top_p) < 1.0
+    if truncated and workspace is None:
+        raise ValueError("sample: top_k / top_p need a workspace (capi.sample_workspace)")
     with torch.cuda.device(logits.device):
-        st = L.lib().nvfp4r_sample(logits.data_ptr(), logits.stride(0), B, V, int(seed) & (2 ** 64 - 1),
-                                   draws.data_ptr(), None if last_ids is None else last_ids.data_ptr(),
-                                   out.data_ptr(), _stream())
+        if truncated:
+            st = L.lib().nvfp4r_sample_top_k_top_p(
+                logits.data_ptr(), logits.stride(0), B, V, int(top_k), float(top_p), int(seed) & (2 ** 64 - 1),
+                draws.data_ptr(), None if last_ids is None else last_ids.data_ptr(), out.data_ptr(),
+                workspace.data_ptr(), workspace.numel() * workspace.element_size(), _stream())
+        else:
+            st = L.lib().nvfp4r_sample(logits.data_ptr(), logits.stride(0), B, V, int(seed) & (2 ** 64 - 1),
+                                       draws.data_ptr(), None if last_ids is None else last_ids.data_ptr(),
+                                       out.data_ptr(), _stream())
     L.check(st, "nvfp4r_sample")
     return out
+
+
+def sample_workspace(B: int, device) -> torch.Tensor:
+    """Zeroed scratch of ``sample(..., top_k=, top_p=)`` for up to ``B`` rows."""
+    n = L.lib().nvfp4r_sample_workspace_bytes(B)
+    return torch.zeros((n + 7) // 8, dtype=torch.int64, device=device)
 
 
 def linear_packed_push(x: torch.Tensor, global_scale_inv: torch.Tensor, packed: torch.Tensor, N: int,

@@ -497,10 +497,34 @@ __device__ __forceinline__ float gumbel_noise(unsigned long long key, int i) {
 
 // kGumbel: the slice's maximum of logits[i] + Gumbel noise (sampling from softmax(logits) by
 // the Gumbel-max rule) instead of the plain maximum.
+// Order-preserving map of a float onto an unsigned key (larger value, larger key): the top-k /
+// top-p truncation selects on these keys with a radix descent.
+__device__ __forceinline__ uint32_t sortable_key(float x) {
+    const uint32_t u = __float_as_uint(x);
+    return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+}
+
+// Per-row state of the truncated sampler, in caller scratch (all zero before its first use;
+// every call leaves the histograms zeroed again).
+constexpr int kSampleBins = 2048;
+struct SampleRow {
+    unsigned long long mass[kSampleBins];   // fixed-point sum of exp(x - max) per bin
+    unsigned int count[kSampleBins];
+    unsigned long long above_mass;          // mass of the keys above the current prefix
+    unsigned long long target_mass;         // top_p * (mass of the candidate set)
+    unsigned long long set_mass;            // mass of the keys kept by top-k (candidate set of top-p)
+    unsigned int above_count;
+    unsigned int prefix;                    // the high bits selected so far
+    unsigned int min_key;                   // candidates have key >= min_key (result of top-k)
+    unsigned int thr_key;                   // final threshold: sample among key >= thr_key
+    unsigned int all;                       // 1: truncation keeps everything left (no bin reached the target)
+    unsigned int pad;
+};
+
 template <bool kGumbel>
 __global__ void __launch_bounds__(256)
 argmax_partial_kernel(const float* __restrict__ logits, int64_t row_stride, int V, unsigned long long seed,
-                      const unsigned long long* __restrict__ draws) {
+                      const unsigned long long* __restrict__ draws, const SampleRow* __restrict__ trunc) {
     __shared__ float smax[8];
     __shared__ int sarg[8];
     pdl_wait_prior();
@@ -512,9 +536,13 @@ argmax_partial_kernel(const float* __restrict__ logits, int64_t row_stride, int 
     unsigned long long key = 0;
     if (kGumbel)
         key = mix64(seed ^ mix64((static_cast<unsigned long long>(blockIdx.y) << 40) + draws[blockIdx.y]));
+    const uint32_t thr = (kGumbel && trunc != nullptr) ? trunc[blockIdx.y].thr_key : 0u;
     for (int i = lo + threadIdx.x; i < hi; i += blockDim.x) {
         float v = row[i];
-        if (kGumbel) v += gumbel_noise(key, i);
+        if (kGumbel) {
+            if (sortable_key(v) < thr) continue;           // outside the top-k / top-p set
+            v += gumbel_noise(key, i);
+        }
         if (v > best) { best = v; arg = i; }
     }
     argmax_block_reduce(best, arg, smax, sarg);
@@ -544,6 +572,161 @@ argmax_final_kernel(int* __restrict__ out, unsigned long long* __restrict__ draw
             last_ids[2 * blockIdx.x] = last_ids[2 * blockIdx.x + 1];
             last_ids[2 * blockIdx.x + 1] = arg;
         }
+    }
+}
+
+// ---- top-k / top-p truncation: radix descent over the sortable keys ---------------------------
+// Three levels (11 + 11 + 10 key bits). A level is two launches: sample_hist_kernel adds count and
+// fixed-point probability mass of the keys that share the prefix found so far into 2048 bins,
+// sample_select_kernel walks the bins from the top and picks the one in which the running count
+// reaches k (top-k) or the running mass reaches top_p * (mass of the candidate set) (top-p),
+// extends the prefix and zeroes the bins. After the last level the prefix IS the key of the last
+// token kept; keys equal to it are all kept (ties are not split). Mass is exp(x - row max) scaled by
+// 2^32 and truncated to an integer, summed with integer atomics: the result does not depend on the
+// order of the additions, so the draw is reproducible.
+__host__ __device__ constexpr int level_shift(int level) { return level == 0 ? 21 : (level == 1 ? 10 : 0); }
+__host__ __device__ constexpr int level_bins(int level) { return level == 2 ? 1024 : 2048; }
+
+__global__ void __launch_bounds__(256)
+sample_hist_kernel(const float* __restrict__ logits, int64_t row_stride, int V, SampleRow* __restrict__ rows,
+                   int level) {
+    __shared__ unsigned long long s_mass[kSampleBins];
+    __shared__ unsigned int s_cnt[kSampleBins];
+    __shared__ float s_max;
+    pdl_launch_dependents();
+    pdl_wait_prior();
+    SampleRow* r = rows + blockIdx.y;
+    if (r->all) return;
+    for (int i = threadIdx.x; i < kSampleBins; i += blockDim.x) { s_mass[i] = 0ull; s_cnt[i] = 0u; }
+    if (threadIdx.x < 32) {
+        float m = fmaxf(g_argmax_val[blockIdx.y * kArgmaxParts + threadIdx.x],
+                        g_argmax_val[blockIdx.y * kArgmaxParts + 32 + threadIdx.x]);
+        m = warp_max_f(m);
+        if (threadIdx.x == 0) s_max = m;
+    }
+    __syncthreads();
+    const float m = s_max;
+    const float* row = logits + blockIdx.y * row_stride;
+    const int per = (V + kArgmaxParts - 1) / kArgmaxParts;
+    const int lo = blockIdx.x * per, hi = min(V, lo + per);
+    const uint32_t prefix = r->prefix, min_key = r->min_key;
+    const int shift = level_shift(level);
+    const int prev_shift = level == 0 ? 31 : level_shift(level - 1);
+    for (int i = lo + threadIdx.x; i < hi; i += blockDim.x) {
+        const float x = row[i];
+        if (!(x > -INFINITY)) continue;                               // -inf and NaN never enter the set
+        const uint32_t key = sortable_key(x);
+        if (key < min_key) continue;
+        if (level > 0 && (key >> prev_shift) != prefix) continue;
+        const int bin = static_cast<int>((key >> shift) & static_cast<uint32_t>(level_bins(level) - 1));
+        const unsigned long long w = __float2ull_rd(__expf(x - m) * 4294967296.0f);
+        atomicAdd(&s_mass[bin], w);
+        atomicAdd(&s_cnt[bin], 1u);
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < kSampleBins; i += blockDim.x)
+        if (s_cnt[i] != 0u) {
+            atomicAdd(&r->mass[i], s_mass[i]);
+            atomicAdd(&r->count[i], s_cnt[i]);
+        }
+}
+
+// mode 0: top-k (by count, k > 0); mode 1: top-p (by mass). One CTA of 1024 threads per row, thread t
+// owns bins 2047 - 2t and 2046 - 2t (descending order).
+__global__ void __launch_bounds__(1024)
+sample_select_kernel(SampleRow* __restrict__ rows, int level, int mode, int k, float top_p) {
+    __shared__ unsigned long long s_wm[32], s_wc[32];
+    __shared__ int s_pick;
+    pdl_launch_dependents();
+    pdl_wait_prior();
+    SampleRow* r = rows + blockIdx.x;
+    if (r->all) return;
+    const int t = threadIdx.x, lane = t & 31, warp = t >> 5;
+    const int b0 = kSampleBins - 1 - 2 * t, b1 = b0 - 1;
+    const unsigned long long m0 = r->mass[b0], m1 = r->mass[b1];
+    const unsigned long long c0 = r->count[b0], c1 = r->count[b1];
+    if (t == 0) s_pick = 0x7fffffff;
+    // inclusive scan (descending bins) of mass and count over the block
+    unsigned long long sm = m0 + m1, sc = c0 + c1;
+#pragma unroll
+    for (int d = 1; d < 32; d <<= 1) {
+        const unsigned long long om = __shfl_up_sync(0xffffffffu, sm, d), oc = __shfl_up_sync(0xffffffffu, sc, d);
+        if (lane >= d) { sm += om; sc += oc; }
+    }
+    if (lane == 31) { s_wm[warp] = sm; s_wc[warp] = sc; }
+    __syncthreads();
+    if (warp == 0) {
+        unsigned long long wm = s_wm[lane], wc = s_wc[lane];
+#pragma unroll
+        for (int d = 1; d < 32; d <<= 1) {
+            const unsigned long long om = __shfl_up_sync(0xffffffffu, wm, d), oc = __shfl_up_sync(0xffffffffu, wc, d);
+            if (lane >= d) { wm += om; wc += oc; }
+        }
+        s_wm[lane] = wm;
+        s_wc[lane] = wc;
+    }
+    __syncthreads();
+    const unsigned long long base_m = warp > 0 ? s_wm[warp - 1] : 0ull, base_c = warp > 0 ? s_wc[warp - 1] : 0ull;
+    const unsigned long long incl1_m = base_m + sm, incl1_c = base_c + sc;           // through bin b1
+    const unsigned long long incl0_m = incl1_m - m1, incl0_c = incl1_c - c1;         // through bin b0
+    const unsigned long long total_m = s_wm[31];
+    unsigned long long target = r->target_mass;
+    if (mode == 1 && level == 0) {
+        // candidate set = everything counted at level 0 (the top-k set when top-k ran before)
+        target = static_cast<unsigned long long>(ceil(static_cast<double>(top_p) * static_cast<double>(total_m)));
+        if (target < 1ull) target = 1ull;
+    }
+    const unsigned long long am = r->above_mass;
+    const unsigned int ac = r->above_count;
+    auto reached = [&](unsigned long long im, unsigned long long ic) {
+        return mode == 0 ? (ac + ic >= static_cast<unsigned long long>(k)) : (am + im >= target);
+    };
+    int mine = 0x7fffffff;                    // position in descending order of the first bin that reaches the goal
+    if (c0 != 0ull && reached(incl0_m, incl0_c)) mine = 2 * t;
+    else if (c1 != 0ull && reached(incl1_m, incl1_c)) mine = 2 * t + 1;
+    if (mine != 0x7fffffff) atomicMin(&s_pick, mine);
+    __syncthreads();
+    const int pick = s_pick;
+    // zero this level's bins for the next level / the next call
+    r->mass[b0] = 0ull; r->mass[b1] = 0ull; r->count[b0] = 0u; r->count[b1] = 0u;
+    if (pick == 0x7fffffff) {
+        // the goal is never reached (fewer finite candidates than k): keep everything that is left
+        if (t == 0) { r->all = 1u; r->thr_key = r->min_key; }
+        return;
+    }
+    if (pick == 2 * t || pick == 2 * t + 1) {
+        const bool first = pick == 2 * t;
+        const int bin = first ? b0 : b1;
+        const unsigned long long strictly_m = (first ? incl0_m - m0 : incl1_m - m1);
+        const unsigned long long strictly_c = (first ? incl0_c - c0 : incl1_c - c1);
+        const unsigned long long bin_m = first ? m0 : m1;
+        const int bits = level == 2 ? 10 : 11;
+        const unsigned int prefix = (level == 0 ? 0u : (r->prefix << bits)) | static_cast<unsigned int>(bin);
+        r->prefix = prefix;
+        r->above_mass = am + strictly_m;
+        r->above_count = ac + static_cast<unsigned int>(strictly_c);
+        if (mode == 1 && level == 0) r->target_mass = target;
+        if (level == 2) {
+            r->thr_key = prefix;
+            if (mode == 0) {              // top-k done: its set is the candidate set of a following top-p
+                r->min_key = prefix;
+                r->set_mass = am + strictly_m + bin_m;
+            }
+            r->prefix = 0u; r->above_mass = 0ull; r->above_count = 0u; r->target_mass = 0ull;
+        }
+    }
+}
+
+// Start of a call (keep_set = 0: no truncation decided yet; the histograms are zero already) or
+// of the top-p descent after top-k (keep_set = 1: the top-k set stays, the descent state restarts).
+__global__ void sample_reset_kernel(SampleRow* __restrict__ rows, int keep_set) {
+    pdl_launch_dependents();
+    pdl_wait_prior();
+    SampleRow* r = rows + blockIdx.x;
+    if (threadIdx.x == 0) {
+        r->above_mass = 0ull; r->target_mass = 0ull;
+        r->above_count = 0u; r->prefix = 0u; r->all = 0u;
+        if (!keep_set) { r->set_mass = 0ull; r->min_key = 0u; r->thr_key = 0u; }
     }
 }
 
@@ -678,7 +861,8 @@ int nvfp4r_argmax(const float* logits, int64_t row_stride, int B, int V, int32_t
     if (!logits || !out || B <= 0 || V <= 0) return NVFP4R_ERR_INVALID_ARGUMENT;
     if (B > kArgmaxMaxRows) return NVFP4R_ERR_UNSUPPORTED_SHAPE;
     cudaError_t e = launch_pdl(argmax_partial_kernel<false>, dim3(kArgmaxParts, B), dim3(256), 0, st(stream), logits,
-                               row_stride, V, 0ull, static_cast<const unsigned long long*>(nullptr));
+                               row_stride, V, 0ull, static_cast<const unsigned long long*>(nullptr),
+                               static_cast<const SampleRow*>(nullptr));
     if (e != cudaSuccess) return NVFP4R_ERR_CUDA;
     return done(launch_pdl(argmax_final_kernel, dim3(B), dim3(kArgmaxParts), 0, st(stream), out,
                            static_cast<unsigned long long*>(nullptr), static_cast<int*>(nullptr)));
@@ -690,7 +874,48 @@ int nvfp4r_sample(const float* logits, int64_t row_stride, int B, int V, uint64_
     if (B > kArgmaxMaxRows) return NVFP4R_ERR_UNSUPPORTED_SHAPE;
     cudaError_t e = launch_pdl(argmax_partial_kernel<true>, dim3(kArgmaxParts, B), dim3(256), 0, st(stream), logits,
                                row_stride, V, static_cast<unsigned long long>(seed),
-                               reinterpret_cast<const unsigned long long*>(draws));
+                               reinterpret_cast<const unsigned long long*>(draws),
+                               static_cast<const SampleRow*>(nullptr));
+    if (e != cudaSuccess) return NVFP4R_ERR_CUDA;
+    return done(launch_pdl(argmax_final_kernel, dim3(B), dim3(kArgmaxParts), 0, st(stream), out,
+                           reinterpret_cast<unsigned long long*>(draws), last_ids));
+}
+
+size_t nvfp4r_sample_workspace_bytes(int B) {
+    return B > 0 ? static_cast<size_t>(B) * sizeof(SampleRow) : 0;
+}
+
+int nvfp4r_sample_top_k_top_p(const float* logits, int64_t row_stride, int B, int V, int top_k, float top_p,
+                              uint64_t seed, uint64_t* draws, int32_t* last_ids, int32_t* out,
+                              void* workspace, size_t workspace_bytes, void* stream) {
+    if (!logits || !out || !draws || B <= 0 || V <= 0) return NVFP4R_ERR_INVALID_ARGUMENT;
+    if (B > kArgmaxMaxRows) return NVFP4R_ERR_UNSUPPORTED_SHAPE;
+    if (!(top_p > 0.0f)) return NVFP4R_ERR_INVALID_ARGUMENT;
+    const bool use_k = top_k > 0 && top_k < V, use_p = top_p < 1.0f;
+    if (!use_k && !use_p) return nvfp4r_sample(logits, row_stride, B, V, seed, draws, last_ids, out, stream);
+    if (!workspace || workspace_bytes < nvfp4r_sample_workspace_bytes(B) ||
+        (reinterpret_cast<uintptr_t>(workspace) & 7))
+        return NVFP4R_ERR_INVALID_ARGUMENT;
+    SampleRow* rows = static_cast<SampleRow*>(workspace);
+    // row maxima (the partial maxima stay in the arg-max scratch, which the histogram kernels read)
+    cudaError_t e = launch_pdl(argmax_partial_kernel<false>, dim3(kArgmaxParts, B), dim3(256), 0, st(stream), logits,
+                               row_stride, V, 0ull, static_cast<const unsigned long long*>(nullptr),
+                               static_cast<const SampleRow*>(nullptr));
+    if (e == cudaSuccess) e = launch_pdl(sample_reset_kernel, dim3(B), dim3(32), 0, st(stream), rows, 0);
+    for (int mode = 0; mode < 2 && e == cudaSuccess; ++mode) {
+        if ((mode == 0 && !use_k) || (mode == 1 && !use_p)) continue;
+        if (mode == 1 && use_k) e = launch_pdl(sample_reset_kernel, dim3(B), dim3(32), 0, st(stream), rows, 1);
+        for (int level = 0; level < 3 && e == cudaSuccess; ++level) {
+            e = launch_pdl(sample_hist_kernel, dim3(kArgmaxParts, B), dim3(256), 0, st(stream), logits, row_stride, V,
+                           rows, level);
+            if (e == cudaSuccess)
+                e = launch_pdl(sample_select_kernel, dim3(B), dim3(1024), 0, st(stream), rows, level, mode, top_k, top_p);
+        }
+    }
+    if (e == cudaSuccess)
+        e = launch_pdl(argmax_partial_kernel<true>, dim3(kArgmaxParts, B), dim3(256), 0, st(stream), logits, row_stride,
+                       V, static_cast<unsigned long long>(seed), reinterpret_cast<const unsigned long long*>(draws),
+                       static_cast<const SampleRow*>(rows));
     if (e != cudaSuccess) return NVFP4R_ERR_CUDA;
     return done(launch_pdl(argmax_final_kernel, dim3(B), dim3(kArgmaxParts), 0, st(stream), out,
                            reinterpret_cast<unsigned long long*>(draws), last_ids));

@@ -329,7 +329,8 @@ class DecodeStep:
             capi.reset_step_per_request(full, d.states, d.params_dev, last_ids=self.last_ids,
                                         nl_bitmaps=d.nl_bitmaps, dnl_bitmaps=d.dnl_bitmaps,
                                         n_id_sets=d.n_id_sets, decisions=d.decisions, workspace=d.workspace)
-            capi.sample(full, self.draws, seed=self.sample_seed, last_ids=self.last_ids, out=self.token)
+            capi.sample(full, self.draws, seed=self.sample_seed, last_ids=self.last_ids, out=self.token,
+                        top_k=self.top_k, top_p=self.top_p, workspace=self.sample_ws)
             return
         L.check(lib.nvfp4r_argmax(full.data_ptr(), full.stride(0), 1, full.shape[1], self.token.data_ptr(),
                                   self._stream()), "argmax")
@@ -361,18 +362,21 @@ class DecodeStep:
         self.graph.replay()
 
     def enable_reset(self, t_high: float = 1.0, t_low: float = 0.1, tau0: float = 0.5505, window: int = 32,
-                     nl_ids=(), dnl_ids=(), seed: int = 0) -> None:
+                     nl_ids=(), dnl_ids=(), seed: int = 0, top_k: int = 0, top_p: float = 1.0) -> None:
         """End every step with the ReSET processor (reset/reset/logits_processor.py:62-134) and a
-        draw from the softmax of the scaled logits instead of the arg-max. Every rank holds the
-        full logits after the gather and runs the same processor with the same seed, so all
-        ranks draw the same token. Call before :meth:`capture`; call again to start a new
-        request (state, counters and recent ids are cleared)."""
+        draw from the softmax of the scaled logits instead of the arg-max, optionally restricted
+        to the top-k / top-p set as vLLM's sampler would. Every rank holds the full logits after
+        the gather and runs the same processor with the same seed, so all ranks draw the same
+        token. Call before :meth:`capture`; call again to start a new request (state, counters
+        and recent ids are cleared)."""
         from .reset.logits_processor import _DeviceReset
         self.reset = _DeviceReset(1, self.cfg.vocab, self.device)
         self.reset.set_slot(0, t_high, t_low, tau0, window, nl_ids, dnl_ids)
         self.last_ids = torch.full((1, 2), -1, dtype=torch.int32, device=self.device)
         self.draws = torch.zeros(1, dtype=torch.int64, device=self.device)
         self.sample_seed = int(seed)
+        self.top_k, self.top_p = int(top_k), float(top_p)
+        self.sample_ws = capi.sample_workspace(1, self.device)
         self.graph = None
 
     def set_position(self, pos: int) -> None:

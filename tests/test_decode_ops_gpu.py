@@ -273,6 +273,98 @@ def test_sample_frequencies_match_softmax():
     assert chi2 < 2.2 * (V - 1)                          # mean V-1, sd sqrt(2(V-1)) ~ 9.9
 
 
+def _truncated_distribution(row: torch.Tensor, top_k: int, top_p: float):
+    """vLLM's order: top-k first, then top-p on the distribution renormalised over the top-k set.
+    Returns (probabilities over the vocabulary in float64, distance of the nucleus boundary from
+    top_p in probability mass)."""
+    V = row.numel()
+    x = row.double()
+    keep = torch.ones(V, dtype=torch.bool)
+    if 0 < top_k < V:
+        kth = torch.topk(x, top_k).values[-1]
+        keep &= x >= kth
+    p = torch.softmax(torch.where(keep, x, torch.full_like(x, float("-inf"))), dim=0)
+    margin = 1.0
+    if top_p < 1.0:
+        order = torch.argsort(p, descending=True)
+        cum = torch.cumsum(p[order], dim=0)
+        n_keep = int((cum < top_p).sum().item()) + 1           # smallest prefix whose mass reaches top_p
+        margin = float(min(abs(cum[n_keep - 1] - top_p), abs(cum[n_keep - 2] - top_p) if n_keep > 1 else 1.0))
+        mask = torch.zeros(V, dtype=torch.bool)
+        mask[order[:n_keep]] = True
+        p = torch.where(mask, p, torch.zeros_like(p))
+        p = p / p.sum()
+    return p, margin
+
+
+@pytest.mark.parametrize("V,top_k,top_p", [(1000, 0, 0.9), (1000, 20, 1.0), (1000, 50, 0.8), (151936, 0, 0.95),
+                                           (151936, 64, 1.0), (4096, 5, 0.5), (333, 0, 0.3)])
+def test_sample_top_k_top_p_support_and_frequencies(V, top_k, top_p):
+    """The truncated draw: every drawn id lies in the exact top-k / top-p set, every member of
+    the set is reachable, and the frequencies follow the renormalised softmax
+    (torch.multinomial on the same truncated distribution gives the reference counts)."""
+    from reset_b200 import capi
+    B, calls = 256, 40
+    g = torch.Generator().manual_seed(1000 + V + top_k)
+    row = torch.randn(V, generator=g) * 2.0
+    row[int(torch.randint(0, V, (1,), generator=g))] += 6.0
+    p, margin = _truncated_distribution(row, top_k, top_p)
+    if margin < 1e-4:
+        pytest.skip("nucleus boundary within 1e-4 of top_p: the fixed-point mass may place it one token off")
+    logits = row.repeat(B, 1).contiguous().cuda()
+    draws = torch.zeros(B, dtype=torch.int64, device="cuda")
+    ws = capi.sample_workspace(B, "cuda")
+    counts = torch.zeros(V, dtype=torch.int64)
+    for _ in range(calls):
+        ids = capi.sample(logits, draws, seed=5, top_k=top_k, top_p=top_p, workspace=ws)
+        counts += torch.bincount(ids.cpu().long(), minlength=V)
+    torch.cuda.synchronize()
+    n = B * calls
+    support = p > 0
+    assert int(counts[~support].sum()) == 0, "a draw fell outside the truncated set"
+    assert int(ws.count_nonzero().item()) <= 8 * B          # histograms zeroed again (only the small per-row record is left)
+    big = p > 20.0 / n                                      # members with enough expected draws
+    sigma = torch.sqrt(p * (1 - p) / n)
+    z = ((counts.double() / n - p).abs() / sigma.clamp_min(1e-12))[big]
+    assert float(z.max()) < 5.5, (float(z.max()), int(z.argmax()))
+    ref = torch.bincount(torch.multinomial(p, n, replacement=True, generator=g), minlength=V)
+    # same test statistic for our counts and for torch.multinomial's: both are samples of p
+    chi_ours = float((((counts.double() - n * p) ** 2)[big] / (n * p)[big]).sum())
+    chi_ref = float((((ref.double() - n * p) ** 2)[big] / (n * p)[big]).sum())
+    dof = int(big.sum())
+    assert chi_ours < dof + 6 * (2 * dof) ** 0.5 + 10, (chi_ours, chi_ref, dof)
+
+
+def test_sample_truncation_edge_rows():
+    """One-hot rows (what ReSET writes for temperature 0), rows with fewer finite entries than k,
+    top_p so small that one token remains, and the untruncated call through the same entry."""
+    from reset_b200 import capi
+    V = 2048
+    logits = torch.full((4, V), float("-inf"))
+    logits[0, 77] = 0.0                                   # one-hot
+    logits[1, :3] = torch.tensor([1.0, 2.0, 3.0])         # three finite entries, k = 10
+    logits[2] = torch.randn(V, generator=torch.Generator().manual_seed(3))
+    logits[2, 500] = 30.0                                 # one dominant token: any top_p keeps only it
+    logits[3] = torch.linspace(-4, 4, V)
+    dev = logits.cuda()
+    draws = torch.zeros(4, dtype=torch.int64, device="cuda")
+    ws = capi.sample_workspace(4, "cuda")
+    seen3 = set()
+    for it in range(50):
+        ids = capi.sample(dev, draws, seed=it, top_k=10, top_p=0.9, workspace=ws).tolist()
+        assert ids[0] == 77 and ids[1] in (0, 1, 2) and ids[2] == 500
+        assert ids[3] >= V - 10                            # the ten largest of an increasing row
+        seen3.add(ids[3])
+    assert len(seen3) > 1
+    assert draws.tolist() == [50, 50, 50, 50]
+    # top_k >= V and top_p = 1: no truncation, same ids as the plain call with the same counters
+    d1 = torch.zeros(4, dtype=torch.int64, device="cuda")
+    d2 = torch.zeros(4, dtype=torch.int64, device="cuda")
+    a = capi.sample(dev, d1, seed=9, top_k=V, top_p=1.0, workspace=ws)
+    b = capi.sample(dev, d2, seed=9)
+    assert torch.equal(a, b)
+
+
 def test_decode_step_with_reset_processor_and_sampling_in_the_graph():
     from reset_b200 import _lib
     from reset_b200.decode import DecodeConfig, DecodeStep
