@@ -457,6 +457,26 @@ NVFP4R_API int nvfp4r_set_peer_poll_limit(unsigned polls);
  * NVFP4R_ERR_DEVICE_TIMEOUT if a bounded wait inside a kernel gave up. */
 NVFP4R_API int nvfp4r_check_device_status(void);
 
+/* The same information WITHOUT a device synchronisation: *host_word points at one int in
+ * pinned, mapped host memory (allocated at the first call on the current device; this call
+ * allocates, the launches never do). A kernel whose bounded wait gives up stores a non-zero code
+ * there (1 GEMV ring, 2 tensor-core GEMM, 3 packed linear, 4 peer all-reduce, 5 ReSET step) next
+ * to setting its device flag; the host may read the word at any time, e.g. every few decode
+ * steps, and writes 0 to clear it. A time-out means the output of that launch is undefined and
+ * the scratch it used (split-K slots, ReSET workspace, peer receive memory) is mid-exchange:
+ * zero it before the next use.
+ *
+ * Residency. nvfp4r_linear_packed*, the single-launch form of nvfp4r_reset_step* and
+ * push_gather wait for other CTAs of their own grid (or of a peer GPU's grid). Their grids are
+ * sized to be resident all at once on an otherwise idle device (at most two CTAs per SM; the
+ * ReSET launcher falls back to its three-launch form when the occupancy calculation says the
+ * grid does not fit). A kernel of ANOTHER stream that holds SMs at the same time can delay the
+ * missing CTAs; the waits then last until that kernel leaves, or give up after their poll limit
+ * and report through this word. Run them on one stream, or keep concurrent kernels small.
+ * No counterpart in the reference (its kernels' mbarrier waits are unbounded,
+ * kernels/cuda/gemm/gemm_nvfp4.cu:44-56). */
+NVFP4R_API int nvfp4r_status_mirror(volatile int** host_word);
+
 /* ------------------------------------------------------------------------- *
  * Batch-1 decode-step operators around the linears (bf16 activations). None of these
  * has a counterpart in the reference: in its deployment vLLM provides them. They let the

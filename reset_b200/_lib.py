@@ -88,6 +88,7 @@ PROTOTYPES = {
     "nvfp4r_reset_step_static": (_i, [_vp, _i64, _i, _i, _vp, _vp, _vp, _vp, _vp,
                                       C.POINTER(ResetParams), _vp, _vp]),
     "nvfp4r_entropy": (_i, [_vp, _i64, _i, _i, _vp, _vp, _sz, _vp]),
+    "nvfp4r_status_mirror": (_i, [C.POINTER(C.POINTER(C.c_int))]),
     "nvfp4r_set_gemv_tuning": (_i, [_i, _i, _i]),
     "nvfp4r_set_gemv_rows_tuning": (_i, [_i, _i, _i]),
     "nvfp4r_add_rmsnorm": (_i, [_vp, _vp, _vp, _vp, _i, _i, _f, _vp]),
@@ -139,3 +140,12 @@ def check(status: int, what: str) -> None:
         l = lib()
         raise Nvfp4rError(f"{what}: {l.nvfp4r_status_string(status).decode()} "
                           f"({status}): {l.nvfp4r_last_error().decode()}")
+
+
+def status_mirror():
+    """ctypes pointer to the host-visible time-out word of the current device
+    (``nvfp4r_status_mirror``): ``p[0]`` is 0 or the code of the kernel family whose bounded
+    wait gave up; reading it synchronises nothing; assign ``p[0] = 0`` to clear."""
+    p = C.POINTER(C.c_int)()
+    check(lib().nvfp4r_status_mirror(C.byref(p)), "nvfp4r_status_mirror")
+    return p

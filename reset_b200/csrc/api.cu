@@ -553,6 +553,32 @@ int nvfp4r_set_gemv_rows_tuning(int mode, int rows_per_step, int warps_per_sm) {
     return NVFP4R_OK;
 }
 
+int nvfp4r_status_mirror(volatile int** host_word) {
+    if (!host_word) return fail(NVFP4R_ERR_INVALID_ARGUMENT, "status_mirror: null pointer");
+    static int* host_ptr[64] = {};
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return cuda_fail(e, "status_mirror");
+    if (dev < 0 || dev >= 64) return fail(NVFP4R_ERR_INVALID_ARGUMENT, "status_mirror: device index");
+    if (host_ptr[dev] == nullptr) {
+        int* h = nullptr;
+        int* d = nullptr;
+        e = cudaHostAlloc(reinterpret_cast<void**>(&h), sizeof(int), cudaHostAllocMapped);
+        if (e != cudaSuccess) return cuda_fail(e, "status_mirror: cudaHostAlloc");
+        *h = 0;
+        e = cudaHostGetDevicePointer(reinterpret_cast<void**>(&d), h, 0);
+        if (e == cudaSuccess) e = nvfp4r::set_status_mirror_gemv(d);
+        if (e == cudaSuccess) e = nvfp4r::set_status_mirror_tc(d);
+        if (e == cudaSuccess) e = nvfp4r::set_status_mirror_packed(d);
+        if (e == cudaSuccess) e = nvfp4r::set_status_mirror_peer(d);
+        if (e == cudaSuccess) e = nvfp4r::set_status_mirror_reset(d);
+        if (e != cudaSuccess) { cudaFreeHost(h); return cuda_fail(e, "status_mirror: set-up"); }
+        host_ptr[dev] = h;
+    }
+    *host_word = host_ptr[dev];
+    return NVFP4R_OK;
+}
+
 int nvfp4r_check_device_status(void) {
     int flag = 0, flag2 = 0;
     cudaError_t e = nvfp4r::read_and_clear_device_status(&flag);

@@ -30,6 +30,7 @@
 #include <unordered_map>
 
 #include "kernels.h"
+#include "status_mirror.cuh"
 #include "quant_core.cuh"
 #include "tcgen05_ptx.cuh"
 
@@ -319,7 +320,7 @@ linear_tc_kernel(const __grid_constant__ TcParams p) {
         }
     }
 
-    if (wf.failed && lane == 0) atomicExch(&g_tc_status, 1);
+    if (wf.failed && lane == 0) report_timeout(&g_tc_status, 2);
     tc_fence_before();
     __syncthreads();
     if (warp == 1) {
@@ -505,6 +506,8 @@ void set_tc_tuning(int splits, int stages) {
     g_force_splits = splits;
     g_force_stages = stages;
 }
+
+cudaError_t set_status_mirror_tc(int* p) { return set_status_mirror_here(p); }
 
 cudaError_t read_and_clear_tc_status(int* flag) {
     cudaError_t e = cudaMemcpyFromSymbol(flag, g_tc_status, sizeof(int));

@@ -16,6 +16,7 @@
 // one f32 FMA by the weight scale; alpha is applied in f32 at the store.
 #include "kernels.h"
 #include "quant_core.cuh"
+#include "status_mirror.cuh"
 
 namespace nvfp4r {
 namespace {
@@ -291,7 +292,7 @@ gemv_stream_kernel(const __grid_constant__ StreamParams p) {
     }
 
     if (timed_out) {
-        if (lane == 0) atomicExch(&g_device_status, 1);
+        if (lane == 0) report_timeout(&g_device_status, 1);
         // Give copies that are still in flight a bounded time to land before
         // this CTA's shared memory is released.
         for (int i = 0; i < 64; ++i) __nanosleep(1000);
@@ -376,6 +377,8 @@ cudaError_t read_and_clear_device_status(int* flag) {
     const int zero = 0;
     return cudaMemcpyToSymbol(g_device_status, &zero, sizeof(int));
 }
+
+cudaError_t set_status_mirror_gemv(int* p) { return set_status_mirror_here(p); }
 
 GemvTuning& gemv_tuning() {
     static GemvTuning t = {0, 1, 0};

@@ -38,6 +38,7 @@
 // warps 2-5 = epilogue (one TMEM lane quadrant each).
 #include "../../include/nvfp4r_b200.h"
 #include "kernels.h"
+#include "status_mirror.cuh"
 #include "quant_core.cuh"
 #include "tcgen05_ptx.cuh"
 
@@ -668,7 +669,7 @@ linear_packed_kernel(const __grid_constant__ PackedParams p) {
         if (warp == 2) TRACE(9);
     }
 
-    if (wf.failed && lane == 0) atomicExch(&g_packed_status, 1);
+    if (wf.failed && lane == 0) report_timeout(&g_packed_status, 3);
     tc_fence_before();
     __syncthreads();
     if (warp == 1) {
@@ -843,6 +844,8 @@ cudaError_t read_packed_trace(unsigned long long* out512) {
     return cudaMemcpyFromSymbol(out512, g_packed_times, 8 * 64 * sizeof(unsigned long long));
 }
 #endif
+
+cudaError_t set_status_mirror_packed(int* p) { return set_status_mirror_here(p); }
 
 cudaError_t read_and_clear_packed_status(int* flag) {
     cudaError_t e = cudaMemcpyFromSymbol(flag, g_packed_status, sizeof(int));

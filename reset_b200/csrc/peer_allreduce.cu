@@ -23,6 +23,7 @@
 
 #include "../../include/nvfp4r_b200.h"
 #include "kernels.h"
+#include "status_mirror.cuh"
 #include "nvfp4_ptx.cuh"
 
 namespace nvfp4r {
@@ -111,7 +112,7 @@ peer_allreduce_kernel(const PeerParams p) {
     }
     __syncthreads();
     if (threadIdx.x == 0) {
-        if (s_failed) atomicExch(&g_peer_status, 1);
+        if (s_failed) report_timeout(&g_peer_status, 4);
         if (p.mode & 2) {
             // the last CTA to finish advances the call counter: nobody of this launch reads it any more
             __threadfence();
@@ -127,6 +128,8 @@ peer_allreduce_kernel(const PeerParams p) {
 }  // namespace
 
 uint32_t peer_poll_limit() { return g_peer_poll_limit; }
+
+cudaError_t set_status_mirror_peer(int* p) { return set_status_mirror_here(p); }
 
 cudaError_t read_and_clear_peer_status(int* flag) {
     cudaError_t e = cudaMemcpyFromSymbol(flag, g_peer_status, sizeof(int));

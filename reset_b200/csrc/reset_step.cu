@@ -15,6 +15,7 @@
 // dependents at once, so launch latency overlaps the kernel before; each reads what the
 // previous kernel wrote only after griddepcontrol.wait.
 #include "kernels.h"
+#include "status_mirror.cuh"
 #include "nvfp4_ptx.cuh"
 #include "reset_kernels.h"
 
@@ -455,7 +456,7 @@ reset_fused_kernel(const ResetLaunch p, const int scale) {
     }
     __syncthreads();
     if (s_fail) {
-        if (threadIdx.x == 0) atomicExch(&g_reset_status, 1);
+        if (threadIdx.x == 0) report_timeout(&g_reset_status, 5);
         return;
     }
     // lane s owns slice s; fixed shuffle trees: every warp of every CTA computes the same bits
@@ -513,7 +514,7 @@ reset_fused_kernel(const ResetLaunch p, const int scale) {
         __syncthreads();
         if (threadIdx.x == 0) {
             if (s_fail) {
-                atomicExch(&g_reset_status, 1);
+                report_timeout(&g_reset_status, 5);
             } else {
                 double h = 0.0;
                 for (int s = 0; s < p.n_slices; ++s) {                 // slice order, like the three-launch path
@@ -550,7 +551,7 @@ reset_fused_kernel(const ResetLaunch p, const int scale) {
     if (threadIdx.x < 2) {
         uint32_t v = threadIdx.x;                                      // on a time-out: mode 1, leave the slice alone
         if (!rs_poll(threadIdx.x == 0 ? &sl->temp : &sl->mode, epoch, &v)) {
-            atomicExch(&g_reset_status, 1);
+            report_timeout(&g_reset_status, 5);
             v = threadIdx.x;
         }
         s_word[threadIdx.x] = v;
@@ -658,6 +659,8 @@ cudaError_t launch_reset(ResetLaunch p, bool scale, cudaStream_t stream) {
     if (scale) e = launch_pdl(reset_scale_kernel, grid, p, true, stream);
     return e;
 }
+
+cudaError_t set_status_mirror_reset(int* p) { return set_status_mirror_here(p); }
 
 cudaError_t read_and_clear_reset_status(int* flag) {
     cudaError_t e = cudaMemcpyFromSymbol(flag, g_reset_status, sizeof(int));

@@ -216,6 +216,10 @@ class ReSETBatchProcessor:
         self._last_host = torch.full((self.max_reqs, 2), -1, dtype=torch.int32, pin_memory=self.pin)
         self._slots_dev = torch.full((self.max_reqs,), -1, dtype=torch.int32, device=self.device)
         self._last_dev = torch.full((self.max_reqs, 2), -1, dtype=torch.int32, device=self.device)
+        # host-visible time-out word (no synchronisation to read it); looked at every few steps
+        self._mirror = None
+        self._steps = 0
+        self.check_every = 16
 
     def is_argmax_invariant(self) -> bool:
         return False
@@ -275,7 +279,26 @@ class ReSETBatchProcessor:
                                     decisions=d.decisions, workspace=d.workspace)
         if work is not logits:
             logits.copy_(work)
+        self._steps += 1
+        if self.check_every and self._steps % self.check_every == 0:
+            self.raise_on_device_timeout()
         return logits
+
+    def raise_on_device_timeout(self) -> None:
+        """Reads the pinned-host twin of the kernels' time-out flags (no device synchronisation).
+        A non-zero word means a bounded wait inside an earlier launch gave up: that step's logits
+        are undefined and the processor's scratch is mid-exchange, so it is zeroed and the error
+        is raised instead of serving wrong temperatures silently."""
+        if self._mirror is None:
+            with torch.cuda.device(self.device):
+                self._mirror = _lib.status_mirror()
+        code = int(self._mirror[0])
+        if code != 0:
+            self._mirror[0] = 0
+            if self._dev is not None:
+                self._dev.workspace.zero_()
+            raise RuntimeError(f"nvfp4r: a device-side wait timed out (kernel family {code}); "
+                               "the logits of that step are undefined")
 
 
 _BATCH_CLASS = None

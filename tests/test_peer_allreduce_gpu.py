@@ -291,10 +291,19 @@ def test_missing_peer_is_reported_not_waited_for_forever():
         x = torch.ones(512, dtype=torch.bfloat16, device="cuda")
         stream = torch.cuda.current_stream().cuda_stream
         L.check(lib.nvfp4r_check_device_status(), "clean before")
+        mirror = L.status_mirror()                                     # host-visible twin of the flag
+        mirror[0] = 0
         L.check(lib.nvfp4r_set_peer_poll_limit(100000), "limit")       # a few tens of milliseconds
         # rank 0 pushes and gathers, "rank 1" never shows up
         L.check(lib.nvfp4r_peer_allreduce_bf16(C.byref(c), x.data_ptr(), x.data_ptr(), 512, L.PEER_ALLREDUCE, stream),
                 "launch")
+        # the host learns of it without synchronising the device: poll the pinned word
+        import time
+        t0 = time.time()
+        while mirror[0] == 0 and time.time() - t0 < 20.0:
+            time.sleep(0.001)
+        assert mirror[0] == 4                                          # code of the peer all-reduce
+        mirror[0] = 0
         torch.cuda.synchronize()
         assert lib.nvfp4r_check_device_status() == -5                  # NVFP4R_ERR_DEVICE_TIMEOUT, and cleared
         L.check(lib.nvfp4r_check_device_status(), "cleared")
