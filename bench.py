@@ -802,9 +802,13 @@ def run_published(args):
 def run_reset_loop(args):
     """ReSET decode loop: vocab 151936, batch 1..8, a delimiter every 40-120
     tokens, t_high 1.0 / t_low 0.1 / tau_0 0.5505 / w 32. GPU: one fused step per token for the
-    whole batch (three launches), CUDA-graph replay over a pool of distinct logits buffers larger
-    than L2, restored before every replay because the step divides in place. CPU: the oracle's
-    per-request processor (the reference's algorithm) on the host cores, same logits."""
+    whole batch (ONE launch), CUDA-graph replay over a pool of distinct logits buffers larger
+    than L2, restored before every replay because the step divides in place. With these logits
+    every step chooses T = t_high = 1 and nothing is written back (x / 1 = x), so the loop is timed
+    a second time with tau_0 = 100, where every step chooses t_low and the scaled row is written
+    (`gpu_us_t_low`). CPU: the oracle's per-request processor (the reference's algorithm) on the
+    host cores, same logits; the temperatures the device chose on those steps are compared with
+    the oracle's (`temps_equal`)."""
     import ctypes as C
 
     import numpy as np
@@ -824,7 +828,6 @@ def run_reset_loop(args):
         pool = pristine.clone()
         states = torch.zeros(B * C.sizeof(_lib.ResetState), dtype=torch.uint8, device=device)
         ws = capi.reset_workspace(B, device)
-        params = _lib.ResetParams(1.0, 0.1, 0.5505, 32, 0)
         bm = torch.zeros((V + 31) // 32, dtype=torch.int32, device=device)
         bm[delim // 32] = 1 << (delim % 32)
         nl = torch.zeros_like(bm)
@@ -832,44 +835,63 @@ def run_reset_loop(args):
         last = [torch.from_numpy(np.ascontiguousarray(streams[:, t:t + 2]).astype(np.int32)).to(device)
                 for t in range(pool_n)]
 
-        def one_pass():
-            for t in range(pool_n):
-                capi.reset_step(pool[t], states, params, last_ids=last[t], nl_bitmap=nl, dnl_bitmap=bm,
-                                workspace=ws)
+        decisions = torch.zeros(pool_n * B * C.sizeof(_lib.ResetDecision), dtype=torch.uint8, device=device)
+        dec_rows = decisions.view(pool_n, B * C.sizeof(_lib.ResetDecision))
+        timed = {}
+        for label, tau0 in (("t_high", 0.5505), ("t_low", 100.0)):
+            params = _lib.ResetParams(1.0, 0.1, tau0, 32, 0)
+            states.zero_()
+            pool.copy_(pristine)
 
-        side = torch.cuda.Stream(device=device)
-        side.wait_stream(torch.cuda.current_stream())
-        with torch.cuda.stream(side):
-            one_pass()
-            pool.copy_(pristine)
-            g = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(g, stream=side):
+            def one_pass():
+                for t in range(pool_n):
+                    capi.reset_step(pool[t], states, params, last_ids=last[t], nl_bitmap=nl, dnl_bitmap=bm,
+                                    decisions=dec_rows[t], workspace=ws)
+
+            side = torch.cuda.Stream(device=device)
+            side.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(side):
                 one_pass()
-        torch.cuda.current_stream().wait_stream(side)
-        ts = []
-        for _ in range(max(3, steps // pool_n)):
-            pool.copy_(pristine)
-            torch.cuda.synchronize()
-            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            e0.record()
-            g.replay()
-            e1.record()
-            torch.cuda.synchronize()
-            ts.append(e0.elapsed_time(e1) / pool_n * 1e3)
-        gpu_us = sorted(ts)[len(ts) // 2]
+                pool.copy_(pristine)
+                states.zero_()
+                g = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g, stream=side):
+                    one_pass()
+            torch.cuda.current_stream().wait_stream(side)
+            ts = []
+            for _ in range(max(3, steps // pool_n)):
+                pool.copy_(pristine)
+                states.zero_()
+                torch.cuda.synchronize()
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+                g.replay()
+                e1.record()
+                torch.cuda.synchronize()
+                ts.append(e0.elapsed_time(e1) / pool_n * 1e3)
+            timed[label] = sorted(ts)[len(ts) // 2]
+            if label == "t_high":
+                dec_t_high = np.frombuffer(decisions.cpu().numpy().tobytes(), dtype="f8").reshape(pool_n, B, -1)[:, :, 3].copy()
+            del g
+        gpu_us = timed["t_high"]
         # CPU: the per-request processor, one call per row per step
         host = pristine[: min(pool_n, 24)].cpu()
         pols = [orp.ResetPolicy(1.0, 0.1, 0.5505, 32, frozenset(), frozenset([delim])) for _ in range(B)]
+        temps_equal = True
         t0 = time.perf_counter()
         for t in range(host.shape[0]):
             for b in range(B):
-                pols[b](streams[b][: t + 2].tolist(), host[t, b])
+                _, d = pols[b](streams[b][: t + 2].tolist(), host[t, b])
+                temps_equal = temps_equal and d.temp == dec_t_high[t, b]
         cpu_us = (time.perf_counter() - t0) / host.shape[0] * 1e6
-        out["reset_loop"][f"B{B}"] = {"gpu_us": round(gpu_us, 2), "cpu_oracle_us": round(cpu_us, 1),
+        out["reset_loop"][f"B{B}"] = {"gpu_us": round(gpu_us, 2), "gpu_us_t_low": round(timed["t_low"], 2),
+                                      "cpu_oracle_us": round(cpu_us, 1),
                                       "speedup": round(cpu_us / gpu_us, 1),
-                                      "gbs": round(2 * B * V * 4 / gpu_us / 1e3, 1),
+                                      "gbs_read_only": round(B * V * 4 / gpu_us / 1e3, 1),
+                                      "gbs_t_low_read_write": round(2 * B * V * 4 / timed["t_low"] / 1e3, 1),
+                                      "temps_equal_to_oracle": bool(temps_equal),
                                       "logits_pool_mb": round(pool_n * B * V * 4 / 1e6)}
-        del pool, pristine, g
+        del pool, pristine
         torch.cuda.empty_cache()
     out["reset_loop"]["cpu_threads"] = torch.get_num_threads()
     return out
