@@ -292,12 +292,16 @@ void set_gemv_rows_tuning(int mode, int rows, int target_warps) {
 // for weights of 16 MB and more, for rows longer than 8192 elements and for every shape the
 // ring kernel cannot take (K % 256 != 0), the ring kernel below that (measured on B200,
 // L2-cold: 6144x4096 5.1 vs 5.3 us, 6400x5120 6.7 vs 6.3 us, 4096x12288 10.9 vs 7.8 us,
-// 5120x3200 11.1 (plain loads) vs 4.9 us). More tokens: the ring kernel.
+// 5120x3200 11.1 (plain loads) vs 4.9 us), and for N where the ring kernel's groups of 4 rows
+// leave a second round to under a quarter of its warps (N = 5120: 5120x5120 7.3 us on the ring
+// kernel). More tokens: the ring kernel.
 cudaError_t launch_gemv_auto(const GemvArgs& a, cudaStream_t stream) {
     const bool ring = gemv_stream_supported(a);
     if (!gemv_tuning().force_generic && gemv_rows_supported(a)) {
         const int64_t wbytes = static_cast<int64_t>(a.N) * a.K * 9 / 16;
-        if (g_rows_tuning.mode > 0 || !ring || wbytes >= 16000000 || a.K > 8192)
+        const int ring_warps = device_sm_count() * 8, groups = (a.N + 3) / 4;
+        const bool poor_ring_fit = groups > ring_warps && groups <= ring_warps + ring_warps / 4;
+        if (g_rows_tuning.mode > 0 || !ring || wbytes >= 16000000 || a.K > 8192 || poor_ring_fit)
             return launch_gemv_rows(a, stream);
     }
     return ring ? launch_gemv_stream(a, stream) : launch_gemv_generic(a, stream);
