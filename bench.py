@@ -214,7 +214,7 @@ def run_ours(args, rank, world, local_rank):
     from reset_b200.nvfp4r import _config as nv_config
 
     if args.no_fused_gather:
-        nv_config.FUSED_GATHER = False
+        nv_config.FUSED_GATHER = "0"
     if args.packed_tuning:
         from reset_b200 import _lib
         _lib.check(_lib.lib().nvfp4r_set_packed_tuning(args.packed_tuning), "packed tuning")
@@ -471,7 +471,7 @@ def run_ours(args, rank, world, local_rank):
                    "parallelism": f"tp{world}",
                    "allreduce": "none" if world == 1 else
                                 (("push + sum inside the row-parallel linear's own launch over NVLink peer memory"
-                                  if nv_config.FUSED_GATHER else
+                                  if nv_config.fused_gather(world) else
                                   "push in the linear epilogue + one-shot gather kernel over NVLink peer memory")
                                  if peer is not None else "NCCL")},
         "e2e": {"value": round(gbs_e2e, 1), "unit": "GB/s",

@@ -30,6 +30,20 @@ GEMV_MIN_K = 1024
 GEMV_RING_WARPS = 148 * 8
 GEMV_SHORT_ROW_K = 1280
 
-# Tensor-parallel row-parallel linears: complete the all-reduce inside the linear's own launch
-# (1) or push in the epilogue and gather in a second launch (0).
-FUSED_GATHER = os.environ.get("NVFP4R_FUSED_GATHER", "1") == "1"
+# Tensor-parallel row-parallel linears through `linear_auto(..., reduce=)`: complete the
+# all-reduce inside the linear's own launch, or push in the epilogue and gather in a second
+# launch. Measured on B200 (Qwen3-8B linear set, independent linears back to back): the single
+# launch wins at two ranks (3480 vs 3400 GB/s) and loses at eight (3214 vs 3766 GB/s), where its
+# CTAs hold the SMs while they wait for seven peers and the next linear's early loads cannot
+# start; a step whose next kernel needs the sum anyway (a decode layer) gains at every width
+# (Qwen3-32B TP 8: 353 vs 348 tok/s). "auto" = single launch up to FUSED_GATHER_MAX_WORLD ranks.
+FUSED_GATHER = os.environ.get("NVFP4R_FUSED_GATHER", "auto").lower()      # "auto", "1" or "0"
+FUSED_GATHER_MAX_WORLD = 2
+
+
+def fused_gather(world: int) -> bool:
+    if FUSED_GATHER in ("1", "true", "on"):
+        return True
+    if FUSED_GATHER in ("0", "false", "off"):
+        return False
+    return world <= FUSED_GATHER_MAX_WORLD

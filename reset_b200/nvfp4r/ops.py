@@ -130,7 +130,7 @@ def linear_auto(x, global_scale_inv, weight, weight_scale_flat, packed, N: int, 
             return reduce.all_reduce_(out)
         ws = _out_workspace(x.device, L.lib().nvfp4r_linear_packed_workspace_bytes(M, N, K))
         # push in the epilogue and, in the same launch, the sum over the ranks (one GPU per rank)
-        if M <= 32 and _config.FUSED_GATHER:
+        if M <= 32 and _config.fused_gather(reduce.world):
             return capi.linear_packed_push(x, global_scale_inv, packed, N, alpha, ws, reduce.comm, out,
                                            rcp_mode=rcp_mode, gather=True)
         capi.linear_packed_push(x, global_scale_inv, packed, N, alpha, ws, reduce.comm, out, rcp_mode=rcp_mode)
