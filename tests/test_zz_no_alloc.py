@@ -3,9 +3,9 @@ memory when they need it (a sampler plug-in inside an engine whose pool already 
 GPU, a C host holding only fixed input/output buffers). Its scratch is a static array in
 the library, so the call takes no workspace. Checked here through the C ABI against the
 regular entry point, on two consecutive steps (the static array keeps the previous call's
-contents, which must not leak into the next result), bit for bit: both run the same
-kernels in the same order. Collected last on purpose, so a failure here cannot hide
-another test's result in a stop-at-first-failure run."""
+contents, which must not leak into the next result), bit for bit: the regular entry point
+takes the single-launch kernel, the static one the three-launch form of the same arithmetic,
+and the two are required to agree exactly."""
 
 from __future__ import annotations
 
