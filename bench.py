@@ -480,7 +480,7 @@ def run_ours(args, rank, world, local_rank):
         "clocks": clocks,
         "roofline": {"bound": "hbm", "achieved": round(gbs / world, 1), "peak": peak, "unit": "GB/s",
                      "frac": round(gbs / world / peak, 4), "peak_kind": f"of {peak_kind}",
-                     "kernel": "linear_packed_kernel / gemv_stream_kernel by measured crossover (16 launches per step)",
+                     "kernel": "linear_packed_kernel (13 launches) / gemv_stream_kernel / gemv_rows_kernel by measured crossover (16 launches per step)",
                      "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH if world == 1 else None},
         "detail_us_gbs": {**detail, **target_detail},
         "decode": decode,

@@ -241,9 +241,19 @@ NVFP4R_API int nvfp4r_linear_packed_ex(const nvfp4r_prologue* pro, const void* x
                                        int N, float alpha, void* out, int out_dtype, int rcp_mode,
                                        void* workspace, size_t workspace_bytes, void* stream);
 
+/* The fused prologues on the FLAT weight (codes [N,K/2] + scales [N,K/16]) through the CUDA-core
+ * GEMV, for the launches the crossover gives to it (single token, small or medium weights: at
+ * tensor-parallel shard sizes the GEMV's shorter fixed part wins). Same `pro` kinds, arithmetic
+ * and roundings as nvfp4r_linear_packed_ex; M = 1 only; push_to is not available here.
+ * NVFP4R_PROLOGUE_NONE forwards to nvfp4r_linear. */
+NVFP4R_API int nvfp4r_linear_ex(const nvfp4r_prologue* pro, const void* x, int64_t x_row_stride,
+                                int M, int K, const float* global_scale_inv, const void* weight,
+                                const void* weight_scale, int N, float alpha, void* out,
+                                int out_dtype, int rcp_mode, void* stream);
+
 /* Debug/tuning of the packed linear: bits 0-7 force the K split (0 = automatic), bit 8 records
- * an in-kernel time line of eight CTAs (bits 12-23: the first of them), bit 9 runs one CTA per
- * SM instead of two. */
+ * an in-kernel time line of eight CTAs (bits 12-23: the first of them; only in a build with
+ * -DNVFP4R_TRACE, ignored otherwise), bit 9 runs one CTA per SM instead of two. */
 NVFP4R_API int nvfp4r_set_packed_tuning(int splits);
 
 /* Debug/tuning: force the K split and ring depth of the tensor-core kernel (0 = automatic). */

@@ -76,6 +76,7 @@ PROTOTYPES = {
     "nvfp4r_linear_packed": (_i, [_vp, _i64, _i, _i, _vp, _vp, _i, _f, _vp, _i, _i, _vp, _sz, _vp]),
     "nvfp4r_linear_packed_ex": (_i, [C.POINTER(Prologue), _vp, _i64, _i, _i, _vp, _vp, _i, _f, _vp, _i, _i,
                                      _vp, _sz, _vp]),
+    "nvfp4r_linear_ex": (_i, [C.POINTER(Prologue), _vp, _i64, _i, _i, _vp, _vp, _vp, _i, _f, _vp, _i, _i, _vp]),
     "nvfp4r_set_packed_tuning": (_i, [_i]),
     "nvfp4r_gemm": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _f, _i, _i, _vp, _sz, _vp]),
     "nvfp4r_unswizzle_blockscale": (_i, [_vp, _vp, _i, _i, _vp]),

@@ -206,6 +206,42 @@ def linear_packed_rmsnorm(delta, residual_in: torch.Tensor, residual_out: torch.
     return out
 
 
+def linear_rmsnorm(delta, residual_in: torch.Tensor, residual_out: torch.Tensor, norm_weight: torch.Tensor,
+                   eps: float, global_scale_inv: torch.Tensor, weight: torch.Tensor,
+                   weight_scale_flat: torch.Tensor, alpha: float, out: torch.Tensor,
+                   rcp_mode: int = L.RCP_APPROX) -> torch.Tensor:
+    """residual_out = residual_in + delta; out = linear(RMSNorm(residual_out) * norm_weight) through the
+    CUDA-core GEMV on the flat weight, one launch, one token (M = 1)."""
+    _need_cuda(residual_in, residual_out, norm_weight, global_scale_inv, weight, weight_scale_flat, delta, out)
+    M, K = residual_in.shape
+    N = weight.shape[0]
+    pro = L.Prologue(L.PROLOGUE_ADD_RMSNORM, float(eps), None if delta is None else delta.data_ptr(),
+                     residual_in.data_ptr(), residual_out.data_ptr(), norm_weight.data_ptr())
+    with torch.cuda.device(residual_in.device):
+        st = L.lib().nvfp4r_linear_ex(C.byref(pro), None, 0, M, K, global_scale_inv.data_ptr(), weight.data_ptr(),
+                                      weight_scale_flat.data_ptr(), N, float(alpha), out.data_ptr(),
+                                      _DTYPE_CODE[out.dtype], rcp_mode, _stream())
+    L.check(st, "nvfp4r_linear_ex")
+    return out
+
+
+def linear_silu(gate_up: torch.Tensor, global_scale_inv: torch.Tensor, weight: torch.Tensor,
+                weight_scale_flat: torch.Tensor, alpha: float, out: torch.Tensor,
+                rcp_mode: int = L.RCP_APPROX) -> torch.Tensor:
+    """out = linear(silu(gate) * up) with gate_up = [1, 2K] bf16 through the CUDA-core GEMV on the
+    flat weight, one launch."""
+    _need_cuda(gate_up, global_scale_inv, weight, weight_scale_flat, out)
+    M, K2 = gate_up.shape
+    N = weight.shape[0]
+    pro = L.Prologue(L.PROLOGUE_SILU_MUL, 0.0, None, None, None, None)
+    with torch.cuda.device(gate_up.device):
+        st = L.lib().nvfp4r_linear_ex(C.byref(pro), gate_up.data_ptr(), gate_up.stride(0), M, K2 // 2,
+                                      global_scale_inv.data_ptr(), weight.data_ptr(), weight_scale_flat.data_ptr(),
+                                      N, float(alpha), out.data_ptr(), _DTYPE_CODE[out.dtype], rcp_mode, _stream())
+    L.check(st, "nvfp4r_linear_ex")
+    return out
+
+
 def linear_packed_silu(gate_up: torch.Tensor, global_scale_inv: torch.Tensor, packed: torch.Tensor, N: int,
                        alpha: float, workspace: torch.Tensor, out_dtype: torch.dtype = torch.bfloat16,
                        rcp_mode: int = L.RCP_APPROX, out: torch.Tensor | None = None, push=None,

@@ -171,6 +171,57 @@ int nvfp4r_linear(const void* x, int64_t x_row_stride, int M, int K, const float
     return NVFP4R_OK;
 }
 
+int nvfp4r_linear_ex(const nvfp4r_prologue* pro, const void* x, int64_t x_row_stride, int M, int K,
+                     const float* gs, const void* weight, const void* weight_scale, int N, float alpha,
+                     void* out, int out_dtype, int rcp_mode, void* stream) {
+    NVFP4R_RANGE("nvfp4r_linear_ex");
+    if (!pro) return fail(NVFP4R_ERR_INVALID_ARGUMENT, "linear_ex: null prologue");
+    if (pro->push_to != nullptr)
+        return fail(NVFP4R_ERR_UNSUPPORTED_SHAPE, "linear_ex: push_to needs the packed linear (nvfp4r_linear_packed_ex)");
+    if (pro->kind == NVFP4R_PROLOGUE_NONE)
+        return nvfp4r_linear(x, x_row_stride, M, K, gs, weight, weight_scale, N, alpha, out, out_dtype, rcp_mode, stream);
+    if (pro->kind != NVFP4R_PROLOGUE_ADD_RMSNORM && pro->kind != NVFP4R_PROLOGUE_SILU_MUL)
+        return fail(NVFP4R_ERR_INVALID_ARGUMENT, "linear_ex: bad prologue kind");
+    if (!gs || !weight || !weight_scale || !out) return fail(NVFP4R_ERR_INVALID_ARGUMENT, "linear_ex: null pointer");
+    if (M != 1) return fail(NVFP4R_ERR_UNSUPPORTED_SHAPE, "linear_ex: the GEMV's fused prologues take one token (M = 1)");
+    if (N <= 0 || K <= 0 || K % 32 != 0) return fail(NVFP4R_ERR_UNSUPPORTED_SHAPE, "linear_ex: K must be a multiple of 32");
+    if (out_dtype < NVFP4R_BF16 || out_dtype > NVFP4R_F32) return fail(NVFP4R_ERR_INVALID_ARGUMENT, "linear_ex: bad out_dtype");
+    if (rcp_mode != NVFP4R_RCP_EXACT && rcp_mode != NVFP4R_RCP_APPROX)
+        return fail(NVFP4R_ERR_INVALID_ARGUMENT, "linear_ex: bad rcp_mode");
+    if (!aligned(weight, 16) || !aligned(weight_scale, 2)) return fail(NVFP4R_ERR_ALIGNMENT, "linear_ex: weight alignment");
+    nvfp4r::GemvArgs a = {};
+    a.w = static_cast<const uint8_t*>(weight);
+    a.wsf = static_cast<const uint8_t*>(weight_scale);
+    a.w_stride_n = K / 2;
+    a.wsf_stride_n = K / 16;
+    a.gs = gs;
+    a.rcp_mode = rcp_mode;
+    a.out = out;
+    a.out_stride = N;
+    a.out_dtype = out_dtype;
+    a.N = N;
+    a.K = K;
+    a.M = 1;
+    a.alpha = alpha;
+    a.pro_kind = pro->kind;
+    if (pro->kind == NVFP4R_PROLOGUE_ADD_RMSNORM) {
+        if (!pro->residual_in || !pro->residual_out || !pro->norm_weight)
+            return fail(NVFP4R_ERR_INVALID_ARGUMENT, "linear_ex: RMSNorm prologue needs residual_in/out and norm_weight");
+        if (pro->residual_in == pro->residual_out)
+            return fail(NVFP4R_ERR_INVALID_ARGUMENT, "linear_ex: residual_out must not alias residual_in");
+        a.delta = pro->delta; a.residual_in = pro->residual_in; a.residual_out = pro->residual_out;
+        a.norm_w = pro->norm_weight; a.eps = pro->eps;
+    } else {
+        if (!x || !aligned(x, 16) || (x_row_stride % 8) || x_row_stride < 2 * static_cast<int64_t>(K))
+            return fail(NVFP4R_ERR_INVALID_ARGUMENT, "linear_ex: SiLU prologue needs x = [M, 2K] gate|up, 16-byte aligned");
+        a.xb = x; a.xb_stride = x_row_stride;
+    }
+    if (!nvfp4r::gemv_rows_supported(a))
+        return fail(NVFP4R_ERR_UNSUPPORTED_SHAPE, "linear_ex: shape or alignment outside the register-resident GEMV");
+    cudaError_t e = nvfp4r::launch_gemv_auto(a, as_stream(stream));
+    return e == cudaSuccess ? NVFP4R_OK : cuda_fail(e, "linear_ex launch");
+}
+
 size_t nvfp4r_gemm_workspace_bytes(int M, int N, int K) {
     return nvfp4r::gemm_workspace_bytes(M, N, K);
 }

@@ -95,6 +95,25 @@ __device__ __forceinline__ void butterfly(float (&v)[NV], int lane) {
     }
 }
 
+// ---- bf16 vector helpers of the fused prologues (same roundings as the packed linear's) ------
+__device__ __forceinline__ void unpack8(const uint4& v, float f[8]) {
+    const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        f[2 * i] = __uint_as_float(w[i] << 16);
+        f[2 * i + 1] = __uint_as_float(w[i] & 0xFFFF0000u);
+    }
+}
+__device__ __forceinline__ uint32_t pack2_bf16(float a, float b) {
+    const __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+    return *reinterpret_cast<const uint32_t*>(&h);
+}
+__device__ __forceinline__ uint4 pack8(const float f[8]) {
+    return make_uint4(pack2_bf16(f[0], f[1]), pack2_bf16(f[2], f[3]), pack2_bf16(f[4], f[5]),
+                      pack2_bf16(f[6], f[7]));
+}
+__device__ __forceinline__ float round_bf16(float v) { return __bfloat162float(__float2bfloat16_rn(v)); }
+
 template <int R>
 struct Stage {
     uint4 c[R];
@@ -136,6 +155,7 @@ gemv_rows_kernel(const __grid_constant__ RowsParams p) {
     constexpr int NV = 2 * R * MT;
     constexpr int kShift = NV == 2 ? 4 : NV == 4 ? 3 : NV == 8 ? 2 : NV == 16 ? 1 : 0;
     extern __shared__ float part[];      // [stream][local row * MT + m][kc]
+    __shared__ float s_ss[kMaxWarps];    // RMSNorm prologue: per-warp sum of squares
 
     const int tid = threadIdx.x, lane = tid & 31, wi = tid >> 5;
     const int cw = p.cw;
@@ -172,7 +192,7 @@ gemv_rows_kernel(const __grid_constant__ RowsParams p) {
     Stage<R> sa, sb;
     load(sa, 0);
     load(sb, 1);
-    const float gs = (p.a.xb != nullptr) ? __ldg(p.a.gs) : 1.0f;
+    const float gs = (p.a.xb != nullptr || p.a.pro_kind != 0) ? __ldg(p.a.gs) : 1.0f;
     pdl_launch_dependents();
     pdl_wait_prior();
 
@@ -183,7 +203,102 @@ gemv_rows_kernel(const __grid_constant__ RowsParams p) {
     for (int m = 0; m < MT; ++m) {
         uint4 codes = make_uint4(0u, 0u, 0u, 0u);
         uint32_t sf2 = 0u;
-        if (active && m < M) {
+        if (p.a.pro_kind == 1) {
+            // activation = bf16( bf16(residual + delta) * rsqrt(mean_sq + eps) * norm_w ); every
+            // stream computes the whole row (its cw warps cover it once); the first stream of the
+            // first CTA writes the new residual. All warps of the CTA pass the barrier.
+            const __nv_bfloat16* rin = static_cast<const __nv_bfloat16*>(p.a.residual_in) + static_cast<int64_t>(m) * p.a.K;
+            const __nv_bfloat16* dl = p.a.delta ? static_cast<const __nv_bfloat16*>(p.a.delta) + static_cast<int64_t>(m) * p.a.K : nullptr;
+            // The 32 values of the slice stay packed as bf16 pairs (they are bf16 after the add)
+            // across the barrier: 16 registers instead of 32.
+            uint4 rr[4] = {make_uint4(0, 0, 0, 0), make_uint4(0, 0, 0, 0), make_uint4(0, 0, 0, 0), make_uint4(0, 0, 0, 0)};
+            float ss = 0.0f;
+            if (active && m < M) {
+                const uint4* rp = reinterpret_cast<const uint4*>(rin + u * 32);
+                const uint4* dp = reinterpret_cast<const uint4*>(dl + u * 32);
+#pragma unroll
+                for (int qd = 0; qd < 4; ++qd) rr[qd] = __ldg(rp + qd);
+                if (dl != nullptr) {
+                    uint4 dd[4];
+#pragma unroll
+                    for (int qd = 0; qd < 4; ++qd) dd[qd] = __ldg(dp + qd);
+#pragma unroll
+                    for (int qd = 0; qd < 4; ++qd) {
+                        float r[8], d[8];
+                        unpack8(rr[qd], r);
+                        unpack8(dd[qd], d);
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) r[j] = r[j] + d[j];
+                        rr[qd] = pack8(r);                      // the bf16 rounding of the separate add
+                    }
+                }
+                if (blockIdx.x == 0 && s == 0) {
+                    uint4* op = reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(p.a.residual_out) +
+                                                         static_cast<int64_t>(m) * p.a.K + u * 32);
+#pragma unroll
+                    for (int qd = 0; qd < 4; ++qd) op[qd] = rr[qd];
+                }
+#pragma unroll
+                for (int qd = 0; qd < 4; ++qd) {
+                    float r[8];
+                    unpack8(rr[qd], r);
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) ss += r[j] * r[j];
+                }
+            }
+#pragma unroll
+            for (int sft = 16; sft > 0; sft >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, sft);
+            __syncthreads();                         // s_ss free (a previous token's readers are done)
+            if (lane == 0) s_ss[wi] = ss;
+            __syncthreads();
+            float tot = 0.0f;
+            for (int j = 0; j < cw; ++j) tot += s_ss[s * cw + j];
+            const float inv = rsqrtf(tot / static_cast<float>(p.a.K) + p.a.eps);
+            if (active && m < M) {
+                const uint4* wp4 = reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(p.a.norm_w) + u * 32);
+                uint4 vq[4];
+#pragma unroll
+                for (int qd = 0; qd < 4; ++qd) {
+                    float r[8], t[8];
+                    unpack8(rr[qd], r);
+                    unpack8(__ldg(wp4 + qd), t);
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) r[j] = r[j] * inv * t[j];
+                    vq[qd] = pack8(r);
+                }
+                uint32_t c0[2], c1[2];
+                const bool exact = p.a.rcp_mode == kRcpExact;
+                const QuantScales q = exact ? make_quant_scales<kRcpExact>(gs) : make_quant_scales<kRcpApprox>(gs);
+                const uint32_t sf0 = quantize_block16_rt(vq[0], vq[1], q, exact, c0);
+                const uint32_t sf1 = quantize_block16_rt(vq[2], vq[3], q, exact, c1);
+                codes = make_uint4(c0[0], c0[1], c1[0], c1[1]);
+                sf2 = sf0 | (sf1 << 8);
+            }
+        } else if (p.a.pro_kind == 2) {
+            // activation = bf16(silu(gate) * up), row = [gate (K) | up (K)]
+            if (active && m < M) {
+                const __nv_bfloat16* row = static_cast<const __nv_bfloat16*>(p.a.xb) + m * p.a.xb_stride + u * 32;
+                const uint4* gp = reinterpret_cast<const uint4*>(row);
+                const uint4* up = reinterpret_cast<const uint4*>(row + p.a.K);
+                uint4 vq[4];
+#pragma unroll
+                for (int qd = 0; qd < 4; ++qd) {
+                    float g[8], uu[8];
+                    unpack8(__ldg(gp + qd), g);
+                    unpack8(__ldg(up + qd), uu);
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) g[j] = g[j] / (1.0f + __expf(-g[j])) * uu[j];
+                    vq[qd] = pack8(g);
+                }
+                uint32_t c0[2], c1[2];
+                const bool exact = p.a.rcp_mode == kRcpExact;
+                const QuantScales q = exact ? make_quant_scales<kRcpExact>(gs) : make_quant_scales<kRcpApprox>(gs);
+                const uint32_t sf0 = quantize_block16_rt(vq[0], vq[1], q, exact, c0);
+                const uint32_t sf1 = quantize_block16_rt(vq[2], vq[3], q, exact, c1);
+                codes = make_uint4(c0[0], c0[1], c1[0], c1[1]);
+                sf2 = sf0 | (sf1 << 8);
+            }
+        } else if (active && m < M) {
             if (p.a.xb != nullptr) {
                 const uint4* src = reinterpret_cast<const uint4*>(
                     static_cast<const __nv_bfloat16*>(p.a.xb) + m * p.a.xb_stride + u * 32);
@@ -296,6 +411,8 @@ void set_gemv_rows_tuning(int mode, int rows, int target_warps) {
 // leave a second round to under a quarter of its warps (N = 5120: 5120x5120 7.3 us on the ring
 // kernel). More tokens: the ring kernel.
 cudaError_t launch_gemv_auto(const GemvArgs& a, cudaStream_t stream) {
+    if (a.pro_kind != 0)         // fused prologues exist in the register-resident kernel only
+        return gemv_rows_supported(a) ? launch_gemv_rows(a, stream) : cudaErrorNotSupported;
     const bool ring = gemv_stream_supported(a);
     if (!gemv_tuning().force_generic && gemv_rows_supported(a)) {
         const int64_t wbytes = static_cast<int64_t>(a.N) * a.K * 9 / 16;
@@ -370,9 +487,17 @@ bool gemv_rows_supported(const GemvArgs& a) {
     if ((reinterpret_cast<uintptr_t>(a.w) & 15) || (a.w_stride_n % 16) != 0) return false;
     if ((reinterpret_cast<uintptr_t>(a.wsf) & 1) || (a.wsf_stride_n % 2) != 0) return false;
     if (a.w_stride_n > (1 << 28) || a.wsf_stride_n > (1 << 28)) return false;     // 32-bit row offsets inside a step
-    if (a.xb != nullptr) {
+    if (a.pro_kind == 1) {
+        if (!a.residual_in || !a.residual_out || !a.norm_w || !a.gs) return false;
+        if ((reinterpret_cast<uintptr_t>(a.residual_in) | reinterpret_cast<uintptr_t>(a.residual_out) |
+             reinterpret_cast<uintptr_t>(a.norm_w) | reinterpret_cast<uintptr_t>(a.delta)) & 15)
+            return false;
+        if (a.K % 8 != 0) return false;
+    } else if (a.xb != nullptr) {
         if ((reinterpret_cast<uintptr_t>(a.xb) & 15) || (a.xb_stride % 8) != 0) return false;
+        if (a.pro_kind == 2 && (a.K % 8 != 0 || a.xb_stride < 2 * static_cast<int64_t>(a.K))) return false;
     } else {
+        if (a.pro_kind != 0) return false;
         if ((reinterpret_cast<uintptr_t>(a.x) & 15) || (a.x_stride % 16) != 0) return false;
         if ((reinterpret_cast<uintptr_t>(a.xsf) & 1) || (a.xsf_stride % 2) != 0) return false;
     }

@@ -37,6 +37,15 @@ struct GemvArgs {
     int out_dtype;
     int N, K, M;
     float alpha;
+    // Fused producer of the activation (register-resident kernel, one token): 0 none,
+    // 1 add + RMSNorm (xb unused), 2 SiLU * up (xb = [M, 2K] gate|up). Same arithmetic and
+    // roundings as the packed linear's prologues.
+    int pro_kind;
+    const void* delta;
+    const void* residual_in;
+    void* residual_out;
+    const void* norm_w;
+    float eps;
 };
 
 // True when the streaming (bulk-copy ring) kernel can take these arguments.

@@ -93,10 +93,20 @@ class _Linear:
                                   rcp_mode=L.RCP_APPROX, out=out)
 
     def after_rmsnorm(self, delta, res_in, res_out, norm_w, eps, out):
+        # The tensor-core kernel wherever the weight is packed, also where the stand-alone crossover
+        # would pick the GEMV: inside a decode layer the GEMV with this prologue measured slower
+        # (Qwen3-32B shards, one GPU, exchanges left out: 213.6 / 405 / 439 tok/s against 221 / 430 /
+        # 469 at TP 1 / 4 / 8): its CTAs fill the register file, so the attention launch that follows
+        # cannot start fetching its cache rows early. The GEMV form serves shapes that cannot be packed.
+        if self.packed is None:
+            return capi.linear_rmsnorm(delta, res_in, res_out, norm_w, eps, self.gs_inv, self.w, self.s,
+                                       self.alpha, out, rcp_mode=L.RCP_APPROX)
         return capi.linear_packed_rmsnorm(delta, res_in, res_out, norm_w, eps, self.gs_inv, self.packed,
                                           self.N, self.alpha, self.ws.buf, rcp_mode=L.RCP_APPROX, out=out)
 
     def after_silu_mul(self, gate_up, out, push=None, gather: bool = False):
+        if self.packed is None:
+            return capi.linear_silu(gate_up, self.gs_inv, self.w, self.s, self.alpha, out, rcp_mode=L.RCP_APPROX)
         return capi.linear_packed_silu(gate_up, self.gs_inv, self.packed, self.N, self.alpha, self.ws.buf,
                                        rcp_mode=L.RCP_APPROX, out=out, push=push, gather=gather)
 
@@ -162,7 +172,8 @@ class DecodeStep:
         self.gu_out = torch.zeros(1, 2 * inter, **bf)
         self.down_out = torch.zeros(1, H, **bf)
         probe = self.layers[0]
-        self.fused = bool(fused) and all(probe[n].packed is not None for n in ("qkv", "gate_up", "down"))
+        self.fused = bool(fused) and all(probe[n].packed is not None or probe[n].K % 32 == 0
+                                         for n in ("qkv", "gate_up", "down"))
         self.q = torch.zeros(1, self.hq * D, **bf)
         self.attn = torch.zeros(1, self.hq * D, **bf)
         self.act = torch.zeros(1, inter, **bf)
@@ -223,7 +234,8 @@ class DecodeStep:
         self.feed_tokens = self.embed.shape[0] >= c.vocab
         self.ws.allocate()
         probe = self.layers[0]
-        self.fused = self.fused and all(probe[n].packed is not None for n in ("qkv", "gate_up", "down"))
+        self.fused = self.fused and all(probe[n].packed is not None or probe[n].K % 32 == 0
+                                        for n in ("qkv", "gate_up", "down"))
         self.graph = None
 
     # -- thin wrappers over the C ABI ------------------------------------------------
