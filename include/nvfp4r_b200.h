@@ -402,7 +402,7 @@ NVFP4R_API int nvfp4r_entropy(const float* logits, int64_t row_stride, int B, in
  *   ctas_per_sm   grid size = SM count * ctas_per_sm; 0 = automatic (default): one CTA per SM
  *                 with a three-slot ring per warp, or three CTAs per SM with two-slot rings
  *                 for single-token launches that have more row groups than one CTA per SM
- *                 has warps (N >= 6144) and K <= 8192, where 24 warps per SM hide the
+ *                 has warps (N >= 6144) and K <= 4096, where 24 warps per SM hide the
  *                 latency of the decode chains better than 8 (measured)
  *   use_pdl       1 = launch with programmatic stream serialization (default 1)
  *   force_generic 1 = always use the plain-load fallback kernel (default 0)

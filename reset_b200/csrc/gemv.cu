@@ -424,7 +424,9 @@ cudaError_t launch_gemv_stream(const GemvArgs& a, cudaStream_t stream) {
     // Automatic choice (measured, M = 1: 24576x4096 17.4 -> 12.8 us, 6144x4096 5.8 -> 5.1 us with
     // three CTAs per SM; 4096x4096 3.6 -> 4.7 us and 5120x25600 34 -> 41 us, hence the bounds:
     // every CTA quantizes the whole activation row, which is what long rows pay for).
-    const bool wide = a.M == 1 && p.n_groups >= 1536 && a.K <= 8192;
+    // K <= 4096: three CTAs of 73 728 B ring + activations + 1 KB reserved fit an SM (231 KB for
+    // 227 KB would not at K = 5120); longer rows stay on one CTA per SM.
+    const bool wide = a.M == 1 && p.n_groups >= 1536 && a.K <= 4096;
     int ctas_per_sm = tune.ctas_per_sm > 0 ? tune.ctas_per_sm : (wide ? 3 : 1);
     if (a.M > 1 && ctas_per_sm > 2) ctas_per_sm = 2;     // register budget of the M > 1 variants
     const bool two_slots = ctas_per_sm >= 3;
