@@ -488,7 +488,7 @@ def run_ours(args, rank, world, local_rank):
     if tp_check is not None:
         line["tp_check"] = tp_check
     if world == 1:
-        line["cpu_baseline"] = cpu_baseline(sample_repeats=2)
+        line["cpu_baseline"] = cpu_baseline(sample_repeats=4)
     return line
 
 
@@ -898,13 +898,16 @@ def run_reset_loop(args):
 
 # ---------------------------------------------------------------------- reference / CPU
 
-def _cpu_pass(weights, xs, gs_inv):
-    """One M=1 pass over the four linears with the torch-CPU port of the reference's
-    dequantise-then-matmul (incl. the activation quantizer)."""
+def _cpu_step(weights, xs, gs_inv):
+    """One STEP of the workload on the host: the four linears at M = 1, 2, 4, 8 (16 pairs), each
+    with the activation quantizer, through the torch-CPU port of the reference's
+    dequantise-then-matmul (the weight is dequantised again for every pair, as the reference's
+    path does per call)."""
     from oracle import torch_port as otp
-    for (w, s), x in zip(weights, xs):
-        xc, xsf = otp.quantize_torch(x, gs_inv)
-        otp.linear_torch(w, s, xc, xsf, 1.0)
+    for M in M_VALUES:
+        for (w, s), x in zip(weights, xs):
+            xc, xsf = otp.quantize_torch(x[:M], gs_inv)
+            otp.linear_torch(w, s, xc, xsf, 1.0)
 
 
 def _cpu_setup():
@@ -913,44 +916,44 @@ def _cpu_setup():
     for name, N, K, _ in LINEARS:
         weights.append((torch.randint(0, 256, (N, K // 2), dtype=torch.uint8, generator=g),
                         torch.randint(1, 0x38, (N, K // 16), dtype=torch.uint8, generator=g)))
-        xs.append(torch.randn(1, K, generator=g).to(torch.bfloat16))
-    nbytes = sum(linear_bytes(N, K, 1) for _, N, K, _ in LINEARS)
-    return weights, xs, nbytes
+        xs.append(torch.randn(max(M_VALUES), K, generator=g).to(torch.bfloat16))
+    return weights, xs, step_bytes()
 
 
 def cpu_baseline(sample_repeats: int) -> dict:
     torch.set_num_threads(os.cpu_count() or 1)
     weights, xs, nbytes = _cpu_setup()
-    _cpu_pass(weights, xs, 100.0)
+    _cpu_step(weights, xs, 100.0)
     ts = []
     for _ in range(sample_repeats):
         t0 = time.perf_counter()
-        _cpu_pass(weights, xs, 100.0)
+        _cpu_step(weights, xs, 100.0)
         ts.append(time.perf_counter() - t0)
     t = sorted(ts)[len(ts) // 2]
     return {"value": round(nbytes / t / 1e9, 3), "unit": "GB/s", "cores": torch.get_num_threads(),
             "kind": "port",
-            "sample": f"M=1 pass over the four Qwen3-8B linears (1 of the 4 M values), "
-                      f"median of {sample_repeats}, {t * 1e3:.0f} ms per pass"}
+            "sample": f"{sample_repeats + 1} whole steps (the same 16 (linear, M) pairs as the GPU step) on the host "
+                      f"cores, median {t * 1e3:.0f} ms per step"}
 
 
 def run_reference(args, rank, world):
     """The reference's CPU implementation of the path (PyTorch gather-dequantise +
     fp32 matmul, kernels/tests/conftest.py:23-55) timed on the host cores through its
     port in oracle/torch_port.py; the Python reference itself is not present on the
-    GPU box."""
+    GPU box. A step is the SAME step as the GPU arm's: the four Qwen3-8B linears at
+    M = 1, 2, 4, 8 with the activation quantizer (about a second of host time)."""
     if rank != 0:
         return None
     torch.set_num_threads(os.cpu_count() or 1)
     weights, xs, nbytes = _cpu_setup()
     for _ in range(args.warmup):
-        _cpu_pass(weights, xs, 100.0)
+        _cpu_step(weights, xs, 100.0)
     t0 = time.perf_counter()
     for _ in range(args.steps):
-        _cpu_pass(weights, xs, 100.0)
+        _cpu_step(weights, xs, 100.0)
     t = (time.perf_counter() - t0) / args.steps
     gbs = nbytes / t / 1e9
-    sample = "each step = the M=1 pass over the four Qwen3-8B linears incl. activation quantization"
+    sample = "each step = the whole workload step: 16 (linear, M) pairs incl. activation quantization"
     return {
         "impl": "reference",
         "metric": "HBM GB/s over the Qwen3-8B NVFP4 W4A4 decode linear set, M=1..8, incl. activation quantization",
@@ -958,7 +961,7 @@ def run_reference(args, rank, world):
         "ms_per_step": round(t * 1e3, 3), "higher_is_better": True, "scaling": "strong",
         "vs_baseline": None, "dtype": "f32 dequantise + f32 matmul on CPU", "data": "synthetic",
         "config": {"workload": "Qwen3-8B decode linears qkv/o/gate_up/down x M{1,2,4,8}, fused quant+GEMV",
-                   "sample": sample, "parallelism": "host cores"},
+                   "launches_per_step": 16, "sample": sample, "parallelism": "host cores"},
         "cpu_baseline": {"value": round(gbs, 3), "unit": "GB/s", "cores": torch.get_num_threads(),
                          "kind": "port", "sample": sample},
         "e2e": {"value": round(gbs, 3), "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
