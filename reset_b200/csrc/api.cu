@@ -1,6 +1,7 @@
 // extern "C" entry points: argument checks, then the kernel launchers.
 #include <cstdio>
 #include <cstring>
+#include <mutex>
 
 #include <nvtx3/nvToolsExt.h>
 
@@ -607,6 +608,8 @@ int nvfp4r_set_gemv_rows_tuning(int mode, int rows_per_step, int warps_per_sm) {
 int nvfp4r_status_mirror(volatile int** host_word) {
     if (!host_word) return fail(NVFP4R_ERR_INVALID_ARGUMENT, "status_mirror: null pointer");
     static int* host_ptr[64] = {};
+    static std::mutex mu;                       // two threads may make the first call at once
+    std::lock_guard<std::mutex> lock(mu);
     int dev = 0;
     cudaError_t e = cudaGetDevice(&dev);
     if (e != cudaSuccess) return cuda_fail(e, "status_mirror");
