@@ -366,6 +366,33 @@ NVFP4R_API int nvfp4r_reset_step_per_request(float* logits, int64_t row_stride, 
                                              nvfp4r_reset_decision* decisions,
                                              void* workspace, size_t workspace_bytes, void* stream);
 
+/* lm_head and the ReSET step of ONE token in one launch: the logits are produced, judged and
+ * divided on the chip and reach memory once, already divided by the temperature, instead of
+ * being written by nvfp4r_lm_head, read and rewritten by nvfp4r_reset_step. No counterpart in
+ * the reference (vLLM computes the logits and calls the processor, reset/reset/
+ * logits_processor.py:175-189, as separate steps); it stands for that pair for a batch of one.
+ *   x        bf16 [H], the final-norm output of the token
+ *   weight   bf16 [V, H] row-major (16-byte aligned), H % 256 == 0, H <= 12288
+ *   logits   fp32 [V] out: W.x / temperature (one-hot form for temperature <= 1e-6)
+ *   states, state_slots ([1] or NULL), last_ids ([1,2]), nl_bitmaps / dnl_bitmaps / n_id_sets,
+ *   slot_params, decisions ([1] or NULL): as nvfp4r_reset_step_per_request with B = 1;
+ *            state_slots[0] < 0 writes the plain logits and leaves the request state alone
+ *   workspace  >= nvfp4r_lm_head_reset_workspace_bytes() bytes, 8-byte aligned, ALL ZERO before
+ *            its first use, one per token row in flight
+ * The logits equal nvfp4r_lm_head's bit for bit before the division; the entropy is summed
+ * over a different partition of the row than nvfp4r_reset_step uses (same terms, agreement to
+ * float rounding). One CTA per SM, all resident at once (see "Residency" below);
+ * NVFP4R_ERR_UNSUPPORTED_SHAPE when V exceeds 64 rows per warp of that grid (V > 303 104 on
+ * 148 SMs). */
+NVFP4R_API size_t nvfp4r_lm_head_reset_workspace_bytes(void);
+NVFP4R_API int nvfp4r_lm_head_reset_step(const void* x, const void* weight, float* logits, int V, int H,
+                                         nvfp4r_reset_state* states, const int32_t* state_slots,
+                                         const int32_t* last_ids,
+                                         const uint32_t* nl_bitmaps, const uint32_t* dnl_bitmaps,
+                                         int n_id_sets, const nvfp4r_reset_params* slot_params,
+                                         nvfp4r_reset_decision* decisions,
+                                         void* workspace, size_t workspace_bytes, void* stream);
+
 /* ReSET step without any caller-provided scratch. No counterpart in the reference (its
  * processor is PyTorch code and allocates freely); it exists for hosts that cannot
  * allocate device memory when they need the processor: a sampler plug-in inside an engine
@@ -476,8 +503,8 @@ NVFP4R_API int nvfp4r_check_device_status(void);
  * the scratch it used (split-K slots, ReSET workspace, peer receive memory) is mid-exchange:
  * zero it before the next use.
  *
- * Residency. nvfp4r_linear_packed*, the single-launch form of nvfp4r_reset_step* and
- * push_gather wait for other CTAs of their own grid (or of a peer GPU's grid). Their grids are
+ * Residency. nvfp4r_linear_packed*, the single-launch form of nvfp4r_reset_step*,
+ * nvfp4r_lm_head_reset_step and push_gather wait for other CTAs of their own grid (or of a peer GPU's grid). Their grids are
  * sized to be resident all at once on an otherwise idle device (at most two CTAs per SM; the
  * ReSET launcher falls back to its three-launch form when the occupancy calculation says the
  * grid does not fit). A kernel of ANOTHER stream that holds SMs at the same time can delay the

@@ -86,6 +86,9 @@ PROTOTYPES = {
                                C.POINTER(ResetParams), _vp, _vp, _sz, _vp]),
     "nvfp4r_reset_step_per_request": (_i, [_vp, _i64, _i, _i, _vp, _vp, _vp, _vp, _vp, _i, _vp, _vp,
                                            _vp, _sz, _vp]),
+    "nvfp4r_lm_head_reset_workspace_bytes": (_sz, []),
+    "nvfp4r_lm_head_reset_step": (_i, [_vp, _vp, _vp, _i, _i, _vp, _vp, _vp, _vp, _vp, _i, _vp, _vp,
+                                       _vp, _sz, _vp]),
     "nvfp4r_reset_step_static": (_i, [_vp, _i64, _i, _i, _vp, _vp, _vp, _vp, _vp,
                                       C.POINTER(ResetParams), _vp, _vp]),
     "nvfp4r_entropy": (_i, [_vp, _i64, _i, _i, _vp, _vp, _sz, _vp]),

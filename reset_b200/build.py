@@ -25,7 +25,7 @@ LIB_NAME = "libnvfp4r_b200.so"
 EXT_NAME = "_C" + (sysconfig.get_config_var("EXT_SUFFIX") or ".so")
 
 CUDA_SOURCES = ["api.cu", "quant.cu", "gemv.cu", "gemv_rows.cu", "reset_step.cu", "gemm_tcgen05.cu", "linear_packed.cu",
-                "no_alloc.cu", "decode_ops.cu", "peer_allreduce.cu"]
+                "no_alloc.cu", "decode_ops.cu", "peer_allreduce.cu", "lm_head_reset.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "-Xcompiler", "-fPIC,-fvisibility=hidden", "--expt-relaxed-constexpr",

@@ -356,6 +356,42 @@ def reset_step_per_request(logits: torch.Tensor, states: torch.Tensor, slot_para
     L.check(st, "nvfp4r_reset_step_per_request")
 
 
+def lm_head_reset_workspace(device) -> torch.Tensor:
+    """All-zero workspace of :func:`lm_head_reset_step` for one token row."""
+    return torch.zeros((L.lib().nvfp4r_lm_head_reset_workspace_bytes() + 7) // 8, dtype=torch.int64, device=device)
+
+
+def lm_head_reset_step(x: torch.Tensor, weight: torch.Tensor, logits: torch.Tensor, states: torch.Tensor,
+                       slot_params: torch.Tensor, *, state_slots: torch.Tensor | None = None,
+                       last_ids: torch.Tensor | None = None, nl_bitmaps: torch.Tensor | None = None,
+                       dnl_bitmaps: torch.Tensor | None = None, n_id_sets: int = 0,
+                       decisions: torch.Tensor | None = None, workspace: torch.Tensor) -> None:
+    """lm_head (bf16 ``weight`` [V,H] times the token ``x`` [H] or [1,H]) ending in the ReSET step of
+    that token, one launch: ``logits`` (fp32 [V] or [1,V]) receives W.x divided by the chosen
+    temperature. The ReSET arguments are those of :func:`reset_step_per_request` with B = 1."""
+    _need_cuda(x, weight, logits, states, slot_params, state_slots, last_ids, nl_bitmaps, dnl_bitmaps, decisions,
+               workspace)
+    if weight.dtype != torch.bfloat16 or weight.dim() != 2 or not weight.is_contiguous():
+        raise ValueError("lm_head_reset_step: weight must be contiguous bf16 [V,H]")
+    V, H = weight.shape
+    if x.dtype != torch.bfloat16 or x.numel() != H or not x.is_contiguous():
+        raise ValueError("lm_head_reset_step: x must be contiguous bf16 with H elements")
+    if logits.dtype != torch.float32 or logits.numel() != V or not logits.is_contiguous():
+        raise ValueError("lm_head_reset_step: logits must be contiguous fp32 with V elements")
+    words = (V + 31) // 32
+    if n_id_sets > 0:
+        for bm in (nl_bitmaps, dnl_bitmaps):
+            if bm is None or bm.numel() * bm.element_size() < n_id_sets * words * 4:
+                raise ValueError("lm_head_reset_step: bitmaps must hold n_id_sets * ceil(V/32) words")
+    ptr = lambda t: t.data_ptr() if t is not None else None
+    with torch.cuda.device(logits.device):
+        st = L.lib().nvfp4r_lm_head_reset_step(
+            x.data_ptr(), weight.data_ptr(), logits.data_ptr(), V, H, states.data_ptr(), ptr(state_slots),
+            ptr(last_ids), ptr(nl_bitmaps), ptr(dnl_bitmaps), int(n_id_sets), slot_params.data_ptr(),
+            ptr(decisions), workspace.data_ptr(), workspace.numel() * workspace.element_size(), _stream())
+    L.check(st, "nvfp4r_lm_head_reset_step")
+
+
 def sample(logits: torch.Tensor, draws: torch.Tensor, *, seed: int = 0,
            last_ids: torch.Tensor | None = None, out: torch.Tensor | None = None,
            top_k: int = 0, top_p: float = 1.0, workspace: torch.Tensor | None = None) -> torch.Tensor:

@@ -525,6 +525,49 @@ int nvfp4r_reset_step_per_request(float* logits, int64_t row_stride, int B, int 
     return e == cudaSuccess ? NVFP4R_OK : cuda_fail(e, "reset_step_per_request launch");
 }
 
+size_t nvfp4r_lm_head_reset_workspace_bytes(void) { return nvfp4r::lm_head_reset_workspace_bytes(); }
+
+int nvfp4r_lm_head_reset_step(const void* x, const void* weight, float* logits, int V, int H,
+                              nvfp4r_reset_state* states, const int32_t* state_slots,
+                              const int32_t* last_ids, const uint32_t* nl_bitmaps,
+                              const uint32_t* dnl_bitmaps, int n_id_sets,
+                              const nvfp4r_reset_params* slot_params,
+                              nvfp4r_reset_decision* decisions, void* workspace,
+                              size_t workspace_bytes, void* stream) {
+    NVFP4R_RANGE("nvfp4r_lm_head_reset_step");
+    if (!x || !weight || !logits || !states || !slot_params || !workspace)
+        return fail(NVFP4R_ERR_INVALID_ARGUMENT, "lm_head_reset_step: null pointer");
+    if (V <= 0 || H <= 0 || n_id_sets < 0)
+        return fail(NVFP4R_ERR_INVALID_ARGUMENT, "lm_head_reset_step: bad sizes");
+    if (H % 256 != 0 || H > 12288)
+        return fail(NVFP4R_ERR_UNSUPPORTED_SHAPE, "lm_head_reset_step: H must be a multiple of 256, at most 12288");
+    if (workspace_bytes < nvfp4r::lm_head_reset_workspace_bytes())
+        return fail(NVFP4R_ERR_INVALID_ARGUMENT, "lm_head_reset_step: workspace too small");
+    if (!aligned(workspace, 8) || !aligned(logits, 4) || !aligned(states, 8) || !aligned(slot_params, 8) ||
+        !aligned(x, 2) || !aligned(weight, 16))
+        return fail(NVFP4R_ERR_ALIGNMENT, "lm_head_reset_step: weight needs 16-byte, workspace/states/params 8-byte alignment");
+    nvfp4r::ResetLaunch p = {};
+    p.logits = logits;
+    p.row_stride = V;
+    p.B = 1;
+    p.V = V;
+    p.states = states;
+    p.state_slots = state_slots;
+    p.last_ids = last_ids;
+    p.nl_bitmap = n_id_sets > 0 ? nl_bitmaps : nullptr;
+    p.dnl_bitmap = n_id_sets > 0 ? dnl_bitmaps : nullptr;
+    p.slot_params = slot_params;
+    p.bitmap_words = (V + 31) / 32;
+    p.decisions = decisions;
+    p.needs_state = 1;
+    cudaError_t e = nvfp4r::launch_lm_head_reset(x, weight, H, p, workspace, as_stream(stream));
+    if (e == cudaErrorInvalidConfiguration)
+        return fail(NVFP4R_ERR_UNSUPPORTED_SHAPE,
+                    "lm_head_reset_step: vocabulary too large for one resident grid; use nvfp4r_lm_head "
+                    "followed by nvfp4r_reset_step_per_request");
+    return e == cudaSuccess ? NVFP4R_OK : cuda_fail(e, "lm_head_reset_step launch");
+}
+
 int nvfp4r_reset_step_static(float* logits, int64_t row_stride, int B, int V,
                              nvfp4r_reset_state* states, const int32_t* state_slots,
                              const int32_t* last_ids, const uint32_t* nl_bitmap,
@@ -626,6 +669,7 @@ int nvfp4r_status_mirror(volatile int** host_word) {
         if (e == cudaSuccess) e = nvfp4r::set_status_mirror_packed(d);
         if (e == cudaSuccess) e = nvfp4r::set_status_mirror_peer(d);
         if (e == cudaSuccess) e = nvfp4r::set_status_mirror_reset(d);
+        if (e == cudaSuccess) e = nvfp4r::set_status_mirror_head(d);
         if (e != cudaSuccess) { cudaFreeHost(h); return cuda_fail(e, "status_mirror: set-up"); }
         host_ptr[dev] = h;
     }
@@ -642,7 +686,9 @@ int nvfp4r_check_device_status(void) {
     int flag4 = 0, flag5 = 0;
     if (e == cudaSuccess) e = nvfp4r::read_and_clear_peer_status(&flag4);
     if (e == cudaSuccess) e = nvfp4r::read_and_clear_reset_status(&flag5);
-    flag4 |= flag5;
+    int flag6 = 0;
+    if (e == cudaSuccess) e = nvfp4r::read_and_clear_head_status(&flag6);
+    flag4 |= flag5 | flag6;
     if (e != cudaSuccess) return cuda_fail(e, "device status");
     flag |= flag2 | flag3 | flag4;
     return flag ? fail(NVFP4R_ERR_DEVICE_TIMEOUT, "a bounded device-side wait gave up") : NVFP4R_OK;

@@ -138,6 +138,7 @@ cudaError_t read_and_clear_device_status(int* flag);
 cudaError_t read_and_clear_peer_status(int* flag);
 uint32_t peer_poll_limit();      // polls a wait for a peer GPU may take (nvfp4r_set_peer_poll_limit)
 cudaError_t read_and_clear_reset_status(int* flag);
+cudaError_t read_and_clear_head_status(int* flag);
 
 // Pinned-host twin of the time-out flags: one setter per kernel file (status_mirror.cuh).
 cudaError_t set_status_mirror_gemv(int* device_ptr);
@@ -145,6 +146,7 @@ cudaError_t set_status_mirror_tc(int* device_ptr);
 cudaError_t set_status_mirror_packed(int* device_ptr);
 cudaError_t set_status_mirror_peer(int* device_ptr);
 cudaError_t set_status_mirror_reset(int* device_ptr);
+cudaError_t set_status_mirror_head(int* device_ptr);
 
 int device_sm_count();
 

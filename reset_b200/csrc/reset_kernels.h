@@ -61,5 +61,11 @@ int reset_pick_slices(int B, int V);
 cudaError_t launch_reset(ResetLaunch p, bool scale, cudaStream_t stream);
 // Same step with the scratch taken from a static device array (no_alloc.cu).
 cudaError_t launch_reset_static(ResetLaunch p, cudaStream_t stream);
+// lm_head (bf16 weight [V, H], one token) ending in the ReSET step of that token, one launch
+// (lm_head_reset.cu). `p.logits` is the output row; cudaErrorInvalidConfiguration = shape or
+// residency not supported.
+size_t lm_head_reset_workspace_bytes();
+cudaError_t launch_lm_head_reset(const void* x, const void* weight, int H, ResetLaunch p, void* workspace,
+                                 cudaStream_t stream);
 
 }  // namespace nvfp4r

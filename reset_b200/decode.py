@@ -163,6 +163,7 @@ class DecodeStep:
         self.token = torch.zeros(1, dtype=torch.int32, device=self.device)
         self.feed_tokens = False          # random model: the embedding table is a 1024-row stand-in
         self.reset = None                 # set by enable_reset(): ReSET processor + sampling instead of arg-max
+        self.head_ws = None               # workspace of the fused lm_head + ReSET launch (enable_reset)
         self.ws.allocate()
         self.res = [torch.zeros(1, H, **bf), torch.zeros(1, H, **bf)]     # ping-pong residual stream
         self.residual = self.res[0]
@@ -327,6 +328,16 @@ class DecodeStep:
             self._all_reduce(self.down_out, pushed=push is not None)
             x = self.down_out
         self._add_rmsnorm(x, self.res[cur], self.final_ln)
+        if self.reset is not None and self.head_ws is not None:
+            # one rank holds the whole vocabulary: lm_head and the ReSET step are one launch, the
+            # logits reach memory once, already divided by the temperature
+            d = self.reset
+            capi.lm_head_reset_step(self.normed, self.lm_head, self.logits_local, d.states, d.params_dev,
+                                    last_ids=self.last_ids, nl_bitmaps=d.nl_bitmaps, dnl_bitmaps=d.dnl_bitmaps,
+                                    n_id_sets=d.n_id_sets, decisions=d.decisions, workspace=self.head_ws)
+            capi.sample(self.logits_local, self.draws, seed=self.sample_seed, last_ids=self.last_ids,
+                        out=self.token, top_k=self.top_k, top_p=self.top_p, workspace=self.sample_ws)
+            return
         L.check(lib.nvfp4r_lm_head(self.normed.data_ptr(), self.lm_head.data_ptr(), self.logits_local.data_ptr(),
                                    self.vocab_local, c.hidden, self._stream()), "lm_head")
         if self.world > 1 and not self.skip_exchange:
@@ -374,7 +385,8 @@ class DecodeStep:
         self.graph.replay()
 
     def enable_reset(self, t_high: float = 1.0, t_low: float = 0.1, tau0: float = 0.5505, window: int = 32,
-                     nl_ids=(), dnl_ids=(), seed: int = 0, top_k: int = 0, top_p: float = 1.0) -> None:
+                     nl_ids=(), dnl_ids=(), seed: int = 0, top_k: int = 0, top_p: float = 1.0,
+                     fused_head: bool = True) -> None:
         """End every step with the ReSET processor (reset/reset/logits_processor.py:62-134) and a
         draw from the softmax of the scaled logits instead of the arg-max, optionally restricted
         to the top-k / top-p set as vLLM's sampler would. Every rank holds the full logits after
@@ -389,6 +401,11 @@ class DecodeStep:
         self.sample_seed = int(seed)
         self.top_k, self.top_p = int(top_k), float(top_p)
         self.sample_ws = capi.sample_workspace(1, self.device)
+        # lm_head + ReSET in one launch when this rank has the whole vocabulary and a warp of the
+        # one-CTA-per-SM grid holds at most 64 logits
+        sms = torch.cuda.get_device_properties(self.device).multi_processor_count
+        fits = self.world == 1 and self.cfg.vocab <= 64 * 32 * min(sms, 256) and self.cfg.hidden % 256 == 0
+        self.head_ws = capi.lm_head_reset_workspace(self.device) if (fits and fused_head) else None
         self.graph = None
 
     def set_position(self, pos: int) -> None:
@@ -423,4 +440,4 @@ class DecodeStep:
                 for name in ("o", "down"):
                     pushed = not probe[name].use_gemv and (self.fused or name == "o")
                     per_layer += 0 if (pushed and self.fused_gather) else 1
-        return self.cfg.layers * per_layer + 5 + (1 if self.reset is not None else 0)
+        return self.cfg.layers * per_layer + 5 + (1 if self.reset is not None and self.head_ws is None else 0)
