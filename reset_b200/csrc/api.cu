@@ -416,7 +416,7 @@ int nvfp4r_linear_packed_ex(const nvfp4r_prologue* pro, const void* x, int64_t x
 }
 
 int nvfp4r_set_packed_tuning(int splits) {
-    if (splits < 0 || (splits & 0xff) > 64 || splits >= (1 << 24)) return fail(NVFP4R_ERR_INVALID_ARGUMENT, "packed tuning: splits 0..64");
+    if (splits < 0 || (splits & 0xff) > 64 || splits >= (1 << 28)) return fail(NVFP4R_ERR_INVALID_ARGUMENT, "packed tuning: splits 0..64");
     nvfp4r::set_packed_tuning(splits);
     return NVFP4R_OK;
 }

@@ -94,6 +94,8 @@ struct PackedParams {
     // the call counter - the whole all-reduce inside this launch, no gather kernel after it.
     int push_gather;
     uint32_t push_poll_limit;
+    // stages beyond the ring that the producer asks L2 to fetch before the activations are ready
+    int l2_stages;
 };
 
 __device__ int g_packed_status = 0;
@@ -338,6 +340,20 @@ linear_packed_kernel(const __grid_constant__ PackedParams p) {
     pdl_launch_dependents();
     pdl_wait_prior();
     if (warp == 0) TRACE(2);
+    if (tid == 0) {
+        // The ring is full until the first MMA frees a stage, which is the prologue away (load
+        // and quantize the activations). The stages that follow are asked into L2 now - not
+        // before the wait, where they would compete with the last stages of the kernel before -
+        // so that HBM keeps streaming through the prologue and the ring later refills from L2.
+#pragma unroll 1
+        for (int k = issued; k < total && k < issued + p.l2_stages; ++k) {
+            const int ti = k / stages_per_tile, j = k - ti * stages_per_tile;
+            const int nb = min(kBlocksPerStage, nkb - j * kBlocksPerStage);
+            bulk_prefetch_l2(p.packed + (static_cast<int64_t>(rank + ti * cpp) * p.kblocks + kb0 +
+                                         j * kBlocksPerStage) * kBlockBytes,
+                             static_cast<uint32_t>(nb) * kBlockBytes);
+        }
+    }
 
     // ---- prologue: quantize this part's activations into operand layout --------------
     if (my_tiles > 0) {
@@ -502,8 +518,13 @@ linear_packed_kernel(const __grid_constant__ PackedParams p) {
             if (!wf.wait(bar_empty + 8 * s, ((issued / kStages) - 1) & 1)) break;
             issue_next();
         }
-    } else if (tid == 32 && my_tiles > 0) {
+    } else if (warp == 1 && my_tiles > 0) {
         // ---------------- MMA issuer -----------------------------------------------------
+        // The whole warp walks the loops (waits included) and one elected lane issues: descriptors
+        // and addresses are then warp-uniform values, which is what the tensor-core instructions
+        // take their operands from (a single active lane of a diverged warp paid about 70 cycles
+        // per instruction to get them there).
+        const bool leader = elect_one();
         constexpr uint32_t idesc = (1u << 7) | (1u << 10) | (static_cast<uint32_t>(BN >> 3) << 17) |
                                    (static_cast<uint32_t>(kTileRows >> 7) << 27);
         int i = 0;
@@ -520,6 +541,7 @@ linear_packed_kernel(const __grid_constant__ PackedParams p) {
                 if (i == 0) TRACE(4);
                 // the activation scales of this stage's blocks are in tensor memory (first tile only)
                 if (ti == 0 && !wf.wait(bar_sfb + 8 * j, 0)) break;
+                if (i == 0) TRACE(10);
                 tc_fence_after();
                 const int nb = min(kBlocksPerStage, nkb - j * kBlocksPerStage);
 #pragma unroll 1
@@ -531,17 +553,24 @@ linear_packed_kernel(const __grid_constant__ PackedParams p) {
                     const uint64_t sfa_desc = desc_scales(a_smem + kCodesBytes);
                     const uint32_t sfa_col = tmem + kColSFA + 16 * b;
                     const uint32_t sfb_col = tmem + kColSFB + 16 * blk;
-#pragma unroll 1
-                    for (int k = 0; k < 4; ++k) {
-                        // descriptors advance by (bytes >> 4): 512 B per scale chunk, 32 B per K64 of codes
-                        tc_cp_scales(sfa_col + 4 * k, sfa_desc + 32 * k);
-                        tc_mma_nvf4(d_tmem, a_desc + 2 * k, b_desc + 2 * k, idesc, sfa_col + 4 * k,
-                                    sfb_col + 4 * k, (blk | k) != 0 ? 1u : 0u);
+                    if (leader) {
+                        // descriptors advance by (bytes >> 4): 512 B per scale chunk, 32 B per K64 of
+                        // codes; the four weight-scale copies go first so that no MMA waits behind
+                        // its own copy
+#pragma unroll
+                        for (int k = 0; k < 4; ++k) tc_cp_scales(sfa_col + 4 * k, sfa_desc + 32 * k);
+#pragma unroll
+                        for (int k = 0; k < 4; ++k)
+                            tc_mma_nvf4(d_tmem, a_desc + 2 * k, b_desc + 2 * k, idesc, sfa_col + 4 * k,
+                                        sfb_col + 4 * k, (blk | k) != 0 ? 1u : 0u);
                     }
                 }
-                tc_commit(bar_empty + 8 * s);
+                if (i == 0) TRACE(11);
+                if (leader) tc_commit(bar_empty + 8 * s);
+                if (i == 0) TRACE(12);
+                __syncwarp();
             }
-            tc_commit(bar_accfull + 8 * buf);
+            if (leader) tc_commit(bar_accfull + 8 * buf);
             if (ti == 0) TRACE(5);
         }
         TRACE(6);
@@ -692,6 +721,7 @@ linear_packed_kernel(const __grid_constant__ PackedParams p) {
 struct PackedPlan { int splits, grid, bn; size_t smem; };
 int g_force_packed_splits = 0;
 int g_packed_ctas_per_sm = 2;
+int g_packed_l2_stages = 2;          // measured best on B200 (0: 3248, 2: 3254 -> with the warp-uniform issuer 3459 GB/s; 3+: worse)
 
 // Parts of at most kMaxPartBlocks K blocks; among the admissible split counts take the
 // one with the smallest estimated time.
@@ -797,6 +827,7 @@ cudaError_t launch_linear_packed(const PackedLinearArgs& g, cudaStream_t stream,
             p.push_gather = g.push_gather ? 1 : 0;
             p.push_poll_limit = peer_poll_limit();
         }
+        p.l2_stages = g_packed_l2_stages;
 
         void (*kern)(PackedParams) = plan.bn == 16 ? linear_packed_kernel<16> : linear_packed_kernel<32>;
         static bool attr_done[2][64] = {};
@@ -832,6 +863,7 @@ cudaError_t launch_linear_packed(const PackedLinearArgs& g, cudaStream_t stream,
 void set_packed_tuning(int splits) {
     g_force_packed_splits = splits & 0xff;
     g_packed_ctas_per_sm = ((splits >> 9) & 1) ? 1 : 2;
+    if ((splits >> 24) & 0xf) g_packed_l2_stages = ((splits >> 24) & 0xf) - 1;   // bits 24..27: L2 prefetch depth + 1
 #ifdef NVFP4R_TRACE
     // bit 8: record the time line of eight CTAs; bits 12..23: the first of them
     const int trace = ((splits >> 8) & 1) ? 1 + ((splits >> 12) & 0xfff) : 0;

@@ -164,6 +164,12 @@ __device__ __forceinline__ void bulk_g2s(uint32_t dst, const void* src, uint32_t
         :: "r"(dst), "l"(src), "r"(bytes), "r"(bar), "l"(policy) : "memory");
 }
 
+// Bulk prefetch of global memory into L2 (no destination, no completion signal).
+// src 16-byte aligned; bytes a multiple of 16.
+__device__ __forceinline__ void bulk_prefetch_l2(const void* src, uint32_t bytes) {
+    asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" :: "l"(src), "r"(bytes) : "memory");
+}
+
 // --------------------------------------------------------------------------
 // Programmatic dependent launch
 // --------------------------------------------------------------------------
