@@ -285,29 +285,37 @@ linear_packed_kernel(const __grid_constant__ PackedParams p) {
     constexpr uint32_t kColSFA = 2 * BN;                              // 16 columns per block of a stage
     constexpr uint32_t kColSFB = kColSFA + 16 * kBlocksPerStage;      // 16 per block of the K part
 
-    // producer state (thread 0 only): next stage = K-block pair p_j of this CTA's p_ti-th tile
+    // producer state (kept by every lane of warp 0, one elected lane issues): next stage = K-block
+    // pair p_j of this CTA's p_ti-th tile. Addresses and sizes are computed by the whole warp so
+    // that they are warp-uniform values when the bulk copy takes them.
     int issued = 0, p_ti = 0, p_j = 0;
     const uint64_t policy = l2_policy_evict_first();
+    const bool lead0 = (warp == 0) && elect_one();
     auto issue_next = [&]() {
         const int tile = rank + p_ti * cpp;
         const int s = issued & (kStages - 1);
         const int nb = min(kBlocksPerStage, nkb - p_j * kBlocksPerStage);
         const uint32_t bytes = static_cast<uint32_t>(nb) * kBlockBytes;
-        mbar_expect_tx(bar_full + 8 * s, bytes);
-        bulk_g2s(ring + s * kStageBytes,
-                 p.packed + (static_cast<int64_t>(tile) * p.kblocks + kb0 + p_j * kBlocksPerStage) * kBlockBytes,
-                 bytes, bar_full + 8 * s, policy);
+        const uint8_t* src =
+            p.packed + (static_cast<int64_t>(tile) * p.kblocks + kb0 + p_j * kBlocksPerStage) * kBlockBytes;
+        if (lead0) {
+            mbar_expect_tx(bar_full + 8 * s, bytes);
+            bulk_g2s(ring + s * kStageBytes, src, bytes, bar_full + 8 * s, policy);
+        }
         ++issued;
         if (++p_j == stages_per_tile) { p_j = 0; ++p_ti; }
     };
 
-    // The weights do not depend on the previous kernel: thread 0 arms the barriers and starts
+    // The weights do not depend on the previous kernel: warp 0 arms the barriers and starts
     // the first stages before anything else happens in this CTA.
-    if (tid == 0) {
+    if (warp == 0) {
+        if (lead0) {
 #pragma unroll 1
-        for (int i = 0; i < 2 * kStages + 4 + kMaxPartBlocks / kBlocksPerStage; ++i)   // accempty: one arrival per epilogue warp
-            mbar_init(bar_full + 8 * i, (i >= 2 * kStages + 2 && i < 2 * kStages + 4) ? 4u : 1u);
-        mbar_fence_init();
+            for (int i = 0; i < 2 * kStages + 4 + kMaxPartBlocks / kBlocksPerStage; ++i)   // accempty: one arrival per epilogue warp
+                mbar_init(bar_full + 8 * i, (i >= 2 * kStages + 2 && i < 2 * kStages + 4) ? 4u : 1u);
+            mbar_fence_init();
+        }
+        __syncwarp();
 #pragma unroll 1
         while (issued < total && issued < kStages) issue_next();
     }
@@ -340,7 +348,7 @@ linear_packed_kernel(const __grid_constant__ PackedParams p) {
     pdl_launch_dependents();
     pdl_wait_prior();
     if (warp == 0) TRACE(2);
-    if (tid == 0) {
+    if (lead0) {
         // The ring is full until the first MMA frees a stage, which is the prologue away (load
         // and quantize the activations). The stages that follow are asked into L2 now - not
         // before the wait, where they would compete with the last stages of the kernel before -
@@ -510,13 +518,14 @@ linear_packed_kernel(const __grid_constant__ PackedParams p) {
     if (warp == 0) TRACE(3);
 
     WaitFail wf;
-    if (tid == 0) {
-        // ---------------- producer -------------------------------------------------------
+    if (warp == 0) {
+        // ---------------- producer (whole warp waits, the elected lane issues) --------------
 #pragma unroll 1
         while (issued < total) {
             const int s = issued & (kStages - 1);
             if (!wf.wait(bar_empty + 8 * s, ((issued / kStages) - 1) & 1)) break;
             issue_next();
+            __syncwarp();
         }
     } else if (warp == 1 && my_tiles > 0) {
         // ---------------- MMA issuer -----------------------------------------------------
@@ -578,18 +587,21 @@ linear_packed_kernel(const __grid_constant__ PackedParams p) {
         // ---------------- epilogue (warps 2..5) ------------------------------------------
         const int q = warp & 3;                                   // TMEM lane quadrant of this warp
         const int row_in_tile = q * 32 + lane;
-        if (tid == 64 && my_tiles > 0) {
+        if (warp == 2 && my_tiles > 0) {
             // activation scales of the whole K part go into tensor memory once, issued from
-            // this thread so that they overlap the MMA thread's weight-scale copies; one
-            // commit per stage of the K part
+            // this warp's elected lane so that they overlap the MMA warp's weight-scale copies;
+            // one commit per stage of the K part
+            const bool lead2 = elect_one();
             const uint64_t d0 = desc_scales(b_sf);
 #pragma unroll 1
             for (int j = 0; j < stages_per_tile; ++j) {
                 const int c0 = j * kBlocksPerStage * 4, c1 = min(nkb * 4, c0 + kBlocksPerStage * 4);
+                if (lead2) {
 #pragma unroll 1
-                for (int ch = c0; ch < c1; ++ch)
-                    tc_cp_scales(tmem + kColSFB + 4 * ch, d0 + ch * (kSfbStride >> 4));
-                tc_commit(bar_sfb + 8 * j);
+                    for (int ch = c0; ch < c1; ++ch)
+                        tc_cp_scales(tmem + kColSFB + 4 * ch, d0 + ch * (kSfbStride >> 4));
+                    tc_commit(bar_sfb + 8 * j);
+                }
             }
         }
         __syncwarp();
