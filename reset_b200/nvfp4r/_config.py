@@ -15,20 +15,18 @@ FALLBACK_BACKEND = os.environ.get("NVFP4R_FALLBACK_BACKEND", "vllm-cutlass").low
 # Measured crossover between the CUDA-core GEMV and the packed tensor-core linear on B200
 # (L2-cold weights, CUDA-graph replay; Qwen3-8B / 14B / 32B shapes and their tensor-parallel
 # shards at TP 2 / 4 / 8). The GEMV's shorter fixed latency wins for single tokens on weights up
-# to GEMV_MAX_WEIGHT_BYTES[1] (3584x5120 4.6 vs 5.1 us, 8704x5120 6.5 vs 6.9 us, 10240x5120 8.1
-# vs 8.6 us, 4096x12288 7.5 vs 8.0 us; level at 17408x5120 and above), and for two to four tokens
-# only on the smallest weights with short rows; everything else goes to the tensor cores (every
-# M >= 2 of the 14B sweep). Index = M.
-GEMV_MAX_WEIGHT_BYTES = {1: 30_000_000, 2: 5_000_000, 3: 2_500_000, 4: 2_500_000}
-# ... and, above one token, only for short rows (the GEMV's time grows with M * K per row)
-GEMV_MAX_K_MULTI_TOKEN = 2048
+# to GEMV_MAX_WEIGHT_BYTES[1] (1280x5120 3.5 vs 5.0 us, 5120x2048 3.3 vs 3.6 us, 4096x4096 3.7 vs
+# 4.2 us; level at 3584x5120, 4.7 us both; 5120x4096 5.1 vs 4.4 us, 6144x4096 5.0 vs 4.7 us,
+# 4096x12288 7.3 vs 6.2 us, 10240x5120 7.8 vs 6.3 us above it). From two tokens on the tensor
+# cores win on every shape measured (5120x1024 3.5 vs 3.4 us, 1280x5120 6.1 vs 5.0 us). Index = M.
+GEMV_MAX_WEIGHT_BYTES = {1: 10_000_000}
 # Rows shorter than this stay on the tensor cores at every M (5120x640: 3.6 vs 3.8 us).
 GEMV_MIN_K = 1024
 # The ring kernel deals groups of 4 rows to GEMV_RING_WARPS warps; with N between 4 and 5 times
 # that count a second round runs on under a quarter of the warps and the tensor cores win unless
-# the rows are short (5120x2560 4.4 vs 4.8 us, 5120x5120 5.4 vs 7.5 us; 5120x1280 3.9 vs 3.2 us).
+# the rows are short (5120x2560 4.4 vs 4.8 us; 5120x2048 3.3 vs 3.6 us, 5120x1024 2.6 vs 3.3 us).
 GEMV_RING_WARPS = 148 * 8
-GEMV_SHORT_ROW_K = 1280
+GEMV_SHORT_ROW_K = 2048
 
 # Tensor-parallel row-parallel linears through `linear_auto(..., reduce=)`: complete the
 # all-reduce inside the linear's own launch, or push in the epilogue and gather in a second

@@ -80,9 +80,7 @@ def use_gemv(M: int, N: int, K: int, gemv_max_m: int) -> bool:
     ring = _config.GEMV_RING_WARPS
     if 4 * ring < N <= 5 * ring and K > _config.GEMV_SHORT_ROW_K:
         return False
-    if N * K * 9 // 16 > _config.GEMV_MAX_WEIGHT_BYTES[M]:
-        return False
-    return M == 1 or K <= _config.GEMV_MAX_K_MULTI_TOKEN
+    return N * K * 9 // 16 <= _config.GEMV_MAX_WEIGHT_BYTES[M]
 
 
 _OUT_WORKSPACE: dict = {}          # device -> zeroed split-K workspace of the out= path

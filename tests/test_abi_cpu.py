@@ -73,18 +73,16 @@ def test_enable_disable_configure_status(monkeypatch):
 
 def test_crossover_rule():
     from reset_b200.nvfp4r.ops import use_gemv
-    assert use_gemv(1, 4096, 4096, 4) and use_gemv(2, 4096, 2048, 4) and use_gemv(4, 4096, 1024, 4)
-    assert not use_gemv(2, 4096, 4096, 4) and not use_gemv(1, 5120, 5120, 4)
-    # single tokens: the GEMV up to 30 MB of weight (measured on the 8B / 14B / 32B shapes and shards)
-    assert use_gemv(1, 6144, 4096, 4) and use_gemv(1, 8704, 5120, 4) and use_gemv(1, 10240, 5120, 4)
-    assert use_gemv(1, 4096, 12288, 4) and use_gemv(1, 3584, 5120, 4)
-    assert not use_gemv(1, 17408, 5120, 4) and not use_gemv(2, 6144, 4096, 4)
-    assert not use_gemv(2, 1280, 5120, 4)                     # long rows go to the tensor cores above one token
-    assert not use_gemv(1, 24576, 4096, 4) and not use_gemv(4, 4096, 4096, 4)
+    # single tokens: the GEMV up to 10 MB of weight (measured on the 8B / 14B / 32B shapes and shards)
+    assert use_gemv(1, 4096, 4096, 4) and use_gemv(1, 1280, 5120, 4) and use_gemv(1, 2560, 5120, 4)
+    assert not use_gemv(1, 5120, 4096, 4) and not use_gemv(1, 6144, 4096, 4) and not use_gemv(1, 5120, 5120, 4)
+    assert not use_gemv(1, 4096, 12288, 4) and not use_gemv(1, 10240, 5120, 4) and not use_gemv(1, 24576, 4096, 4)
+    # from two tokens on: the tensor cores on every shape
+    assert not use_gemv(2, 4096, 2048, 4) and not use_gemv(4, 4096, 1024, 4) and not use_gemv(2, 1280, 5120, 4)
     # N = 5120 (a poor fit for the ring kernel's warp count): only with short rows
-    assert use_gemv(1, 5120, 1024, 4) and not use_gemv(1, 5120, 2560, 4) and not use_gemv(1, 5120, 8192, 4)
+    assert use_gemv(1, 5120, 1024, 4) and use_gemv(1, 5120, 2048, 4) and not use_gemv(1, 5120, 2560, 4)
     assert not use_gemv(1, 5120, 640, 4)                      # very short rows stay on the tensor cores
-    assert use_gemv(1, 5120, 3200 - 3200 % 32 + 0, 4) is False
+    assert use_gemv(1, 5120, 3200, 4) is False
     assert not use_gemv(3, 4096, 1024, 2)                     # above gemv_max_m
     assert not use_gemv(1, 4096, 4096, 0)                     # gemv_max_m = 0 disables the GEMV
 
