@@ -421,9 +421,6 @@ linear_packed_kernel(const __grid_constant__ PackedParams p) {
             __syncthreads();
         }
 
-        // One 16-element block per thread per round. Prologue 0 prefetches the next round's
-        // block while the current one is quantized.
-        uint4 nlo = make_uint4(0, 0, 0, 0), nhi = nlo;
         auto src0 = [&](int i) {
             const int m = static_cast<int>((static_cast<uint32_t>(i) * inv_blocks) >> 20), blk = i - m * blocks;
             return reinterpret_cast<const uint4*>(xb + (p.m0 + m) * p.xb_stride + static_cast<int64_t>(blk0 + blk) * 16);
@@ -432,26 +429,46 @@ linear_packed_kernel(const __grid_constant__ PackedParams p) {
             const int m = static_cast<int>((static_cast<uint32_t>(i) * inv_blocks) >> 20);
             return i - m * blocks < real;
         };
-        if (kind == 0 && tid < n_items && inside(tid)) {
-            const uint4* s0 = src0(tid);
-            nlo = __ldg(s0);
-            nhi = __ldg(s0 + 1);
-        }
+        // quantize block i (16 bf16 values in lo, hi) into the operand layout
+        auto emit = [&](int i, const uint4& lo, const uint4& hi) {
+            const int m = static_cast<int>((static_cast<uint32_t>(i) * inv_blocks) >> 20), blk = i - m * blocks;
+            uint32_t cw[2];
+            const uint32_t sf = quantize_block16_rt(lo, hi, q, exact, cw);
+            *reinterpret_cast<uint2*>(b_tile_g + (blk >> 4) * (BN * 128) + swz128(m, (blk & 15) * 8)) =
+                make_uint2(cw[0], cw[1]);
+            b_sf_g[(blk >> 2) * kSfbStride + m * 16 + (blk & 3)] = static_cast<uint8_t>(sf);
+        };
+        if (kind == 0) {
+            // Two 16-element blocks per thread per round (two independent quantizer chains), the
+            // next round's two blocks fetched while the current ones are quantized.
+            auto fetch = [&](int i, uint4& lo, uint4& hi) {
+                lo = make_uint4(0, 0, 0, 0);
+                hi = lo;
+                if (i < n_items && inside(i)) {
+                    const uint4* s0 = src0(i);
+                    lo = __ldg(s0);
+                    hi = __ldg(s0 + 1);
+                }
+            };
+            uint4 a_lo, a_hi, b_lo, b_hi;
+            fetch(tid, a_lo, a_hi);
+            fetch(tid + kThreadsP, b_lo, b_hi);
 #pragma unroll 1
-        for (int i = tid; i < n_items; i += kThreadsP) {
+            for (int i = tid; i < n_items; i += 2 * kThreadsP) {
+                uint4 na_lo, na_hi, nb_lo, nb_hi;
+                fetch(i + 2 * kThreadsP, na_lo, na_hi);
+                fetch(i + 3 * kThreadsP, nb_lo, nb_hi);
+                emit(i, a_lo, a_hi);
+                if (i + kThreadsP < n_items) emit(i + kThreadsP, b_lo, b_hi);
+                a_lo = na_lo; a_hi = na_hi; b_lo = nb_lo; b_hi = nb_hi;
+            }
+        }
+        // prologues 1 and 2: one block per thread per round
+#pragma unroll 1
+        for (int i = tid; kind != 0 && i < n_items; i += kThreadsP) {
             const int m = static_cast<int>((static_cast<uint32_t>(i) * inv_blocks) >> 20), blk = i - m * blocks;
             uint4 lo, hi;
-            if (kind == 0) {
-                lo = nlo;
-                hi = nhi;
-                nlo = make_uint4(0, 0, 0, 0);
-                nhi = nlo;
-                if (i + kThreadsP < n_items && inside(i + kThreadsP)) {
-                    const uint4* s0 = src0(i + kThreadsP);
-                    nlo = __ldg(s0);
-                    nhi = __ldg(s0 + 1);
-                }
-            } else if (kind == 2) {
+            if (kind == 2) {
                 // activation = bf16(silu(gate) * up), gate_up row = [gate (K) | up (K)]
                 const __nv_bfloat16* row = xb + (p.m0 + m) * p.xb_stride + static_cast<int64_t>(blk0 + blk) * 16;
                 uint4 g0 = make_uint4(0, 0, 0, 0), g1 = g0, u0 = g0, u1 = g0;
@@ -504,11 +521,7 @@ linear_packed_kernel(const __grid_constant__ PackedParams p) {
                 lo = pack8(r);
                 hi = pack8(r + 8);
             }
-            uint32_t cw[2];
-            const uint32_t sf = quantize_block16_rt(lo, hi, q, exact, cw);
-            *reinterpret_cast<uint2*>(b_tile_g + (blk >> 4) * (BN * 128) + swz128(m, (blk & 15) * 8)) =
-                make_uint2(cw[0], cw[1]);
-            b_sf_g[(blk >> 2) * kSfbStride + m * 16 + (blk & 3)] = static_cast<uint8_t>(sf);
+            emit(i, lo, hi);
         }
         // Rows M..BN-1 of the operand are never written: whatever they hold only reaches
         // accumulator columns that are not stored.
