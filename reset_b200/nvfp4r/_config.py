@@ -16,10 +16,10 @@ FALLBACK_BACKEND = os.environ.get("NVFP4R_FALLBACK_BACKEND", "vllm-cutlass").low
 # (L2-cold weights, CUDA-graph replay; Qwen3-8B / 14B / 32B shapes and their tensor-parallel
 # shards at TP 2 / 4 / 8). The GEMV's shorter fixed latency wins for single tokens on weights up
 # to GEMV_MAX_WEIGHT_BYTES[1] (1280x5120 3.5 vs 5.0 us, 5120x2048 3.3 vs 3.6 us, 4096x4096 3.7 vs
-# 4.2 us; level at 3584x5120, 4.7 us both; 5120x4096 5.1 vs 4.4 us, 6144x4096 5.0 vs 4.7 us,
+# 4.2 us, 3584x5120 4.55 vs 4.8 us; 5120x4096 5.1 vs 4.4 us, 6144x4096 5.0 vs 4.7 us,
 # 4096x12288 7.3 vs 6.2 us, 10240x5120 7.8 vs 6.3 us above it). From two tokens on the tensor
 # cores win on every shape measured (5120x1024 3.5 vs 3.4 us, 1280x5120 6.1 vs 5.0 us). Index = M.
-GEMV_MAX_WEIGHT_BYTES = {1: 10_000_000}
+GEMV_MAX_WEIGHT_BYTES = {1: 10_500_000}
 # Rows shorter than this stay on the tensor cores at every M (5120x640: 3.6 vs 3.8 us).
 GEMV_MIN_K = 1024
 # The ring kernel deals groups of 4 rows to GEMV_RING_WARPS warps; with N between 4 and 5 times

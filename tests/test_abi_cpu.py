@@ -73,8 +73,8 @@ def test_enable_disable_configure_status(monkeypatch):
 
 def test_crossover_rule():
     from reset_b200.nvfp4r.ops import use_gemv
-    # single tokens: the GEMV up to 10 MB of weight (measured on the 8B / 14B / 32B shapes and shards)
-    assert use_gemv(1, 4096, 4096, 4) and use_gemv(1, 1280, 5120, 4) and use_gemv(1, 2560, 5120, 4)
+    # single tokens: the GEMV up to 10.5 MB of weight (measured on the 8B / 14B / 32B shapes and shards)
+    assert use_gemv(1, 4096, 4096, 4) and use_gemv(1, 1280, 5120, 4) and use_gemv(1, 3584, 5120, 4)
     assert not use_gemv(1, 5120, 4096, 4) and not use_gemv(1, 6144, 4096, 4) and not use_gemv(1, 5120, 5120, 4)
     assert not use_gemv(1, 4096, 12288, 4) and not use_gemv(1, 10240, 5120, 4) and not use_gemv(1, 24576, 4096, 4)
     # from two tokens on: the tensor cores on every shape
