@@ -73,6 +73,10 @@ struct PackedParams {
     // work split, computed on the host: S parts of kb_q or kb_q + 1 K blocks (the first
     // kb_r parts have one more), ctas_per_part CTAs per part
     int tiles, splits, kblocks, ctas_per_part, kb_q, kb_r;
+    // the same split without divisions in the kernel: ceil(2^32 / splits) (exact quotients for
+    // CTA indices below 2^16), and tiles = tiles_q * ctas_per_part + tiles_r
+    uint32_t inv_splits;
+    int tiles_q, tiles_r;
     unsigned long long* slots; // split-K hand-over slots {flag:32 | fp32 bits:32}, all zero between launches
     // fused prologue (what produces the bf16 activations that get quantized)
     int pro_kind;                  // 0: xb as is; 1: RMSNorm(residual_in + delta) * norm_w; 2: silu(g) * u
@@ -258,12 +262,13 @@ linear_packed_kernel(const __grid_constant__ PackedParams p) {
     if (warp == 0) TRACE(0);
 
     const int S = p.splits;
-    const int rank = static_cast<int>(blockIdx.x) / S, part = static_cast<int>(blockIdx.x) - rank * S;
+    const int rank = S == 1 ? static_cast<int>(blockIdx.x) : static_cast<int>(__umulhi(blockIdx.x, p.inv_splits));
+    const int part = static_cast<int>(blockIdx.x) - rank * S;
     const int kb0 = part * p.kb_q + min(part, p.kb_r);
     const int nkb = p.kb_q + (part < p.kb_r ? 1 : 0);                   // 1 .. kMaxPartBlocks
     const int stages_per_tile = (nkb + kBlocksPerStage - 1) / kBlocksPerStage;
     const int cpp = p.ctas_per_part;
-    const int my_tiles = (rank < cpp && rank < p.tiles) ? (p.tiles - rank + cpp - 1) / cpp : 0;
+    const int my_tiles = rank < cpp ? p.tiles_q + (rank < p.tiles_r ? 1 : 0) : 0;
     const int total = my_tiles * stages_per_tile;
 
     const uint32_t ring = smem_base;
@@ -289,6 +294,7 @@ linear_packed_kernel(const __grid_constant__ PackedParams p) {
     // pair p_j of this CTA's p_ti-th tile. Addresses and sizes are computed by the whole warp so
     // that they are warp-uniform values when the bulk copy takes them.
     int issued = 0, p_ti = 0, p_j = 0;
+    if (warp == 0) TRACE(13);
     const uint64_t policy = l2_policy_evict_first();
     const bool lead0 = (warp == 0) && elect_one();
     auto issue_next = [&]() {
@@ -309,13 +315,16 @@ linear_packed_kernel(const __grid_constant__ PackedParams p) {
     // The weights do not depend on the previous kernel: warp 0 arms the barriers and starts
     // the first stages before anything else happens in this CTA.
     if (warp == 0) {
-        if (lead0) {
-#pragma unroll 1
-            for (int i = 0; i < 2 * kStages + 4 + kMaxPartBlocks / kBlocksPerStage; ++i)   // accempty: one arrival per epilogue warp
-                mbar_init(bar_full + 8 * i, (i >= 2 * kStages + 2 && i < 2 * kStages + 4) ? 4u : 1u);
+        // one barrier per lane (a rolled loop of eleven initialisations on one lane, fetched
+        // cold, held the first copy back by 0.45 us); accempty counts one arrival per epilogue warp
+        constexpr int kBars = 2 * kStages + 4 + kMaxPartBlocks / kBlocksPerStage;
+        static_assert(kBars <= 32, "one barrier per lane");
+        if (lane < kBars) {
+            mbar_init(bar_full + 8 * lane, (lane >= 2 * kStages + 2 && lane < 2 * kStages + 4) ? 4u : 1u);
             mbar_fence_init();
         }
         __syncwarp();
+        TRACE(14);
 #pragma unroll 1
         while (issued < total && issued < kStages) issue_next();
     }
@@ -836,6 +845,9 @@ cudaError_t launch_linear_packed(const PackedLinearArgs& g, cudaStream_t stream,
         p.ctas_per_part = plan.grid / plan.splits;
         p.kb_q = p.kblocks / plan.splits;
         p.kb_r = p.kblocks % plan.splits;
+        p.inv_splits = static_cast<uint32_t>((0x100000000ull + static_cast<unsigned>(plan.splits) - 1) / static_cast<unsigned>(plan.splits));
+        p.tiles_q = p.tiles / p.ctas_per_part;
+        p.tiles_r = p.tiles % p.ctas_per_part;
         p.pro_kind = g.pro_kind;
         p.delta = g.delta;
         p.residual_in = g.residual_in;
