@@ -255,7 +255,7 @@ NVFP4R_API int nvfp4r_linear_ex(const nvfp4r_prologue* pro, const void* x, int64
  * an in-kernel time line of eight CTAs (bits 12-23: the first of them; only in a build with
  * -DNVFP4R_TRACE, ignored otherwise), bit 9 runs one CTA per SM instead of two, bits 24-27 hold
  * 1 + the number of pipeline stages each CTA asks into L2 ahead of its ring right after the
- * wait for the previous kernel (0 = keep; default depth 2). */
+ * wait for the previous kernel (0 = keep; depth 0, 1 or 2, default 2). */
 NVFP4R_API int nvfp4r_set_packed_tuning(int splits);
 
 /* Debug/tuning: force the K split and ring depth of the tensor-core kernel (0 = automatic). */

@@ -354,22 +354,33 @@ linear_packed_kernel(const __grid_constant__ PackedParams p) {
             nw_first1 = __ldg(src + 1);
         }
     }
+    // sources of the L2 run-ahead (the two stages after the ring in this CTA's sequence)
+    const uint8_t* pf_src0 = nullptr;
+    const uint8_t* pf_src1 = nullptr;
+    uint32_t pf_bytes0 = 0, pf_bytes1 = 0;
+    if (warp == 0) {
+        int ti = p_ti, j = p_j;
+        if (issued < total && p.l2_stages >= 1) {
+            pf_src0 = p.packed + (static_cast<int64_t>(rank + ti * cpp) * p.kblocks + kb0 + j * kBlocksPerStage) * kBlockBytes;
+            pf_bytes0 = static_cast<uint32_t>(min(kBlocksPerStage, nkb - j * kBlocksPerStage)) * kBlockBytes;
+            if (++j == stages_per_tile) { j = 0; ++ti; }
+            if (issued + 1 < total && p.l2_stages >= 2) {
+                pf_src1 = p.packed + (static_cast<int64_t>(rank + ti * cpp) * p.kblocks + kb0 + j * kBlocksPerStage) * kBlockBytes;
+                pf_bytes1 = static_cast<uint32_t>(min(kBlocksPerStage, nkb - j * kBlocksPerStage)) * kBlockBytes;
+            }
+        }
+    }
     pdl_launch_dependents();
     pdl_wait_prior();
     if (warp == 0) TRACE(2);
+    // The ring is full until the first MMA frees a stage, which is the prologue away (load and
+    // quantize the activations). The two stages that follow are asked into L2 now - not before
+    // the wait, where they would compete with the last stages of the kernel before - so that
+    // HBM keeps streaming through the prologue and the ring later refills from L2. (Their
+    // addresses were worked out before the wait: warp 0 is part of the prologue.)
     if (lead0) {
-        // The ring is full until the first MMA frees a stage, which is the prologue away (load
-        // and quantize the activations). The stages that follow are asked into L2 now - not
-        // before the wait, where they would compete with the last stages of the kernel before -
-        // so that HBM keeps streaming through the prologue and the ring later refills from L2.
-#pragma unroll 1
-        for (int k = issued; k < total && k < issued + p.l2_stages; ++k) {
-            const int ti = k / stages_per_tile, j = k - ti * stages_per_tile;
-            const int nb = min(kBlocksPerStage, nkb - j * kBlocksPerStage);
-            bulk_prefetch_l2(p.packed + (static_cast<int64_t>(rank + ti * cpp) * p.kblocks + kb0 +
-                                         j * kBlocksPerStage) * kBlockBytes,
-                             static_cast<uint32_t>(nb) * kBlockBytes);
-        }
+        if (pf_bytes0 != 0) bulk_prefetch_l2(pf_src0, pf_bytes0);
+        if (pf_bytes1 != 0) bulk_prefetch_l2(pf_src1, pf_bytes1);
     }
 
     // ---- prologue: quantize this part's activations into operand layout --------------
@@ -900,7 +911,7 @@ cudaError_t launch_linear_packed(const PackedLinearArgs& g, cudaStream_t stream,
 void set_packed_tuning(int splits) {
     g_force_packed_splits = splits & 0xff;
     g_packed_ctas_per_sm = ((splits >> 9) & 1) ? 1 : 2;
-    if ((splits >> 24) & 0xf) g_packed_l2_stages = ((splits >> 24) & 0xf) - 1;   // bits 24..27: L2 prefetch depth + 1
+    if ((splits >> 24) & 0xf) g_packed_l2_stages = ((splits >> 24) & 0xf) - 1;   // bits 24..27: L2 run-ahead depth + 1 (0..2 stages)
 #ifdef NVFP4R_TRACE
     // bit 8: record the time line of eight CTAs; bits 12..23: the first of them
     const int trace = ((splits >> 8) & 1) ? 1 + ((splits >> 12) & 0xfff) : 0;
