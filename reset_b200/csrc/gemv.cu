@@ -147,12 +147,14 @@ gemv_stream_kernel(const __grid_constant__ StreamParams p) {
     __syncwarp();
 
     // Weights do not depend on the preceding kernel: start streaming at once.
+    // (group, chunk) of the next tile to issue, advanced one tile at a time: no division per tile
+    int nxt_g = 0, nxt_c = 0;
 #pragma unroll
     for (int t = 0; t < kSlots; ++t) {
         if (t < my_tiles) {
-            const int gi = t / p.n_chunks, c = t - gi * p.n_chunks;
-            issue_tile(p, lane, g_first + gi * g_step, c, my_ring + t * kSlotBytes,
+            issue_tile(p, lane, g_first + nxt_g * g_step, nxt_c, my_ring + t * kSlotBytes,
                        my_bars + 8 * t, policy);
+            if (++nxt_c == p.n_chunks) { nxt_c = 0; ++nxt_g; }
         }
     }
     // The global scale is a constant of the layer (not written by the preceding kernel): its
@@ -200,16 +202,16 @@ gemv_stream_kernel(const __grid_constant__ StreamParams p) {
         for (int m = 0; m < MT; ++m) acc[r][m] = 0.0f;
 
     bool timed_out = false;
+    int gi = 0, c = 0, slot = 0;
+    uint32_t phase = 0;                                  // parity of this slot's current fill
     for (int t = 0; t < my_tiles; ++t) {
-        const int slot = t % kSlots;
         const uint32_t slot_addr = my_ring + slot * kSlotBytes;
         const uint32_t bar = my_bars + 8 * slot;
-        const int gi = t / p.n_chunks, c = t - gi * p.n_chunks;
         const int group = g_first + gi * g_step;
         const int chunk_off = c * kChunkBytes;
         const int chunk_bytes = min(kChunkBytes, K2 - chunk_off);
 
-        if (!mbar_wait_bounded(bar, (t / kSlots) & 1)) { timed_out = true; break; }
+        if (!mbar_wait_bounded(bar, phase)) { timed_out = true; break; }
 
 #pragma unroll
         for (int j = 0; j < kUnitsPerLane; ++j) {
@@ -258,10 +260,9 @@ gemv_stream_kernel(const __grid_constant__ StreamParams p) {
         __syncwarp();
 
         // Refill this slot with the tile kSlots ahead.
-        const int tn = t + kSlots;
-        if (tn < my_tiles) {
-            const int gn = tn / p.n_chunks, cn = tn - gn * p.n_chunks;
-            issue_tile(p, lane, g_first + gn * g_step, cn, slot_addr, bar, policy);
+        if (t + kSlots < my_tiles) {
+            issue_tile(p, lane, g_first + nxt_g * g_step, nxt_c, slot_addr, bar, policy);
+            if (++nxt_c == p.n_chunks) { nxt_c = 0; ++nxt_g; }
         }
 
         if (c == p.n_chunks - 1) {                 // group finished: reduce and store
@@ -289,6 +290,8 @@ gemv_stream_kernel(const __grid_constant__ StreamParams p) {
 #pragma unroll
                 for (int mm = 0; mm < MT; ++mm) acc[rr][mm] = 0.0f;
         }
+        if (++c == p.n_chunks) { c = 0; ++gi; }
+        if (++slot == kSlots) { slot = 0; phase ^= 1u; }
     }
 
     if (timed_out) {
