@@ -77,6 +77,8 @@ struct PackedParams {
     // CTA indices below 2^16), and tiles = tiles_q * ctas_per_part + tiles_r
     uint32_t inv_splits;
     int tiles_q, tiles_r;
+    // ceil(2^20 / (16 * K blocks of a part)) for parts of kb_q + 1 and of kb_q blocks
+    uint32_t inv_blocks_hi, inv_blocks_lo;
     unsigned long long* slots; // split-K hand-over slots {flag:32 | fp32 bits:32}, all zero between launches
     // fused prologue (what produces the bf16 activations that get quantized)
     int pro_kind;                  // 0: xb as is; 1: RMSNorm(residual_in + delta) * norm_w; 2: silu(g) * u
@@ -394,7 +396,7 @@ linear_packed_kernel(const __grid_constant__ PackedParams p) {
         // i / blocks as a multiply and a shift: exact for blocks = 16 .. 128 in steps of 16 and
         // i < 4608 (M <= 32 tokens of at most 128 blocks); a real division costs ~20 instructions
         // and the loop below needs two per block
-        const uint32_t inv_blocks = ((1u << 20) + static_cast<uint32_t>(blocks) - 1u) / static_cast<uint32_t>(blocks);
+        const uint32_t inv_blocks = part < p.kb_r ? p.inv_blocks_hi : p.inv_blocks_lo;   // from the host: no division here
         const __nv_bfloat16* xb = static_cast<const __nv_bfloat16*>(p.xb);
         const __nv_bfloat16* rin = static_cast<const __nv_bfloat16*>(p.residual_in);
         const __nv_bfloat16* dl = static_cast<const __nv_bfloat16*>(p.delta);
@@ -857,6 +859,11 @@ cudaError_t launch_linear_packed(const PackedLinearArgs& g, cudaStream_t stream,
         p.kb_q = p.kblocks / plan.splits;
         p.kb_r = p.kblocks % plan.splits;
         p.inv_splits = static_cast<uint32_t>((0x100000000ull + static_cast<unsigned>(plan.splits) - 1) / static_cast<unsigned>(plan.splits));
+        {
+            const uint32_t b_hi = static_cast<uint32_t>(p.kb_q + 1) * (kBlockK / 16), b_lo = static_cast<uint32_t>(p.kb_q) * (kBlockK / 16);
+            p.inv_blocks_hi = ((1u << 20) + b_hi - 1u) / b_hi;
+            p.inv_blocks_lo = b_lo ? ((1u << 20) + b_lo - 1u) / b_lo : 0u;
+        }
         p.tiles_q = p.tiles / p.ctas_per_part;
         p.tiles_r = p.tiles % p.ctas_per_part;
         p.pro_kind = g.pro_kind;
