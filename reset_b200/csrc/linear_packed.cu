@@ -356,6 +356,24 @@ linear_packed_kernel(const __grid_constant__ PackedParams p) {
             nw_first1 = __ldg(src + 1);
         }
     }
+    // Plain-input prologue: where this thread's first two activation blocks live is known before
+    // the wait (only their contents are not), so the loads can go out the moment it returns.
+    const uint4* pre_a = nullptr;
+    const uint4* pre_b = nullptr;
+    if (p.pro_kind == 0 && my_tiles > 0) {
+        const int blk0 = kb0 * (kBlockK / 16), blocks = nkb * (kBlockK / 16);
+        const int n_items = p.M * blocks, real = min(blocks, p.K / 16 - blk0);
+        const uint32_t inv_blocks = part < p.kb_r ? p.inv_blocks_hi : p.inv_blocks_lo;
+        auto where = [&](int i) -> const uint4* {
+            if (i >= n_items) return nullptr;
+            const int m = static_cast<int>((static_cast<uint32_t>(i) * inv_blocks) >> 20), blk = i - m * blocks;
+            if (blk >= real) return nullptr;
+            return reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(p.xb) + (p.m0 + m) * p.xb_stride +
+                                                  static_cast<int64_t>(blk0 + blk) * 16);
+        };
+        pre_a = where(tid);
+        pre_b = where(tid + kThreadsP);
+    }
     // sources of the L2 run-ahead (the two stages after the ring in this CTA's sequence)
     const uint8_t* pf_src0 = nullptr;
     const uint8_t* pf_src1 = nullptr;
@@ -374,6 +392,9 @@ linear_packed_kernel(const __grid_constant__ PackedParams p) {
     }
     pdl_launch_dependents();
     pdl_wait_prior();
+    uint4 a_lo = make_uint4(0, 0, 0, 0), a_hi = a_lo, b_lo = a_lo, b_hi = a_lo;
+    if (pre_a != nullptr) { a_lo = __ldg(pre_a); a_hi = __ldg(pre_a + 1); }
+    if (pre_b != nullptr) { b_lo = __ldg(pre_b); b_hi = __ldg(pre_b + 1); }
     if (warp == 0) TRACE(2);
     // The ring is full until the first MMA frees a stage, which is the prologue away (load and
     // quantize the activations). The two stages that follow are asked into L2 now - not before
@@ -472,9 +493,6 @@ linear_packed_kernel(const __grid_constant__ PackedParams p) {
                     hi = __ldg(s0 + 1);
                 }
             };
-            uint4 a_lo, a_hi, b_lo, b_hi;
-            fetch(tid, a_lo, a_hi);
-            fetch(tid + kThreadsP, b_lo, b_hi);
 #pragma unroll 1
             for (int i = tid; i < n_items; i += 2 * kThreadsP) {
                 uint4 na_lo, na_hi, nb_lo, nb_hi;
