@@ -170,7 +170,8 @@ gemv_stream_kernel(const __grid_constant__ StreamParams p) {
         const QuantScales qe = make_quant_scales<kRcpExact>(gs);
         const QuantScales qa = make_quant_scales<kRcpApprox>(gs);
         for (int i = tid; i < M * blocks_per_tok; i += kThreads) {
-            const int m = i / blocks_per_tok, b = i - m * blocks_per_tok;
+            // one token (the usual case): no division on the path between the wait and the loads
+            const int m = (MT == 1) ? 0 : i / blocks_per_tok, b = i - m * blocks_per_tok;
             const uint4* src = reinterpret_cast<const uint4*>(xb + m * p.a.xb_stride + b * kBlockElems);
             const uint4 lo = __ldg(src), hi = __ldg(src + 1);
             uint32_t c[2];

@@ -239,7 +239,10 @@ __device__ __forceinline__ bool token_gather(unsigned long long* tok, int S, int
 
 // ---- the linear ---------------------------------------------------------------------
 
-template <int BN>
+// kKind = p.pro_kind as a compile-time value: one kernel per prologue, so that each carries only
+// its own prologue's code and registers (with the three in one kernel, a change to the plain
+// path moved the RMSNorm path by up to 1.1 us per launch).
+template <int BN, int kKind>
 __global__ void __launch_bounds__(kThreadsP, 2)
 linear_packed_kernel(const __grid_constant__ PackedParams p) {
     extern __shared__ __align__(1024) uint8_t smem_raw[];
@@ -346,7 +349,7 @@ linear_packed_kernel(const __grid_constant__ PackedParams p) {
     // out of L1 after the mean-square pass, so the norm weight was the prologue's second trip
     // to L2).
     uint4 nw_first0 = make_uint4(0, 0, 0, 0), nw_first1 = nw_first0;
-    if (p.pro_kind == 1 && my_tiles > 0 && tid < p.M * nkb * (kBlockK / 16)) {
+    if (kKind == 1 && my_tiles > 0 && tid < p.M * nkb * (kBlockK / 16)) {
         const int blocks = nkb * (kBlockK / 16);
         const int blk = tid % blocks;
         if (kb0 * (kBlockK / 16) + blk < p.K / 16) {
@@ -360,7 +363,7 @@ linear_packed_kernel(const __grid_constant__ PackedParams p) {
     // the wait (only their contents are not), so the loads can go out the moment it returns.
     const uint4* pre_a = nullptr;
     const uint4* pre_b = nullptr;
-    if (p.pro_kind == 0 && my_tiles > 0) {
+    if (kKind == 0 && my_tiles > 0) {
         const int blk0 = kb0 * (kBlockK / 16), blocks = nkb * (kBlockK / 16);
         const int n_items = p.M * blocks, real = min(blocks, p.K / 16 - blk0);
         const uint32_t inv_blocks = part < p.kb_r ? p.inv_blocks_hi : p.inv_blocks_lo;
@@ -421,7 +424,7 @@ linear_packed_kernel(const __grid_constant__ PackedParams p) {
         const __nv_bfloat16* xb = static_cast<const __nv_bfloat16*>(p.xb);
         const __nv_bfloat16* rin = static_cast<const __nv_bfloat16*>(p.residual_in);
         const __nv_bfloat16* dl = static_cast<const __nv_bfloat16*>(p.delta);
-        const int kind = p.pro_kind;
+        constexpr int kind = kKind;
 
         if (kind == 1) {
             // Every CTA needs each row's mean square over the whole K: recomputed here from
@@ -902,16 +905,21 @@ cudaError_t launch_linear_packed(const PackedLinearArgs& g, cudaStream_t stream,
         }
         p.l2_stages = g_packed_l2_stages;
 
-        void (*kern)(PackedParams) = plan.bn == 16 ? linear_packed_kernel<16> : linear_packed_kernel<32>;
-        static bool attr_done[2][64] = {};
+        using Kern = void (*)(PackedParams);
+        static const Kern table[2][3] = {
+            {linear_packed_kernel<16, 0>, linear_packed_kernel<16, 1>, linear_packed_kernel<16, 2>},
+            {linear_packed_kernel<32, 0>, linear_packed_kernel<32, 1>, linear_packed_kernel<32, 2>}};
+        if (g.pro_kind < 0 || g.pro_kind > 2) { *why = "packed linear: unknown prologue kind"; return cudaSuccess; }
+        const Kern kern = table[plan.bn == 16 ? 0 : 1][g.pro_kind];
+        static bool attr_done[2][3][64] = {};
         int dev = 0;
         cudaError_t e = cudaGetDevice(&dev);
         if (e != cudaSuccess) return e;
         const int ki = plan.bn == 16 ? 0 : 1;
-        if (dev >= 0 && dev < 64 && !attr_done[ki][dev]) {
+        if (dev >= 0 && dev < 64 && !attr_done[ki][g.pro_kind][dev]) {
             e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
             if (e != cudaSuccess) return e;
-            attr_done[ki][dev] = true;
+            attr_done[ki][g.pro_kind][dev] = true;
         }
         cudaLaunchConfig_t cfg = {};
         cfg.gridDim = dim3(static_cast<unsigned>(plan.grid));
