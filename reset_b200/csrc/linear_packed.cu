@@ -242,7 +242,9 @@ __device__ __forceinline__ bool token_gather(unsigned long long* tok, int S, int
 // kKind = p.pro_kind as a compile-time value: one kernel per prologue, so that each carries only
 // its own prologue's code and registers (with the three in one kernel, a change to the plain
 // path moved the RMSNorm path by up to 1.1 us per launch).
-template <int BN, int kKind>
+// kPush: the tensor-parallel epilogue (push to the peers, optional sum in the same launch) is
+// compiled in; single-GPU launches run the variant without it.
+template <int BN, int kKind, bool kPush>
 __global__ void __launch_bounds__(kThreadsP, 2)
 linear_packed_kernel(const __grid_constant__ PackedParams p) {
     extern __shared__ __align__(1024) uint8_t smem_raw[];
@@ -664,7 +666,7 @@ linear_packed_kernel(const __grid_constant__ PackedParams p) {
         // Which half of the peers' receive memory this call uses: the call counter in this rank's
         // own header, final before this kernel started (its writer is an earlier kernel).
         const unsigned push_parity =
-            p.push_world > 1 ? (*reinterpret_cast<volatile unsigned*>(p.push_base[p.push_rank]) & 1u) : 0u;
+            (kPush && p.push_world > 1) ? (*reinterpret_cast<volatile unsigned*>(p.push_base[p.push_rank]) & 1u) : 0u;
 #pragma unroll 1
         for (int ti = 0; ti < my_tiles; ++ti) {
             const int buf = ti & 1;
@@ -706,7 +708,7 @@ linear_packed_kernel(const __grid_constant__ PackedParams p) {
                 if (S > 1 && !token_gather(tile_slots + static_cast<int64_t>(m) * S * kTileRows, S, part, val, &val))
                     wf.failed = true;
                 const float o = val * p.alpha;
-                if (p.push_world > 1) {
+                if (kPush && p.push_world > 1) {
                     // adjacent weight rows sit in adjacent lanes: the even lane sends the pair
                     const float o2 = __shfl_down_sync(0xffffffffu, o, 1);
                     if ((lane & 1) == 0) {
@@ -773,7 +775,7 @@ linear_packed_kernel(const __grid_constant__ PackedParams p) {
         tc_fence_after();
         tmem_dealloc(tmem, kTmemCols);
     }
-    if (p.push_world > 1 && p.push_gather && tid == 0) {
+    if (kPush && p.push_world > 1 && p.push_gather && tid == 0) {
         // the last CTA of the grid to finish advances the call counter: nobody of this launch
         // reads it any more (same rule as the stand-alone gather kernel)
         unsigned* header = reinterpret_cast<unsigned*>(p.push_base[p.push_rank]);
@@ -906,20 +908,23 @@ cudaError_t launch_linear_packed(const PackedLinearArgs& g, cudaStream_t stream,
         p.l2_stages = g_packed_l2_stages;
 
         using Kern = void (*)(PackedParams);
-        static const Kern table[2][3] = {
-            {linear_packed_kernel<16, 0>, linear_packed_kernel<16, 1>, linear_packed_kernel<16, 2>},
-            {linear_packed_kernel<32, 0>, linear_packed_kernel<32, 1>, linear_packed_kernel<32, 2>}};
+        static const Kern table[2][2][3] = {
+            {{linear_packed_kernel<16, 0, false>, linear_packed_kernel<16, 1, false>, linear_packed_kernel<16, 2, false>},
+             {linear_packed_kernel<32, 0, false>, linear_packed_kernel<32, 1, false>, linear_packed_kernel<32, 2, false>}},
+            {{linear_packed_kernel<16, 0, true>, linear_packed_kernel<16, 1, true>, linear_packed_kernel<16, 2, true>},
+             {linear_packed_kernel<32, 0, true>, linear_packed_kernel<32, 1, true>, linear_packed_kernel<32, 2, true>}}};
         if (g.pro_kind < 0 || g.pro_kind > 2) { *why = "packed linear: unknown prologue kind"; return cudaSuccess; }
-        const Kern kern = table[plan.bn == 16 ? 0 : 1][g.pro_kind];
-        static bool attr_done[2][3][64] = {};
+        const int pi = p.push_world > 1 ? 1 : 0;
+        const Kern kern = table[pi][plan.bn == 16 ? 0 : 1][g.pro_kind];
+        static bool attr_done[2][2][3][64] = {};
         int dev = 0;
         cudaError_t e = cudaGetDevice(&dev);
         if (e != cudaSuccess) return e;
         const int ki = plan.bn == 16 ? 0 : 1;
-        if (dev >= 0 && dev < 64 && !attr_done[ki][g.pro_kind][dev]) {
+        if (dev >= 0 && dev < 64 && !attr_done[pi][ki][g.pro_kind][dev]) {
             e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
             if (e != cudaSuccess) return e;
-            attr_done[ki][g.pro_kind][dev] = true;
+            attr_done[pi][ki][g.pro_kind][dev] = true;
         }
         cudaLaunchConfig_t cfg = {};
         cfg.gridDim = dim3(static_cast<unsigned>(plan.grid));
