@@ -242,9 +242,9 @@ __device__ __forceinline__ bool token_gather(unsigned long long* tok, int S, int
 // kKind = p.pro_kind as a compile-time value: one kernel per prologue, so that each carries only
 // its own prologue's code and registers (with the three in one kernel, a change to the plain
 // path moved the RMSNorm path by up to 1.1 us per launch).
-// kPush: the tensor-parallel epilogue (push to the peers, optional sum in the same launch) is
-// compiled in; single-GPU launches run the variant without it.
-template <int BN, int kKind, bool kPush>
+// kPush: how much of the tensor-parallel epilogue is compiled in: 0 none (single-GPU launches),
+// 1 the push to the peers' receive memory, 2 the push and the sum in the same launch.
+template <int BN, int kKind, int kPush>
 __global__ void __launch_bounds__(kThreadsP, 2)
 linear_packed_kernel(const __grid_constant__ PackedParams p) {
     extern __shared__ __align__(1024) uint8_t smem_raw[];
@@ -666,7 +666,7 @@ linear_packed_kernel(const __grid_constant__ PackedParams p) {
         // Which half of the peers' receive memory this call uses: the call counter in this rank's
         // own header, final before this kernel started (its writer is an earlier kernel).
         const unsigned push_parity =
-            (kPush && p.push_world > 1) ? (*reinterpret_cast<volatile unsigned*>(p.push_base[p.push_rank]) & 1u) : 0u;
+            (kPush != 0 && p.push_world > 1) ? (*reinterpret_cast<volatile unsigned*>(p.push_base[p.push_rank]) & 1u) : 0u;
 #pragma unroll 1
         for (int ti = 0; ti < my_tiles; ++ti) {
             const int buf = ti & 1;
@@ -708,7 +708,7 @@ linear_packed_kernel(const __grid_constant__ PackedParams p) {
                 if (S > 1 && !token_gather(tile_slots + static_cast<int64_t>(m) * S * kTileRows, S, part, val, &val))
                     wf.failed = true;
                 const float o = val * p.alpha;
-                if (kPush && p.push_world > 1) {
+                if (kPush != 0 && p.push_world > 1) {
                     // adjacent weight rows sit in adjacent lanes: the even lane sends the pair
                     const float o2 = __shfl_down_sync(0xffffffffu, o, 1);
                     if ((lane & 1) == 0) {
@@ -723,7 +723,7 @@ linear_packed_kernel(const __grid_constant__ PackedParams p) {
                                 (static_cast<unsigned long long>(push_parity) * p.push_world + p.push_rank) * p.push_max_pairs + i;
                             asm volatile("st.relaxed.sys.global.u64 [%0], %1;" :: "l"(slot), "l"(w) : "memory");
                         }
-                        if (p.push_gather) {
+                        if (kPush == 2 && p.push_gather) {
                             unsigned long long* mine =
                                 reinterpret_cast<unsigned long long*>(p.push_base[p.push_rank] + 256) +
                                 static_cast<unsigned long long>(push_parity) * p.push_world * p.push_max_pairs + i;
@@ -775,7 +775,7 @@ linear_packed_kernel(const __grid_constant__ PackedParams p) {
         tc_fence_after();
         tmem_dealloc(tmem, kTmemCols);
     }
-    if (kPush && p.push_world > 1 && p.push_gather && tid == 0) {
+    if (kPush == 2 && p.push_world > 1 && p.push_gather && tid == 0) {
         // the last CTA of the grid to finish advances the call counter: nobody of this launch
         // reads it any more (same rule as the stand-alone gather kernel)
         unsigned* header = reinterpret_cast<unsigned*>(p.push_base[p.push_rank]);
@@ -908,15 +908,16 @@ cudaError_t launch_linear_packed(const PackedLinearArgs& g, cudaStream_t stream,
         p.l2_stages = g_packed_l2_stages;
 
         using Kern = void (*)(PackedParams);
-        static const Kern table[2][2][3] = {
-            {{linear_packed_kernel<16, 0, false>, linear_packed_kernel<16, 1, false>, linear_packed_kernel<16, 2, false>},
-             {linear_packed_kernel<32, 0, false>, linear_packed_kernel<32, 1, false>, linear_packed_kernel<32, 2, false>}},
-            {{linear_packed_kernel<16, 0, true>, linear_packed_kernel<16, 1, true>, linear_packed_kernel<16, 2, true>},
-             {linear_packed_kernel<32, 0, true>, linear_packed_kernel<32, 1, true>, linear_packed_kernel<32, 2, true>}}};
+#define NVFP4R_PACKED_ROW(BN, PUSH) \
+    {linear_packed_kernel<BN, 0, PUSH>, linear_packed_kernel<BN, 1, PUSH>, linear_packed_kernel<BN, 2, PUSH>}
+        static const Kern table[3][2][3] = {{NVFP4R_PACKED_ROW(16, 0), NVFP4R_PACKED_ROW(32, 0)},
+                                            {NVFP4R_PACKED_ROW(16, 1), NVFP4R_PACKED_ROW(32, 1)},
+                                            {NVFP4R_PACKED_ROW(16, 2), NVFP4R_PACKED_ROW(32, 2)}};
+#undef NVFP4R_PACKED_ROW
         if (g.pro_kind < 0 || g.pro_kind > 2) { *why = "packed linear: unknown prologue kind"; return cudaSuccess; }
-        const int pi = p.push_world > 1 ? 1 : 0;
+        const int pi = p.push_world > 1 ? (p.push_gather ? 2 : 1) : 0;
         const Kern kern = table[pi][plan.bn == 16 ? 0 : 1][g.pro_kind];
-        static bool attr_done[2][2][3][64] = {};
+        static bool attr_done[3][2][3][64] = {};
         int dev = 0;
         cudaError_t e = cudaGetDevice(&dev);
         if (e != cudaSuccess) return e;
