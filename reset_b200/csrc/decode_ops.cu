@@ -107,6 +107,27 @@ __device__ __forceinline__ void head_norm_rope(const __nv_bfloat16* __restrict__
     }
 }
 
+// The same with the layer constants already in registers: wv = the four norm weights of this
+// lane, cs/sn = cos and sin of its two rotary pairs. Only `src` is read here, so a caller that
+// fetched the constants before its dependency wait pays one trip to L2 after it, not three.
+__device__ __forceinline__ void head_norm_rope_pre(const __nv_bfloat16* __restrict__ src, const float wv[4],
+                                                   const float cs[2], const float sn[2], float eps, int lane,
+                                                   float o[4]) {
+    constexpr int D = 128;
+    float v[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) v[j] = __bfloat162float(src[lane + 32 * j]);
+    const float ss = v[0] * v[0] + v[1] * v[1] + v[2] * v[2] + v[3] * v[3];
+    const float inv = rsqrtf(warp_sum_f(ss) / static_cast<float>(D) + eps);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) v[j] = __bfloat162float(__float2bfloat16_rn(v[j] * inv * wv[j]));
+#pragma unroll
+    for (int j = 0; j < 2; ++j) {
+        o[j] = v[j] * cs[j] - v[j + 2] * sn[j];
+        o[j + 2] = v[j + 2] * cs[j] + v[j] * sn[j];
+    }
+}
+
 // One warp per head of the fused qkv row: q and k heads get RMSNorm(head) * w and the
 // rotary embedding (rotate-half pairs d, d + D/2); k and v are written to the cache at
 // `*position`; q goes to q_out. D == 128.
@@ -235,6 +256,28 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __restric
             }
         }
     }
+    // Fused rope: the head-norm weights and the rotary angles of position len - 1 are layer / step
+    // constants, fetched (or computed) before the wait like the cache rows above.
+    float wq[4] = {0.f, 0.f, 0.f, 0.f}, wk[4] = {0.f, 0.f, 0.f, 0.f}, rcs[2] = {1.f, 1.f}, rsn[2] = {0.f, 0.f};
+    if (kFusedRope && np > 0) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            wq[j] = __bfloat162float(rope.q_w[lane + 32 * j]);
+            wk[j] = __bfloat162float(rope.k_w[lane + 32 * j]);
+        }
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+            const int d = lane + 32 * j;
+            if (rope.table != nullptr) {
+                const float2 t = __ldg(rope.table + static_cast<int64_t>(len - 1) * (kAttnD / 2) + d);
+                rcs[j] = t.x;
+                rsn[j] = t.y;
+            } else {
+                const float freq = powf(rope.theta, -static_cast<float>(2 * d) / static_cast<float>(kAttnD));
+                sincosf(static_cast<float>(len - 1) * freq, &rsn[j], &rcs[j]);
+            }
+        }
+    }
     pdl_wait_prior();
     if (np > 0) {
         const int r = len - 1 - p0;                            // the newest row, if it is in this chunk
@@ -257,7 +300,7 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __restric
             // the row position is len - 1 (the token being decoded)
             if (warp < group) {
                 float o[4];
-                head_norm_rope(q + static_cast<int64_t>(qh) * kAttnD, rope.q_w, len - 1, rope.theta, rope.eps, lane, o, rope.table);
+                head_norm_rope_pre(q + static_cast<int64_t>(qh) * kAttnD, wq, rcs, rsn, rope.eps, lane, o);
                 __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(qs + warp * kAttnPitch);
 #pragma unroll
                 for (int j = 0; j < 4; ++j) dst[lane + 32 * j] = __float2bfloat16_rn(o[j]);
@@ -267,7 +310,7 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __restric
                 const int64_t g = (static_cast<int64_t>(kvh) * Tmax + len - 1) * kAttnD;
                 if (warp == 0) {
                     float o[4];
-                    head_norm_rope(q + static_cast<int64_t>(Hq + kvh) * kAttnD, rope.k_w, len - 1, rope.theta, rope.eps, lane, o, rope.table);
+                    head_norm_rope_pre(q + static_cast<int64_t>(Hq + kvh) * kAttnD, wk, rcs, rsn, rope.eps, lane, o);
                     __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(ks + r * kAttnPitch);
 #pragma unroll
                     for (int j = 0; j < 4; ++j) {
