@@ -165,6 +165,16 @@ __device__ __forceinline__ uint4 pack8(const float f[8]) {
                       pack2_bf16(f[6], f[7]));
 }
 __device__ __forceinline__ float round_bf16(float v) { return __bfloat162float(__float2bfloat16_rn(v)); }
+// bf16(a + b) for eight packed values: one rounding of the exact sum per element, the same bits as
+// adding in fp32 and rounding to bf16 (the sum of two bf16 values is exact in fp32 unless one is
+// below a quarter ulp of the other, where both give the larger operand).
+__device__ __forceinline__ uint32_t add_bf16x2(uint32_t a, uint32_t b) {
+    const __nv_bfloat162 r = __hadd2(*reinterpret_cast<const __nv_bfloat162*>(&a), *reinterpret_cast<const __nv_bfloat162*>(&b));
+    return *reinterpret_cast<const uint32_t*>(&r);
+}
+__device__ __forceinline__ uint4 add_bf16x8(const uint4& a, const uint4& b) {
+    return make_uint4(add_bf16x2(a.x, b.x), add_bf16x2(a.y, b.y), add_bf16x2(a.z, b.z), add_bf16x2(a.w, b.w));
+}
 
 __device__ __forceinline__ void tmem_ld4(uint32_t taddr, float v[4]) {
     asm volatile("tcgen05.ld.sync.aligned.32x32b.x4.b32 {%0,%1,%2,%3}, [%4];"
@@ -379,6 +389,18 @@ linear_packed_kernel(const __grid_constant__ PackedParams p) {
         pre_a = where(tid);
         pre_b = where(tid + kThreadsP);
     }
+    // RMSNorm prologue: the residual and delta values of this thread's first block are requested
+    // right after the wait, together with the loads of the mean-square pass, and kept for the
+    // second pass (addresses worked out here).
+    int64_t own_off = -1;
+    if (kKind == 1 && my_tiles > 0) {
+        const int blocks = nkb * (kBlockK / 16), blk0 = kb0 * (kBlockK / 16);
+        if (tid < p.M * blocks) {
+            const int m = tid / blocks, blk = tid - m * blocks;
+            if (blk0 + blk < p.K / 16)
+                own_off = static_cast<int64_t>(p.m0 + m) * p.K + static_cast<int64_t>(blk0 + blk) * 16;
+        }
+    }
     // sources of the L2 run-ahead (the two stages after the ring in this CTA's sequence)
     const uint8_t* pf_src0 = nullptr;
     const uint8_t* pf_src1 = nullptr;
@@ -400,6 +422,17 @@ linear_packed_kernel(const __grid_constant__ PackedParams p) {
     uint4 a_lo = make_uint4(0, 0, 0, 0), a_hi = a_lo, b_lo = a_lo, b_hi = a_lo;
     if (pre_a != nullptr) { a_lo = __ldg(pre_a); a_hi = __ldg(pre_a + 1); }
     if (pre_b != nullptr) { b_lo = __ldg(pre_b); b_hi = __ldg(pre_b + 1); }
+    uint4 own_r0 = make_uint4(0, 0, 0, 0), own_r1 = own_r0, own_d0 = own_r0, own_d1 = own_r0;
+    if (kKind == 1 && own_off >= 0) {
+        const __nv_bfloat16* rin_e = static_cast<const __nv_bfloat16*>(p.residual_in);
+        own_r0 = __ldg(reinterpret_cast<const uint4*>(rin_e + own_off));
+        own_r1 = __ldg(reinterpret_cast<const uint4*>(rin_e + own_off) + 1);
+        if (p.delta != nullptr) {
+            const __nv_bfloat16* dl_e = static_cast<const __nv_bfloat16*>(p.delta);
+            own_d0 = __ldg(reinterpret_cast<const uint4*>(dl_e + own_off));
+            own_d1 = __ldg(reinterpret_cast<const uint4*>(dl_e + own_off) + 1);
+        }
+    }
     if (warp == 0) TRACE(2);
     // The ring is full until the first MMA frees a stage, which is the prologue away (load and
     // quantize the activations). The two stages that follow are asked into L2 now - not before
@@ -450,13 +483,8 @@ linear_packed_kernel(const __grid_constant__ PackedParams p) {
 #pragma unroll
                     for (int u = 0; u < 4; ++u) {
                         if (c0 + u * kThreadsP < p.K / 8) {
-                            float r[8], d[8];
-                            unpack8(r4[u], r);
-                            if (dl != nullptr) {
-                                unpack8(d4[u], d);
-#pragma unroll
-                                for (int j = 0; j < 8; ++j) r[j] = round_bf16(r[j] + d[j]);
-                            }
+                            float r[8];
+                            unpack8(dl != nullptr ? add_bf16x8(r4[u], d4[u]) : r4[u], r);
 #pragma unroll
                             for (int j = 0; j < 8; ++j) ss += r[j] * r[j];
                         }
@@ -536,26 +564,28 @@ linear_packed_kernel(const __grid_constant__ PackedParams p) {
                 __nv_bfloat16* rout = static_cast<__nv_bfloat16*>(p.residual_out);
                 const int64_t koff = static_cast<int64_t>(blk0 + blk) * 16;
                 const int64_t off = static_cast<int64_t>(p.m0 + m) * p.K + koff;
-                const uint4 r0 = __ldg(reinterpret_cast<const uint4*>(rin + off));
-                const uint4 r1 = __ldg(reinterpret_cast<const uint4*>(rin + off) + 1);
-                uint4 w0 = nw_first0, w1 = nw_first1;
+                uint4 r0 = own_r0, r1 = own_r1, w0 = nw_first0, w1 = nw_first1;
                 if (i != tid) {
+                    r0 = __ldg(reinterpret_cast<const uint4*>(rin + off));
+                    r1 = __ldg(reinterpret_cast<const uint4*>(rin + off) + 1);
                     w0 = __ldg(reinterpret_cast<const uint4*>(nw + koff));
                     w1 = __ldg(reinterpret_cast<const uint4*>(nw + koff) + 1);
                 }
-                float r[16], t[16];
-                unpack8(r0, r); unpack8(r1, r + 8);
                 if (dl != nullptr) {
-                    const uint4 d0 = __ldg(reinterpret_cast<const uint4*>(dl + off));
-                    const uint4 d1 = __ldg(reinterpret_cast<const uint4*>(dl + off) + 1);
-                    unpack8(d0, t); unpack8(d1, t + 8);
-#pragma unroll
-                    for (int j = 0; j < 16; ++j) r[j] = round_bf16(r[j] + t[j]);
+                    uint4 d0 = own_d0, d1 = own_d1;
+                    if (i != tid) {
+                        d0 = __ldg(reinterpret_cast<const uint4*>(dl + off));
+                        d1 = __ldg(reinterpret_cast<const uint4*>(dl + off) + 1);
+                    }
+                    r0 = add_bf16x8(r0, d0);
+                    r1 = add_bf16x8(r1, d1);
                 }
                 if (rank == 0) {
-                    *reinterpret_cast<uint4*>(rout + off) = pack8(r);
-                    *(reinterpret_cast<uint4*>(rout + off) + 1) = pack8(r + 8);
+                    *reinterpret_cast<uint4*>(rout + off) = r0;
+                    *(reinterpret_cast<uint4*>(rout + off) + 1) = r1;
                 }
+                float r[16], t[16];
+                unpack8(r0, r); unpack8(r1, r + 8);
                 float tot = 0.0f;
 #pragma unroll
                 for (int w = 0; w < kWarpsP; ++w) tot += s_red[m * 8 + w];
