@@ -176,3 +176,17 @@ def test_batch_processor_is_a_vllm_logits_processor():
     assert lp._load_logitsprocs_by_fqcns([cls]) == [cls]
     assert lp._load_logitsprocs_by_fqcns(["reset_b200.reset:ReSETBatchProcessor"]) == [cls]
     assert issubclass(reset.ReSETAdapter, lp.LogitsProcessor)
+
+
+def test_reciprocals_the_packed_linear_divides_with_are_exact():
+    """The tensor-core linear takes its CTA index apart with multiply-high by ceil(2^32 / splits)
+    and its activation-block index with multiply + shift by ceil(2^20 / blocks) (the divisions
+    happen on the host, once per launch): exact over everything a launch can ask for."""
+    for splits in range(2, 65):
+        inv = ((1 << 32) + splits - 1) // splits
+        assert inv < (1 << 32)
+        assert all((b * inv) >> 32 == b // splits for b in range(0, 1 << 16, 7)) and \
+            all((b * inv) >> 32 == b // splits for b in range((1 << 16) - 600, 1 << 16))
+    for blocks in range(16, 129, 16):
+        inv = ((1 << 20) + blocks - 1) // blocks
+        assert all((i * inv) >> 20 == i // blocks for i in range(32 * 128 + 3 * 192 + 1))
