@@ -244,8 +244,13 @@ NVFP4R_API int nvfp4r_linear_packed_ex(const nvfp4r_prologue* pro, const void* x
 /* The fused prologues on the FLAT weight (codes [N,K/2] + scales [N,K/16]) through the CUDA-core
  * GEMV, for the launches the crossover gives to it (single token, small or medium weights: at
  * tensor-parallel shard sizes the GEMV's shorter fixed part wins). Same `pro` kinds, arithmetic
- * and roundings as nvfp4r_linear_packed_ex; M = 1 only; push_to is not available here.
- * NVFP4R_PROLOGUE_NONE forwards to nvfp4r_linear. */
+ * and roundings as nvfp4r_linear_packed_ex; M = 1 only. NVFP4R_PROLOGUE_NONE without push_to
+ * forwards to nvfp4r_linear.
+ * push_to (NVFP4R_PROLOGUE_NONE only, push_gather = 1 required): a row-parallel shard small
+ * enough for the GEMV completes the tensor-parallel sum inside the GEMV's own launch: the lane
+ * that finishes a pair of rows stores it into every rank's receive memory and adds the ranks'
+ * contributions out of its own (protocol of nvfp4r_peer_allreduce_bf16, same buffers, same call
+ * counter). One token, bf16 out, even N, K % 256 == 0, one GPU per rank. */
 NVFP4R_API int nvfp4r_linear_ex(const nvfp4r_prologue* pro, const void* x, int64_t x_row_stride,
                                 int M, int K, const float* global_scale_inv, const void* weight,
                                 const void* weight_scale, int N, float alpha, void* out,

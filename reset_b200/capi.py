@@ -434,6 +434,27 @@ def sample_workspace(B: int, device) -> torch.Tensor:
     return torch.zeros((n + 7) // 8, dtype=torch.int64, device=device)
 
 
+def linear_push(x: torch.Tensor, global_scale_inv: torch.Tensor, weight: torch.Tensor,
+                weight_scale_flat: torch.Tensor, alpha: float, push, out: torch.Tensor,
+                rcp_mode: int = L.RCP_APPROX) -> torch.Tensor:
+    """Row-parallel shard small enough for the CUDA-core GEMV (one token): the GEMV's own launch
+    pushes its bf16 result into the peers' receive memory (``push``: a ``_lib.PeerComm``) and sums
+    the ranks' contributions into ``out``; no all-reduce launch follows. One GPU per rank."""
+    _need_cuda(x, global_scale_inv, weight, weight_scale_flat, out)
+    M, K = x.shape
+    w, ws = _u8(weight), _u8(weight_scale_flat)
+    N = w.shape[0]
+    if M != 1 or out.dtype != torch.bfloat16 or tuple(out.shape) != (1, N) or not out.is_contiguous():
+        raise ValueError("linear_push: one token, out bf16 [1,N] contiguous")
+    pro = L.Prologue(L.PROLOGUE_NONE, 0.0, None, None, None, None, C.addressof(push), 1)
+    with torch.cuda.device(x.device):
+        st = L.lib().nvfp4r_linear_ex(C.byref(pro), x.data_ptr(), x.stride(0), M, K, global_scale_inv.data_ptr(),
+                                      w.data_ptr(), ws.data_ptr(), N, float(alpha), out.data_ptr(),
+                                      _DTYPE_CODE[out.dtype], rcp_mode, _stream())
+    L.check(st, "nvfp4r_linear_ex")
+    return out
+
+
 def linear_packed_push(x: torch.Tensor, global_scale_inv: torch.Tensor, packed: torch.Tensor, N: int,
                        alpha: float, workspace: torch.Tensor, push, out: torch.Tensor,
                        rcp_mode: int = L.RCP_APPROX, gather: bool = False) -> torch.Tensor:

@@ -177,8 +177,47 @@ int nvfp4r_linear_ex(const nvfp4r_prologue* pro, const void* x, int64_t x_row_st
                      void* out, int out_dtype, int rcp_mode, void* stream) {
     NVFP4R_RANGE("nvfp4r_linear_ex");
     if (!pro) return fail(NVFP4R_ERR_INVALID_ARGUMENT, "linear_ex: null prologue");
-    if (pro->push_to != nullptr)
-        return fail(NVFP4R_ERR_UNSUPPORTED_SHAPE, "linear_ex: push_to needs the packed linear (nvfp4r_linear_packed_ex)");
+    if (pro->push_to != nullptr) {
+        // Row-parallel shard small enough for the GEMV: push and sum inside the GEMV's launch.
+        const nvfp4r_peer_comm* c = pro->push_to;
+        if (pro->kind != NVFP4R_PROLOGUE_NONE || !pro->push_gather)
+            return fail(NVFP4R_ERR_UNSUPPORTED_SHAPE,
+                        "linear_ex: with push_to the GEMV takes no fused prologue and always sums in its own launch "
+                        "(push_gather = 1); other forms need the packed linear (nvfp4r_linear_packed_ex)");
+        if (!x || !gs || !weight || !weight_scale || !out) return fail(NVFP4R_ERR_INVALID_ARGUMENT, "linear_ex: null pointer");
+        if (M != 1 || out_dtype != NVFP4R_BF16 || N <= 0 || (N & 1) || K <= 0)
+            return fail(NVFP4R_ERR_UNSUPPORTED_SHAPE, "linear_ex: push_to takes one token, bf16 output, even N");
+        if (c->world < 2 || c->world > NVFP4R_PEER_MAX_WORLD || c->rank < 0 || c->rank >= c->world ||
+            static_cast<size_t>(N) > c->max_elems)
+            return fail(NVFP4R_ERR_INVALID_ARGUMENT, "linear_ex: bad communicator or output larger than its slots");
+        if (rcp_mode != NVFP4R_RCP_EXACT && rcp_mode != NVFP4R_RCP_APPROX)
+            return fail(NVFP4R_ERR_INVALID_ARGUMENT, "linear_ex: bad rcp_mode");
+        nvfp4r::GemvArgs a = {};
+        a.w = static_cast<const uint8_t*>(weight);
+        a.wsf = static_cast<const uint8_t*>(weight_scale);
+        a.w_stride_n = K / 2;
+        a.wsf_stride_n = K / 16;
+        a.xb = x;
+        a.xb_stride = x_row_stride;
+        a.gs = gs;
+        a.rcp_mode = rcp_mode;
+        a.out = out;
+        a.out_stride = N;
+        a.out_dtype = out_dtype;
+        a.N = N;
+        a.K = K;
+        a.M = 1;
+        a.alpha = alpha;
+        a.push_world = c->world;
+        a.push_rank = c->rank;
+        a.push_max_pairs = (c->max_elems + 1) / 2;
+        for (int r = 0; r < c->world; ++r) a.push_base[r] = static_cast<unsigned char*>(c->base[r]);
+        a.push_poll_limit = nvfp4r::peer_poll_limit();
+        if (!nvfp4r::gemv_stream_supported(a))
+            return fail(NVFP4R_ERR_UNSUPPORTED_SHAPE, "linear_ex: shape or alignment outside the streaming GEMV (K % 256, 16-byte rows)");
+        cudaError_t e = nvfp4r::launch_gemv_auto(a, as_stream(stream));
+        return e == cudaSuccess ? NVFP4R_OK : cuda_fail(e, "linear_ex launch");
+    }
     if (pro->kind == NVFP4R_PROLOGUE_NONE)
         return nvfp4r_linear(x, x_row_stride, M, K, gs, weight, weight_scale, N, alpha, out, out_dtype, rcp_mode, stream);
     if (pro->kind != NVFP4R_PROLOGUE_ADD_RMSNORM && pro->kind != NVFP4R_PROLOGUE_SILU_MUL)

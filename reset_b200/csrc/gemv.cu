@@ -114,7 +114,8 @@ __device__ __forceinline__ void issue_tile(const StreamParams& p, int lane, int 
     }
 }
 
-template <int MT, int kSlots>
+// kPush: the tensor-parallel epilogue (GemvArgs::push_*) is compiled in; one token only.
+template <int MT, int kSlots, bool kPush = false>
 __global__ void __launch_bounds__(kThreads, kSlots == 2 ? 3 : 1)
 gemv_stream_kernel(const __grid_constant__ StreamParams p) {
     constexpr int kRingBytes = ring_bytes(kSlots);
@@ -164,6 +165,10 @@ gemv_stream_kernel(const __grid_constant__ StreamParams p) {
 
     // Activations come from the preceding kernel.
     pdl_wait_prior();
+    // which half of the receive memory this call uses: the call counter in this rank's own header,
+    // final before this kernel started (its writer is an earlier kernel)
+    unsigned push_parity = 0;
+    if (kPush) push_parity = *reinterpret_cast<volatile unsigned*>(p.a.push_base[p.a.push_rank]) & 1u;
     if (p.a.xb != nullptr) {
         const int blocks_per_tok = K / kBlockElems;
         const __nv_bfloat16* xb = static_cast<const __nv_bfloat16*>(p.a.xb);
@@ -284,7 +289,42 @@ gemv_stream_kernel(const __grid_constant__ StreamParams p) {
                     if (lane == m * kRowsPerGroup + r) mine = acc[r][m];
             const int r = lane % kRowsPerGroup, m = lane / kRowsPerGroup;
             const int row = group * kRowsPerGroup + r;
-            if (m < M && m < MT && row < N)
+            if (kPush) {
+                // lanes 0 and 2 hold rows 0 and 2 of the group: each sends the pair (row, row + 1)
+                const float o = mine * p.a.alpha;
+                const float o2 = __shfl_down_sync(0xffffffffu, o, 1);
+                if (lane < kRowsPerGroup && (lane & 1) == 0 && row < N) {
+                    const __nv_bfloat162 pk = __floats2bfloat162_rn(o, row + 1 < N ? o2 : 0.0f);
+                    const unsigned long long w = (1ull << 32) | *reinterpret_cast<const uint32_t*>(&pk);
+                    const unsigned long long i = static_cast<unsigned long long>(row) >> 1;
+                    const int W = p.a.push_world;
+#pragma unroll 1
+                    for (int d = 0; d < W; ++d) {
+                        const int dst = (p.a.push_rank + d) % W;
+                        unsigned long long* slot = reinterpret_cast<unsigned long long*>(p.a.push_base[dst] + 256) +
+                            (static_cast<unsigned long long>(push_parity) * W + p.a.push_rank) * p.a.push_max_pairs + i;
+                        asm volatile("st.relaxed.sys.global.u64 [%0], %1;" :: "l"(slot), "l"(w) : "memory");
+                    }
+                    unsigned long long* own = reinterpret_cast<unsigned long long*>(p.a.push_base[p.a.push_rank] + 256) +
+                                              static_cast<unsigned long long>(push_parity) * W * p.a.push_max_pairs + i;
+                    float lo = 0.0f, hi = 0.0f;
+#pragma unroll 1
+                    for (int s = 0; s < W; ++s) {            // rank order: every rank adds the same sequence
+                        unsigned long long v = 0;
+                        uint32_t it = 0;
+                        do {
+                            asm volatile("ld.relaxed.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(own + s * p.a.push_max_pairs) : "memory");
+                        } while ((v >> 32) != 1ull && ++it <= p.a.push_poll_limit);
+                        if ((v >> 32) != 1ull) timed_out = true;
+                        const uint32_t bits = static_cast<uint32_t>(v);
+                        lo += __uint_as_float(bits << 16);
+                        hi += __uint_as_float(bits & 0xFFFF0000u);
+                        own[s * p.a.push_max_pairs] = 0ull;
+                    }
+                    const __nv_bfloat162 sum = __floats2bfloat162_rn(lo, hi);
+                    static_cast<uint32_t*>(p.a.out)[i] = *reinterpret_cast<const uint32_t*>(&sum);
+                }
+            } else if (m < M && m < MT && row < N)
                 store_out(p.a.out, p.a.out_dtype, m * p.a.out_stride + row, mine * p.a.alpha);
 #pragma unroll
             for (int rr = 0; rr < kRowsPerGroup; ++rr)
@@ -295,7 +335,21 @@ gemv_stream_kernel(const __grid_constant__ StreamParams p) {
         if (++slot == kSlots) { slot = 0; phase ^= 1u; }
     }
 
-    if (timed_out) {
+    if (kPush) {
+        // the last CTA of the grid to finish advances the call counter: nobody of this launch reads
+        // it any more (same rule as the stand-alone all-reduce kernel)
+        __syncthreads();
+        if (tid == 0) {
+            unsigned* header = reinterpret_cast<unsigned*>(p.a.push_base[p.a.push_rank]);
+            __threadfence();
+            const unsigned t = atomicAdd(header + 1, 1u);
+            if (t == gridDim.x - 1) {
+                header[1] = 0u;
+                header[0] = header[0] + 1u;
+            }
+        }
+    }
+    if (__any_sync(0xffffffffu, timed_out)) {
         if (lane == 0) report_timeout(&g_device_status, 1);
         // Give copies that are still in flight a bounded time to land before
         // this CTA's shared memory is released.
@@ -443,16 +497,23 @@ cudaError_t launch_gemv_stream(const GemvArgs& a, cudaStream_t stream) {
         {gemv_stream_kernel<4, 3>, gemv_stream_kernel<4, 3>},
         {gemv_stream_kernel<8, 3>, gemv_stream_kernel<8, 3>}};
     const int ki = a.M == 1 ? 0 : a.M == 2 ? 1 : a.M <= 4 ? 2 : 3;
-    const Kern kern = table[ki][two_slots ? 1 : 0];
+    Kern kern = table[ki][two_slots ? 1 : 0];
+    const bool push = a.push_world > 1;
+    if (push) {
+        // the all-reduce inside the launch: one token, bf16 pairs of rows
+        if (a.M != 1 || a.out_dtype != 0 || (a.N & 1) || a.out_stride != a.N) return cudaErrorInvalidValue;
+        kern = two_slots ? gemv_stream_kernel<1, 2, true> : gemv_stream_kernel<1, 3, true>;
+    }
 
-    static bool attr_done[4][2][64] = {};
+    static bool attr_done[5][2][64] = {};
     int dev = 0;
     cudaError_t e = cudaGetDevice(&dev);
     if (e != cudaSuccess) return e;
-    if (dev >= 0 && dev < 64 && !attr_done[ki][two_slots][dev]) {
+    const int ai = push ? 4 : ki;
+    if (dev >= 0 && dev < 64 && !attr_done[ai][two_slots][dev]) {
         e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024 - 1024);
         if (e != cudaSuccess) return e;
-        attr_done[ki][two_slots][dev] = true;
+        attr_done[ai][two_slots][dev] = true;
     }
 
     int grid = device_sm_count() * ctas_per_sm;

@@ -411,6 +411,8 @@ void set_gemv_rows_tuning(int mode, int rows, int target_warps) {
 // leave a second round to under a quarter of its warps (N = 5120: 5120x5120 7.3 us on the ring
 // kernel). More tokens: the ring kernel.
 cudaError_t launch_gemv_auto(const GemvArgs& a, cudaStream_t stream) {
+    if (a.push_world > 1)        // the all-reduce inside the launch exists in the ring kernel only
+        return (a.pro_kind == 0 && gemv_stream_supported(a)) ? launch_gemv_stream(a, stream) : cudaErrorNotSupported;
     if (a.pro_kind != 0)         // fused prologues exist in the register-resident kernel only
         return gemv_rows_supported(a) ? launch_gemv_rows(a, stream) : cudaErrorNotSupported;
     const bool ring = gemv_stream_supported(a);

@@ -46,6 +46,14 @@ struct GemvArgs {
     void* residual_out;
     const void* norm_w;
     float eps;
+    // Row-parallel shard of a tensor-parallel layer (ring kernel, one token, bf16 out): the lane that
+    // finishes a pair of rows stores it into every rank's receive memory (layout and protocol of
+    // peer_allreduce.cu), then sums the ranks' contributions to that pair out of its own receive
+    // memory into `out`: the all-reduce inside the GEMV's launch. push_world <= 1: plain store.
+    int push_world, push_rank;
+    unsigned long long push_max_pairs;
+    unsigned char* push_base[NVFP4R_PEER_MAX_WORLD];
+    uint32_t push_poll_limit;
 };
 
 // True when the streaming (bulk-copy ring) kernel can take these arguments.

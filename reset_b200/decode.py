@@ -88,9 +88,16 @@ class _Linear:
             return capi.linear_packed_push(x, self.gs_inv, self.packed, self.N, self.alpha, self.ws.buf, push, out,
                                            gather=gather)
         if self.use_gemv:
+            if push is not None:
+                # a shard small enough for the GEMV: push and sum inside the GEMV's own launch
+                return capi.linear_push(x, self.gs_inv, self.w, self.s, self.alpha, push, out, rcp_mode=L.RCP_APPROX)
             return capi.linear(x, self.gs_inv, self.w, self.s, self.alpha, out=out, rcp_mode=L.RCP_APPROX)
         return capi.linear_packed(x, self.gs_inv, self.packed, self.N, self.alpha, self.ws.buf,
                                   rcp_mode=L.RCP_APPROX, out=out)
+
+    def gemv_can_push(self) -> bool:
+        """The streaming GEMV's in-launch all-reduce takes rows of K % 256 == 0 and an even N."""
+        return self.use_gemv and self.K % 256 == 0 and self.N % 2 == 0
 
     def after_rmsnorm(self, delta, res_in, res_out, norm_w, eps, out):
         # The tensor-core kernel wherever the weight is packed, also where the stand-alone crossover
@@ -283,9 +290,18 @@ class DecodeStep:
         elif self.world > 1:
             torch.distributed.all_reduce(t, group=self.pg)
 
-    def _push(self, lin):
-        """The communicator to push into from this linear's epilogue, or None."""
-        return self.peer.comm if (self.peer is not None and not lin.use_gemv) else None
+    def _push(self, lin, silu: bool = False):
+        """The communicator to push into from this linear's epilogue, or None. A GEMV-sized shard
+        pushes only in the form that also sums in its own launch: the streaming GEMV for a plain
+        linear, the tensor-core kernel where the SiLU prologue rides along."""
+        if self.peer is None:
+            return None
+        if not lin.use_gemv:
+            return self.peer.comm
+        if not self.fused_gather:
+            return None
+        ok = (lin.packed is not None) if silu else lin.gemv_can_push()
+        return self.peer.comm if ok else None
 
     # -- the step ---------------------------------------------------------------------
     def step(self) -> None:
@@ -316,7 +332,7 @@ class DecodeStep:
                 layer["gate_up"].after_rmsnorm(self.o_out, self.res[cur], self.res[1 - cur], layer["ln2"], c.eps,
                                                self.gu_out)
                 cur = 1 - cur
-                push = self._push(layer["down"])
+                push = self._push(layer["down"], silu=True)
                 layer["down"].after_silu_mul(self.gu_out, self.down_out, push=push, gather=self.fused_gather)
             else:
                 push = None
@@ -438,6 +454,9 @@ class DecodeStep:
                 # after a GEMV-sized linear
                 probe = self.layers[0]
                 for name in ("o", "down"):
-                    pushed = not probe[name].use_gemv and (self.fused or name == "o")
+                    lin = probe[name]
+                    pushed = (not lin.use_gemv and (self.fused or name == "o")) or \
+                        (lin.use_gemv and self.fused_gather and
+                         (lin.gemv_can_push() if name == "o" else (self.fused and lin.packed is not None)))
                     per_layer += 0 if (pushed and self.fused_gather) else 1
         return self.cfg.layers * per_layer + 5 + (1 if self.reset is not None and self.head_ws is None else 0)

@@ -124,6 +124,12 @@ def linear_auto(x, global_scale_inv, weight, weight_scale_flat, packed, N: int, 
         if out is None:
             out = torch.empty((M, N), dtype=torch.bfloat16, device=x.device)
         if gemv:
+            # a shard small enough for the GEMV: push and sum inside its own launch where that form
+            # exists (one token, K % 256 == 0, even N) and the width allows it, else GEMV + one
+            # all-reduce launch
+            if M == 1 and K % 256 == 0 and N % 2 == 0 and packed is not None and _config.fused_gather(reduce.world):
+                return capi.linear_push(x, global_scale_inv, weight, weight_scale_flat, alpha, reduce.comm, out,
+                                        rcp_mode=rcp_mode)
             capi.linear(x, global_scale_inv, weight, weight_scale_flat, alpha, out=out, rcp_mode=rcp_mode)
             return reduce.all_reduce_(out)
         ws = _out_workspace(x.device, L.lib().nvfp4r_linear_packed_workspace_bytes(M, N, K))

@@ -167,6 +167,39 @@ for N, K, M in [(5120, 4096, 1), (5120, 12800, 1), (5120, 4096, 8), (4096, 2048,
     mine = part.clone(); ar.all_reduce_(mine)
     torch.cuda.synchronize()
     ok = ok and torch.equal(out2, want) and torch.equal(mine, want)
+# shards small enough for the CUDA-core GEMV: push and sum inside the GEMV's own launch
+for N, K in [(4096, 2048), (5120, 1024), (5120, 2048), (1536, 4096)]:
+    w = torch.randint(0, 256, (N, K // 2), dtype=torch.uint8, device=dev, generator=gen)
+    s = torch.randint(1, 0x38, (N, K // 16), dtype=torch.uint8, device=dev, generator=gen)
+    x = torch.randn(1, K, device=dev, generator=gen).to(torch.bfloat16)
+    part = capi.linear(x, gs, w, s, 0.01, rcp_mode=1)
+    parts = [torch.empty_like(part) for _ in range(world)]
+    dist.all_gather(parts, part)
+    acc = torch.zeros_like(part, dtype=torch.float32)
+    for p in parts: acc += p.float()
+    want = acc.to(torch.bfloat16)
+    for rep in range(3):
+        out = torch.full((1, N), float("nan"), dtype=torch.bfloat16, device=dev)
+        capi.linear_push(x, gs, w, s, 0.01, ar.comm, out, rcp_mode=1)
+        torch.cuda.synchronize()
+        ok = ok and torch.equal(out, want)
+    mine = part.clone(); ar.all_reduce_(mine)                                     # the same call counter serves both
+    torch.cuda.synchronize()
+    ok = ok and torch.equal(mine, want)
+    if N == 4096:                                                                # the crossover sends this one to the GEMV
+        packed = capi.pack_weight(w, s)
+        out = torch.zeros((1, N), dtype=torch.bfloat16, device=dev)
+        nvfp4r.linear_auto(x, gs, w, s, packed, N, 0.01, out=out, reduce=ar)
+        side = torch.cuda.Stream(); side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, stream=side):
+                for _ in range(3):
+                    nvfp4r.linear_auto(x, gs, w, s, packed, N, 0.01, out=out, reduce=ar)
+        torch.cuda.current_stream().wait_stream(side)
+        for _ in range(3):
+            out.zero_(); g.replay(); torch.cuda.synchronize()
+            ok = ok and torch.equal(out, want)
 # through the public call, captured and replayed
 N, K, M = 5120, 4096, 1
 w = torch.randint(0, 256, (N, K // 2), dtype=torch.uint8, device=dev, generator=gen)
