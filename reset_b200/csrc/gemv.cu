@@ -305,24 +305,6 @@ gemv_stream_kernel(const __grid_constant__ StreamParams p) {
                             (static_cast<unsigned long long>(push_parity) * W + p.a.push_rank) * p.a.push_max_pairs + i;
                         asm volatile("st.relaxed.sys.global.u64 [%0], %1;" :: "l"(slot), "l"(w) : "memory");
                     }
-                    unsigned long long* own = reinterpret_cast<unsigned long long*>(p.a.push_base[p.a.push_rank] + 256) +
-                                              static_cast<unsigned long long>(push_parity) * W * p.a.push_max_pairs + i;
-                    float lo = 0.0f, hi = 0.0f;
-#pragma unroll 1
-                    for (int s = 0; s < W; ++s) {            // rank order: every rank adds the same sequence
-                        unsigned long long v = 0;
-                        uint32_t it = 0;
-                        do {
-                            asm volatile("ld.relaxed.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(own + s * p.a.push_max_pairs) : "memory");
-                        } while ((v >> 32) != 1ull && ++it <= p.a.push_poll_limit);
-                        if ((v >> 32) != 1ull) timed_out = true;
-                        const uint32_t bits = static_cast<uint32_t>(v);
-                        lo += __uint_as_float(bits << 16);
-                        hi += __uint_as_float(bits & 0xFFFF0000u);
-                        own[s * p.a.push_max_pairs] = 0ull;
-                    }
-                    const __nv_bfloat162 sum = __floats2bfloat162_rn(lo, hi);
-                    static_cast<uint32_t*>(p.a.out)[i] = *reinterpret_cast<const uint32_t*>(&sum);
                 }
             } else if (m < M && m < MT && row < N)
                 store_out(p.a.out, p.a.out_dtype, m * p.a.out_stride + row, mine * p.a.alpha);
@@ -335,6 +317,37 @@ gemv_stream_kernel(const __grid_constant__ StreamParams p) {
         if (++slot == kSlots) { slot = 0; phase ^= 1u; }
     }
 
+    if (kPush && !timed_out) {
+        // Second half, after all of this warp's pushes are on their way (waiting inside the loop
+        // would hold back the pushes of its later groups, which the peers wait for): sum the
+        // ranks' contributions to every pair this warp pushed, out of this rank's own receive memory.
+        const int W = p.a.push_world;
+#pragma unroll 1
+        for (int g2 = 0; g2 < my_groups; ++g2) {
+            const int row = (g_first + g2 * g_step) * kRowsPerGroup + lane;
+            if (lane < kRowsPerGroup && (lane & 1) == 0 && row < N) {
+                const unsigned long long i = static_cast<unsigned long long>(row) >> 1;
+                unsigned long long* own = reinterpret_cast<unsigned long long*>(p.a.push_base[p.a.push_rank] + 256) +
+                                          static_cast<unsigned long long>(push_parity) * W * p.a.push_max_pairs + i;
+                float lo = 0.0f, hi = 0.0f;
+#pragma unroll 1
+                for (int s = 0; s < W; ++s) {            // rank order: every rank adds the same sequence
+                    unsigned long long v = 0;
+                    uint32_t it = 0;
+                    do {
+                        asm volatile("ld.relaxed.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(own + s * p.a.push_max_pairs) : "memory");
+                    } while ((v >> 32) != 1ull && ++it <= p.a.push_poll_limit);
+                    if ((v >> 32) != 1ull) timed_out = true;
+                    const uint32_t bits = static_cast<uint32_t>(v);
+                    lo += __uint_as_float(bits << 16);
+                    hi += __uint_as_float(bits & 0xFFFF0000u);
+                    own[s * p.a.push_max_pairs] = 0ull;
+                }
+                const __nv_bfloat162 sum = __floats2bfloat162_rn(lo, hi);
+                static_cast<uint32_t*>(p.a.out)[i] = *reinterpret_cast<const uint32_t*>(&sum);
+            }
+        }
+    }
     if (kPush) {
         // the last CTA of the grid to finish advances the call counter: nobody of this launch reads
         // it any more (same rule as the stand-alone all-reduce kernel)
