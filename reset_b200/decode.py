@@ -300,7 +300,8 @@ class DecodeStep:
             return self.peer.comm
         if not self.fused_gather:
             return None
-        ok = (lin.packed is not None) if silu else lin.gemv_can_push()
+        from .nvfp4r import _config
+        ok = (lin.packed is not None) if silu else (lin.gemv_can_push() and self.world <= _config.GEMV_PUSH_MAX_WORLD)
         return self.peer.comm if ok else None
 
     # -- the step ---------------------------------------------------------------------
@@ -444,6 +445,7 @@ class DecodeStep:
     def kernels_per_step(self) -> int:
         """Launches of this library per token on this rank (the logits all-gather of a
         tensor-parallel run is NCCL's and not counted)."""
+        from .nvfp4r import _config
         per_layer = 5 if self.fused else 9
         if self.world > 1:
             if self.peer is None:
@@ -457,6 +459,7 @@ class DecodeStep:
                     lin = probe[name]
                     pushed = (not lin.use_gemv and (self.fused or name == "o")) or \
                         (lin.use_gemv and self.fused_gather and
-                         (lin.gemv_can_push() if name == "o" else (self.fused and lin.packed is not None)))
+                         ((lin.gemv_can_push() and self.world <= _config.GEMV_PUSH_MAX_WORLD) if name == "o"
+                          else (self.fused and lin.packed is not None)))
                     per_layer += 0 if (pushed and self.fused_gather) else 1
         return self.cfg.layers * per_layer + 5 + (1 if self.reset is not None and self.head_ws is None else 0)
