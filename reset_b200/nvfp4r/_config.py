@@ -42,7 +42,7 @@ FUSED_GATHER_MAX_WORLD = 2
 # The same choice for shards small enough for the CUDA-core GEMV inside a decode layer (o_proj at
 # TP 4 / 8): the sum inside the GEMV's launch saves a launch per layer and wins up to four ranks
 # (Qwen3-32B: 373.9 vs 367.0 tok/s at N = 4); with eight its CTAs wait for seven peers while they
-# hold the SMs and the separate all-reduce launch wins (359.2 vs 381.2 tok/s).
+# hold the SMs and the separate all-reduce launch wins (359 vs 381-400 tok/s).
 GEMV_PUSH_MAX_WORLD = 4
 
 
