@@ -6,7 +6,10 @@
 //     mbarrier complete_tx) and drains with CUDA-core math. A slot holds a
 //     4-row x 2048-element tile of the weight (codes + block scales). The
 //     activations (1..8 tokens) are quantized or copied into shared memory once
-//     per CTA. No cross-warp synchronisation after the prologue.
+//     per CTA. No cross-warp synchronisation after the prologue. A second instance
+//     (one token) ends in the tensor-parallel sum: every finished pair of rows is stored
+//     into the receive memory of all ranks, and after its last group a warp adds the
+//     ranks' contributions to its pairs out of its own receive memory.
 //   * gemv_generic_kernel - any stride / any K % 32 == 0; one warp per output
 //     row with direct global loads. Correctness fallback for odd shapes.
 //
