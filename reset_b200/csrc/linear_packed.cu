@@ -401,6 +401,17 @@ linear_packed_kernel(const __grid_constant__ PackedParams p) {
                 own_off = static_cast<int64_t>(p.m0 + m) * p.K + static_cast<int64_t>(blk0 + blk) * 16;
         }
     }
+    // SiLU prologue: likewise the gate and up values of this thread's first block (offset of the
+    // gate block in the [M, 2K] input, -1 = none).
+    int64_t silu_off = -1;
+    if (kKind == 2 && my_tiles > 0) {
+        const int blocks = nkb * (kBlockK / 16), blk0 = kb0 * (kBlockK / 16);
+        if (tid < p.M * blocks) {
+            const int m = tid / blocks, blk = tid - m * blocks;
+            if (blk0 + blk < p.K / 16)
+                silu_off = (p.m0 + m) * p.xb_stride + static_cast<int64_t>(blk0 + blk) * 16;
+        }
+    }
     // sources of the L2 run-ahead (the two stages after the ring in this CTA's sequence)
     const uint8_t* pf_src0 = nullptr;
     const uint8_t* pf_src1 = nullptr;
@@ -432,6 +443,14 @@ linear_packed_kernel(const __grid_constant__ PackedParams p) {
             own_d0 = __ldg(reinterpret_cast<const uint4*>(dl_e + own_off));
             own_d1 = __ldg(reinterpret_cast<const uint4*>(dl_e + own_off) + 1);
         }
+    }
+    if (kKind == 2 && silu_off >= 0) {
+        // gate into own_r*, up into own_d* (the registers the RMSNorm instance uses for its own block)
+        const __nv_bfloat16* gate = static_cast<const __nv_bfloat16*>(p.xb) + silu_off;
+        own_r0 = __ldg(reinterpret_cast<const uint4*>(gate));
+        own_r1 = __ldg(reinterpret_cast<const uint4*>(gate) + 1);
+        own_d0 = __ldg(reinterpret_cast<const uint4*>(gate + p.K));
+        own_d1 = __ldg(reinterpret_cast<const uint4*>(gate + p.K) + 1);
     }
     if (warp == 0) TRACE(2);
     // The ring is full until the first MMA frees a stage, which is the prologue away (load and
@@ -544,8 +563,12 @@ linear_packed_kernel(const __grid_constant__ PackedParams p) {
             if (kind == 2) {
                 // activation = bf16(silu(gate) * up), gate_up row = [gate (K) | up (K)]
                 const __nv_bfloat16* row = xb + (p.m0 + m) * p.xb_stride + static_cast<int64_t>(blk0 + blk) * 16;
-                uint4 g0 = make_uint4(0, 0, 0, 0), g1 = g0, u0 = g0, u1 = g0;
-                if (blk < real) {
+                uint4 g0 = own_r0, g1 = own_r1, u0 = own_d0, u1 = own_d1;     // the first block: fetched right after the wait
+                if (i != tid) {
+                    g0 = make_uint4(0, 0, 0, 0);
+                    g1 = g0; u0 = g0; u1 = g0;
+                }
+                if (i != tid && blk < real) {
                     g0 = __ldg(reinterpret_cast<const uint4*>(row));
                     g1 = __ldg(reinterpret_cast<const uint4*>(row) + 1);
                     u0 = __ldg(reinterpret_cast<const uint4*>(row + p.K));
