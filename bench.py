@@ -13,8 +13,9 @@ M is) + M*K*2 (bf16 activations in) + M*N*2 (bf16 out).
 
 ``python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]``; under
 torchrun (N > 1) the linears are tensor-parallel: qkv/gate_up column-sharded, o/down
-row-sharded with an NCCL all-reduce of the [M, hidden] partial sums after each.
-Rank 0 prints one JSON line.
+row-sharded with a sum of the [M, hidden] partial results after each (this library's
+exchange over NVLink peer memory, fused into the linear's launch where that wins;
+``--allreduce nccl`` for NCCL). Rank 0 prints one JSON line.
 """
 
 from __future__ import annotations
