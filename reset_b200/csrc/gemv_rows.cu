@@ -149,7 +149,9 @@ __device__ __forceinline__ void load_stage_clamped(Stage<R>& st, const uint8_t* 
 // Work is dealt in steps of R consecutive rows and in pairs of steps (one butterfly sums the
 // 2 R MT values of a pair). A row stream owns the pairs [pair_begin, pair_end); its per-warp
 // sums go to shared memory and are added over the stream's warps once, at the end.
-template <int MT, int R, int MAXT, int MINB>
+// kPlain: the instance without the fused prologues' code (activations arrive quantized, or as
+// bf16 to quantize), for launches whose prologue kind is 0.
+template <int MT, int R, int MAXT, int MINB, bool kPlain>
 __global__ void __launch_bounds__(MAXT, MINB)
 gemv_rows_kernel(const __grid_constant__ RowsParams p) {
     constexpr int NV = 2 * R * MT;
@@ -192,7 +194,7 @@ gemv_rows_kernel(const __grid_constant__ RowsParams p) {
     Stage<R> sa, sb;
     load(sa, 0);
     load(sb, 1);
-    const float gs = (p.a.xb != nullptr || p.a.pro_kind != 0) ? __ldg(p.a.gs) : 1.0f;
+    const float gs = (p.a.xb != nullptr || (!kPlain && p.a.pro_kind != 0)) ? __ldg(p.a.gs) : 1.0f;
     pdl_launch_dependents();
     pdl_wait_prior();
 
@@ -203,7 +205,7 @@ gemv_rows_kernel(const __grid_constant__ RowsParams p) {
     for (int m = 0; m < MT; ++m) {
         uint4 codes = make_uint4(0u, 0u, 0u, 0u);
         uint32_t sf2 = 0u;
-        if (p.a.pro_kind == 1) {
+        if (!kPlain && p.a.pro_kind == 1) {
             // activation = bf16( bf16(residual + delta) * rsqrt(mean_sq + eps) * norm_w ); every
             // stream computes the whole row (its cw warps cover it once); the first stream of the
             // first CTA writes the new residual. All warps of the CTA pass the barrier.
@@ -274,7 +276,7 @@ gemv_rows_kernel(const __grid_constant__ RowsParams p) {
                 codes = make_uint4(c0[0], c0[1], c1[0], c1[1]);
                 sf2 = sf0 | (sf1 << 8);
             }
-        } else if (p.a.pro_kind == 2) {
+        } else if (!kPlain && p.a.pro_kind == 2) {
             // activation = bf16(silu(gate) * up), row = [gate (K) | up (K)]
             if (active && m < M) {
                 const __nv_bfloat16* row = static_cast<const __nv_bfloat16*>(p.a.xb) + m * p.a.xb_stride + u * 32;
@@ -519,14 +521,18 @@ cudaError_t launch_gemv_rows(const GemvArgs& a, cudaStream_t stream) {
     const int streams = p.streams;
 
     using Kern = void (*)(RowsParams);
-    static const Kern table[3][2] = {
-        // half (R 4 / R 2), full (R 4 / R 2), wide (R 2)
-        {gemv_rows_kernel<1, 4, 384, 2>, gemv_rows_kernel<1, 2, 384, 2>},
-        {gemv_rows_kernel<1, 4, 768, 1>, gemv_rows_kernel<1, 2, 768, 1>},
-        {gemv_rows_kernel<1, 2, 1024, 1>, gemv_rows_kernel<1, 2, 1024, 1>}};
+#define NVFP4R_ROWS_SHAPES(PLAIN)                                                           \
+    {{gemv_rows_kernel<1, 4, 384, 2, PLAIN>, gemv_rows_kernel<1, 2, 384, 2, PLAIN>},        \
+     {gemv_rows_kernel<1, 4, 768, 1, PLAIN>, gemv_rows_kernel<1, 2, 768, 1, PLAIN>},        \
+     {gemv_rows_kernel<1, 2, 1024, 1, false>, gemv_rows_kernel<1, 2, 1024, 1, false>}}
+    // [with prologues / plain][half (R 4 / R 2), full (R 4 / R 2), wide (R 2)]; at the wide shape's
+    // 64 registers the plain instance spills more than the full one, so both entries are the latter
+    static const Kern table[2][3][2] = {NVFP4R_ROWS_SHAPES(false), NVFP4R_ROWS_SHAPES(true)};
+#undef NVFP4R_ROWS_SHAPES
+    const int plain = a.pro_kind == 0 ? 1 : 0;
     const int rsel = R == 2 ? 1 : 0;
-    const Kern kern = table[shape][rsel];
-    const int ki = shape * 2 + rsel;
+    const Kern kern = table[plain][shape][rsel];
+    const int ki = (plain * 3 + shape) * 2 + rsel;
     (void)MT;
     static bool attr_done[12][64] = {};
     int dev = 0;
