@@ -516,7 +516,6 @@ cudaError_t launch_gemv_rows(const GemvArgs& a, cudaStream_t stream) {
     size_t smem = 0;
     int R = 4, shape = kShapeHalf;
     if (!plan_rows(a, &p, &smem, &R, &shape)) return cudaErrorInvalidConfiguration;
-    const int MT = a.M == 1 ? 1 : 2;
     const int grid = p.total_streams / p.streams;
     const int streams = p.streams;
 
@@ -533,7 +532,6 @@ cudaError_t launch_gemv_rows(const GemvArgs& a, cudaStream_t stream) {
     const int rsel = R == 2 ? 1 : 0;
     const Kern kern = table[plain][shape][rsel];
     const int ki = (plain * 3 + shape) * 2 + rsel;
-    (void)MT;
     static bool attr_done[12][64] = {};
     int dev = 0;
     cudaError_t e = cudaGetDevice(&dev);
