@@ -87,6 +87,20 @@ def test_crossover_rule():
     assert not use_gemv(1, 4096, 4096, 0)                     # gemv_max_m = 0 disables the GEMV
 
 
+def test_single_launch_all_reduce_rule(monkeypatch):
+    """Which tensor-parallel widths complete the all-reduce inside the row-parallel linear's own
+    launch: the tensor-core kernel up to two ranks when called one linear at a time, the streaming
+    GEMV up to four inside a decode layer; NVFP4R_FUSED_GATHER forces either answer."""
+    from reset_b200.nvfp4r import _config
+    monkeypatch.setattr(_config, "FUSED_GATHER", "auto")
+    assert [_config.fused_gather(w) for w in (1, 2, 4, 8)] == [True, True, False, False]
+    assert _config.GEMV_PUSH_MAX_WORLD == 4 and _config.FUSED_GATHER_MAX_WORLD == 2
+    monkeypatch.setattr(_config, "FUSED_GATHER", "1")
+    assert all(_config.fused_gather(w) for w in (2, 4, 8))
+    monkeypatch.setattr(_config, "FUSED_GATHER", "0")
+    assert not any(_config.fused_gather(w) for w in (1, 2, 4, 8))
+
+
 def test_ops_are_registered_with_the_reference_schemas():
     import torch
     from reset_b200 import nvfp4r  # noqa: F401
